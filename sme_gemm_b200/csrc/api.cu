@@ -1,0 +1,838 @@
+// The C ABI (include/smeg_api.h): weight handles, argument checks, kernel
+// dispatch, host-pointer wrappers and the drop-in entry points carrying the
+// reference's own signatures.  No CPU compute path exists behind any of these:
+// a failure returns non-zero and leaves the outputs untouched.
+#include <cuda_runtime.h>
+#include <stdio.h>
+#include <stdlib.h>
+#include <string.h>
+
+#include <chrono>
+#include <map>
+#include <mutex>
+#include <tuple>
+#include <vector>
+
+#include "../../include/smeg_api.h"
+#include "kernels.h"
+#include "layout.h"
+#include "pack.h"
+
+using namespace smeg;
+
+// ---------------------------------------------------------------------------
+// per-process device state
+// ---------------------------------------------------------------------------
+namespace {
+
+struct DeviceState {
+    bool ok = false;
+    int device = -1;
+    int sm_count = 0;
+    size_t hbm = 0;
+    unsigned* status = nullptr;   // device status word (smeg::STATUS_*)
+};
+std::mutex g_mu;
+std::map<int, DeviceState> g_dev;
+int g_trace = -1;
+
+DeviceState* dev_state() {
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess) return nullptr;
+    std::lock_guard<std::mutex> lk(g_mu);
+    DeviceState& s = g_dev[dev];
+    if (!s.ok) {
+        cudaDeviceProp prop;
+        if (cudaGetDeviceProperties(&prop, dev) != cudaSuccess) return nullptr;
+        if (prop.major != 10) {
+            fprintf(stderr, "smeg: device %d is sm_%d%d; this library is built for sm_100a only\n", dev, prop.major, prop.minor);
+            return nullptr;
+        }
+        s.device = dev;
+        s.sm_count = prop.multiProcessorCount;
+        s.hbm = prop.totalGlobalMem;
+        if (cudaMalloc(&s.status, sizeof(unsigned)) != cudaSuccess) return nullptr;
+        cudaMemset(s.status, 0, sizeof(unsigned));
+        // keep freed stream-ordered allocations cached instead of returning them
+        cudaMemPool_t pool;
+        if (cudaDeviceGetDefaultMemPool(&pool, dev) == cudaSuccess) {
+            unsigned long long thr = ~0ull;
+            cudaMemPoolSetAttribute(pool, cudaMemPoolAttrReleaseThreshold, &thr);
+        }
+        s.ok = true;
+    }
+    return &s;
+}
+
+bool tracing() {
+    if (g_trace < 0) {
+        const char* e = getenv("SMEG_TRACE");
+        g_trace = (e && e[0] == '1') ? 1 : 0;
+    }
+    return g_trace == 1;
+}
+
+struct TraceScope {
+    const char* name; size_t m, n, k;
+    std::chrono::steady_clock::time_point t0;
+    bool on;
+    TraceScope(const char* nm, size_t m_, size_t n_, size_t k_) : name(nm), m(m_), n(n_), k(k_), on(tracing()) {
+        if (on) t0 = std::chrono::steady_clock::now();
+    }
+    ~TraceScope() {
+        if (!on) return;
+        const double us = std::chrono::duration<double, std::micro>(std::chrono::steady_clock::now() - t0).count();
+        fprintf(stderr, "smeg: %s %zux%zux%zu %.1f us\n", name, m, n, k, us);
+    }
+};
+
+bool is_pow2(size_t x) { return x != 0 && (x & (x - 1)) == 0; }
+bool mul_overflows(size_t a, size_t b) { return a != 0 && b > (size_t)-1 / a; }
+
+template <typename T>
+int upload(const std::vector<T>& v, T** out) {
+    *out = nullptr;
+    const size_t bytes = v.size() * sizeof(T);
+    if (cudaMalloc(out, bytes ? bytes : 16) != cudaSuccess) return -2;
+    if (bytes && cudaMemcpy(*out, v.data(), bytes, cudaMemcpyHostToDevice) != cudaSuccess) {
+        cudaFree(*out);
+        *out = nullptr;
+        return -2;
+    }
+    return 0;
+}
+
+// Resolve an ep_desc16 into kernel parameters.  With device operand pointers
+// (dev = true) nodes are used as they are; `ext_buf` receives a stream-ordered
+// device array when the graph is longer than the inline capacity.
+int make_ep(const ep_desc16* ep, size_t n, EpParams* out, cudaStream_t stream, EpNodeDev** ext_buf) {
+    out->n_nodes = 0;
+    out->ext = nullptr;
+    *ext_buf = nullptr;
+    if (!ep || ep->n_nodes == 0 || !ep->nodes) return 0;
+    std::vector<EpNodeDev> nodes(ep->n_nodes);
+    for (uint32_t i = 0; i < ep->n_nodes; ++i) {
+        const EpNode& s = ep->nodes[i];
+        if (s.op > 24u) return -4;
+        EpNodeDev d;
+        d.op = (s.op & 0xffu) | ((s.aux & 0xffu) << 8);
+        d.scalar = s.scalar;
+        d.ptr = static_cast<const uint16_t*>(s.ptr);
+        d.ld = s.ld == 0 ? n : s.ld;
+        nodes[i] = d;
+    }
+    out->n_nodes = (int)ep->n_nodes;
+    if (ep->n_nodes <= (uint32_t)kMaxInlineNodes) {
+        for (uint32_t i = 0; i < ep->n_nodes; ++i) out->nodes[i] = nodes[i];
+        return 0;
+    }
+    const size_t bytes = nodes.size() * sizeof(EpNodeDev);
+    if (cudaMallocAsync(ext_buf, bytes, stream) != cudaSuccess) return -2;
+    if (cudaMemcpyAsync(*ext_buf, nodes.data(), bytes, cudaMemcpyHostToDevice, stream) != cudaSuccess) return -2;
+    // pageable source: the copy has been staged by the time the call returns
+    out->ext = *ext_buf;
+    return 0;
+}
+
+bool op_is_row(uint32_t op) { return op == 2 || op == 3 || op == 12 || op == 16 || op == 19 || op == 22; }
+bool op_is_col(uint32_t op) { return op == 4 || op == 5 || op == 13 || op == 17 || op == 20 || op == 23; }
+bool op_is_tensor(uint32_t op) { return op == 6 || op == 7 || op == 14 || op == 18 || op == 21 || op == 24; }
+
+// Copies a host-pointer op-graph's operands to the device (one allocation) and
+// returns a node array with device pointers.  Operand extents follow
+// validate_ep (src/exec/guard.rs:112-150): ROW m, COL n, TENSOR (m-1)*ld + n.
+struct HostEp {
+    std::vector<EpNode> nodes;
+    ep_desc16 desc{0, nullptr};
+    void* dbuf = nullptr;
+    ~HostEp() { if (dbuf) cudaFree(dbuf); }
+    int build(const ep_desc16* ep, size_t m, size_t n) {
+        if (!ep || ep->n_nodes == 0 || !ep->nodes) return 0;
+        nodes.assign(ep->nodes, ep->nodes + ep->n_nodes);
+        size_t total = 0;
+        std::vector<size_t> off(nodes.size(), 0), len(nodes.size(), 0);
+        for (size_t i = 0; i < nodes.size(); ++i) {
+            const EpNode& s = nodes[i];
+            size_t l = 0;
+            if (op_is_row(s.op)) l = m;
+            else if (op_is_col(s.op)) l = n;
+            else if (op_is_tensor(s.op)) {
+                const size_t ld = s.ld == 0 ? n : s.ld;
+                if (ld < n) return -4;
+                l = m == 0 ? 0 : (m - 1) * ld + n;
+            }
+            if (l && !s.ptr) return -4;
+            len[i] = l;
+            off[i] = total;
+            total += (l * 2 + 15) / 16 * 16;
+        }
+        if (total) {
+            if (cudaMalloc(&dbuf, total) != cudaSuccess) return -2;
+            for (size_t i = 0; i < nodes.size(); ++i)
+                if (len[i]) {
+                    if (cudaMemcpy((char*)dbuf + off[i], nodes[i].ptr, len[i] * 2, cudaMemcpyHostToDevice) != cudaSuccess) return -2;
+                    nodes[i].ptr = (char*)dbuf + off[i];
+                }
+        }
+        desc.n_nodes = (uint32_t)nodes.size();
+        desc.nodes = nodes.data();
+        return 0;
+    }
+    const ep_desc16* get() const { return desc.n_nodes ? &desc : nullptr; }
+};
+
+}  // namespace
+
+// ---------------------------------------------------------------------------
+// handles
+// ---------------------------------------------------------------------------
+struct smeg_q4 {
+    PackedDims d;
+    unsigned char* codes = nullptr;
+    uint16_t* scales = nullptr;
+    size_t code_bytes = 0, scale_elems = 0;
+};
+struct smeg_lowbit {
+    PackedDims d;
+    int bits = 0;
+    uint32_t lut = 0;
+    int8_t codebook[4] = {0, 0, 0, 0};
+    unsigned char* codes = nullptr;
+    uint16_t* scales = nullptr;
+    size_t code_bytes = 0, scale_elems = 0;
+};
+struct smeg_mlp {
+    const smeg_q4* gate_up;
+    const smeg_q4* down;
+    uint32_t act;
+};
+
+extern "C" {
+
+const char* smeg_version(void) { return "sme-gemm-b200 0.1 (sm_100a)"; }
+
+int smeg_device_info(int* sm_count, size_t* hbm_bytes) {
+    DeviceState* s = dev_state();
+    if (!s) return -5;
+    if (sm_count) *sm_count = s->sm_count;
+    if (hbm_bytes) *hbm_bytes = s->hbm;
+    return 0;
+}
+
+unsigned smeg_last_status(void) {
+    DeviceState* s = dev_state();
+    if (!s) return ~0u;
+    unsigned v = 0;
+    if (cudaDeviceSynchronize() != cudaSuccess) return ~0u;
+    cudaMemcpy(&v, s->status, sizeof(v), cudaMemcpyDeviceToHost);
+    if (v) cudaMemset(s->status, 0, sizeof(unsigned));
+    return v;
+}
+
+void smeg_trace(int on) { g_trace = on ? 1 : 0; }
+
+// ---- Q4 handles ----
+static int q4_finish(const std::vector<uint8_t>& quants, const std::vector<uint16_t>& scales, size_t n, size_t k,
+                     size_t block, smeg_q4** out) {
+    if (!dev_state()) return -5;
+    smeg_q4* h = new smeg_q4();
+    h->d = make_dims(n, k, block, kQ4UnitDepth);
+    std::vector<uint8_t> codes;
+    std::vector<uint16_t> sc;
+    q4_pack(quants.data(), scales.data(), h->d, codes, sc);
+    h->code_bytes = codes.size();
+    h->scale_elems = sc.size();
+    if (upload(codes, &h->codes) || upload(sc, &h->scales)) {
+        smeg_q4_destroy(h);
+        return -2;
+    }
+    *out = h;
+    return 0;
+}
+
+int smeg_q4_create(const uint8_t* quants, const uint16_t* scales, const uint16_t* mins, size_t n, size_t k,
+                   size_t block, smeg_q4** out) {
+    if (!out) return -4;
+    *out = nullptr;
+    if (!is_pow2(block)) return -1;
+    if (mins) return -3;
+    if (mul_overflows(n, k) || ((n != 0 && k != 0) && (!quants || !scales))) return -4;
+    const size_t nbk = div_up(k, block);
+    std::vector<uint8_t> q(quants, quants + (n * k + 1) / 2);
+    std::vector<uint16_t> s(scales, scales + n * nbk);
+    return q4_finish(q, s, n, k, block, out);
+}
+
+int smeg_q4_quantize(const float* w, int layout, size_t n, size_t k, size_t block, int affine, smeg_q4** out) {
+    if (!out) return -4;
+    *out = nullptr;
+    if (!is_pow2(block)) return -1;
+    if (affine) return -3;
+    if (mul_overflows(n, k) || ((n != 0 && k != 0) && !w)) return -4;
+    std::vector<uint8_t> q;
+    std::vector<uint16_t> s, mn;
+    q4_quantize_host(w, layout, n, k, block, 0, q, s, mn);
+    return q4_finish(q, s, n, k, block, out);
+}
+
+int smeg_q4_from_band(const uint8_t* nibbles, const uint16_t* scales, const uint16_t* mins, size_t n, size_t k,
+                      size_t block, smeg_q4** out) {
+    if (!out) return -4;
+    *out = nullptr;
+    if (!is_pow2(block)) return -1;
+    if (mins) return -3;
+    if (mul_overflows(n, k) || ((n != 0 && k != 0) && (!nibbles || !scales))) return -4;
+    std::vector<uint8_t> q;
+    std::vector<uint16_t> s, mn;
+    q4_from_band(nibbles, scales, nullptr, n, k, block, q, s, mn);
+    return q4_finish(q, s, n, k, block, out);
+}
+
+void smeg_q4_destroy(smeg_q4* w) {
+    if (!w) return;
+    if (w->codes) cudaFree(w->codes);
+    if (w->scales) cudaFree(w->scales);
+    delete w;
+}
+size_t smeg_q4_n(const smeg_q4* w) { return w->d.n; }
+size_t smeg_q4_k(const smeg_q4* w) { return w->d.k; }
+size_t smeg_q4_block(const smeg_q4* w) { return w->d.block; }
+size_t smeg_q4_device_bytes(const smeg_q4* w) { return w->code_bytes + w->scale_elems * 2; }
+
+int smeg_q4_unpack(const smeg_q4* w, uint8_t* quants, uint16_t* scales) {
+    if (!w || !quants || !scales) return -4;
+    std::vector<uint8_t> codes(w->code_bytes);
+    std::vector<uint16_t> sc(w->scale_elems);
+    if (w->code_bytes && cudaMemcpy(codes.data(), w->codes, w->code_bytes, cudaMemcpyDeviceToHost) != cudaSuccess) return -2;
+    if (w->scale_elems && cudaMemcpy(sc.data(), w->scales, w->scale_elems * 2, cudaMemcpyDeviceToHost) != cudaSuccess) return -2;
+    q4_unpack(codes.data(), sc.data(), w->d, quants, scales);
+    return 0;
+}
+
+// ---- 2-bit / 1-bit handles ----
+static int lowbit_finish(int bits, const uint8_t* wbits, int layout, const uint16_t* scales, size_t n, size_t k,
+                         size_t block, const int8_t* codebook, smeg_lowbit** out) {
+    if (!dev_state()) return -5;
+    smeg_lowbit* h = new smeg_lowbit();
+    h->bits = bits;
+    h->d = make_dims(n, k, block, bits == 2 ? kQ2UnitDepth : kQ1UnitDepth);
+    if (codebook) {
+        memcpy(h->codebook, codebook, 4);
+        h->lut = (uint32_t)(uint8_t)codebook[0] | ((uint32_t)(uint8_t)codebook[1] << 8) |
+                 ((uint32_t)(uint8_t)codebook[2] << 16) | ((uint32_t)(uint8_t)codebook[3] << 24);
+    }
+    std::vector<uint8_t> codes;
+    std::vector<uint16_t> sc;
+    if (bits == 2) q2_pack(wbits, scales, h->d, codes, sc);
+    else q1_pack(wbits, layout, scales, h->d, codes, sc);
+    h->code_bytes = codes.size();
+    h->scale_elems = sc.size();
+    if (upload(codes, &h->codes) || upload(sc, &h->scales)) {
+        smeg_lowbit_destroy(h);
+        return -2;
+    }
+    *out = h;
+    return 0;
+}
+static bool lowbit_block_ok(size_t block) { return is_pow2(block) && block >= 16 && block <= 65536; }
+
+int smeg_q2_create(const uint8_t* codes, const uint16_t* scales, size_t n, size_t k, size_t block,
+                   const int8_t codebook[4], smeg_lowbit** out) {
+    if (!out || !codebook) return -4;
+    *out = nullptr;
+    if (!lowbit_block_ok(block)) return -1;
+    if (mul_overflows(n, k) || ((n != 0 && k != 0) && (!codes || !scales))) return -4;
+    return lowbit_finish(2, codes, 1, scales, n, k, block, codebook, out);
+}
+int smeg_q2_quantize(const float* w, int layout, size_t n, size_t k, size_t block, const int8_t codebook[4],
+                     smeg_lowbit** out) {
+    if (!out || !codebook) return -4;
+    *out = nullptr;
+    if (!lowbit_block_ok(block)) return -1;
+    if (mul_overflows(n, k) || ((n != 0 && k != 0) && !w)) return -4;
+    std::vector<uint8_t> codes;
+    std::vector<uint16_t> sc;
+    if (q2_quantize_host(w, layout, n, k, block, codebook, codes, sc)) return -2;
+    return lowbit_finish(2, codes.data(), 1, sc.data(), n, k, block, codebook, out);
+}
+int smeg_q1_create(const uint8_t* signs, const uint16_t* scales, int layout, size_t n, size_t k, size_t block,
+                   smeg_lowbit** out) {
+    if (!out) return -4;
+    *out = nullptr;
+    if (!lowbit_block_ok(block)) return -1;
+    if (mul_overflows(n, k) || ((n != 0 && k != 0) && (!signs || !scales))) return -4;
+    return lowbit_finish(1, signs, layout, scales, n, k, block, nullptr, out);
+}
+int smeg_q1_quantize(const float* w, int layout, size_t n, size_t k, size_t block, smeg_lowbit** out) {
+    if (!out) return -4;
+    *out = nullptr;
+    if (!lowbit_block_ok(block)) return -1;
+    if (mul_overflows(n, k) || ((n != 0 && k != 0) && !w)) return -4;
+    std::vector<uint8_t> signs;
+    std::vector<uint16_t> sc;
+    q1_quantize_host(w, layout, n, k, block, signs, sc);
+    return lowbit_finish(1, signs.data(), 0, sc.data(), n, k, block, nullptr, out);
+}
+int smeg_q2_from_band(const uint8_t* codes, const uint16_t* scales, size_t n, size_t k, size_t block,
+                      const int8_t codebook[4], smeg_lowbit** out) {
+    if (!out || !codebook) return -4;
+    *out = nullptr;
+    if (!lowbit_block_ok(block)) return -1;
+    if (mul_overflows(n, k) || ((n != 0 && k != 0) && (!codes || !scales))) return -4;
+    std::vector<uint8_t> c;
+    std::vector<uint16_t> s;
+    q2_from_band(codes, scales, n, k, block, c, s);
+    return lowbit_finish(2, c.data(), 1, s.data(), n, k, block, codebook, out);
+}
+int smeg_q1_from_band(const uint8_t* signs, const uint16_t* scales, size_t n, size_t k, size_t block,
+                      smeg_lowbit** out) {
+    if (!out) return -4;
+    *out = nullptr;
+    if (!lowbit_block_ok(block)) return -1;
+    if (mul_overflows(n, k) || ((n != 0 && k != 0) && (!signs || !scales))) return -4;
+    std::vector<uint8_t> c;
+    std::vector<uint16_t> s;
+    q1_from_band(signs, scales, n, k, block, c, s);
+    return lowbit_finish(1, c.data(), 0, s.data(), n, k, block, nullptr, out);
+}
+void smeg_lowbit_destroy(smeg_lowbit* w) {
+    if (!w) return;
+    if (w->codes) cudaFree(w->codes);
+    if (w->scales) cudaFree(w->scales);
+    delete w;
+}
+size_t smeg_lowbit_n(const smeg_lowbit* w) { return w->d.n; }
+size_t smeg_lowbit_k(const smeg_lowbit* w) { return w->d.k; }
+size_t smeg_lowbit_block(const smeg_lowbit* w) { return w->d.block; }
+int smeg_lowbit_bits(const smeg_lowbit* w) { return w->bits; }
+size_t smeg_lowbit_device_bytes(const smeg_lowbit* w) { return w->code_bytes + w->scale_elems * 2; }
+int smeg_lowbit_unpack(const smeg_lowbit* w, uint8_t* bits_out, uint16_t* scales) {
+    if (!w || !bits_out || !scales) return -4;
+    std::vector<uint8_t> codes(w->code_bytes);
+    std::vector<uint16_t> sc(w->scale_elems);
+    if (w->code_bytes && cudaMemcpy(codes.data(), w->codes, w->code_bytes, cudaMemcpyDeviceToHost) != cudaSuccess) return -2;
+    if (w->scale_elems && cudaMemcpy(sc.data(), w->scales, w->scale_elems * 2, cudaMemcpyDeviceToHost) != cudaSuccess) return -2;
+    if (w->bits == 2) q2_unpack(codes.data(), sc.data(), w->d, bits_out, scales);
+    else q1_unpack(codes.data(), sc.data(), w->d, bits_out, scales);
+    return 0;
+}
+
+// ---- host-side preparation on caller buffers (no device) ----
+static int unit_depth_of(int bits) { return bits == 4 ? kQ4UnitDepth : (bits == 2 ? kQ2UnitDepth : (bits == 1 ? kQ1UnitDepth : 0)); }
+
+size_t smeg_packed_code_bytes(int bits, size_t n, size_t k) {
+    const int ud = unit_depth_of(bits);
+    if (!ud) return 0;
+    return div_up(n, 16) * div_up(k, (size_t)ud) * kUnitBytes;
+}
+size_t smeg_packed_scale_elems(int bits, size_t n, size_t k, size_t block) {
+    const int ud = unit_depth_of(bits);
+    if (!ud || !is_pow2(block)) return 0;
+    const PackedDims d = make_dims(n, k, block, ud);
+    return d.n16 * d.nb * 16;
+}
+int smeg_host_pack(int bits, const uint8_t* wbits, int layout, const uint16_t* scales, size_t n, size_t k,
+                   size_t block, uint8_t* codes_out, uint16_t* scales_out) {
+    const int ud = unit_depth_of(bits);
+    if (!ud || !is_pow2(block) || mul_overflows(n, k)) return -4;
+    const PackedDims d = make_dims(n, k, block, ud);
+    std::vector<uint8_t> codes;
+    std::vector<uint16_t> sc;
+    if (bits == 4) q4_pack(wbits, scales, d, codes, sc);
+    else if (bits == 2) q2_pack(wbits, scales, d, codes, sc);
+    else q1_pack(wbits, layout, scales, d, codes, sc);
+    if (!codes.empty()) memcpy(codes_out, codes.data(), codes.size());
+    if (!sc.empty()) memcpy(scales_out, sc.data(), sc.size() * 2);
+    return 0;
+}
+int smeg_host_unpack(int bits, const uint8_t* codes, const uint16_t* packed_scales, size_t n, size_t k,
+                     size_t block, uint8_t* wbits_out, uint16_t* scales_out) {
+    const int ud = unit_depth_of(bits);
+    if (!ud || !is_pow2(block) || mul_overflows(n, k)) return -4;
+    const PackedDims d = make_dims(n, k, block, ud);
+    if (bits == 4) q4_unpack(codes, packed_scales, d, wbits_out, scales_out);
+    else if (bits == 2) q2_unpack(codes, packed_scales, d, wbits_out, scales_out);
+    else q1_unpack(codes, packed_scales, d, wbits_out, scales_out);
+    return 0;
+}
+int smeg_host_q4_quantize(const float* w, int layout, size_t n, size_t k, size_t block, uint8_t* quants,
+                          uint16_t* scales) {
+    if (!is_pow2(block)) return -1;
+    if (mul_overflows(n, k)) return -4;
+    std::vector<uint8_t> q;
+    std::vector<uint16_t> s, mn;
+    q4_quantize_host(w, layout, n, k, block, 0, q, s, mn);
+    if (!q.empty()) memcpy(quants, q.data(), q.size());
+    if (!s.empty()) memcpy(scales, s.data(), s.size() * 2);
+    return 0;
+}
+int smeg_host_q2_quantize(const float* w, int layout, size_t n, size_t k, size_t block, const int8_t codebook[4],
+                          uint8_t* codes, uint16_t* scales) {
+    if (!lowbit_block_ok(block)) return -1;
+    if (mul_overflows(n, k) || !codebook) return -4;
+    std::vector<uint8_t> c;
+    std::vector<uint16_t> s;
+    if (q2_quantize_host(w, layout, n, k, block, codebook, c, s)) return -2;
+    if (!c.empty()) memcpy(codes, c.data(), c.size());
+    if (!s.empty()) memcpy(scales, s.data(), s.size() * 2);
+    return 0;
+}
+int smeg_host_q1_quantize(const float* w, int layout, size_t n, size_t k, size_t block, uint8_t* signs,
+                          uint16_t* scales) {
+    if (!lowbit_block_ok(block)) return -1;
+    if (mul_overflows(n, k)) return -4;
+    std::vector<uint8_t> sg;
+    std::vector<uint16_t> s;
+    q1_quantize_host(w, layout, n, k, block, sg, s);
+    if (!sg.empty()) memcpy(signs, sg.data(), sg.size());
+    if (!s.empty()) memcpy(scales, s.data(), s.size() * 2);
+    return 0;
+}
+
+// ---------------------------------------------------------------------------
+// device-pointer compute
+// ---------------------------------------------------------------------------
+static int q4_dev(const smeg_q4* w, const uint16_t* a, uint16_t* c, size_t m, const ep_desc16* ep, int bf16,
+                  cudaStream_t stream, float* c32 = nullptr) {
+    if (!w) return -4;
+    const size_t n = w->d.n, k = w->d.k;
+    if (m == 0 || n == 0) return 0;
+    if ((!c && !c32) || (k && !a) || m > 0x7fffffffu || n > 0x7fffffffu || k > 0x7fffffffu) return -4;
+    DeviceState* ds = dev_state();
+    if (!ds) return -5;
+    Q4GemvArgs g;
+    memset(&g, 0, sizeof(g));
+    EpNodeDev* ext = nullptr;
+    int rc = make_ep(ep, n, &g.ep, stream, &ext);
+    if (rc) { if (ext) cudaFreeAsync(ext, stream); return rc; }
+    g.codes = w->codes; g.scales = w->scales; g.a = a; g.c = c; g.c32 = c32;
+    g.m = (int)m; g.n = (int)n; g.k = (int)k;
+    g.n16 = (int)w->d.n16; g.k64 = (int)w->d.ku; g.nb = (int)w->d.nb;
+    g.log2_block = w->d.log2_block;
+    g.a_vec_ok = (k % 8 == 0) && ((uintptr_t)a % 16 == 0);
+    g.status = ds->status;
+    cudaError_t e = q4_gemv_launch(g, bf16, ds->sm_count, stream);
+    if (ext) cudaFreeAsync(ext, stream);
+    return e == cudaSuccess ? 0 : -6;
+}
+
+int smeg_matmul_q4_f16_dev(const smeg_q4* w, const uint16_t* a, uint16_t* c, size_t m, const ep_desc16* ep, void* stream) {
+    return q4_dev(w, a, c, m, ep, 0, (cudaStream_t)stream);
+}
+int smeg_matmul_q4_bf16_dev(const smeg_q4* w, const uint16_t* a, uint16_t* c, size_t m, const ep_desc16* ep, void* stream) {
+    return q4_dev(w, a, c, m, ep, 1, (cudaStream_t)stream);
+}
+
+static int lowbit_dev(const smeg_lowbit* w, const uint16_t* a, uint16_t* c, size_t m, const ep_desc16* ep,
+                      int8_t* q_out, float* sa_out, int32_t* sums_out, cudaStream_t stream) {
+    if (!w) return -4;
+    const size_t n = w->d.n, k = w->d.k;
+    if (m == 0 || n == 0) return 0;
+    if (!c || (k && !a) || m > 0x7fffffffu || n > 0x7fffffffu || k > 0x7fffffffu) return -4;
+    DeviceState* ds = dev_state();
+    if (!ds) return -5;
+    const size_t kq = w->d.ku * (size_t)w->d.unit_depth, nb = w->d.nb;
+    // scratch: int8 activations, their per-block scales and (1-bit) sums
+    const size_t q_bytes = (m * kq + 255) / 256 * 256, sa_bytes = (m * nb * 4 + 255) / 256 * 256;
+    char* ws = nullptr;
+    if (cudaMallocAsync(&ws, q_bytes + 2 * sa_bytes + 256, stream) != cudaSuccess) return -2;
+    ActQuantArgs aq;
+    aq.a = a; aq.q = (int8_t*)ws; aq.sa = (float*)(ws + q_bytes);
+    aq.qsum = w->bits == 1 ? (int32_t*)(ws + q_bytes + sa_bytes) : nullptr;
+    aq.m = (int)m; aq.k = (int)k; aq.kq = (int)kq; aq.nbq = (int)nb; aq.log2_block = w->d.log2_block;
+    LowbitGemvArgs g;
+    memset(&g, 0, sizeof(g));
+    EpNodeDev* ext = nullptr;
+    int rc = make_ep(ep, n, &g.ep, stream, &ext);
+    cudaError_t e = cudaSuccess;
+    if (!rc) {
+        e = act_quant_launch(aq, stream);
+        g.codes = w->codes; g.scales = w->scales; g.q = aq.q; g.sa = aq.sa; g.qsum = aq.qsum; g.c = c;
+        g.sums_out = sums_out;
+        g.m = (int)m; g.n = (int)n; g.k = (int)k; g.kq = (int)kq;
+        g.n16 = (int)w->d.n16; g.ku = (int)w->d.ku; g.nb = (int)nb; g.nb_real = (int)w->d.nb_real;
+        g.log2_block = w->d.log2_block; g.lut = w->lut; g.status = ds->status;
+        if (e == cudaSuccess) e = lowbit_gemv_launch(g, w->bits, ds->sm_count, stream);
+        if (e == cudaSuccess && q_out)
+            e = cudaMemcpy2DAsync(q_out, k, aq.q, kq, k, m, cudaMemcpyDeviceToDevice, stream);
+        if (e == cudaSuccess && sa_out)
+            e = cudaMemcpy2DAsync(sa_out, w->d.nb_real * 4, aq.sa, nb * 4, w->d.nb_real * 4, m, cudaMemcpyDeviceToDevice, stream);
+    }
+    if (ext) cudaFreeAsync(ext, stream);
+    cudaFreeAsync(ws, stream);
+    if (rc) return rc;
+    return e == cudaSuccess ? 0 : -6;
+}
+
+int smeg_matmul_lowbit_dev(const smeg_lowbit* w, const uint16_t* a, uint16_t* c, size_t m, const ep_desc16* ep, void* stream) {
+    return lowbit_dev(w, a, c, m, ep, nullptr, nullptr, nullptr, (cudaStream_t)stream);
+}
+int smeg_matmul_lowbit_debug_dev(const smeg_lowbit* w, const uint16_t* a, uint16_t* c, size_t m, int8_t* q_out,
+                                 float* sa_out, int32_t* sums_out, void* stream) {
+    return lowbit_dev(w, a, c, m, nullptr, q_out, sa_out, sums_out, (cudaStream_t)stream);
+}
+
+int smeg_glu_f16_dev(uint16_t* out, const uint16_t* both, size_t m, size_t n, uint32_t act, void* stream) {
+    if (act != SMEG_ACT_SILU && act != SMEG_ACT_GELU) return -4;
+    return glu_launch(out, both, m, n, act, (cudaStream_t)stream) == cudaSuccess ? 0 : -6;
+}
+int smeg_add_f16_to_f32_dev(float* dst, const uint16_t* src, size_t len, void* stream) {
+    return add_f16_to_f32_launch(dst, src, len, (cudaStream_t)stream) == cudaSuccess ? 0 : -6;
+}
+int smeg_act_f16_dev(uint16_t* dst, const uint16_t* src, size_t len, uint32_t act, void* stream) {
+    return act_f16_launch(dst, src, len, act, (cudaStream_t)stream) == cudaSuccess ? 0 : -6;
+}
+int smeg_f32_to_f16_dev(uint16_t* dst, const float* src, size_t len, void* stream) {
+    return f32_to_f16_launch(dst, src, len, (cudaStream_t)stream) == cudaSuccess ? 0 : -6;
+}
+int smeg_f16_to_f32_dev(float* dst, const uint16_t* src, size_t len, void* stream) {
+    return f16_to_f32_launch(dst, src, len, (cudaStream_t)stream) == cudaSuccess ? 0 : -6;
+}
+
+// ---------------------------------------------------------------------------
+// host-pointer wrappers
+// ---------------------------------------------------------------------------
+}  // extern "C"
+namespace {
+struct DevBuf {
+    void* p = nullptr;
+    ~DevBuf() { if (p) cudaFree(p); }
+    int alloc(size_t bytes) { return cudaMalloc(&p, bytes ? bytes : 16) == cudaSuccess ? 0 : -2; }
+};
+
+// status word check after a synchronous call
+int finish_sync(DeviceState* ds) {
+    if (cudaDeviceSynchronize() != cudaSuccess) return -6;
+    unsigned v = 0;
+    if (cudaMemcpy(&v, ds->status, sizeof(v), cudaMemcpyDeviceToHost) != cudaSuccess) return -6;
+    if (v) {
+        cudaMemset(ds->status, 0, sizeof(unsigned));
+        return -7;
+    }
+    return 0;
+}
+
+template <typename F>
+int host_matmul(size_t m, size_t n, size_t k, const uint16_t* a, uint16_t* c, const ep_desc16* ep, F run) {
+    if (m == 0 || n == 0) return 0;
+    if (mul_overflows(m, k) || mul_overflows(m, n) || !c || (k && !a)) return -4;
+    DeviceState* ds = dev_state();
+    if (!ds) return -5;
+    DevBuf da, dc;
+    HostEp hep;
+    if (da.alloc(m * k * 2) || dc.alloc(m * n * 2)) return -2;
+    int rc = hep.build(ep, m, n);
+    if (rc) return rc;
+    if (k && cudaMemcpy(da.p, a, m * k * 2, cudaMemcpyHostToDevice) != cudaSuccess) return -6;
+    rc = run((const uint16_t*)da.p, (uint16_t*)dc.p, hep.get());
+    if (rc) return rc;
+    rc = finish_sync(ds);
+    if (rc) return rc;
+    if (cudaMemcpy(c, dc.p, m * n * 2, cudaMemcpyDeviceToHost) != cudaSuccess) return -6;
+    return 0;
+}
+}  // namespace
+extern "C" {
+
+int smeg_matmul_q4_f16(const smeg_q4* w, const uint16_t* a, uint16_t* c, size_t m, const ep_desc16* ep) {
+    if (!w) return -4;
+    TraceScope ts("matmul_q4_f16", m, w->d.n, w->d.k);
+    return host_matmul(m, w->d.n, w->d.k, a, c, ep, [&](const uint16_t* da, uint16_t* dc, const ep_desc16* dep) {
+        return q4_dev(w, da, dc, m, dep, 0, 0);
+    });
+}
+int smeg_matmul_q4_bf16(const smeg_q4* w, const uint16_t* a, uint16_t* c, size_t m, const ep_desc16* ep) {
+    if (!w) return -4;
+    TraceScope ts("matmul_q4_bf16", m, w->d.n, w->d.k);
+    return host_matmul(m, w->d.n, w->d.k, a, c, ep, [&](const uint16_t* da, uint16_t* dc, const ep_desc16* dep) {
+        return q4_dev(w, da, dc, m, dep, 1, 0);
+    });
+}
+int smeg_matmul_lowbit(const smeg_lowbit* w, const uint16_t* a, uint16_t* c, size_t m, const ep_desc16* ep) {
+    if (!w) return -4;
+    TraceScope ts(w->bits == 2 ? "matmul_q2" : "matmul_q1", m, w->d.n, w->d.k);
+    return host_matmul(m, w->d.n, w->d.k, a, c, ep, [&](const uint16_t* da, uint16_t* dc, const ep_desc16* dep) {
+        return lowbit_dev(w, da, dc, m, dep, nullptr, nullptr, nullptr, 0);
+    });
+}
+
+// ---------------------------------------------------------------------------
+// MLP block
+// ---------------------------------------------------------------------------
+int smeg_mlp_create(const smeg_q4* gate_up, const smeg_q4* down, uint32_t gate_act, smeg_mlp** out) {
+    if (!out || !gate_up || !down) return -4;
+    *out = nullptr;
+    if (gate_act != SMEG_ACT_SILU && gate_act != SMEG_ACT_GELU) return -4;
+    if (gate_up->d.n % 2 != 0 || down->d.k != gate_up->d.n / 2) return -4;   // "down takes up's outputs"
+    smeg_mlp* h = new smeg_mlp{gate_up, down, gate_act};
+    *out = h;
+    return 0;
+}
+void smeg_mlp_destroy(smeg_mlp* mlp) { delete mlp; }
+
+// both = x @ gate_up (f16), hid = glu(both), then the down projection either
+// rounded to f16 and added into y (partial == nullptr) or left as f32 partial sums.
+static int mlp_run(smeg_mlp* mlp, const uint16_t* x, float* y, float* partial, size_t m, cudaStream_t stream) {
+    if (!mlp) return -4;
+    if (m == 0) return 0;
+    const size_t h = mlp->down->d.k, d_out = mlp->down->d.n;
+    if (mul_overflows(m, 2 * h)) return -4;
+    char* ws = nullptr;
+    const size_t both_bytes = (m * 2 * h * 2 + 255) / 256 * 256, hid_bytes = (m * h * 2 + 255) / 256 * 256;
+    const size_t out_bytes = (m * d_out * 2 + 255) / 256 * 256;
+    if (cudaMallocAsync(&ws, both_bytes + hid_bytes + out_bytes, stream) != cudaSuccess) return -2;
+    uint16_t* both = (uint16_t*)ws;
+    uint16_t* hid = (uint16_t*)(ws + both_bytes);
+    uint16_t* out = (uint16_t*)(ws + both_bytes + hid_bytes);
+    int rc = q4_dev(mlp->gate_up, x, both, m, nullptr, 0, stream);
+    if (!rc) rc = glu_launch(hid, both, m, h, mlp->act, stream) == cudaSuccess ? 0 : -6;
+    if (!rc) {
+        if (partial) {
+            rc = q4_dev(mlp->down, hid, nullptr, m, nullptr, 0, stream, partial);
+        } else {
+            rc = q4_dev(mlp->down, hid, out, m, nullptr, 0, stream);
+            if (!rc) rc = add_f16_to_f32_launch(y, out, m * d_out, stream) == cudaSuccess ? 0 : -6;
+        }
+    }
+    cudaFreeAsync(ws, stream);
+    return rc;
+}
+
+int smeg_mlp_accumulate_dev(smeg_mlp* mlp, const uint16_t* x, float* y, size_t m, void* stream) {
+    return mlp_run(mlp, x, y, nullptr, m, (cudaStream_t)stream);
+}
+int smeg_mlp_partial_dev(smeg_mlp* mlp, const uint16_t* x, float* partial, size_t m, void* stream) {
+    return mlp_run(mlp, x, nullptr, partial, m, (cudaStream_t)stream);
+}
+int smeg_mlp_finish_dev(float* y, const float* sum, size_t len, void* stream) {
+    return round_add_f32_launch(y, sum, len, (cudaStream_t)stream) == cudaSuccess ? 0 : -6;
+}
+int smeg_mlp_accumulate(smeg_mlp* mlp, const uint16_t* x, float* y, size_t m) {
+    if (!mlp) return -4;
+    if (m == 0) return 0;
+    DeviceState* ds = dev_state();
+    if (!ds) return -5;
+    const size_t k = mlp->gate_up->d.k, d_out = mlp->down->d.n;
+    TraceScope ts("mlp_accumulate", m, d_out, k);
+    DevBuf dx, dy;
+    if (dx.alloc(m * k * 2) || dy.alloc(m * d_out * 4)) return -2;
+    if (cudaMemcpy(dx.p, x, m * k * 2, cudaMemcpyHostToDevice) != cudaSuccess) return -6;
+    if (cudaMemcpy(dy.p, y, m * d_out * 4, cudaMemcpyHostToDevice) != cudaSuccess) return -6;
+    int rc = mlp_run(mlp, (const uint16_t*)dx.p, (float*)dy.p, nullptr, m, 0);
+    if (rc) return rc;
+    rc = finish_sync(ds);
+    if (rc) return rc;
+    if (cudaMemcpy(y, dy.p, m * d_out * 4, cudaMemcpyDeviceToHost) != cudaSuccess) return -6;
+    return 0;
+}
+
+// ---------------------------------------------------------------------------
+// drop-in entry points (the reference's signatures, band-major host arrays)
+// ---------------------------------------------------------------------------
+}  // extern "C"
+namespace {
+struct CacheKey {
+    const void* ptr; size_t n, k, block; int kind;
+    bool operator<(const CacheKey& o) const {
+        return std::tie(ptr, n, k, block, kind) < std::tie(o.ptr, o.n, o.k, o.block, o.kind);
+    }
+};
+struct CacheVal { smeg_q4* q4 = nullptr; smeg_lowbit* lb = nullptr; };
+std::mutex g_cache_mu;
+std::map<CacheKey, CacheVal> g_cache;
+}  // namespace
+extern "C" {
+
+static smeg_q4* cached_q4(const uint8_t* nibbles, const uint16_t* scales, const uint16_t* mins, size_t n, size_t k,
+                          size_t block, int* rc) {
+    std::lock_guard<std::mutex> lk(g_cache_mu);
+    CacheKey key{nibbles, n, k, block, 4};
+    auto it = g_cache.find(key);
+    if (it != g_cache.end()) { *rc = 0; return it->second.q4; }
+    smeg_q4* h = nullptr;
+    *rc = smeg_q4_from_band(nibbles, scales, mins, n, k, block, &h);
+    if (*rc) return nullptr;
+    g_cache[key].q4 = h;
+    return h;
+}
+static smeg_lowbit* cached_lowbit(int bits, const uint8_t* packed, const uint16_t* scales, const int8_t* codebook,
+                                  size_t n, size_t k, size_t block, int* rc) {
+    std::lock_guard<std::mutex> lk(g_cache_mu);
+    CacheKey key{packed, n, k, block, bits};
+    auto it = g_cache.find(key);
+    if (it != g_cache.end() && (bits == 1 || memcmp(it->second.lb->codebook, codebook, 4) == 0)) { *rc = 0; return it->second.lb; }
+    if (it != g_cache.end()) { smeg_lowbit_destroy(it->second.lb); g_cache.erase(it); }
+    smeg_lowbit* h = nullptr;
+    *rc = bits == 2 ? smeg_q2_from_band(packed, scales, n, k, block, codebook, &h)
+                    : smeg_q1_from_band(packed, scales, n, k, block, &h);
+    if (*rc) return nullptr;
+    g_cache[key].lb = h;
+    return h;
+}
+
+void smeg_forget(const void* packed) {
+    std::lock_guard<std::mutex> lk(g_cache_mu);
+    for (auto it = g_cache.begin(); it != g_cache.end();) {
+        if (it->first.ptr == packed) {
+            if (it->second.q4) smeg_q4_destroy(it->second.q4);
+            if (it->second.lb) smeg_lowbit_destroy(it->second.lb);
+            it = g_cache.erase(it);
+        } else ++it;
+    }
+}
+
+int gemm_sme_f16f16_q4(size_t m, size_t n, size_t k, uint16_t* dst, const uint16_t* lhs, const uint8_t* nibbles,
+                       const uint16_t* scales, const uint16_t* mins, size_t block, const ep_desc16* ep) {
+    if (m == 0 || n == 0) return 0;
+    int rc = 0;
+    smeg_q4* w = cached_q4(nibbles, scales, mins, n, k, block, &rc);
+    if (!w) return rc;
+    return smeg_matmul_q4_f16(w, lhs, dst, m, ep);
+}
+int gemm_sme_b16b16_q4(size_t m, size_t n, size_t k, uint16_t* dst, const uint16_t* lhs, const uint8_t* nibbles,
+                       const uint16_t* scales, const uint16_t* mins, const uint16_t* scales_bf16,
+                       const uint16_t* mins_bf16, size_t block, const ep_desc16* ep) {
+    (void)scales_bf16; (void)mins_bf16;
+    if (m == 0 || n == 0) return 0;
+    int rc = 0;
+    smeg_q4* w = cached_q4(nibbles, scales, mins, n, k, block, &rc);
+    if (!w) return rc;
+    return smeg_matmul_q4_bf16(w, lhs, dst, m, ep);
+}
+int gemm_sme_f16_q1(size_t m, size_t n, size_t k, uint16_t* dst, const uint16_t* lhs, const uint8_t* signs,
+                    const uint16_t* scales, size_t block, const ep_desc16* ep) {
+    if (m == 0 || n == 0) return 0;
+    int rc = 0;
+    smeg_lowbit* w = cached_lowbit(1, signs, scales, nullptr, n, k, block, &rc);
+    if (!w) return rc;
+    return smeg_matmul_lowbit(w, lhs, dst, m, ep);
+}
+int gemm_sme_f16_q2(size_t m, size_t n, size_t k, uint16_t* dst, const uint16_t* lhs, const uint8_t* codes,
+                    const uint16_t* scales, const int8_t* codebook, size_t block, const ep_desc16* ep) {
+    if (m == 0 || n == 0) return 0;
+    if (!codebook) return -4;
+    int rc = 0;
+    smeg_lowbit* w = cached_lowbit(2, codes, scales, codebook, n, k, block, &rc);
+    if (!w) return rc;
+    return smeg_matmul_lowbit(w, lhs, dst, m, ep);
+}
+
+void neon_glu_f16(uint16_t* out, const uint16_t* in, size_t m, size_t n, uint32_t act) {
+    if (m * n == 0 || !dev_state()) return;
+    DevBuf di, dout;
+    if (di.alloc(m * 2 * n * 2) || dout.alloc(m * n * 2)) return;
+    if (cudaMemcpy(di.p, in, m * 2 * n * 2, cudaMemcpyHostToDevice) != cudaSuccess) return;
+    if (glu_launch((uint16_t*)dout.p, (const uint16_t*)di.p, m, n, act, 0) != cudaSuccess) return;
+    cudaMemcpy(out, dout.p, m * n * 2, cudaMemcpyDeviceToHost);
+}
+void neon_add_f16_to_f32(float* dst, const uint16_t* src, size_t n) {
+    if (n == 0 || !dev_state()) return;
+    DevBuf dd, dsrc;
+    if (dd.alloc(n * 4) || dsrc.alloc(n * 2)) return;
+    if (cudaMemcpy(dd.p, dst, n * 4, cudaMemcpyHostToDevice) != cudaSuccess) return;
+    if (cudaMemcpy(dsrc.p, src, n * 2, cudaMemcpyHostToDevice) != cudaSuccess) return;
+    if (add_f16_to_f32_launch((float*)dd.p, (const uint16_t*)dsrc.p, n, 0) != cudaSuccess) return;
+    cudaMemcpy(dst, dd.p, n * 4, cudaMemcpyDeviceToHost);
+}
+
+}  // extern "C"

@@ -1,0 +1,102 @@
+// Shared device helpers for the sm_100a kernels: mbarrier + bulk-copy (TMA)
+// wrappers with bounded waits, 16-bit float conversions, the status word.
+#pragma once
+#include <cuda_bf16.h>
+#include <cuda_fp16.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+namespace smeg {
+
+// Error bits written to the library's device status word by a kernel that gave
+// up on a bounded wait.  The host entry point turns a non-zero word into rc != 0.
+enum : unsigned {
+    STATUS_MBAR_TIMEOUT = 1u,   // a shared-memory barrier never completed
+    STATUS_TMEM_TIMEOUT = 2u,   // a tensor-memory pipeline barrier never completed
+    STATUS_PEER_TIMEOUT = 4u,   // a peer flag never arrived (multi-GPU reduce)
+};
+
+// Upper bound on try_wait polls before a wait is abandoned.  Each poll can
+// itself suspend for the hardware's time slice, so this is seconds of wall
+// clock at most and never reached unless a copy was lost.
+constexpr unsigned kSpinLimit = 1u << 22;
+
+__device__ __forceinline__ uint32_t smem_u32(const void* p) {
+    return static_cast<uint32_t>(__cvta_generic_to_shared(p));
+}
+
+__device__ __forceinline__ void mbar_init(uint64_t* bar, unsigned count) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(bar)), "r"(count) : "memory");
+}
+__device__ __forceinline__ void fence_barrier_init() {
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+}
+__device__ __forceinline__ void fence_proxy_async() {
+    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+}
+__device__ __forceinline__ void mbar_expect_tx(uint64_t* bar, unsigned bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(bar)), "r"(bytes)
+                 : "memory");
+}
+__device__ __forceinline__ void mbar_arrive(uint64_t* bar) {
+    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(bar)) : "memory");
+}
+__device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, unsigned parity) {
+    unsigned ok;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(ok)
+        : "r"(smem_u32(bar)), "r"(parity)
+        : "memory");
+    return ok != 0;
+}
+// Bounded wait.  Returns false (and raises `status`) if the barrier never
+// flipped; `abort_flag` in shared memory then short-circuits every later wait
+// of the CTA so the kernel still ends quickly.
+__device__ __forceinline__ bool mbar_wait(uint64_t* bar, unsigned parity, volatile int* abort_flag,
+                                          unsigned* status, unsigned code = STATUS_MBAR_TIMEOUT) {
+    if (mbar_try_wait(bar, parity)) return true;
+    for (unsigned it = 0; it < kSpinLimit; ++it) {
+        if (*abort_flag) return false;
+        if (mbar_try_wait(bar, parity)) return true;
+    }
+    *abort_flag = 1;
+    if (status) atomicOr(status, code);
+    return false;
+}
+
+// One contiguous global -> shared copy on the bulk-copy (TMA) engine.  Both
+// addresses 16-byte aligned, bytes a multiple of 16.
+__device__ __forceinline__ void bulk_g2s(void* smem_dst, const void* gsrc, unsigned bytes, uint64_t* bar) {
+    asm volatile("cp.async.bulk.shared::cta.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(
+                     smem_u32(smem_dst)),
+                 "l"(gsrc), "r"(bytes), "r"(smem_u32(bar))
+                 : "memory");
+}
+
+// Programmatic dependent launch: let the next kernel in the stream start its
+// prologue / wait for the previous kernel's memory to be visible.
+__device__ __forceinline__ void pdl_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+
+// ---- 16-bit element helpers (T = 0: f16, 1: bf16), bit patterns in uint16 ----
+template <int BF16>
+__device__ __forceinline__ float t_to_f32(uint16_t v) {
+    if (BF16) return __uint_as_float(static_cast<uint32_t>(v) << 16);
+    return __half2float(__ushort_as_half(v));
+}
+template <int BF16>
+__device__ __forceinline__ uint16_t f32_to_t(float x) {
+    if (BF16) return __bfloat16_as_ushort(__float2bfloat16_rn(x));
+    return __half_as_ushort(__float2half_rn(x));
+}
+
+__device__ __forceinline__ uint32_t lop3_and_or(uint32_t a, uint32_t mask, uint32_t orv) {
+    uint32_t r;
+    asm("lop3.b32 %0, %1, %2, %3, 0xea;" : "=r"(r) : "r"(a), "r"(mask), "r"(orv));  // (a & mask) | orv
+    return r;
+}
+
+}  // namespace smeg

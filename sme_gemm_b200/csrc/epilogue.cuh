@@ -1,0 +1,123 @@
+// The fused epilogue op-graph, evaluated per output cell at the C store.
+//
+// Semantics follow the reference's scalar evaluator exactly (ep_apply_cell,
+// src/exec/scalar.rs:58-120, reached through apply_ep_scalar :125-140): the
+// product is first rounded to the output type T, widened to f32, every node is
+// one separately rounded f32 operation (no fused multiply-add), MAX/MIN are
+// maxNum/minNum, and the result is rounded to T once more.  Named trailing
+// activations arrive here already appended as a final ACT node
+// (resolve_nodes, src/exec/scalar.rs:28-53).
+//
+// The opcodes and activation kinds are the values of enum ep_op / enum ep_act in
+// csrc/epilogue.h:136-200 of the reference.
+#pragma once
+#include "common.cuh"
+
+namespace smeg {
+
+constexpr int kMaxInlineNodes = 16;
+
+struct EpNodeDev {
+    uint32_t op;       // low 8 bits: opcode; bits 8..15: activation kind
+    float scalar;      // *_SCALAR operand, or alpha of leaky_relu / elu
+    const uint16_t* ptr;  // ROW / COL / TENSOR operand (T bit patterns), device memory
+    size_t ld;         // TENSOR row stride in elements (already resolved, never 0)
+};
+
+struct EpParams {
+    int n_nodes;                       // 0 = identity
+    const EpNodeDev* ext;              // device array when n_nodes > kMaxInlineNodes
+    EpNodeDev nodes[kMaxInlineNodes];  // inline copy otherwise
+};
+
+// Activations whose reference definition is cheap and exact in f64, or rare:
+// evaluated in double like the reference (act_apply_f64_a,
+// src/epilogue/mod.rs:40-86) and narrowed once.
+static __device__ __noinline__ float act_rare(uint32_t kind, float xf, float alphaf) {
+    double x = (double)xf, alpha = (double)alphaf, r = x;
+    switch (kind) {
+    case 6: r = x >= 0.0 ? x : alpha * x; break;
+    case 7: r = x < 0.0 ? 0.0 : (x > 6.0 ? 6.0 : x); break;
+    case 8: { double t = x / 6.0 + 0.5; r = t < 0.0 ? 0.0 : (t > 1.0 ? 1.0 : t); } break;
+    case 9: { double t = x / 6.0 + 0.5; r = x * (t < 0.0 ? 0.0 : (t > 1.0 ? 1.0 : t)); } break;
+    case 10: r = fabs(x); break;
+    case 11: r = -x; break;
+    case 12: r = x * x; break;
+    case 13: r = x > 0.0 ? 1.0 : (x < 0.0 ? -1.0 : 0.0); break;
+    case 14: r = sqrt(x); break;
+    case 15: r = x / (1.0 + fabs(x)); break;
+    case 16: r = 1.0 / x; break;
+    case 17: r = 1.0 / sqrt(x); break;
+    case 18: r = exp(x); break;
+    case 19: r = log(x); break;
+    case 20: r = x >= 0.0 ? x : alpha * expm1(x); break;
+    case 21: r = 1.0507009873554805 * (x >= 0.0 ? x : 1.6732632423543772 * expm1(x)); break;
+    case 22: r = fmax(x, 0.0) + log1p(exp(-fabs(x))); break;
+    case 23: r = x * tanh(fmax(x, 0.0) + log1p(exp(-fabs(x)))); break;
+    case 24: {  // Abramowitz-Stegun 7.1.26 erf, as src/epilogue/mod.rs:92-103
+        double z = x * 0.70710678118654752440, az = fabs(z);
+        double t = 1.0 / (1.0 + 0.3275911 * az);
+        double poly = ((((1.061405429 * t - 1.453152027) * t + 1.421413741) * t - 0.284496736) * t + 0.254829592) * t;
+        double e = 1.0 - poly * exp(-az * az);
+        r = 0.5 * x * (1.0 + (z < 0.0 ? -e : e));
+    } break;
+    default: break;
+    }
+    return (float)r;
+}
+
+// The five named activations (relu, gelu, silu, tanh, sigmoid) run in f32 with
+// the accurate libdevice functions: within a couple of f32 ulps of the f64
+// reference value, far inside the output type's rounding.
+__device__ __forceinline__ float act_apply(uint32_t kind, float x, float alpha) {
+    switch (kind) {
+    case 0: return x;
+    case 1: return fmaxf(x, 0.0f);
+    case 2: return 0.5f * x * (1.0f + tanhf(0.7978845608f * (x + 0.044715f * x * x * x)));
+    case 3: return __fdiv_rn(x, 1.0f + expf(-x));
+    case 4: return tanhf(x);
+    case 5: return __fdiv_rn(1.0f, 1.0f + expf(-x));
+    default: return act_rare(kind, x, alpha);
+    }
+}
+
+template <int BF16>
+__device__ __forceinline__ float ep_node(const EpNodeDev& nd, float x, size_t i, size_t j) {
+    const uint32_t op = nd.op & 0xffu;
+    float o = nd.scalar;
+    switch (op) {
+    case 2: case 3: case 12: case 16: case 19: case 22: o = t_to_f32<BF16>(nd.ptr[i]); break;
+    case 4: case 5: case 13: case 17: case 20: case 23: o = t_to_f32<BF16>(nd.ptr[j]); break;
+    case 6: case 7: case 14: case 18: case 21: case 24: o = t_to_f32<BF16>(nd.ptr[i * nd.ld + j]); break;
+    default: break;
+    }
+    switch (op) {
+    case 0: case 2: case 4: case 6: return __fadd_rn(x, o);
+    case 1: case 3: case 5: case 7: return __fmul_rn(x, o);
+    case 11: case 12: case 13: case 14: return __fsub_rn(x, o);
+    case 15: case 16: case 17: case 18: return __fdiv_rn(x, o);
+    case 9: case 19: case 20: case 21: return fmaxf(x, o);
+    case 10: case 22: case 23: case 24: return fminf(x, o);
+    case 8: return act_apply((nd.op >> 8) & 0xffu, x, nd.scalar);
+    default: return x;
+    }
+}
+
+// acc (f32 accumulator) -> stored T bits at output cell (i, j).
+template <int BF16>
+__device__ __forceinline__ uint16_t ep_store_value(const EpParams& ep, float acc, size_t i, size_t j) {
+    uint16_t c = f32_to_t<BF16>(acc);
+    const int nn = ep.n_nodes;
+    if (nn == 0) return c;
+    float x = t_to_f32<BF16>(c);
+    if (nn <= kMaxInlineNodes) {
+#pragma unroll 1
+        for (int q = 0; q < nn; ++q) x = ep_node<BF16>(ep.nodes[q], x, i, j);
+    } else {
+#pragma unroll 1
+        for (int q = 0; q < nn; ++q) x = ep_node<BF16>(ep.ext[q], x, i, j);
+    }
+    return f32_to_t<BF16>(x);
+}
+
+}  // namespace smeg

@@ -1,0 +1,64 @@
+// Internal launch interfaces between the C-ABI layer (api.cu) and the kernels.
+#pragma once
+#include <cuda_runtime.h>
+#include <stddef.h>
+#include <stdint.h>
+
+#include "epilogue.cuh"
+
+namespace smeg {
+
+// ---- Q4 GEMV (q4_gemv.cu) ----
+struct Q4GemvArgs {
+    const unsigned char* codes;   // packed units, [n16][k64][512 B]
+    const uint16_t* scales;       // f16 bits, [n16][nb][16]
+    const uint16_t* a;            // activations, row-major m x k (T bits)
+    uint16_t* c;                  // output, row-major m x n (T bits)
+    float* c32;                   // if set: raw f32 accumulators go here instead (no rounding, no epilogue)
+    int m, n, k;
+    int n16, k64, nb;             // column groups, 64-deep units, staged scale rows per group
+    int log2_block;
+    int ns, cg, rps, ka;          // filled in by the launcher
+    int a_vec_ok;                 // rows of `a` are 16-byte aligned (k % 8 == 0 and base aligned)
+    unsigned* status;
+    EpParams ep;
+};
+cudaError_t q4_gemv_launch(Q4GemvArgs a, int bf16, int sm_count, cudaStream_t stream);
+
+// ---- activation int8 quantisation + 2-bit / 1-bit GEMV (lowbit_gemv.cu) ----
+struct ActQuantArgs {
+    const uint16_t* a;    // m x k f16 bits
+    int8_t* q;            // m x kq int8 (kq = k padded to the unit depth, pad = 0)
+    float* sa;            // m x nbq per-block activation scales (amax / 127), padded blocks 0
+    int32_t* qsum;        // m x nbq per-block sums of q (1-bit path only; may be null)
+    int m, k, kq, nbq, log2_block;
+};
+cudaError_t act_quant_launch(const ActQuantArgs& a, cudaStream_t stream);
+
+struct LowbitGemvArgs {
+    const unsigned char* codes;   // packed units [n16][ku][512 B]
+    const uint16_t* scales;       // f16 bits [n16][nb][16]
+    const int8_t* q;              // m x kq
+    const float* sa;              // m x nb
+    const int32_t* qsum;          // m x nb (1-bit)
+    uint16_t* c;                  // m x n f16 bits
+    int32_t* sums_out;            // optional debug: m x n x nb_real exact block sums
+    int m, n, k, kq;
+    int n16, ku, nb, nb_real;     // column groups, units along K, block rows staged / real
+    int log2_block;
+    uint32_t lut;                 // 2-bit codebook, byte c = value of code c
+    int ns, cg, kc;               // launcher-filled: ring depth, groups per CTA, K chunk
+    unsigned* status;
+    EpParams ep;
+};
+cudaError_t lowbit_gemv_launch(LowbitGemvArgs a, int bits, int sm_count, cudaStream_t stream);
+
+// ---- element-wise model ops (elementwise.cu) ----
+cudaError_t glu_launch(uint16_t* out, const uint16_t* both, size_t m, size_t n, uint32_t act, cudaStream_t s);
+cudaError_t add_f16_to_f32_launch(float* dst, const uint16_t* src, size_t n, cudaStream_t s);
+cudaError_t act_f16_launch(uint16_t* dst, const uint16_t* src, size_t n, uint32_t act, cudaStream_t s);
+cudaError_t f32_to_f16_launch(uint16_t* dst, const float* src, size_t n, cudaStream_t s);
+cudaError_t f16_to_f32_launch(float* dst, const uint16_t* src, size_t n, cudaStream_t s);
+cudaError_t round_add_f32_launch(float* y, const float* partial_sum, size_t n, cudaStream_t s);
+
+}  // namespace smeg

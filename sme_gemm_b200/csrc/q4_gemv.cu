@@ -1,0 +1,354 @@
+// Q4 decode GEMV / small-M GEMM for sm_100a:  C[m][n] = ep( A[m][k] @ dequant(W) ),
+// m small (rows are processed in groups of 8 per tensor-core instruction).
+//
+// Replaces the reference's SME Q4 GEMV (run_q4_gemv1 / run_q4_gemv,
+// csrc/gemm_f16f16_q4.h:236-431, and the bf16 twin csrc/gemm_b16b16_q4.h:171-268).
+//
+// HBM-bound design:
+//   * one CTA owns CG groups of 16 output columns for the whole depth K, so no
+//     cross-CTA reduction and a column's result never depends on the grid;
+//   * a producer warp streams that CTA's packed codes and scales, which are
+//     contiguous in the prepacked layout, into a ring of shared-memory stages
+//     with cp.async.bulk (TMA engine) + mbarriers: bytes in flight are set by
+//     the ring depth, not by registers;
+//   * 8 consumer warps split each stage's depth (one 64-deep unit each).  A
+//     lane's 16-byte vector is four A fragments of mma.m16n8k16 (16 weight
+//     columns x 16 depths) -- nibbles become f16 pairs with one lop3 each, the
+//     activations are the 8-wide N operand, accumulation is f32;
+//   * per K-block the raw code sums are folded with the f32 block scale
+//     (accumulator-side scaling), or -- for bf16 and for blocks below 32 -- each
+//     weight is dequantised to exactly the reference's rounded value first;
+//   * warps' partial sums are added in a fixed order through shared memory, the
+//     epilogue graph runs on the rounded product, C is stored once.
+#include "epilogue.cuh"
+#include "kernels.h"
+#include "layout.h"
+
+namespace smeg {
+
+namespace {
+
+constexpr int kConsumerWarps = 8;
+constexpr int kStageDepth = 64 * kConsumerWarps;  // 512 depths per stage
+constexpr int kThreads = 32 * (kConsumerWarps + 1);
+
+__device__ __forceinline__ void mma_f16(float (&d)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1,
+                                        const float (&c)[4]) {
+    asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%10,%11,%12,%13};"
+                 : "=f"(d[0]), "=f"(d[1]), "=f"(d[2]), "=f"(d[3])
+                 : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1), "f"(c[0]), "f"(c[1]), "f"(c[2]), "f"(c[3]));
+}
+__device__ __forceinline__ void mma_bf16(float (&d)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1,
+                                         const float (&c)[4]) {
+    asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%10,%11,%12,%13};"
+                 : "=f"(d[0]), "=f"(d[1]), "=f"(d[2]), "=f"(d[3])
+                 : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1), "f"(c[0]), "f"(c[1]), "f"(c[2]), "f"(c[3]));
+}
+
+// One packed word (8 nibbles, offset binary) -> the four A registers holding
+// the exact integer codes as f16 pairs.
+__device__ __forceinline__ void decode_word_f16(uint32_t w, uint32_t (&a)[4]) {
+    const uint32_t w8 = w >> 8;
+    uint32_t lo0 = lop3_and_or(w, 0x000f000fu, 0x64006400u);   // 1024 + u
+    uint32_t hi0 = lop3_and_or(w, 0x00f000f0u, 0x64006400u);   // 1024 + 16 u
+    uint32_t lo1 = lop3_and_or(w8, 0x000f000fu, 0x64006400u);
+    uint32_t hi1 = lop3_and_or(w8, 0x00f000f0u, 0x64006400u);
+    const __half2 off = __halves2half2(__ushort_as_half(0x6408), __ushort_as_half(0x6408));      // 1032
+    const __half2 sc16 = __halves2half2(__ushort_as_half(0x2c00), __ushort_as_half(0x2c00));     // 1/16
+    const __half2 off16 = __halves2half2(__ushort_as_half(0xd480), __ushort_as_half(0xd480));    // -72
+    __half2 r0 = __hsub2(*reinterpret_cast<__half2*>(&lo0), off);
+    __half2 r1 = __hsub2(*reinterpret_cast<__half2*>(&lo1), off);
+    __half2 r2 = __hfma2(*reinterpret_cast<__half2*>(&hi0), sc16, off16);
+    __half2 r3 = __hfma2(*reinterpret_cast<__half2*>(&hi1), sc16, off16);
+    a[0] = *reinterpret_cast<uint32_t*>(&r0);
+    a[1] = *reinterpret_cast<uint32_t*>(&r1);
+    a[2] = *reinterpret_cast<uint32_t*>(&r2);
+    a[3] = *reinterpret_cast<uint32_t*>(&r3);
+}
+
+template <int BF16>
+__device__ __forceinline__ uint32_t pack2(float lo, float hi) {
+    if (BF16) {
+        __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
+        return *reinterpret_cast<uint32_t*>(&v);
+    }
+    __half2 v = __floats2half2_rn(lo, hi);
+    return *reinterpret_cast<uint32_t*>(&v);
+}
+
+// Operand-side dequant of one word: every weight becomes T(f32(scale) * code),
+// the reference's rounded weight (the f32 product of an f16 scale and a 4-bit
+// code is exact, so this is one rounding; dequant_rows,
+// src/kernels/q4/weights.rs:250-256).  sc points at this column group's staged
+// scale rows [row][16]; d is the depth of the word's first element relative to
+// the first staged row's block start.
+template <int BF16>
+__device__ __forceinline__ void decode_word_scaled(uint32_t w, uint32_t (&a)[4], const uint16_t* sc, int g,
+                                                   int d_rel, int log2_block) {
+    // nibble -> (column half, depth offset): see layout.h
+    float v[8];
+#pragma unroll
+    for (int nb = 0; nb < 8; ++nb) {
+        const int hi_col = (nb >> 1) & 1;
+        const int e = ((nb & 1) << 1) | (nb >> 2);   // nib 0,4,1,5 -> e 0,1,2,3
+        const int code = (int)((w >> (4 * nb)) & 0xfu) - 8;
+        const int row = (d_rel + e) >> log2_block;
+        const float s = __half2float(__ushort_as_half(sc[row * 16 + g + 8 * hi_col]));
+        v[nb] = s * (float)code;
+    }
+    a[0] = pack2<BF16>(v[0], v[4]);   // column g,   depths +0,+1
+    a[1] = pack2<BF16>(v[2], v[6]);   // column g+8, depths +0,+1
+    a[2] = pack2<BF16>(v[1], v[5]);   // column g,   depths +2,+3
+    a[3] = pack2<BF16>(v[3], v[7]);   // column g+8, depths +2,+3
+}
+
+struct Q4GemvSmem {
+    int ns, cg, rps;              // stages, column groups per CTA, staged scale rows per stage
+    int code_bytes, scale_bytes;  // per column group per stage
+};
+
+template <int BF16, int OPSIDE, int MT>
+__global__ void __launch_bounds__(kThreads) q4_gemv_kernel(Q4GemvArgs p) {
+    extern __shared__ __align__(128) unsigned char smem_raw[];
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const int g = lane >> 2, t = lane & 3;
+    const int NS = p.ns, CG = p.cg;
+    const int code_bytes = kUnitBytes * kConsumerWarps;       // per cg per stage
+    const int scale_bytes = p.rps * 32;                       // per cg per stage
+    const int stage_bytes = CG * (code_bytes + scale_bytes);
+
+    // ---- shared memory carve-up ----
+    uint64_t* full = reinterpret_cast<uint64_t*>(smem_raw);
+    uint64_t* empty = full + NS;
+    volatile int* abort_flag = reinterpret_cast<volatile int*>(empty + NS);
+    unsigned char* stages = smem_raw + 256;
+    const int a_stride = p.ka + 8;                            // halves; +16 B keeps LDS.128 conflict-free
+    uint16_t* As = reinterpret_cast<uint16_t*>(stages + (size_t)NS * stage_bytes);
+    float* red = reinterpret_cast<float*>(reinterpret_cast<unsigned char*>(As) + (size_t)8 * MT * a_stride * 2);
+
+    const int cg0 = blockIdx.x * CG;                          // first column group of this CTA
+    const int ncg = min(CG, p.n16 - cg0);
+    const int row0 = blockIdx.y * 8 * MT;                     // first activation row of this CTA
+    const int num_stages = (p.k64 + kConsumerWarps - 1) / kConsumerWarps;
+
+    if (tid == 0) {
+        for (int s = 0; s < NS; ++s) {
+            mbar_init(&full[s], 1);
+            mbar_init(&empty[s], kConsumerWarps);
+        }
+        *abort_flag = 0;
+        fence_barrier_init();
+    }
+    __syncthreads();
+
+    if (warp == kConsumerWarps) {
+        // ================= producer: stream this CTA's weights =================
+        if (lane == 0) {
+            for (int st = 0; st < num_stages; ++st) {
+                const int slot = st % NS;
+                if (st >= NS) mbar_wait(&empty[slot], ((st / NS) - 1) & 1, abort_flag, p.status);
+                const int units = min(kConsumerWarps, p.k64 - st * kConsumerWarps);
+                const int blk0 = (st * kStageDepth) >> p.log2_block;
+                const int blk1 = min(p.nb, ((st * kStageDepth + units * 64 - 1) >> p.log2_block) + 1);
+                const int rows = blk1 - blk0;
+                const unsigned cb = units * kUnitBytes, sb = rows * 32;
+                mbar_expect_tx(&full[slot], ncg * (cb + sb));
+                unsigned char* sbase = stages + (size_t)slot * stage_bytes;
+                for (int c = 0; c < ncg; ++c) {
+                    const size_t cgi = cg0 + c;
+                    bulk_g2s(sbase + c * code_bytes, p.codes + ((cgi * p.k64 + (size_t)st * kConsumerWarps) * kUnitBytes), cb,
+                             &full[slot]);
+                    bulk_g2s(sbase + CG * code_bytes + c * scale_bytes, p.scales + (cgi * p.nb + blk0) * 16, sb, &full[slot]);
+                }
+            }
+        }
+        return;
+    }
+
+    // ================= consumers =================
+    float total[4][MT][4];
+#pragma unroll
+    for (int c = 0; c < 4; ++c)
+#pragma unroll
+        for (int mt = 0; mt < MT; ++mt)
+#pragma unroll
+            for (int r = 0; r < 4; ++r) total[c][mt][r] = 0.0f;
+    const float zero4[4] = {0.f, 0.f, 0.f, 0.f};
+
+    const int kpad = p.k64 * 64;
+    for (int ka0 = 0; ka0 < kpad; ka0 += p.ka) {
+        // ---- stage the activation chunk [8*MT rows][ka] (zero padded) ----
+        asm volatile("bar.sync 1, %0;" ::"n"(32 * kConsumerWarps));
+        const int chunk = min(p.ka, kpad - ka0);
+        const int vec_per_row = chunk / 8;
+        for (int idx = tid; idx < 8 * MT * vec_per_row; idx += 32 * kConsumerWarps) {
+            const int r = idx / vec_per_row, v = idx % vec_per_row;
+            const int row = row0 + r, d = ka0 + v * 8;
+            uint4 val = make_uint4(0, 0, 0, 0);
+            if (row < p.m) {
+                const uint16_t* src = p.a + (size_t)row * p.k + d;
+                if (p.a_vec_ok && d + 8 <= p.k) {
+                    val = *reinterpret_cast<const uint4*>(src);
+                } else {
+                    uint16_t tmp[8];
+#pragma unroll
+                    for (int e = 0; e < 8; ++e) tmp[e] = (d + e < p.k) ? src[e] : (uint16_t)0;
+                    val = *reinterpret_cast<uint4*>(tmp);
+                }
+            }
+            *reinterpret_cast<uint4*>(As + (size_t)r * a_stride + v * 8) = val;
+        }
+        asm volatile("bar.sync 1, %0;" ::"n"(32 * kConsumerWarps));
+
+        const int st_begin = ka0 / kStageDepth, st_end = min(num_stages, (ka0 + chunk) / kStageDepth + ((ka0 + chunk) % kStageDepth ? 1 : 0));
+        for (int st = st_begin; st < st_end; ++st) {
+            const int slot = st % NS;
+            mbar_wait(&full[slot], (st / NS) & 1, abort_flag, p.status);
+            const int units = min(kConsumerWarps, p.k64 - st * kConsumerWarps);
+            if (warp < units) {
+                const unsigned char* sbase = stages + (size_t)slot * stage_bytes;
+                const int d_unit = st * kStageDepth + warp * 64;            // global depth of this unit
+                const int dl = d_unit - ka0;                                // within the staged A chunk
+                const int blk0 = (st * kStageDepth) >> p.log2_block;        // first staged scale row
+                // activation fragments for this unit, shared by every column group
+                uint4 alo[MT], ahi[MT];
+#pragma unroll
+                for (int mt = 0; mt < MT; ++mt) {
+                    const uint16_t* ar = As + (size_t)(8 * mt + g) * a_stride + dl + 8 * t;
+                    alo[mt] = *reinterpret_cast<const uint4*>(ar);
+                    ahi[mt] = *reinterpret_cast<const uint4*>(ar + 32);
+                }
+#pragma unroll
+                for (int c = 0; c < 4; ++c) {
+                    if (c >= ncg) break;
+                    const uint4 wv = *reinterpret_cast<const uint4*>(sbase + c * code_bytes + warp * kUnitBytes + lane * 16);
+                    const uint16_t* sc = reinterpret_cast<const uint16_t*>(sbase + CG * code_bytes + c * scale_bytes);
+                    const uint32_t words[4] = {wv.x, wv.y, wv.z, wv.w};
+                    if (OPSIDE) {
+#pragma unroll
+                        for (int ks = 0; ks < 4; ++ks) {
+                            uint32_t af[4];
+                            const int d_word = d_unit + 32 * (ks >> 1) + 8 * t + 4 * (ks & 1);
+                            decode_word_scaled<BF16>(words[ks], af, sc, g, d_word - (blk0 << p.log2_block), p.log2_block);
+#pragma unroll
+                            for (int mt = 0; mt < MT; ++mt) {
+                                const uint4& av = (ks >> 1) ? ahi[mt] : alo[mt];
+                                const uint32_t b0 = (ks & 1) ? av.z : av.x, b1 = (ks & 1) ? av.w : av.y;
+                                if (BF16) mma_bf16(total[c][mt], af, b0, b1, total[c][mt]);
+                                else mma_f16(total[c][mt], af, b0, b1, total[c][mt]);
+                            }
+                        }
+                    } else {
+                        // accumulator-side scaling: raw code sums per 32-deep half unit,
+                        // folded with the f32 block scale (block >= 32 here)
+#pragma unroll
+                        for (int h = 0; h < 2; ++h) {
+                            uint32_t af0[4], af1[4];
+                            decode_word_f16(words[2 * h], af0);
+                            decode_word_f16(words[2 * h + 1], af1);
+                            const int row = ((d_unit + 32 * h) >> p.log2_block) - blk0;
+                            const float s_lo = __half2float(__ushort_as_half(sc[row * 16 + g]));
+                            const float s_hi = __half2float(__ushort_as_half(sc[row * 16 + g + 8]));
+#pragma unroll
+                            for (int mt = 0; mt < MT; ++mt) {
+                                const uint4& av = h ? ahi[mt] : alo[mt];
+                                float part[4];
+                                mma_f16(part, af0, av.x, av.y, zero4);
+                                mma_f16(part, af1, av.z, av.w, part);
+                                total[c][mt][0] = fmaf(part[0], s_lo, total[c][mt][0]);
+                                total[c][mt][1] = fmaf(part[1], s_lo, total[c][mt][1]);
+                                total[c][mt][2] = fmaf(part[2], s_hi, total[c][mt][2]);
+                                total[c][mt][3] = fmaf(part[3], s_hi, total[c][mt][3]);
+                            }
+                        }
+                    }
+                }
+            }
+            __syncwarp();
+            if (lane == 0) mbar_arrive(&empty[slot]);
+        }
+    }
+
+    // ---- fixed-order reduction over the 8 warps, epilogue, store ----
+    // red[warp][c][mt][r][lane]
+#pragma unroll
+    for (int c = 0; c < 4; ++c) {
+        if (c >= CG) break;
+#pragma unroll
+        for (int mt = 0; mt < MT; ++mt)
+#pragma unroll
+            for (int r = 0; r < 4; ++r) red[((((size_t)warp * CG + c) * MT + mt) * 4 + r) * 32 + lane] = total[c][mt][r];
+    }
+    asm volatile("bar.sync 1, %0;" ::"n"(32 * kConsumerWarps));
+    const int per_warp = CG * MT * 128;
+    for (int o = tid; o < per_warp; o += 32 * kConsumerWarps) {
+        float acc = 0.0f;
+#pragma unroll
+        for (int w = 0; w < kConsumerWarps; ++w) acc += red[(size_t)w * per_warp + o];
+        const int ln = o & 31, r = (o >> 5) & 3, mt = (o >> 7) % MT, c = o / (128 * MT);
+        const int col = (cg0 + c) * 16 + (ln >> 2) + 8 * (r >> 1);
+        const int row = row0 + 8 * mt + 2 * (ln & 3) + (r & 1);
+        if (c < ncg && col < p.n && row < p.m) {
+            if (p.c32) p.c32[(size_t)row * p.n + col] = acc;
+            else p.c[(size_t)row * p.n + col] = ep_store_value<BF16>(p.ep, acc, (size_t)row, (size_t)col);
+        }
+    }
+}
+
+template <int BF16, int OPSIDE, int MT>
+cudaError_t launch(const Q4GemvArgs& a, dim3 grid, size_t smem, cudaStream_t stream) {
+    auto kern = q4_gemv_kernel<BF16, OPSIDE, MT>;
+    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    if (e != cudaSuccess) return e;
+    kern<<<grid, kThreads, smem, stream>>>(a);
+    return cudaGetLastError();
+}
+
+}  // namespace
+
+// Host-side launcher.  Chooses the column groups per CTA so that the grid has
+// at least about two CTAs per SM when the matrix allows it, the ring depth from
+// the shared-memory budget, and the activation chunk from the row count.
+cudaError_t q4_gemv_launch(Q4GemvArgs a, int bf16, int sm_count, cudaStream_t stream) {
+    const int opside = bf16 || a.log2_block < 5;
+    const int rows_left = a.m;
+    int mt = rows_left <= 8 ? 1 : (rows_left <= 16 ? 2 : 4);
+    int cg = 4;
+    while (cg > 1 && (a.n16 + cg - 1) / cg < 2 * sm_count) cg >>= 1;
+    a.cg = cg;
+    const int block = 1 << a.log2_block;
+    // scale rows staged per stage: a stage starts on a block boundary when the
+    // block is shorter than it, and lies inside one block otherwise
+    a.rps = block < kStageDepth ? kStageDepth / block : 1;
+    const int stage_bytes = cg * (kUnitBytes * kConsumerWarps + a.rps * 32);
+    int ns = (72 * 1024) / stage_bytes;
+    if (ns > 8) ns = 8;
+    if (ns < 2) ns = 2;
+    a.ns = ns;
+    const int kpad = a.k64 * 64;
+    int ka = (64 * 1024 / (8 * mt * 2)) / kStageDepth * kStageDepth;   // 64 KB of activations at most
+    if (ka < kStageDepth) ka = kStageDepth;
+    if (ka > kpad) ka = ((kpad + kStageDepth - 1) / kStageDepth) * kStageDepth;
+    if (ka == 0) ka = kStageDepth;
+    a.ka = ka;
+    const size_t smem = 256 + (size_t)ns * stage_bytes + (size_t)8 * mt * (ka + 8) * 2 +
+                        (size_t)kConsumerWarps * cg * mt * 128 * sizeof(float);
+    dim3 grid((a.n16 + cg - 1) / cg, (a.m + 8 * mt - 1) / (8 * mt));
+#define SMEG_Q4_LAUNCH(B, O, M) return launch<B, O, M>(a, grid, smem, stream)
+    if (!bf16 && !opside) {
+        if (mt == 1) SMEG_Q4_LAUNCH(0, 0, 1);
+        if (mt == 2) SMEG_Q4_LAUNCH(0, 0, 2);
+        SMEG_Q4_LAUNCH(0, 0, 4);
+    } else if (!bf16) {
+        if (mt == 1) SMEG_Q4_LAUNCH(0, 1, 1);
+        if (mt == 2) SMEG_Q4_LAUNCH(0, 1, 2);
+        SMEG_Q4_LAUNCH(0, 1, 4);
+    } else {
+        if (mt == 1) SMEG_Q4_LAUNCH(1, 1, 1);
+        if (mt == 2) SMEG_Q4_LAUNCH(1, 1, 2);
+        SMEG_Q4_LAUNCH(1, 1, 4);
+    }
+#undef SMEG_Q4_LAUNCH
+}
+
+}  // namespace smeg
