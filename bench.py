@@ -1,0 +1,429 @@
+#!/usr/bin/env python
+"""Benchmark of the weight-quantised matmul hot path on B200.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl reference]
+
+Headline line (one JSON object on stdout, printed by rank 0): tokens/s of the
+Q4 SwiGLU MLP block of BASELINE.json configs[4] (hidden 4096, intermediate
+14336, M = 256 tokens per step), tensor parallel over N GPUs (gate/up sharded by
+hidden unit, down by the same rows, one all-reduce of the f32 partials).  A step
+is one Mlp::accumulate pass over one synthetic batch.  Total work is fixed as N
+grows ("strong" scaling).  Between steps the weights rotate over enough distinct
+device copies to exceed twice the L2, so every step streams its weights from HBM.
+
+`--impl reference` times the CPU oracle (the C restatement of the reference's
+portable scalar path; the reference itself is Rust and cannot be built here) on
+the host cores with the same metric, on a bounded row sample of the same batch.
+
+The extra "kernels" list reports the single-kernel configs of BASELINE.json
+(Q4 / 2-bit / 1-bit decode GEMV in GB/s, Q4 prefill GEMM in TFLOP/s) measured on
+rank 0 at N = 1.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import subprocess
+import sys
+import threading
+import time
+
+import numpy as np
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+HIDDEN, INTER, BLOCK = 4096, 14336, 32
+L2_BYTES = 126 * 1024 * 1024
+
+
+def measured_peaks():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(path):
+        with open(path) as f:
+            p = json.load(f)
+        return {"hbm_gbs": p["hbm_gbs"], "bf16_tflops": p["bf16_tflops"],
+                "bf16_tflops_sustained": p.get("bf16_tflops_sustained", p["bf16_tflops"]), "source": "measured"}
+    return {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0, "source": "fallback"}
+
+
+class ClockSampler:
+    """Samples SM clocks and throttle reasons with nvidia-smi while a region runs."""
+
+    Q = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,clocks_event_reasons.hw_slowdown,"
+         "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index: int):
+        self.index, self.proc, self.lines = index, None, []
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(["nvidia-smi", f"--id={self.index}", f"--query-gpu={self.Q}", "--format=csv,noheader,nounits",
+                                          "-lms", "100"], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            self.thread = threading.Thread(target=self._read, daemon=True)
+            self.thread.start()
+        except Exception:
+            self.proc = None
+
+    def _read(self):
+        for line in self.proc.stdout:
+            self.lines.append(line.strip())
+
+    def stop(self):
+        if not self.proc:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=2)
+        except Exception:
+            self.proc.kill()
+        sm, mx, reasons = [], [], set()
+        for ln in self.lines:
+            parts = [x.strip() for x in ln.split(",")]
+            if len(parts) < 9:
+                continue
+            try:
+                sm.append(float(parts[1])); mx.append(float(parts[2]))
+            except ValueError:
+                continue
+            for name, val in zip(("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"), parts[5:9]):
+                if val.lower().startswith("active"):
+                    reasons.add(name)
+        return {"sm_mhz": float(np.median(sm)) if sm else None, "sm_max_mhz": max(mx) if mx else None,
+                "samples": len(sm), "reasons": sorted(reasons)}
+
+
+# --------------------------------------------------------------------------- synthetic weights
+
+def mlp_weights_f32(seed: int):
+    """W_gate, W_up [INTER][HIDDEN], W_down [HIDDEN][INTER] ~ N(0, 0.02), f32 (seeded)."""
+    rng = np.random.default_rng(seed)
+    wg = (rng.standard_normal((INTER, HIDDEN), dtype=np.float32) * np.float32(0.02))
+    wu = (rng.standard_normal((INTER, HIDDEN), dtype=np.float32) * np.float32(0.02))
+    wd = (rng.standard_normal((HIDDEN, INTER), dtype=np.float32) * np.float32(0.02))
+    return wg, wu, wd
+
+
+def shard_bounds(rank: int, world: int):
+    """Hidden units [lo, hi) owned by a rank: whole 32-unit interleave chunks (= whole K-blocks of down)."""
+    chunks = INTER // 32
+    lo = (chunks * rank // world) * 32
+    hi = (chunks * (rank + 1) // world) * 32
+    return lo, hi
+
+
+# --------------------------------------------------------------------------- reference arm (CPU oracle)
+
+def run_reference(args):
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    import oracle as orc
+    cores = orc.max_threads()
+    orc.set_threads(cores)
+    m = args.m
+    rows = max(1, min(m, args.ref_rows))
+    rng = np.random.default_rng(1)
+    # synthetic codes / scales with the value distribution of quantised N(0, 0.02) weights
+    wg, wu, wd = mlp_weights_f32(5)
+    import sme_gemm_b200 as sg
+    both = sg.interleave_gate_up(wg, wu, sg.WeightLayout.OutIn, INTER, HIDDEN)
+    guq, gus, _ = orc.q4_quantize(both, 1, 2 * INTER, HIDDEN)
+    dq, ds, _ = orc.q4_quantize(wd, 0, HIDDEN, INTER)
+    del wg, wu, wd, both
+    x = rng.standard_normal((m, HIDDEN)).astype(np.float16)
+    y = np.zeros((m, HIDDEN), np.float32)
+
+    def step():
+        orc.mlp_accumulate(x, y, m, HIDDEN, INTER, guq, gus, dq, ds, BLOCK, 3, 0, rows)
+
+    for _ in range(args.warmup):
+        step()
+    t0 = time.perf_counter()
+    for _ in range(args.steps):
+        step()
+    dt = (time.perf_counter() - t0) / args.steps
+    value = rows / dt
+    sample = (f"{rows} of {m} rows per step through the whole block (per-call dequant of both weight sets included, as the "
+              f"reference's fallback does), tokens/s = rows / time")
+    line = {"impl": "reference", "metric": "q4_mlp_block_tokens_per_s", "value": value, "unit": "tokens/s", "n_gpus": args.gpus,
+            "steps": args.steps, "warmup": args.warmup, "ms_per_step": dt * 1e3, "higher_is_better": True, "scaling": "strong",
+            "vs_baseline": None, "dtype": "f16", "data": "synthetic",
+            "config": workload_config(args, 1),
+            "cpu_baseline": {"value": value, "unit": "tokens/s", "cores": cores, "kind": "port", "sample": sample},
+            "e2e": {"value": value, "unit": "tokens/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}}
+    print(json.dumps(line), flush=True)
+
+
+def workload_config(args, sets):
+    return {"workload": f"Q4 SwiGLU MLP block (BASELINE.json configs[4]): hidden {HIDDEN}, intermediate {INTER}, Q4_0 block {BLOCK}, "
+                        f"M={args.m} tokens per step, f16 activations, f32 residual",
+            "tokens_per_step": args.m, "parallelism": f"tp{args.gpus}",
+            "l2": f"weights rotate over {sets} distinct device copies per rank (> 2x L2) between steps"}
+
+
+# --------------------------------------------------------------------------- our arm
+
+def graph_time_us(torch, fn, n_items, reps=20):
+    """Average device time of fn(i), i over n_items rotating inputs, measured by
+    replaying a CUDA graph of one pass (removes host launch overhead)."""
+    s = torch.cuda.Stream()
+    with torch.cuda.stream(s):
+        for i in range(n_items):
+            fn(i)
+    torch.cuda.synchronize()
+    g = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(g, stream=s):
+        for i in range(n_items):
+            fn(i)
+    for _ in range(3):
+        g.replay()
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(reps):
+        g.replay()
+    e1.record()
+    torch.cuda.synchronize()
+    return e0.elapsed_time(e1) * 1e3 / (reps * n_items)
+
+
+def kernel_configs(torch, sg, orc, peaks):
+    """BASELINE.json configs[0..3] as single kernels on one GPU (device-resident, graph replay)."""
+    out = []
+    rng = np.random.default_rng(7)
+    hbm = peaks["hbm_gbs"]
+
+    def sets_for(bytes_per_set):
+        return max(2, int(np.ceil(2.2 * L2_BYTES / bytes_per_set)))
+
+    # configs[0]: Q4 decode GEMV 1 x 4096 x 4096
+    n = k = 4096
+    w = (rng.standard_normal(n * k) * 0.02).astype(np.float32)
+    q, s, _ = orc.q4_quantize(w, 0, n, k)
+    ws = [sg.Q4Weights.new(q, s, n, k) for _ in range(sets_for(9.4e6))]
+    a = torch.randn(1, k, device="cuda", dtype=torch.float16)
+    c = torch.zeros(1, n, device="cuda", dtype=torch.float16)
+    us = graph_time_us(torch, lambda i: sg.matmul_q4(a, ws[i], c, 1), len(ws))
+    out.append({"config": "q4_gemv_1x4096x4096", "us": us, "value": 9453568 / us / 1e3, "unit": "GB/s",
+                "frac_of_measured_hbm": 9453568 / us / 1e3 / hbm, "algorithmic_bytes": 9453568})
+    del ws
+    # configs[1]: ternary 2-bit GEMV 1 x 4096 x 11008, block 256
+    n = 11008
+    two = rng.integers(0, 3, k * n).astype(np.uint8)
+    codes = (two[0::4] | (two[1::4] << 2) | (two[2::4] << 4) | (two[3::4] << 6)).astype(np.uint8)
+    sc = orc.f32_to_f16_bits(rng.uniform(0.01, 0.05, n * (k // 256)).astype(np.float32))
+    ws = [sg.Q2Weights.new(codes, sc, n, k) for _ in range(sets_for(11.6e6))]
+    c = torch.zeros(1, n, device="cuda", dtype=torch.float16)
+    us = graph_time_us(torch, lambda i: sg.matmul_q2(a, ws[i], c, 1), len(ws))
+    out.append({"config": "q2_ternary_gemv_1x4096x11008", "us": us, "value": 11654656 / us / 1e3, "unit": "GB/s",
+                "frac_of_measured_hbm": 11654656 / us / 1e3 / hbm, "algorithmic_bytes": 11654656})
+    del ws
+    # configs[2]: 1-bit GEMV batch 8 x 4096 x 14336, block 128, mul_col.add_col
+    n = 14336
+    signs = rng.integers(0, 256, k * n // 8).astype(np.uint8)
+    sc = orc.f32_to_f16_bits(rng.uniform(0.005, 0.03, n * (k // 128)).astype(np.float32))
+    ws = [sg.Q1Weights.new(signs, sc, sg.WeightLayout.OutIn, n, k, 128) for _ in range(sets_for(8.6e6))]
+    a8 = torch.randn(8, k, device="cuda", dtype=torch.float16)
+    c8 = torch.zeros(8, n, device="cuda", dtype=torch.float16)
+    sv = torch.empty(n, device="cuda", dtype=torch.float16).uniform_(0.5, 1.5)
+    bv = torch.randn(n, device="cuda", dtype=torch.float16) * 0.1
+    ep = sg.Epilogue().mul_col(sv).add_col(bv)
+    us = graph_time_us(torch, lambda i: sg.matmul_q1_ep(a8, ws[i], c8, 8, ep), len(ws))
+    out.append({"config": "q1_gemv_8x4096x14336_mulcol_addcol", "us": us, "value": 8609792 / us / 1e3, "unit": "GB/s",
+                "frac_of_measured_hbm": 8609792 / us / 1e3 / hbm, "algorithmic_bytes": 8609792})
+    del ws
+    # configs[3]: Q4 prefill GEMM bf16 512 x 4096 x 14336 + add_col.silu.clamp
+    w = (rng.standard_normal(n * k) * 0.02).astype(np.float32)
+    q, s, _ = orc.q4_quantize(w, 0, n, k)
+    ws = [sg.Q4Weights.new(q, s, n, k) for _ in range(sets_for(33e6))]
+    ab = torch.randn(512, k, device="cuda", dtype=torch.bfloat16)
+    cb = torch.zeros(512, n, device="cuda", dtype=torch.bfloat16)
+    bias = (torch.randn(n, device="cuda") * 0.1).to(torch.bfloat16)
+    ep4 = sg.Epilogue("bf16").add_col(bias).silu().clamp(-6.0, 6.0)
+    us = graph_time_us(torch, lambda i: sg.matmul_q4_bf16_ep(ab, ws[i], cb, 512, ep4), len(ws), reps=10)
+    flops = 2.0 * 512 * k * n
+    out.append({"config": "q4_prefill_gemm_bf16_512x4096x14336_addcol_silu_clamp", "us": us, "value": flops / us / 1e6,
+                "unit": "TFLOP/s", "frac_of_measured_bf16_burst": flops / us / 1e6 / peaks["bf16_tflops"],
+                "frac_of_nominal_2250": flops / us / 1e6 / 2250.0, "algorithmic_flops": flops})
+    del ws
+    return out
+
+
+def run_ours(args):
+    import torch
+    import oracle as orc          # checker / CPU baseline only
+    import sme_gemm_b200 as sg
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a CUDA device: there is no CPU fallback for the product path")
+    torch.cuda.set_device(local)
+    dist = None
+    if world > 1:
+        import torch.distributed as dist_mod
+        dist = dist_mod
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local))
+    assert world == args.gpus or world == 1, f"--gpus {args.gpus} but WORLD_SIZE={world}"
+    peaks = measured_peaks()
+    m = args.m
+
+    # ---- weights: this rank's shard, quantised once, uploaded as several distinct copies ----
+    wg, wu, wd = mlp_weights_f32(5)
+    lo, hi = shard_bounds(rank, world)
+    fl = hi - lo
+    both = sg.interleave_gate_up(wg[lo:hi], wu[lo:hi], sg.WeightLayout.OutIn, fl, HIDDEN)
+    guq, gus, _ = orc_quant(sg, both, 1, 2 * fl, HIDDEN)
+    dq, ds, _ = orc_quant(sg, np.ascontiguousarray(wd[:, lo:hi]), 0, HIDDEN, fl)
+    del wg, wu, wd, both
+    bytes_per_set = (2 * fl * HIDDEN + HIDDEN * fl) * 0.5625
+    nsets = max(2, int(np.ceil(2.2 * L2_BYTES / bytes_per_set)))
+    mlps = []
+    for _ in range(nsets):
+        up = sg.GatedLinear(sg.Linear(sg.Q4Weights.new(guq, gus, 2 * fl, HIDDEN)), sg.Gate.Silu)
+        down = sg.Linear(sg.Q4Weights.new(dq, ds, HIDDEN, fl))
+        mlps.append(sg.Mlp.gated(up, down))
+
+    gen = torch.Generator(device="cuda").manual_seed(11)
+    x = torch.randn(m, HIDDEN, device="cuda", dtype=torch.float16, generator=gen)
+    y = torch.zeros(m, HIDDEN, device="cuda", dtype=torch.float32)
+    partial = torch.zeros(m, HIDDEN, device="cuda", dtype=torch.float32)
+    x_host = x.cpu().pin_memory()
+    y_host = torch.zeros(m, HIDDEN, dtype=torch.float32).pin_memory()
+
+    def step(i):
+        mlp = mlps[i % nsets]
+        if world == 1:
+            mlp.accumulate(x, y, m)
+        else:
+            mlp.partial(x, partial, m)
+            dist.all_reduce(partial)
+            sg.Mlp.finish(y, partial)
+
+    def sync():
+        if dist:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    def timed(fn, steps):
+        sync()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for i in range(steps):
+            fn(i)
+        e1.record()
+        sync()
+        ms = torch.tensor([e0.elapsed_time(e1)], device="cuda")
+        if dist:
+            dist.all_reduce(ms, op=dist.ReduceOp.MAX)
+        return float(ms.item())
+
+    for i in range(args.warmup):
+        step(i)
+    sampler = ClockSampler(local) if rank == 0 else None
+    if sampler:
+        sampler.start()
+    ms = timed(step, args.steps)
+    clocks = sampler.stop() if sampler else None
+    value = m * args.steps / (ms * 1e-3)
+
+    # ---- end to end: host buffers in and out every step ----
+    def e2e_step(i):
+        x.copy_(x_host, non_blocking=True)
+        step(i)
+        if rank == 0:
+            y_host.copy_(y, non_blocking=True)
+
+    for i in range(2):
+        e2e_step(i)
+    ms_e2e = timed(e2e_step, args.steps)
+    e2e_value = m * args.steps / (ms_e2e * 1e-3)
+
+    status = sg.last_status()
+    if status != 0:
+        raise SystemExit(f"a kernel abandoned a bounded wait (status {status}); numbers are void")
+
+    if rank != 0:
+        if dist:
+            dist.destroy_process_group()
+        return
+
+    # ---- roofline of the dominant kernel: the gate/up projection (tensor bound), timed alone ----
+    both_out = torch.zeros(m, 2 * fl, device="cuda", dtype=torch.float16)
+    gu = [mm.up.inner.q4 for mm in mlps]
+    us_gu = graph_time_us(torch, lambda i: sg.matmul_q4(x, gu[i], both_out, m), nsets, reps=10)
+    flops_gu = 2.0 * m * HIDDEN * 2 * fl
+    ach = flops_gu / us_gu / 1e6
+    roofline = {"kernel": "gemm_tc_kernel (gate/up projection, this rank's shard)", "bound": "tensor", "achieved": ach,
+                "peak": peaks["bf16_tflops"], "unit": "TFLOP/s", "frac": ach / peaks["bf16_tflops"],
+                "peak_source": peaks["source"] + " (burst: kernel timed alone)", "us_per_launch": us_gu, "traffic": None}
+
+    # ---- CPU baseline beside it: the oracle block on a bounded row sample, all host cores ----
+    cores = orc.max_threads()
+    orc.set_threads(cores)
+    rows = max(1, min(m, args.ref_rows))
+    wg, wu, wd = mlp_weights_f32(5)
+    bothf = sg.interleave_gate_up(wg, wu, sg.WeightLayout.OutIn, INTER, HIDDEN)
+    fguq, fgus, _ = orc.q4_quantize(bothf, 1, 2 * INTER, HIDDEN)
+    fdq, fds, _ = orc.q4_quantize(wd, 0, HIDDEN, INTER)
+    del wg, wu, wd, bothf
+    xs = x_host.numpy()
+    yc = np.zeros((m, HIDDEN), np.float32)
+    orc.mlp_accumulate(xs, yc, m, HIDDEN, INTER, fguq, fgus, fdq, fds, BLOCK, 3, 0, 1)   # warm
+    t0 = time.perf_counter()
+    orc.mlp_accumulate(xs, yc, m, HIDDEN, INTER, fguq, fgus, fdq, fds, BLOCK, 3, 0, rows)
+    cpu_dt = time.perf_counter() - t0
+    cpu = {"value": rows / cpu_dt, "unit": "tokens/s", "cores": cores, "kind": "port",
+           "sample": f"{rows} of {m} rows through the whole block once, per-call dequant included"}
+
+    kernels = kernel_configs(torch, sg, orc, peaks) if (world == 1 and not args.no_kernels) else None
+
+    line = {"metric": "q4_mlp_block_tokens_per_s", "value": value, "unit": "tokens/s", "n_gpus": args.gpus, "steps": args.steps,
+            "warmup": args.warmup, "ms_per_step": ms / args.steps, "higher_is_better": True, "scaling": "strong",
+            "vs_baseline": None, "dtype": "f16", "data": "synthetic", "config": workload_config(args, nsets),
+            "clocks": clocks, "e2e": {"value": e2e_value, "unit": "tokens/s", "h2d_bytes_per_step": m * HIDDEN * 2,
+                                      "d2h_bytes_per_step": m * HIDDEN * 4, "ms_per_step": ms_e2e / args.steps},
+            "gpu_launches": 4 * args.steps, "roofline": roofline, "cpu_baseline": cpu}
+    if kernels is not None:
+        line["kernels"] = kernels
+    print(json.dumps(line), flush=True)
+    if dist:
+        dist.destroy_process_group()
+
+
+def orc_quant(sg, w, layout, n, k):
+    """Quantise with the library's own host quantiser (the product path never calls the oracle)."""
+    import ctypes as C
+    w = np.ascontiguousarray(w, dtype=np.float32).reshape(-1)
+    nbk = -(-k // BLOCK)
+    q = np.zeros((k * n + 1) // 2, np.uint8)
+    s = np.zeros(n * nbk, np.uint16)
+    rc = sg.lib().smeg_host_q4_quantize(w.ctypes.data, layout, n, k, BLOCK, q.ctypes.data, s.ctypes.data)
+    if rc != 0:
+        raise RuntimeError(f"smeg_host_q4_quantize returned {rc}")
+    return q, s, None
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--m", type=int, default=256, help="tokens per step (BASELINE.json: 1 or 256)")
+    ap.add_argument("--ref-rows", type=int, default=4, help="rows of the batch the CPU arm computes per step")
+    ap.add_argument("--no-kernels", action="store_true", help="skip the single-kernel configs")
+    args = ap.parse_args()
+    if args.warmup < 3:
+        args.warmup = 3
+    if args.impl == "reference":
+        run_reference(args)
+    else:
+        run_ours(args)
+
+
+if __name__ == "__main__":
+    main()

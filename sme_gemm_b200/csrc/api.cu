@@ -35,6 +35,14 @@ struct DeviceState {
 std::mutex g_mu;
 std::map<int, DeviceState> g_dev;
 int g_trace = -1;
+// Row count above which the tcgen05 prefill GEMM replaces the decode kernel (the
+// reference switches kernels at Linear::PANEL_ROWS = 8 rows, src/linear.rs:160;
+// the decode kernel here carries up to 32 rows per pass).  SMEG_TC_MIN_ROWS
+// overrides it for tuning.
+int g_tc_min_rows = []() {
+    const char* e = getenv("SMEG_TC_MIN_ROWS");
+    return e ? atoi(e) : 32;
+}();
 
 DeviceState* dev_state() {
     int dev = 0;
@@ -511,7 +519,19 @@ static int q4_dev(const smeg_q4* w, const uint16_t* a, uint16_t* c, size_t m, co
     g.log2_block = w->d.log2_block;
     g.a_vec_ok = (k % 8 == 0) && ((uintptr_t)a % 16 == 0);
     g.status = ds->status;
-    cudaError_t e = q4_gemv_launch(g, bf16, ds->sm_count, stream);
+    cudaError_t e;
+    if ((int)m > g_tc_min_rows && gemm_tc_supported(4, (int)m, (int)k, w->d.log2_block, a)) {
+        GemmTcArgs t;
+        memset(&t, 0, sizeof(t));
+        t.codes = w->codes; t.scales = w->scales; t.a = a; t.c = c; t.c32 = c32;
+        t.m = (int)m; t.n = (int)n; t.k = (int)k;
+        t.n16 = (int)w->d.n16; t.ku = (int)w->d.ku; t.nb = (int)w->d.nb; t.log2_block = w->d.log2_block;
+        t.status = ds->status;
+        t.ep = g.ep;
+        e = gemm_tc_launch(t, bf16, 4, stream);
+    } else {
+        e = q4_gemv_launch(g, bf16, ds->sm_count, stream);
+    }
     if (ext) cudaFreeAsync(ext, stream);
     return e == cudaSuccess ? 0 : -6;
 }

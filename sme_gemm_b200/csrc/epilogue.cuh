@@ -120,4 +120,15 @@ __device__ __forceinline__ uint16_t ep_store_value(const EpParams& ep, float acc
     return f32_to_t<BF16>(x);
 }
 
+// Same, over an explicit node array (shared or global memory).
+template <int BF16>
+__device__ __forceinline__ uint16_t ep_store_nodes(const EpNodeDev* nodes, int nn, float acc, size_t i, size_t j) {
+    uint16_t c = f32_to_t<BF16>(acc);
+    if (nn == 0) return c;
+    float x = t_to_f32<BF16>(c);
+#pragma unroll 1
+    for (int q = 0; q < nn; ++q) x = ep_node<BF16>(nodes[q], x, i, j);
+    return f32_to_t<BF16>(x);
+}
+
 }  // namespace smeg

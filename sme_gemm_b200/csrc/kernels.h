@@ -18,7 +18,7 @@ struct Q4GemvArgs {
     int m, n, k;
     int n16, k64, nb;             // column groups, 64-deep units, staged scale rows per group
     int log2_block;
-    int ns, cg, rps, ka;          // filled in by the launcher
+    int ns, cg, rps, ka, a_rows;  // filled in by the launcher
     int a_vec_ok;                 // rows of `a` are 16-byte aligned (k % 8 == 0 and base aligned)
     unsigned* status;
     EpParams ep;
@@ -52,6 +52,22 @@ struct LowbitGemvArgs {
     EpParams ep;
 };
 cudaError_t lowbit_gemv_launch(LowbitGemvArgs a, int bits, int sm_count, cudaStream_t stream);
+
+// ---- prefill GEMM on tcgen05 (gemm_tc.cu) ----
+struct GemmTcArgs {
+    const unsigned char* codes;   // packed units [n16][ku][512 B]
+    const uint16_t* scales;       // f16 bits [n16][nb][16]
+    const uint16_t* a;            // tokens, row-major m x k (T bits), 16-byte aligned rows
+    uint16_t* c;                  // m x n (T bits)
+    float* c32;                   // if set: raw f32 accumulators instead
+    int m, n, k;
+    int n16, ku, nb, log2_block;
+    int ntok_tile, ntok_pad, ntok_box, nmma, tmem_cols, sc_rows, ns;   // launcher-filled
+    unsigned* status;
+    EpParams ep;
+};
+bool gemm_tc_supported(int wkind, int m, int k, int log2_block, const void* a);
+cudaError_t gemm_tc_launch(GemmTcArgs a, int bf16, int wkind, cudaStream_t stream);
 
 // ---- element-wise model ops (elementwise.cu) ----
 cudaError_t glu_launch(uint16_t* out, const uint16_t* both, size_t m, size_t n, uint32_t act, cudaStream_t s);

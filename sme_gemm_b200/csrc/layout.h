@@ -30,7 +30,9 @@
 //       d = 256*u + 32*s + 8*t + {0..7}
 //   column c0 + 8*(b & 1), depth d + 4*((b >> 1) & 1) + (b >> 3)
 //
-// Scales (all formats): f16 bit patterns, [column group][K-block][16 columns].
+// Scales (all formats): f16 bit patterns, [column group][K-block][16 slots]; column
+// c of the group sits in slot 2*(c % 8) + c / 8, so the two columns a lane holds
+// (g and g + 8) are one aligned 32-bit word.
 // Padding columns / depths hold code 0 (Q4), and padded scales are 0; padded
 // activations are staged as 0, so padding never contributes.
 #pragma once
@@ -45,6 +47,12 @@ constexpr int kQ2UnitDepth = 128;
 constexpr int kQ1UnitDepth = 256;
 
 inline size_t div_up(size_t a, size_t b) { return (a + b - 1) / b; }
+
+// Slot of column c (0..15) of a column group inside a 16-entry scale row.
+#if defined(__CUDACC__)
+__host__ __device__
+#endif
+inline int scale_slot(int c) { return 2 * (c & 7) + (c >> 3); }
 
 // --- Q4 ---
 // Position of (depth d, column j) inside the packed code array: byte offset of

@@ -320,7 +320,7 @@ __global__ void __launch_bounds__(kThreadsLb) lowbit_gemv_kernel(LowbitGemvArgs 
                         const int gr = row0 + r, gc = (cg0 + c) * 16 + col;
                         if (c < ncg && gr < p.m && gc < p.n) p.sums_out[((size_t)gr * p.n + gc) * p.nb_real + blk0 + bl] = s;
                     }
-                    const float sc = __half2float(__ushort_as_half(Ss[(c * bpc + bl) * 16 + col]));
+                    const float sc = __half2float(__ushort_as_half(Ss[(c * bpc + bl) * 16 + scale_slot(col)]));
                     tot = fmaf((float)s, __fmul_rn(sc, SAs[r * bpc + bl]), tot);
                 }
                 total[i] = tot;
@@ -343,8 +343,15 @@ __global__ void __launch_bounds__(kThreadsLb) lowbit_gemv_kernel(LowbitGemvArgs 
 template <int BITS, int MT>
 cudaError_t launch_lb(const LowbitGemvArgs& a, dim3 grid, size_t smem, cudaStream_t stream) {
     auto kern = lowbit_gemv_kernel<BITS, MT>;
-    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-    if (e != cudaSuccess) return e;
+    static int attr_dev = -1;   // the opt-in is per device; set it once (to the maximum) per device
+    int dev = 0;
+    cudaGetDevice(&dev);
+    if (attr_dev != dev) {
+        cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024);
+        if (e != cudaSuccess) return e;
+        attr_dev = dev;
+    }
+    if (smem > 227 * 1024) return cudaErrorInvalidConfiguration;
     kern<<<grid, kThreadsLb, smem, stream>>>(a);
     return cudaGetLastError();
 }

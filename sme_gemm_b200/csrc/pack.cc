@@ -215,11 +215,11 @@ namespace {
 void pack_scales(const uint16_t* scales, const PackedDims& d, std::vector<uint16_t>& sc) {
     sc.assign(d.n16 * d.nb * 16, 0);
     for (size_t j = 0; j < d.n; ++j)
-        for (size_t b = 0; b < d.nb_real; ++b) sc[((j / 16) * d.nb + b) * 16 + j % 16] = scales[j * d.nb_real + b];
+        for (size_t b = 0; b < d.nb_real; ++b) sc[((j / 16) * d.nb + b) * 16 + scale_slot((int)(j % 16))] = scales[j * d.nb_real + b];
 }
 void unpack_scales(const uint16_t* sc, const PackedDims& d, uint16_t* scales) {
     for (size_t j = 0; j < d.n; ++j)
-        for (size_t b = 0; b < d.nb_real; ++b) scales[j * d.nb_real + b] = sc[((j / 16) * d.nb + b) * 16 + j % 16];
+        for (size_t b = 0; b < d.nb_real; ++b) scales[j * d.nb_real + b] = sc[((j / 16) * d.nb + b) * 16 + scale_slot((int)(j % 16))];
 }
 
 struct PackCtx {

@@ -93,7 +93,7 @@ __device__ __forceinline__ void decode_word_scaled(uint32_t w, uint32_t (&a)[4],
         const int e = ((nb & 1) << 1) | (nb >> 2);   // nib 0,4,1,5 -> e 0,1,2,3
         const int code = (int)((w >> (4 * nb)) & 0xfu) - 8;
         const int row = (d_rel + e) >> log2_block;
-        const float s = __half2float(__ushort_as_half(sc[row * 16 + g + 8 * hi_col]));
+        const float s = __half2float(__ushort_as_half(sc[row * 16 + 2 * g + hi_col]));
         v[nb] = s * (float)code;
     }
     a[0] = pack2<BF16>(v[0], v[4]);   // column g,   depths +0,+1
@@ -101,11 +101,6 @@ __device__ __forceinline__ void decode_word_scaled(uint32_t w, uint32_t (&a)[4],
     a[2] = pack2<BF16>(v[1], v[5]);   // column g,   depths +2,+3
     a[3] = pack2<BF16>(v[3], v[7]);   // column g+8, depths +2,+3
 }
-
-struct Q4GemvSmem {
-    int ns, cg, rps;              // stages, column groups per CTA, staged scale rows per stage
-    int code_bytes, scale_bytes;  // per column group per stage
-};
 
 template <int BF16, int OPSIDE, int MT>
 __global__ void __launch_bounds__(kThreads) q4_gemv_kernel(Q4GemvArgs p) {
@@ -120,21 +115,33 @@ __global__ void __launch_bounds__(kThreads) q4_gemv_kernel(Q4GemvArgs p) {
     // ---- shared memory carve-up ----
     uint64_t* full = reinterpret_cast<uint64_t*>(smem_raw);
     uint64_t* empty = full + NS;
-    volatile int* abort_flag = reinterpret_cast<volatile int*>(empty + NS);
+    uint64_t* a_full = empty + NS;                            // [2] activation chunk landed
+    uint64_t* a_empty = a_full + 2;                           // [2] activation chunk released
+    volatile int* abort_flag = reinterpret_cast<volatile int*>(a_empty + 2);
     unsigned char* stages = smem_raw + 256;
     const int a_stride = p.ka + 8;                            // halves; +16 B keeps LDS.128 conflict-free
     uint16_t* As = reinterpret_cast<uint16_t*>(stages + (size_t)NS * stage_bytes);
-    float* red = reinterpret_cast<float*>(reinterpret_cast<unsigned char*>(As) + (size_t)8 * MT * a_stride * 2);
+    const int kpad = p.k64 * 64;
+    const int nchunks = (kpad + p.ka - 1) / p.ka;
+    const int nbuf = nchunks > 1 ? 2 : 1;
+    const size_t a_buf_halves = (size_t)p.a_rows * a_stride;   // only the rows in play are staged
+    float* red = reinterpret_cast<float*>(reinterpret_cast<unsigned char*>(As) + nbuf * a_buf_halves * 2);
 
     const int cg0 = blockIdx.x * CG;                          // first column group of this CTA
     const int ncg = min(CG, p.n16 - cg0);
     const int row0 = blockIdx.y * 8 * MT;                     // first activation row of this CTA
+    const int rows_used = min(8 * MT, p.m - row0);
     const int num_stages = (p.k64 + kConsumerWarps - 1) / kConsumerWarps;
+    const int stages_per_chunk = p.ka / kStageDepth;
 
     if (tid == 0) {
         for (int s = 0; s < NS; ++s) {
             mbar_init(&full[s], 1);
             mbar_init(&empty[s], kConsumerWarps);
+        }
+        for (int b = 0; b < 2; ++b) {
+            mbar_init(&a_full[b], 1);
+            mbar_init(&a_empty[b], kConsumerWarps);
         }
         *abort_flag = 0;
         fence_barrier_init();
@@ -142,9 +149,19 @@ __global__ void __launch_bounds__(kThreads) q4_gemv_kernel(Q4GemvArgs p) {
     __syncthreads();
 
     if (warp == kConsumerWarps) {
-        // ================= producer: stream this CTA's weights =================
+        // ================= producer: stream activations and this CTA's weights =================
         if (lane == 0) {
             for (int st = 0; st < num_stages; ++st) {
+                if (p.a_vec_ok && st % stages_per_chunk == 0) {
+                    // the activation chunk that starts with this stage: one bulk copy per row
+                    const int ch = st / stages_per_chunk, buf = ch & 1;
+                    if (ch >= 2) mbar_wait(&a_empty[buf], ((ch >> 1) - 1) & 1, abort_flag, p.status);
+                    const int ka0 = ch * p.ka;
+                    const unsigned bytes = (unsigned)(min(p.ka, p.k - ka0) * 2);
+                    mbar_expect_tx(&a_full[buf], rows_used * bytes);
+                    for (int r = 0; r < rows_used; ++r)
+                        bulk_g2s(As + buf * a_buf_halves + (size_t)r * a_stride, p.a + (size_t)(row0 + r) * p.k + ka0, bytes, &a_full[buf]);
+                }
                 const int slot = st % NS;
                 if (st >= NS) mbar_wait(&empty[slot], ((st / NS) - 1) & 1, abort_flag, p.status);
                 const int units = min(kConsumerWarps, p.k64 - st * kConsumerWarps);
@@ -175,32 +192,31 @@ __global__ void __launch_bounds__(kThreads) q4_gemv_kernel(Q4GemvArgs p) {
             for (int r = 0; r < 4; ++r) total[c][mt][r] = 0.0f;
     const float zero4[4] = {0.f, 0.f, 0.f, 0.f};
 
-    const int kpad = p.k64 * 64;
-    for (int ka0 = 0; ka0 < kpad; ka0 += p.ka) {
-        // ---- stage the activation chunk [8*MT rows][ka] (zero padded) ----
-        asm volatile("bar.sync 1, %0;" ::"n"(32 * kConsumerWarps));
-        const int chunk = min(p.ka, kpad - ka0);
-        const int vec_per_row = chunk / 8;
-        for (int idx = tid; idx < 8 * MT * vec_per_row; idx += 32 * kConsumerWarps) {
-            const int r = idx / vec_per_row, v = idx % vec_per_row;
-            const int row = row0 + r, d = ka0 + v * 8;
-            uint4 val = make_uint4(0, 0, 0, 0);
-            if (row < p.m) {
-                const uint16_t* src = p.a + (size_t)row * p.k + d;
-                if (p.a_vec_ok && d + 8 <= p.k) {
-                    val = *reinterpret_cast<const uint4*>(src);
-                } else {
-                    uint16_t tmp[8];
-#pragma unroll
-                    for (int e = 0; e < 8; ++e) tmp[e] = (d + e < p.k) ? src[e] : (uint16_t)0;
-                    val = *reinterpret_cast<uint4*>(tmp);
-                }
+    for (int ch = 0; ch < nchunks; ++ch) {
+        const int ka0 = ch * p.ka;
+        const int chunk = min(p.ka, kpad - ka0);               // depths of this chunk (multiple of 64)
+        const int buf = ch & (nbuf - 1);
+        uint16_t* Ab = As + buf * a_buf_halves;
+        const int valid = min(chunk, p.k - ka0);                // depths that exist in A
+        if (p.a_vec_ok) {
+            if (valid < chunk) {
+                // zero the padded tail (the bulk copy writes only the first `valid` depths)
+                for (int idx = tid; idx < rows_used * (chunk - valid); idx += 32 * kConsumerWarps)
+                    Ab[(size_t)(idx / (chunk - valid)) * a_stride + valid + idx % (chunk - valid)] = 0;
+                asm volatile("bar.sync 1, %0;" ::"n"(32 * kConsumerWarps));
             }
-            *reinterpret_cast<uint4*>(As + (size_t)r * a_stride + v * 8) = val;
+            mbar_wait(&a_full[buf], (ch >> 1) & 1, abort_flag, p.status);
+        } else {
+            // rows of A are not 16-byte aligned: cooperative copy (zero padded)
+            asm volatile("bar.sync 1, %0;" ::"n"(32 * kConsumerWarps));
+            for (int r = 0; r < rows_used; ++r) {
+                const uint16_t* src = p.a + (size_t)(row0 + r) * p.k + ka0;
+                for (int d = tid; d < chunk; d += 32 * kConsumerWarps) Ab[(size_t)r * a_stride + d] = d < valid ? src[d] : (uint16_t)0;
+            }
+            asm volatile("bar.sync 1, %0;" ::"n"(32 * kConsumerWarps));
         }
-        asm volatile("bar.sync 1, %0;" ::"n"(32 * kConsumerWarps));
 
-        const int st_begin = ka0 / kStageDepth, st_end = min(num_stages, (ka0 + chunk) / kStageDepth + ((ka0 + chunk) % kStageDepth ? 1 : 0));
+        const int st_begin = ch * stages_per_chunk, st_end = min(num_stages, st_begin + stages_per_chunk);
         for (int st = st_begin; st < st_end; ++st) {
             const int slot = st % NS;
             mbar_wait(&full[slot], (st / NS) & 1, abort_flag, p.status);
@@ -210,13 +226,18 @@ __global__ void __launch_bounds__(kThreads) q4_gemv_kernel(Q4GemvArgs p) {
                 const int d_unit = st * kStageDepth + warp * 64;            // global depth of this unit
                 const int dl = d_unit - ka0;                                // within the staged A chunk
                 const int blk0 = (st * kStageDepth) >> p.log2_block;        // first staged scale row
-                // activation fragments for this unit, shared by every column group
+                // activation fragments for this unit, shared by every column group;
+                // rows past the batch contribute zeros
                 uint4 alo[MT], ahi[MT];
 #pragma unroll
                 for (int mt = 0; mt < MT; ++mt) {
-                    const uint16_t* ar = As + (size_t)(8 * mt + g) * a_stride + dl + 8 * t;
-                    alo[mt] = *reinterpret_cast<const uint4*>(ar);
-                    ahi[mt] = *reinterpret_cast<const uint4*>(ar + 32);
+                    alo[mt] = make_uint4(0, 0, 0, 0);
+                    ahi[mt] = make_uint4(0, 0, 0, 0);
+                    if (8 * mt + g < rows_used) {
+                        const uint16_t* ar = Ab + (size_t)(8 * mt + g) * a_stride + dl + 8 * t;
+                        alo[mt] = *reinterpret_cast<const uint4*>(ar);
+                        ahi[mt] = *reinterpret_cast<const uint4*>(ar + 32);
+                    }
                 }
 #pragma unroll
                 for (int c = 0; c < 4; ++c) {
@@ -247,18 +268,19 @@ __global__ void __launch_bounds__(kThreads) q4_gemv_kernel(Q4GemvArgs p) {
                             decode_word_f16(words[2 * h], af0);
                             decode_word_f16(words[2 * h + 1], af1);
                             const int row = ((d_unit + 32 * h) >> p.log2_block) - blk0;
-                            const float s_lo = __half2float(__ushort_as_half(sc[row * 16 + g]));
-                            const float s_hi = __half2float(__ushort_as_half(sc[row * 16 + g + 8]));
+                            // one 32-bit read: the scales of columns g and g+8 sit side by side
+                            const uint32_t sp = *reinterpret_cast<const uint32_t*>(sc + row * 16 + 2 * g);
+                            const float2 sf = __half22float2(*reinterpret_cast<const __half2*>(&sp));
 #pragma unroll
                             for (int mt = 0; mt < MT; ++mt) {
                                 const uint4& av = h ? ahi[mt] : alo[mt];
                                 float part[4];
                                 mma_f16(part, af0, av.x, av.y, zero4);
                                 mma_f16(part, af1, av.z, av.w, part);
-                                total[c][mt][0] = fmaf(part[0], s_lo, total[c][mt][0]);
-                                total[c][mt][1] = fmaf(part[1], s_lo, total[c][mt][1]);
-                                total[c][mt][2] = fmaf(part[2], s_hi, total[c][mt][2]);
-                                total[c][mt][3] = fmaf(part[3], s_hi, total[c][mt][3]);
+                                total[c][mt][0] = fmaf(part[0], sf.x, total[c][mt][0]);
+                                total[c][mt][1] = fmaf(part[1], sf.x, total[c][mt][1]);
+                                total[c][mt][2] = fmaf(part[2], sf.y, total[c][mt][2]);
+                                total[c][mt][3] = fmaf(part[3], sf.y, total[c][mt][3]);
                             }
                         }
                     }
@@ -267,6 +289,7 @@ __global__ void __launch_bounds__(kThreads) q4_gemv_kernel(Q4GemvArgs p) {
             __syncwarp();
             if (lane == 0) mbar_arrive(&empty[slot]);
         }
+        if (p.a_vec_ok && lane == 0) mbar_arrive(&a_empty[buf]);
     }
 
     // ---- fixed-order reduction over the 8 warps, epilogue, store ----
@@ -298,8 +321,15 @@ __global__ void __launch_bounds__(kThreads) q4_gemv_kernel(Q4GemvArgs p) {
 template <int BF16, int OPSIDE, int MT>
 cudaError_t launch(const Q4GemvArgs& a, dim3 grid, size_t smem, cudaStream_t stream) {
     auto kern = q4_gemv_kernel<BF16, OPSIDE, MT>;
-    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-    if (e != cudaSuccess) return e;
+    static int attr_dev = -1;   // the opt-in is per device; set it once (to the maximum) per device
+    int dev = 0;
+    cudaGetDevice(&dev);
+    if (attr_dev != dev) {
+        cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024);
+        if (e != cudaSuccess) return e;
+        attr_dev = dev;
+    }
+    if (smem > 227 * 1024) return cudaErrorInvalidConfiguration;
     kern<<<grid, kThreads, smem, stream>>>(a);
     return cudaGetLastError();
 }
@@ -311,8 +341,7 @@ cudaError_t launch(const Q4GemvArgs& a, dim3 grid, size_t smem, cudaStream_t str
 // the shared-memory budget, and the activation chunk from the row count.
 cudaError_t q4_gemv_launch(Q4GemvArgs a, int bf16, int sm_count, cudaStream_t stream) {
     const int opside = bf16 || a.log2_block < 5;
-    const int rows_left = a.m;
-    int mt = rows_left <= 8 ? 1 : (rows_left <= 16 ? 2 : 4);
+    const int mt = a.m <= 8 ? 1 : (a.m <= 16 ? 2 : 4);
     int cg = 4;
     while (cg > 1 && (a.n16 + cg - 1) / cg < 2 * sm_count) cg >>= 1;
     a.cg = cg;
@@ -321,17 +350,25 @@ cudaError_t q4_gemv_launch(Q4GemvArgs a, int bf16, int sm_count, cudaStream_t st
     // block is shorter than it, and lies inside one block otherwise
     a.rps = block < kStageDepth ? kStageDepth / block : 1;
     const int stage_bytes = cg * (kUnitBytes * kConsumerWarps + a.rps * 32);
-    int ns = (72 * 1024) / stage_bytes;
+    int ns = (48 * 1024) / stage_bytes;
     if (ns > 8) ns = 8;
     if (ns < 2) ns = 2;
     a.ns = ns;
+    // activation chunk: whole K when it fits 16 KB for the rows in play, else
+    // double-buffered chunks of a whole number of stages
     const int kpad = a.k64 * 64;
-    int ka = (64 * 1024 / (8 * mt * 2)) / kStageDepth * kStageDepth;   // 64 KB of activations at most
-    if (ka < kStageDepth) ka = kStageDepth;
-    if (ka > kpad) ka = ((kpad + kStageDepth - 1) / kStageDepth) * kStageDepth;
+    const int rows = 8 * mt;
+    const int rows_used = a.m < rows ? a.m : rows;
+    int ka = ((kpad + kStageDepth - 1) / kStageDepth) * kStageDepth;
     if (ka == 0) ka = kStageDepth;
+    if ((size_t)rows_used * ka * 2 > 32 * 1024) {
+        ka = (16 * 1024 / (rows_used * 2)) / kStageDepth * kStageDepth;
+        if (ka < kStageDepth) ka = kStageDepth;
+    }
     a.ka = ka;
-    const size_t smem = 256 + (size_t)ns * stage_bytes + (size_t)8 * mt * (ka + 8) * 2 +
+    const int nbuf = kpad > ka ? 2 : 1;
+    a.a_rows = rows_used;
+    const size_t smem = 256 + (size_t)ns * stage_bytes + (size_t)nbuf * rows_used * (ka + 8) * 2 +
                         (size_t)kConsumerWarps * cg * mt * 128 * sizeof(float);
     dim3 grid((a.n16 + cg - 1) / cg, (a.m + 8 * mt - 1) / (8 * mt));
 #define SMEG_Q4_LAUNCH(B, O, M) return launch<B, O, M>(a, grid, smem, stream)

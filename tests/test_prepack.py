@@ -131,8 +131,9 @@ def test_q4_unit_layout_is_the_documented_mma_fragment_order():
                     got_hi = [nib[2] - 8, nib[6] - 8, nib[3] - 8, nib[7] - 8]
                     assert got_lo == list(code[d:d + 4, 16 * cg + g])
                     assert got_hi == list(code[d:d + 4, 16 * cg + g + 8])
-    # scales: [column group][block][16 columns]
-    assert sc.reshape(n // 16, k // block, 16)[1, 2, 5] == scales[(16 + 5) * (k // block) + 2]
+    # scales: [column group][block][16 slots], column c in slot 2*(c % 8) + c // 8
+    assert sc.reshape(n // 16, k // block, 16)[1, 2, 2 * 5] == scales[(16 + 5) * (k // block) + 2]
+    assert sc.reshape(n // 16, k // block, 16)[0, 1, 2 * 3 + 1] == scales[11 * (k // block) + 1]
 
 
 def test_q2_q1_unit_layouts_are_the_documented_fragment_order():
