@@ -84,9 +84,13 @@ class ClockSampler:
             if len(parts) < 9:
                 continue
             try:
-                sm.append(float(parts[1])); mx.append(float(parts[2]))
+                clk, cmax, power = float(parts[1]), float(parts[2]), float(parts[3])
             except ValueError:
                 continue
+            mx.append(cmax)
+            if power < 250.0:        # idle sample (before / after the loaded section)
+                continue
+            sm.append(clk)
             for name, val in zip(("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"), parts[5:9]):
                 if val.lower().startswith("active"):
                     reasons.add(name)
@@ -103,14 +107,6 @@ def mlp_weights_f32(seed: int):
     wu = (rng.standard_normal((INTER, HIDDEN), dtype=np.float32) * np.float32(0.02))
     wd = (rng.standard_normal((HIDDEN, INTER), dtype=np.float32) * np.float32(0.02))
     return wg, wu, wd
-
-
-def shard_bounds(rank: int, world: int):
-    """Hidden units [lo, hi) owned by a rank: whole 32-unit interleave chunks (= whole K-blocks of down)."""
-    chunks = INTER // 32
-    lo = (chunks * rank // world) * 32
-    hi = (chunks * (rank + 1) // world) * 32
-    return lo, hi
 
 
 # --------------------------------------------------------------------------- reference arm (CPU oracle)
@@ -272,8 +268,9 @@ def run_ours(args):
     m = args.m
 
     # ---- weights: this rank's shard, quantised once, uploaded as several distinct copies ----
+    from sme_gemm_b200.tp import shard_bounds
     wg, wu, wd = mlp_weights_f32(5)
-    lo, hi = shard_bounds(rank, world)
+    lo, hi = shard_bounds(INTER, rank, world)
     fl = hi - lo
     both = sg.interleave_gate_up(wg[lo:hi], wu[lo:hi], sg.WeightLayout.OutIn, fl, HIDDEN)
     guq, gus, _ = orc_quant(sg, both, 1, 2 * fl, HIDDEN)
@@ -321,13 +318,19 @@ def run_ours(args):
             dist.all_reduce(ms, op=dist.ReduceOp.MAX)
         return float(ms.item())
 
-    for i in range(args.warmup):
-        step(i)
+    # the timed region is milliseconds long while nvidia-smi samples every 100 ms: sample from
+    # before the warm-up until after the end-to-end region and keep the samples taken under load
     sampler = ClockSampler(local) if rank == 0 else None
     if sampler:
         sampler.start()
+        t_end = time.perf_counter() + 1.0      # at least a second of the same steps before timing
+        while time.perf_counter() < t_end:
+            for i in range(8):
+                step(i)
+            torch.cuda.synchronize()
+    for i in range(args.warmup):
+        step(i)
     ms = timed(step, args.steps)
-    clocks = sampler.stop() if sampler else None
     value = m * args.steps / (ms * 1e-3)
 
     # ---- end to end: host buffers in and out every step ----
@@ -341,6 +344,13 @@ def run_ours(args):
         e2e_step(i)
     ms_e2e = timed(e2e_step, args.steps)
     e2e_value = m * args.steps / (ms_e2e * 1e-3)
+    if sampler:
+        t_end = time.perf_counter() + 0.5
+        while time.perf_counter() < t_end:
+            for i in range(8):
+                step(i)
+            torch.cuda.synchronize()
+    clocks = sampler.stop() if sampler else None
 
     status = sg.last_status()
     if status != 0:

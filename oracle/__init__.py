@@ -160,6 +160,14 @@ def gemm16(a, b, m, n, k, bf16=False) -> np.ndarray:
     return c
 
 
+def gemm16_f32(a, b, m, n, k, bf16=False) -> np.ndarray:
+    """The dense product left in f32 (a tensor-parallel rank's partial sums)."""
+    a, b = _u16(a), _u16(b)
+    c = np.zeros((m, n), np.float32)
+    lib().orc_gemm16_f32(C.c_size_t(m), C.c_size_t(n), C.c_size_t(k), _p(c), _p(a), _p(b), C.c_int(int(bf16)))
+    return c
+
+
 def apply_ep(c, m, n, nodes: Nodes, bf16=False) -> np.ndarray:
     c = _u16(c).copy()
     lib().orc_apply_ep(_p(c), C.c_size_t(m), C.c_size_t(n), nodes.arr, C.c_uint32(nodes.n), C.c_int(int(bf16)))

@@ -294,6 +294,17 @@ void orc_gemm16_rows(size_t m, size_t n, size_t k, uint16_t *c, const uint16_t *
     par_for(first, first + rows, gm_row, &g, sizeof(float) * (n ? n : 1));
     free(bf);
 }
+/* The same product left in f32 (no store rounding): the un-rounded partial sums a
+ * tensor-parallel rank contributes.  Not a reference function. */
+void orc_gemm16_f32(size_t m, size_t n, size_t k, float *c, const uint16_t *a, const uint16_t *b, int bf16) {
+    for (size_t i = 0; i < m; i++) {
+        for (size_t j = 0; j < n; j++) c[i * n + j] = 0.0f;
+        for (size_t l = 0; l < k; l++) {
+            float av = t_to_f32(a[i * k + l], bf16);
+            for (size_t j = 0; j < n; j++) c[i * n + j] += av * t_to_f32(b[l * n + j], bf16);
+        }
+    }
+}
 void orc_gemm16(size_t m, size_t n, size_t k, uint16_t *c, const uint16_t *a, const uint16_t *b,
                 int bf16) {
     orc_gemm16_rows(m, n, k, c, a, b, bf16, 0, m);

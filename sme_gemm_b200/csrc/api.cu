@@ -9,6 +9,7 @@
 
 #include <chrono>
 #include <map>
+#include <utility>
 #include <mutex>
 #include <tuple>
 #include <vector>
@@ -35,13 +36,12 @@ struct DeviceState {
 std::mutex g_mu;
 std::map<int, DeviceState> g_dev;
 int g_trace = -1;
-// Row count above which the tcgen05 prefill GEMM replaces the decode kernel (the
-// reference switches kernels at Linear::PANEL_ROWS = 8 rows, src/linear.rs:160;
-// the decode kernel here carries up to 32 rows per pass).  SMEG_TC_MIN_ROWS
-// overrides it for tuning.
+// Row count above which the tcgen05 kernel runs instead of the warp-level-MMA kernel
+// (the reference switches kernels at Linear::PANEL_ROWS = 8 rows, src/linear.rs:160).
+// The tensor-core kernel covers every row count; SMEG_TC_MIN_ROWS is a tuning knob.
 int g_tc_min_rows = []() {
     const char* e = getenv("SMEG_TC_MIN_ROWS");
-    return e ? atoi(e) : 32;
+    return e ? atoi(e) : 0;
 }();
 
 DeviceState* dev_state() {
@@ -70,6 +70,42 @@ DeviceState* dev_state() {
         s.ok = true;
     }
     return &s;
+}
+
+// Scratch of the depth-split tensor-core GEMM: per-slice partial tiles and one arrival
+// counter per output tile (zero between launches).  One block per stream, so launches
+// that may overlap never share it; grown on demand (a synchronous allocation, so the
+// first call of a new size on a stream must not be inside a stream capture).
+struct TcScratch {
+    float* ws = nullptr;
+    size_t floats = 0;
+    int* counters = nullptr;
+    size_t ncounters = 0;
+};
+std::map<std::pair<int, cudaStream_t>, TcScratch> g_tc_scratch;
+
+int tc_scratch(cudaStream_t stream, size_t floats, size_t ncounters, TcScratch* out) {
+    int dev = 0;
+    cudaGetDevice(&dev);
+    std::lock_guard<std::mutex> lk(g_mu);
+    TcScratch& s = g_tc_scratch[{dev, stream}];
+    if (s.floats < floats) {
+        if (s.ws) cudaFree(s.ws);
+        s.ws = nullptr;
+        s.floats = 0;
+        if (cudaMalloc(&s.ws, floats * sizeof(float)) != cudaSuccess) return -2;
+        s.floats = floats;
+    }
+    if (s.ncounters < ncounters) {
+        if (s.counters) cudaFree(s.counters);
+        s.counters = nullptr;
+        s.ncounters = 0;
+        if (cudaMalloc(&s.counters, ncounters * sizeof(int)) != cudaSuccess) return -2;
+        if (cudaMemset(s.counters, 0, ncounters * sizeof(int)) != cudaSuccess) return -2;
+        s.ncounters = ncounters;
+    }
+    *out = s;
+    return 0;
 }
 
 bool tracing() {
@@ -431,7 +467,8 @@ static int unit_depth_of(int bits) { return bits == 4 ? kQ4UnitDepth : (bits == 
 size_t smeg_packed_code_bytes(int bits, size_t n, size_t k) {
     const int ud = unit_depth_of(bits);
     if (!ud) return 0;
-    return div_up(n, 16) * div_up(k, (size_t)ud) * kUnitBytes;
+    const PackedDims d = make_dims(n, k, 32, ud);
+    return d.n16 * d.ku * kUnitBytes;
 }
 size_t smeg_packed_scale_elems(int bits, size_t n, size_t k, size_t block) {
     const int ud = unit_depth_of(bits);
@@ -528,7 +565,17 @@ static int q4_dev(const smeg_q4* w, const uint16_t* a, uint16_t* c, size_t m, co
         t.n16 = (int)w->d.n16; t.ku = (int)w->d.ku; t.nb = (int)w->d.nb; t.log2_block = w->d.log2_block;
         t.status = ds->status;
         t.ep = g.ep;
-        e = gemm_tc_launch(t, bf16, 4, stream);
+        dim3 grid;
+        size_t smem = 0, ws_floats = 0, ncounters = 0;
+        gemm_tc_plan(t, ds->sm_count, &grid, &smem, &ws_floats, &ncounters);
+        TcScratch sc;
+        if (ws_floats && tc_scratch(stream, ws_floats, ncounters, &sc)) {
+            if (ext) cudaFreeAsync(ext, stream);
+            return -2;
+        }
+        t.ws = sc.ws;
+        t.counters = sc.counters;
+        e = gemm_tc_launch(t, bf16, grid, smem, stream);
     } else {
         e = q4_gemv_launch(g, bf16, ds->sm_count, stream);
     }

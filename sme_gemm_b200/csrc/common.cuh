@@ -16,10 +16,16 @@ enum : unsigned {
     STATUS_PEER_TIMEOUT = 4u,   // a peer flag never arrived (multi-GPU reduce)
 };
 
-// Upper bound on try_wait polls before a wait is abandoned.  Each poll can
-// itself suspend for the hardware's time slice, so this is seconds of wall
-// clock at most and never reached unless a copy was lost.
-constexpr unsigned kSpinLimit = 1u << 22;
+// Wall-clock bound of one wait (nanoseconds of the global timer).  Never reached
+// unless a copy or an arrival was lost; a wait that does reach it raises the
+// status word and every later wait of the CTA returns at once.
+constexpr unsigned long long kWaitLimitNs = 2000000000ull;
+
+__device__ __forceinline__ unsigned long long global_ns() {
+    unsigned long long t;
+    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+    return t;
+}
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) {
     return static_cast<uint32_t>(__cvta_generic_to_shared(p));
@@ -58,9 +64,11 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, unsigned parity) {
 __device__ __forceinline__ bool mbar_wait(uint64_t* bar, unsigned parity, volatile int* abort_flag,
                                           unsigned* status, unsigned code = STATUS_MBAR_TIMEOUT) {
     if (mbar_try_wait(bar, parity)) return true;
-    for (unsigned it = 0; it < kSpinLimit; ++it) {
+    const unsigned long long t0 = global_ns();
+    for (;;) {
         if (*abort_flag) return false;
         if (mbar_try_wait(bar, parity)) return true;
+        if (global_ns() - t0 > kWaitLimitNs) break;
     }
     *abort_flag = 1;
     if (status) atomicOr(status, code);

@@ -1,48 +1,45 @@
-// Prefill GEMM for sm_100a:  C[m][n] = ep( A[m][k] @ dequant(W) ) for large m, on the
-// 5th-generation tensor cores (tcgen05.mma, accumulators in tensor memory).
+// Tensor-core GEMM for sm_100a:  C[m][n] = ep( A[m][k] @ dequant(W) ) on the 5th-generation
+// tensor cores (tcgen05.mma, accumulators in tensor memory), for prefill-sized m and -- with the
+// depth split over several CTAs -- for decode-sized m as well.
 //
-// Replaces the reference's MOPA paths -- unpack_q4_f16 / unpack_q4_bf16 +
-// run_q4_panels (csrc/gemm_f16f16_q4.h:57-117, csrc/gemm_b16b16_q4.h:32-92), the
-// 1-/2-bit unpack_q{1,2}_f16 + lowbit_panels (csrc/gemm_f16f16_lowbit.h:51-169) and
-// the dense run_panels consumer (csrc/gemm_half.h:1093-1169).  As there, every
-// weight is rounded ONCE to the 16-bit operand type exactly as the eager dequant
-// rounds it (dequant_rows, src/kernels/q4/weights.rs:232-259; Codes::dequant,
-// src/kernels/lowbit/matmul.rs:178-197) and the dense product accumulates in f32.
+// Replaces the reference's MOPA paths -- unpack_q4_f16 / unpack_q4_bf16 + run_q4_panels
+// (csrc/gemm_f16f16_q4.h:57-117, csrc/gemm_b16b16_q4.h:32-92) and the dense run_panels consumer
+// (csrc/gemm_half.h:1093-1169).  As there, every weight is rounded ONCE to the 16-bit operand type
+// exactly as the eager dequant rounds it (dequant_rows, src/kernels/q4/weights.rs:232-259) and the
+// dense product accumulates in f32.
 //
-// One CTA owns 128 weight columns (the MMA's M dimension) x a tile of up to 512
-// tokens (the MMA's N dimension, one or two instructions of N <= 256), over the
-// whole depth.  Per 64-deep stage:
-//   warp 4 (producer)   TMA: the token tile (tensor map, 128-byte swizzle) and this
-//                       CTA's 4 KB of packed weight units + their scales (bulk copies)
-//   warps 0-3 (dequant) expand the packed units into the K-major, 128-byte-swizzled
-//                       shared-memory operand: each lane turns its 16-byte vector
-//                       into four 16-byte chunks of 8 consecutive depths
-//   warp 5 (MMA)        one elected thread issues 4 (x1 or x2) tcgen05.mma of K = 16
-//                       and commits the stage back to the producer
-// After the last stage warps 0-3 drain the accumulators from tensor memory
-// (thread = weight column, registers = tokens), run the epilogue graph on the
-// rounded product and store C.  Every wait is bounded.
+// One CTA owns NW x 128 weight columns (the MMA's M dimension; NW = 1 or 2 accumulator sets) x a
+// tile of up to 512 tokens (the MMA's N dimension, one or two instructions of N <= 256) over a
+// slice of the depth.  Roles (320 threads):
+//   warp 8 (producer)   streams 64-deep stages through a ring of P slots: the token tile by TMA
+//                       (tensor map, 128-byte swizzle) and the CTA's packed weight units + scales
+//                       by bulk copies.  P sets the bytes in flight.
+//   warps 0-7 (dequant) expand packed units into the K-major, 128-byte-swizzled MMA operand in a
+//                       second, shallower ring of O slots: a lane's 16-byte vector becomes four
+//                       16-byte chunks of 8 consecutive depths.
+//   warp 9 (MMA)        one thread issues the stage's tcgen05.mma (K = 16 each) and commits the
+//                       stage back to both rings.
+// After the last stage warps 0-7 drain tensor memory (thread = weight column, registers =
+// tokens).  With the depth split (grid.z > 1) each CTA leaves its f32 partial tile in a global
+// workspace; the CTA that finishes a tile last adds the slices in slice order (so the result does
+// not depend on arrival order), runs the epilogue graph on the rounded product and stores C.
+// Every wait is bounded; a timed-out wait raises the status word and the kernel drains and exits.
 #include "epilogue.cuh"
 #include "kernels.h"
 #include "layout.h"
 #include "tc_common.cuh"
 
+#include <stdlib.h>
+
 namespace smeg {
 
 namespace {
 
-constexpr int kTcThreads = 192;
-constexpr int kColsPerCta = 128;       // weight columns per CTA (UMMA M)
-constexpr int kStageK = 64;            // depths per stage (one 128-byte swizzle row of 16-bit values)
-constexpr int kWBytes = kColsPerCta * kStageK * 2;   // dequantised weight operand per stage: 16 KB
-
-// WKIND: 4 = Q4 units, 2 = 2-bit units, 1 = 1-bit units, 16 = dense 16-bit weights (already K-major tiles)
-template <int WKIND>
-struct WSrc {
-    static constexpr int unit_depth = WKIND == 4 ? 64 : (WKIND == 2 ? 128 : 256);
-    // packed bytes of 128 columns x 64 depths
-    static constexpr int stage_bytes = WKIND == 4 ? 4096 : (WKIND == 2 ? 2048 : 1024);
-};
+constexpr int kDeqWarps = 8;
+constexpr int kTcThreads = 32 * (kDeqWarps + 2);
+constexpr int kStageK = 64;                       // depths per stage (one 128-byte swizzle row)
+constexpr int kWTile = 128 * kStageK * 2;         // one 128-column operand tile per stage: 16 KB
+constexpr int kPkTile = 8 * kUnitBytes;           // packed Q4 units of 128 columns x 64 depths: 4 KB
 
 __device__ __forceinline__ uint32_t swz_off(int row, int chunk) {
     // byte offset of 16-byte chunk `chunk` (0..7) of row `row` in a 128B-swizzled K-major tile
@@ -50,20 +47,22 @@ __device__ __forceinline__ uint32_t swz_off(int row, int chunk) {
 }
 
 template <int BF16>
-__device__ __forceinline__ uint4 scale_chunk(const __half2 (&c)[4], float s_f32, __half2 s_h2) {
+__device__ __forceinline__ uint4 scale_chunk(const __half2 (&c)[4], __half s) {
     uint4 out;
     if (BF16) {
+        const float sf = __half2float(s);
         uint32_t* o = reinterpret_cast<uint32_t*>(&out);
 #pragma unroll
         for (int i = 0; i < 4; ++i) {
             const float2 f = __half22float2(c[i]);
-            __nv_bfloat162 v = __floats2bfloat162_rn(__fmul_rn(f.x, s_f32), __fmul_rn(f.y, s_f32));
+            __nv_bfloat162 v = __floats2bfloat162_rn(__fmul_rn(f.x, sf), __fmul_rn(f.y, sf));
             o[i] = *reinterpret_cast<uint32_t*>(&v);
         }
     } else {
+        const __half2 s2 = __half2half2(s);
         __half2* o = reinterpret_cast<__half2*>(&out);
 #pragma unroll
-        for (int i = 0; i < 4; ++i) o[i] = __hmul2(c[i], s_h2);
+        for (int i = 0; i < 4; ++i) o[i] = __hmul2(c[i], s2);
     }
     return out;
 }
@@ -83,190 +82,258 @@ __device__ __forceinline__ void q4_word_codes(uint32_t w, __half2 (&r)[4]) {
     r[3] = __hfma2(*reinterpret_cast<__half2*>(&hi1), sc16, off16);
 }
 
-template <int BF16, int WKIND>
-__global__ void __launch_bounds__(kTcThreads, 1) gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_tok, GemmTcArgs p) {
+// One packed Q4 unit (16 columns x 64 depths) -> rows 16*cu + {g, g+8} of a swizzled operand tile.
+template <int BF16>
+__device__ __forceinline__ void dequant_unit_q4(unsigned char* tile, int cu, const uint4 wv, const uint16_t* sc, int ra,
+                                                int rb, int g, int t) {
+    __half2 w0[4], w1[4], w2[4], w3[4];
+    q4_word_codes(wv.x, w0);
+    q4_word_codes(wv.y, w1);
+    q4_word_codes(wv.z, w2);
+    q4_word_codes(wv.w, w3);
+    // chunks: (col g, depths 8t..8t+7), (col g, 32+8t..), (col g+8, 8t..), (col g+8, 32+8t..)
+    const __half2 lo_a[4] = {w0[0], w0[2], w1[0], w1[2]};
+    const __half2 lo_b[4] = {w2[0], w2[2], w3[0], w3[2]};
+    const __half2 hi_a[4] = {w0[1], w0[3], w1[1], w1[3]};
+    const __half2 hi_b[4] = {w2[1], w2[3], w3[1], w3[3]};
+    const uint32_t sa = *reinterpret_cast<const uint32_t*>(sc + ra * 16 + 2 * g);   // (col g, col g+8) of block ra
+    const uint32_t sb = *reinterpret_cast<const uint32_t*>(sc + rb * 16 + 2 * g);
+    const __half s_lo_a = __ushort_as_half((uint16_t)(sa & 0xffffu)), s_hi_a = __ushort_as_half((uint16_t)(sa >> 16));
+    const __half s_lo_b = __ushort_as_half((uint16_t)(sb & 0xffffu)), s_hi_b = __ushort_as_half((uint16_t)(sb >> 16));
+    const int row_lo = 16 * cu + g, row_hi = row_lo + 8;
+    // chunk order per store keeps the 8 lanes of a quarter warp on distinct banks
+    const int ca = (g & 1) ? 4 + t : t, cb = (g & 1) ? t : 4 + t;
+    const uint4 v_lo_a = scale_chunk<BF16>(lo_a, s_lo_a), v_lo_b = scale_chunk<BF16>(lo_b, s_lo_b);
+    const uint4 v_hi_a = scale_chunk<BF16>(hi_a, s_hi_a), v_hi_b = scale_chunk<BF16>(hi_b, s_hi_b);
+    *reinterpret_cast<uint4*>(tile + swz_off(row_lo, ca)) = (g & 1) ? v_lo_b : v_lo_a;
+    *reinterpret_cast<uint4*>(tile + swz_off(row_lo, cb)) = (g & 1) ? v_lo_a : v_lo_b;
+    *reinterpret_cast<uint4*>(tile + swz_off(row_hi, ca)) = (g & 1) ? v_hi_b : v_hi_a;
+    *reinterpret_cast<uint4*>(tile + swz_off(row_hi, cb)) = (g & 1) ? v_hi_a : v_hi_b;
+}
+
+template <int BF16>
+__global__ void __launch_bounds__(kTcThreads, 2) gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_tok, GemmTcArgs p) {
     extern __shared__ unsigned char smem_dyn[];
     // the swizzled operands need 1024-byte aligned tiles: align the window by hand
     unsigned char* smem_raw = smem_dyn + ((1024u - (smem_u32(smem_dyn) & 1023u)) & 1023u);
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-    const int NS = p.ns;
-    const int tok_bytes = p.ntok_pad * 128;                    // token operand per stage
-    constexpr int pk_bytes = WSrc<WKIND>::stage_bytes;         // packed weights per stage
+    const int P = p.np, O = p.no, NW = p.nw, US = p.us;
+    const int tok_bytes = p.ntok_pad * 128;                    // token operand per 64-deep unit
     const int sc_rows = p.sc_rows;                             // scale rows (blocks) staged per stage
-    const int sc_bytes = 8 * sc_rows * 32;                     // 8 column groups x rows x 16 halves
-    const int stage_stride = kWBytes + tok_bytes + ((pk_bytes + sc_bytes + 1023) / 1024) * 1024;
+    const int pk_slot = ((NW * (US * kPkTile + 8 * sc_rows * 32) + 1023) / 1024) * 1024;
+    const int p_stride = US * tok_bytes + pk_slot;             // ring P slot: [token tiles | packed units | scales]
+    const int o_stride = NW * US * kWTile;                     // ring O slot: NW x US operand tiles
 
-    // carve-up: [stages: W operand | token operand | packed + scales] then barriers
-    unsigned char* stages = smem_raw;
-    uint64_t* bars = reinterpret_cast<uint64_t*>(smem_raw + (size_t)NS * stage_stride);
-    uint64_t* full = bars;                 // packed weights + tokens landed
-    uint64_t* deq = bars + NS;             // dequantised operand written (128 arrivals)
-    uint64_t* empty = bars + 2 * NS;       // MMAs of the stage retired
-    uint64_t* acc_full = bars + 3 * NS;    // all MMAs retired
-    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 3 * NS + 1);
+    unsigned char* ring_o = smem_raw;
+    unsigned char* ring_p = smem_raw + (size_t)O * o_stride;
+    uint64_t* bars = reinterpret_cast<uint64_t*>(ring_p + (size_t)P * p_stride);
+    uint64_t* p_full = bars;                 // [P] tokens + packed landed
+    uint64_t* p_empty = bars + P;            // [P] released: 8 dequant warps + the MMA commit
+    uint64_t* o_full = bars + 2 * P;         // [O] operand written (256 arrivals)
+    uint64_t* o_empty = o_full + O;          // [O] MMAs of the stage retired
+    uint64_t* acc_full = o_empty + O;        // all MMAs retired
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(acc_full + 1);
     volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
-    EpNodeDev* ep_nodes = reinterpret_cast<EpNodeDev*>(bars + 3 * NS + 4);
+    int* last_flag = const_cast<int*>(abort_flag) + 1;
+    EpNodeDev* ep_nodes = reinterpret_cast<EpNodeDev*>(acc_full + 4);
 
-    const int cg0 = blockIdx.x * 8;                            // first 16-column group
-    const int col0 = blockIdx.x * kColsPerCta;
+    const int sg0 = blockIdx.x * NW;                           // first 128-column super-group
+    const int col0 = blockIdx.x * 128 * NW;
     const int tok0 = blockIdx.y * p.ntok_tile;
-    const int num_stages = (p.k + kStageK - 1) / kStageK;
+    const int stages_all = (p.ku + US - 1) / US;
+    const int per_split = (stages_all + (int)gridDim.z - 1) / (int)gridDim.z;
+    const int st_begin = blockIdx.z * per_split;
+    const int st_end = min(stages_all, st_begin + per_split);
+    const int num_stages = max(0, st_end - st_begin);
 
     if (tid == 0) {
-        for (int s = 0; s < NS; ++s) {
-            mbar_init(&full[s], 1);
-            mbar_init(&deq[s], 128);
-            mbar_init(&empty[s], 1);
+        for (int s = 0; s < P; ++s) {
+            mbar_init(&p_full[s], 1);
+            mbar_init(&p_empty[s], kDeqWarps + 1);
+        }
+        for (int s = 0; s < O; ++s) {
+            mbar_init(&o_full[s], 32 * kDeqWarps);
+            mbar_init(&o_empty[s], 1);
         }
         mbar_init(acc_full, 1);
         *abort_flag = 0;
+        *last_flag = 0;
         fence_barrier_init();
     }
     if (tid < p.ep.n_nodes && p.ep.n_nodes <= kMaxInlineNodes) ep_nodes[tid] = p.ep.nodes[tid];
-    if (warp == 5) {
+    if (warp == kDeqWarps + 1) {
         tmem_alloc(tmem_slot, p.tmem_cols);
         tmem_relinquish();
     }
-    if (warp == 4 && lane == 0) tma_prefetch_desc(&tmap_tok);
+    if (warp == kDeqWarps && lane == 0) tma_prefetch_desc(&tmap_tok);
     tc_fence_before();
     __syncthreads();
     tc_fence_after();
     const uint32_t tmem_base = *tmem_slot;
 
-    if (warp == 4) {
+    if (warp == kDeqWarps) {
         // ===================== producer =====================
         if (lane == 0) {
-            for (int st = 0; st < num_stages; ++st) {
-                const int slot = st % NS;
-                if (st >= NS && !mbar_wait(&empty[slot], ((st / NS) - 1) & 1, abort_flag, p.status, STATUS_TMEM_TIMEOUT)) break;
-                unsigned char* sb = stages + (size_t)slot * stage_stride;
-                const int d0 = st * kStageK;
+            for (int i = 0; i < num_stages; ++i) {
+                const int slot = i % P;
+                if (i >= P && !mbar_wait(&p_empty[slot], ((i / P) - 1) & 1, abort_flag, p.status, STATUS_TMEM_TIMEOUT)) break;
+                unsigned char* sb = ring_p + (size_t)slot * p_stride;
+                const int st = st_begin + i;
+                const int u0 = st * US;                                     // first 64-deep unit of the stage
+                const int units = min(US, p.ku - u0);
+                const int d0 = u0 * kStageK;
                 const int blk0 = d0 >> p.log2_block;
-                const int blk1 = min(p.nb, ((d0 + kStageK - 1) >> p.log2_block) + 1);
+                const int blk1 = min(p.nb, ((d0 + units * kStageK - 1) >> p.log2_block) + 1);
                 const int rows = blk1 - blk0;
-                // packed units of this stage: for unit depths above 64 a unit spans several
-                // stages and is copied as a whole by the stage that starts it
-                constexpr int UD = WSrc<WKIND>::unit_depth;
-                const bool copy_units = (d0 % UD) == 0;
-                const unsigned pk = copy_units ? 8u * kUnitBytes : 0u;
-                mbar_expect_tx(&full[slot], (unsigned)tok_bytes + pk + 8u * rows * 32u);
-                // tokens: one or two boxes of ntok_box rows
-                tma_load_2d(sb + kWBytes, &tmap_tok, d0, tok0, &full[slot]);
-                if (p.nmma == 2) tma_load_2d(sb + kWBytes + tok_bytes / 2, &tmap_tok, d0, tok0 + p.ntok_box, &full[slot]);
-                unsigned char* pkdst = sb + kWBytes + tok_bytes;
-                for (int c = 0; c < 8; ++c) {
-                    const size_t cgi = (size_t)min(cg0 + c, p.n16 - 1);     // clamp: tail groups re-read the last one
-                    if (copy_units)
-                        bulk_g2s(pkdst + c * kUnitBytes, p.codes + (cgi * p.ku + (size_t)(d0 / UD)) * kUnitBytes, kUnitBytes, &full[slot]);
-                    bulk_g2s(pkdst + 8 * kUnitBytes + c * sc_rows * 32, p.scales + (cgi * p.nb + blk0) * 16, rows * 32, &full[slot]);
+                mbar_expect_tx(&p_full[slot], (unsigned)(units * tok_bytes) + (unsigned)NW * (units * kPkTile + rows * 256u));
+                for (int uu = 0; uu < units; ++uu) {
+                    tma_load_2d(sb + uu * tok_bytes, &tmap_tok, d0 + uu * kStageK, tok0, &p_full[slot]);
+                    if (p.nmma == 2)
+                        tma_load_2d(sb + uu * tok_bytes + tok_bytes / 2, &tmap_tok, d0 + uu * kStageK, tok0 + p.ntok_box, &p_full[slot]);
+                }
+                unsigned char* pkdst = sb + US * tok_bytes;
+                unsigned char* scdst = pkdst + NW * US * kPkTile;
+                for (int w = 0; w < NW; ++w) {
+                    const size_t sg = (size_t)min(sg0 + w, p.n16 / 8 - 1);  // a tail super-group re-reads the last one
+                    // one contiguous run: [unit][8 column groups][512 B]
+                    bulk_g2s(pkdst + w * US * kPkTile, p.codes + (sg * p.ku + (size_t)u0) * kPkTile, units * kPkTile, &p_full[slot]);
+                    // [block][8 column groups][16 slots]
+                    bulk_g2s(scdst + w * sc_rows * 256, p.scales + (sg * p.nb + blk0) * 128, rows * 256, &p_full[slot]);
                 }
             }
         }
-    } else if (warp == 5) {
+    } else if (warp == kDeqWarps + 1) {
         // ===================== MMA issuer =====================
         if (lane == 0) {
-            const uint32_t idesc = umma_idesc(BF16, kColsPerCta, p.ntok_box);
-            for (int st = 0; st < num_stages; ++st) {
-                const int slot = st % NS;
-                const unsigned ph = (st / NS) & 1;
-                if (!mbar_wait(&full[slot], ph, abort_flag, p.status, STATUS_TMEM_TIMEOUT)) break;
-                if (!mbar_wait(&deq[slot], ph, abort_flag, p.status, STATUS_TMEM_TIMEOUT)) break;
+            const uint32_t idesc = umma_idesc(BF16, 128, p.ntok_box);
+            for (int i = 0; i < num_stages; ++i) {
+                const int ps = i % P, os = i % O;
+                if (!mbar_wait(&p_full[ps], (i / P) & 1, abort_flag, p.status, STATUS_TMEM_TIMEOUT)) break;
+                if (!mbar_wait(&o_full[os], (i / O) & 1, abort_flag, p.status, STATUS_TMEM_TIMEOUT)) break;
                 tc_fence_after();
-                unsigned char* sb = stages + (size_t)slot * stage_stride;
-                const uint64_t a_desc = umma_desc_sw128(smem_u32(sb));
-                const uint64_t b_desc = umma_desc_sw128(smem_u32(sb + kWBytes));
+                const uint32_t tok_addr = smem_u32(ring_p + (size_t)ps * p_stride);
+                const uint32_t w_addr = smem_u32(ring_o + (size_t)os * o_stride);
+                const int units = min(US, p.ku - (st_begin + i) * US);
+                for (int uu = 0; uu < units; ++uu) {
 #pragma unroll
-                for (int ks = 0; ks < kStageK / 16; ++ks) {
-                    const uint32_t accum = (st > 0 || ks > 0) ? 1u : 0u;
-                    umma_f16(tmem_base, a_desc + 2 * ks, b_desc + 2 * ks, idesc, accum);
-                    if (p.nmma == 2)
-                        umma_f16(tmem_base + p.ntok_box, a_desc + 2 * ks, b_desc + (uint64_t)((tok_bytes / 2) >> 4) + 2 * ks, idesc, accum);
+                    for (int ks = 0; ks < kStageK / 16; ++ks) {
+                        const uint32_t accum = (i > 0 || uu > 0 || ks > 0) ? 1u : 0u;
+                        for (int w = 0; w < NW; ++w) {
+                            const uint64_t a_desc = umma_desc_sw128(w_addr + (w * US + uu) * kWTile) + 2 * ks;
+                            for (int h = 0; h < p.nmma; ++h) {
+                                const uint64_t b_desc = umma_desc_sw128(tok_addr + uu * tok_bytes + h * (tok_bytes / 2)) + 2 * ks;
+                                umma_f16(tmem_base + (uint32_t)((w * p.nmma + h) * p.ntok_box), a_desc, b_desc, idesc, accum);
+                            }
+                        }
+                    }
                 }
-                umma_commit(&empty[slot]);
+                umma_commit(&o_empty[os]);
+                umma_commit(&p_empty[ps]);
             }
             umma_commit(acc_full);
         }
     } else {
-        // ===================== dequant warps (0..3), then epilogue =====================
+        // ===================== dequant warps (0..7), then epilogue =====================
         const int g = lane >> 2, t = lane & 3;
-        // this thread's packed vector: column groups 2*warp and 2*warp+1 of the CTA
-        for (int st = 0; st < num_stages; ++st) {
-            const int slot = st % NS;
-            const unsigned ph = (st / NS) & 1;
-            unsigned char* sb = stages + (size_t)slot * stage_stride;
-            if (st >= NS) {
-                // the dequantised operand of this slot is being read by MMAs until empty[] flips
-                if (!mbar_wait(&empty[slot], ((st / NS) - 1) & 1, abort_flag, p.status, STATUS_TMEM_TIMEOUT)) break;
-            }
-            if (!mbar_wait(&full[slot], ph, abort_flag, p.status, STATUS_TMEM_TIMEOUT)) break;
-            const int d0 = st * kStageK;
+        for (int i = 0; i < num_stages; ++i) {
+            const int ps = i % P, os = i % O;
+            if (i >= O && !mbar_wait(&o_empty[os], ((i / O) - 1) & 1, abort_flag, p.status, STATUS_TMEM_TIMEOUT)) break;
+            if (!mbar_wait(&p_full[ps], (i / P) & 1, abort_flag, p.status, STATUS_TMEM_TIMEOUT)) break;
+            const int u0 = (st_begin + i) * US;
+            const int units = min(US, p.ku - u0);
+            const int d0 = u0 * kStageK;
             const int blk0 = d0 >> p.log2_block;
-            const unsigned char* pk = sb + kWBytes + tok_bytes;
-            const uint16_t* scs = reinterpret_cast<const uint16_t*>(pk + 8 * kUnitBytes);
-            if (WKIND == 4) {
-#pragma unroll
-                for (int cc = 0; cc < 2; ++cc) {
-                    const int c = 2 * warp + cc;
-                    const uint4 wv = *reinterpret_cast<const uint4*>(pk + c * kUnitBytes + lane * 16);
-                    __half2 w0[4], w1[4], w2[4], w3[4];
-                    q4_word_codes(wv.x, w0);
-                    q4_word_codes(wv.y, w1);
-                    q4_word_codes(wv.z, w2);
-                    q4_word_codes(wv.w, w3);
-                    // chunks: (col g, depths 8t..8t+7), (col g, 32+8t..), (col g+8, 8t..), (col g+8, 32+8t..)
-                    const __half2 lo_a[4] = {w0[0], w0[2], w1[0], w1[2]};
-                    const __half2 lo_b[4] = {w2[0], w2[2], w3[0], w3[2]};
-                    const __half2 hi_a[4] = {w0[1], w0[3], w1[1], w1[3]};
-                    const __half2 hi_b[4] = {w2[1], w2[3], w3[1], w3[3]};
-                    const int ra = ((d0 + 8 * t) >> p.log2_block) - blk0, rb = ((d0 + 32 + 8 * t) >> p.log2_block) - blk0;
-                    const uint16_t* sc = scs + c * sc_rows * 16;
-                    const __half s_lo_a = __ushort_as_half(sc[ra * 16 + 2 * g]), s_lo_b = __ushort_as_half(sc[rb * 16 + 2 * g]);
-                    const __half s_hi_a = __ushort_as_half(sc[ra * 16 + 2 * g + 1]), s_hi_b = __ushort_as_half(sc[rb * 16 + 2 * g + 1]);
-                    const int row_lo = 16 * c + g, row_hi = row_lo + 8;
-                    // chunk order per store keeps the 8 lanes of a quarter warp on distinct banks
-                    const int ca = (g & 1) ? 4 + t : t, cb = (g & 1) ? t : 4 + t;
-                    const uint4 v_lo_a = scale_chunk<BF16>(lo_a, __half2float(s_lo_a), __half2half2(s_lo_a));
-                    const uint4 v_lo_b = scale_chunk<BF16>(lo_b, __half2float(s_lo_b), __half2half2(s_lo_b));
-                    const uint4 v_hi_a = scale_chunk<BF16>(hi_a, __half2float(s_hi_a), __half2half2(s_hi_a));
-                    const uint4 v_hi_b = scale_chunk<BF16>(hi_b, __half2float(s_hi_b), __half2half2(s_hi_b));
-                    *reinterpret_cast<uint4*>(sb + swz_off(row_lo, ca)) = (g & 1) ? v_lo_b : v_lo_a;
-                    *reinterpret_cast<uint4*>(sb + swz_off(row_lo, cb)) = (g & 1) ? v_lo_a : v_lo_b;
-                    *reinterpret_cast<uint4*>(sb + swz_off(row_hi, ca)) = (g & 1) ? v_hi_b : v_hi_a;
-                    *reinterpret_cast<uint4*>(sb + swz_off(row_hi, cb)) = (g & 1) ? v_hi_a : v_hi_b;
-                }
+            const unsigned char* pk = ring_p + (size_t)ps * p_stride + US * tok_bytes;
+            const uint16_t* scs = reinterpret_cast<const uint16_t*>(pk + NW * US * kPkTile);
+            unsigned char* ob = ring_o + (size_t)os * o_stride;
+            // unit index c = (w * US + uu) * 8 + column group
+            for (int c = warp; c < 8 * NW * US; c += kDeqWarps) {
+                const int cgl = c & 7, wu = c >> 3, uu = wu % US, w = wu / US;
+                if (uu >= units) continue;
+                const int du = d0 + uu * kStageK;
+                const int ra = ((du + 8 * t) >> p.log2_block) - blk0, rb = ((du + 32 + 8 * t) >> p.log2_block) - blk0;
+                const uint4 wv = *reinterpret_cast<const uint4*>(pk + (size_t)wu * kPkTile + cgl * kUnitBytes + lane * 16);
+                // scale rows of this super-group: [block][8 column groups][16 slots]
+                dequant_unit_q4<BF16>(ob + wu * kWTile, cgl, wv, scs + w * sc_rows * 128 + cgl * 16, ra * 8, rb * 8, g, t);
             }
             fence_proxy_async();
-            mbar_arrive(&deq[slot]);
+            mbar_arrive(&o_full[os]);
+            __syncwarp();
+            if (lane == 0) mbar_arrive(&p_empty[ps]);
         }
 
-        // ---- epilogue: thread = weight column (TMEM lane), registers = tokens ----
-        mbar_wait(acc_full, 0, abort_flag, p.status, STATUS_TMEM_TIMEOUT);
+        // ---- drain: thread = weight column (TMEM lane), registers = tokens ----
+        if (num_stages > 0) mbar_wait(acc_full, 0, abort_flag, p.status, STATUS_TMEM_TIMEOUT);
         tc_fence_after();
-        const int col = col0 + 32 * warp + lane;
-        const uint32_t lane_base = tmem_base + ((uint32_t)(32 * warp) << 16);
+        const int q = warp & 3, half = warp >> 2;              // lane quarter, token half
+        const uint32_t lane_base = tmem_base + ((uint32_t)(32 * q) << 16);
         const EpNodeDev* nodes = p.ep.n_nodes <= kMaxInlineNodes ? ep_nodes : p.ep.ext;
-        for (int j0 = 0; j0 < p.ntok_pad; j0 += 16) {
-            uint32_t r[16];
-            tmem_ld16(lane_base + (uint32_t)j0, r);
-            tmem_ld_wait();
-            if (num_stages == 0) {
+        const int ntok = p.ntok_pad;                           // a multiple of 32: both halves are whole 16-groups
+        const int j_begin = half * (ntok / 2), j_end = j_begin + ntok / 2;
+        const int splits = (int)gridDim.z;
+        const int tile_id = blockIdx.y * gridDim.x + blockIdx.x;
+        float* ws_tile = p.ws + ((size_t)tile_id * splits) * (size_t)(NW * 128) * ntok;
+
+        for (int w = 0; w < NW; ++w) {
+            const int col = col0 + 128 * w + 32 * q + lane;
+            for (int j0 = j_begin; j0 < j_end; j0 += 16) {
+                uint32_t r[16];
+                if (num_stages > 0) {
+                    tmem_ld16(lane_base + (uint32_t)(w * ntok + j0), r);
+                    tmem_ld_wait();
+                } else {
 #pragma unroll
-                for (int j = 0; j < 16; ++j) r[j] = 0u;
-            }
+                    for (int j = 0; j < 16; ++j) r[j] = 0u;
+                }
+                if (splits == 1) {
 #pragma unroll
-            for (int j = 0; j < 16; ++j) {
-                const int tok = tok0 + j0 + j;
-                if (tok < p.m && col < p.n) {
-                    const float acc = __uint_as_float(r[j]);
-                    if (p.c32) p.c32[(size_t)tok * p.n + col] = acc;
-                    else p.c[(size_t)tok * p.n + col] = ep_store_nodes<BF16>(nodes, p.ep.n_nodes, acc, (size_t)tok, (size_t)col);
+                    for (int j = 0; j < 16; ++j) {
+                        const int tok = tok0 + j0 + j;
+                        if (tok < p.m && col < p.n) {
+                            const float acc = __uint_as_float(r[j]);
+                            if (p.c32) p.c32[(size_t)tok * p.n + col] = acc;
+                            else p.c[(size_t)tok * p.n + col] = ep_store_nodes<BF16>(nodes, p.ep.n_nodes, acc, (size_t)tok, (size_t)col);
+                        }
+                    }
+                } else {
+                    // partial tile of this depth slice: ws[tile][slice][token][column]
+                    float* dst = ws_tile + ((size_t)blockIdx.z * ntok) * (NW * 128) + (128 * w + 32 * q + lane);
+#pragma unroll
+                    for (int j = 0; j < 16; ++j) dst[(size_t)(j0 + j) * (NW * 128)] = __uint_as_float(r[j]);
                 }
             }
         }
         tc_fence_before();
+
+        if (splits > 1) {
+            // the last CTA of the tile to arrive adds the slices in slice order and stores
+            __threadfence();
+            asm volatile("bar.sync 1, %0;" ::"n"(32 * kDeqWarps));
+            if (tid == 0) {
+                const int prev = atomicAdd(p.counters + tile_id, 1);
+                *last_flag = (prev == splits - 1) ? 1 : 0;
+                if (prev == splits - 1) p.counters[tile_id] = 0;      // ready for the next launch
+            }
+            asm volatile("bar.sync 1, %0;" ::"n"(32 * kDeqWarps));
+            if (*last_flag) {
+                __threadfence();
+                for (int w = 0; w < NW; ++w) {
+                    const int col = col0 + 128 * w + 32 * q + lane;
+                    for (int j = j_begin; j < j_end; ++j) {
+                        const int tok = tok0 + j;
+                        if (tok >= p.m || col >= p.n) continue;
+                        float acc = 0.0f;
+                        for (int z = 0; z < splits; ++z)
+                            acc += __ldcg(ws_tile + ((size_t)z * ntok + j) * (NW * 128) + (128 * w + 32 * q + lane));
+                        if (p.c32) p.c32[(size_t)tok * p.n + col] = acc;
+                        else p.c[(size_t)tok * p.n + col] = ep_store_nodes<BF16>(nodes, p.ep.n_nodes, acc, (size_t)tok, (size_t)col);
+                    }
+                }
+            }
+        }
     }
     __syncthreads();
-    if (warp == 5) {
+    if (warp == kDeqWarps + 1) {
         tc_fence_after();
         tmem_dealloc(tmem_base, p.tmem_cols);
     }
@@ -287,9 +354,9 @@ EncodeTiledFn encode_fn() {
     return fn;
 }
 
-template <int BF16, int WKIND>
+template <int BF16>
 cudaError_t launch_tc(const CUtensorMap& tm, const GemmTcArgs& a, dim3 grid, size_t smem, cudaStream_t stream) {
-    auto kern = gemm_tc_kernel<BF16, WKIND>;
+    auto kern = gemm_tc_kernel<BF16>;
     static int attr_dev = -1;
     int dev = 0;
     cudaGetDevice(&dev);
@@ -312,28 +379,54 @@ bool gemm_tc_supported(int wkind, int m, int k, int log2_block, const void* a) {
     return encode_fn() != nullptr;
 }
 
-cudaError_t gemm_tc_launch(GemmTcArgs a, int bf16, int wkind, cudaStream_t stream) {
-    // token tiling: equal tiles of at most 512 tokens, padded to the MMA's N granularity
+void gemm_tc_plan(GemmTcArgs& a, int sm_count, dim3* grid, size_t* smem, size_t* ws_floats, size_t* n_counters) {
+    // token tiling: equal tiles of at most 512 tokens, padded so that both token halves of the
+    // drain (and both MMA halves above 256) are whole groups of 16
     const int tiles = (a.m + 511) / 512;
-    int tile = (a.m + tiles - 1) / tiles;
-    int pad = tile > 256 ? (tile + 31) / 32 * 32 : (tile + 15) / 16 * 16;
+    const int tile = (a.m + tiles - 1) / tiles;
+    const int pad = (tile + 31) / 32 * 32;
     a.ntok_tile = pad;
     a.ntok_pad = pad;
     a.nmma = pad > 256 ? 2 : 1;
     a.ntok_box = pad / a.nmma;
+    const int col_tiles_1 = (a.n + 127) / 128;
+    // two accumulator sets (256 columns per CTA) halve the token traffic when tensor memory has
+    // room and there are still enough CTAs to fill the machine
+    a.nw = (2 * pad <= 512 && pad >= 64 && col_tiles_1 >= 2 * sm_count * 3 / 4) ? 2 : 1;
     int cols = 32;
-    while (cols < pad) cols *= 2;
+    while (cols < a.nw * pad) cols *= 2;
     a.tmem_cols = cols;
     const int block = 1 << a.log2_block;
-    a.sc_rows = block >= kStageK ? 1 : kStageK / block;
-    const int pk_bytes = wkind == 4 ? 4096 : (wkind == 2 ? 2048 : 1024);
-    const int stage_stride = kWBytes + pad * 128 + ((pk_bytes + 8 * a.sc_rows * 32 + 1023) / 1024) * 1024;
-    int ns = (int)((220 * 1024 - 2048) / stage_stride);
-    if (ns > 8) ns = 8;
-    if (ns < 2) return cudaErrorInvalidConfiguration;
-    a.ns = ns;
-    const size_t smem = 1024 + (size_t)ns * stage_stride + (3 * ns + 4) * 8 + kMaxInlineNodes * sizeof(EpNodeDev) + 64;
+    static const int env_us = []() { const char* e = getenv("SMEG_TC_US"); return e ? atoi(e) : 0; }();
+    a.us = pad <= 64 ? 2 : 1;                                    // 64-deep units per stage
+    if (env_us == 1 || env_us == 2 || env_us == 4) a.us = env_us;
+    const int sk = a.us * kStageK;
+    a.sc_rows = block >= sk ? 1 : sk / block;
+    const int col_tiles = (a.n + 128 * a.nw - 1) / (128 * a.nw);
+    // depth split: only for small token counts, until the grid covers about two CTAs per SM
+    const int stages_all = (a.ku + a.us - 1) / a.us;
+    int splits = 1;
+    if (pad <= 64) {
+        while (col_tiles * tiles * splits < 2 * sm_count && splits < 16 && stages_all / (splits * 2) >= 4) splits *= 2;
+    }
+    const int tok_bytes = pad * 128;
+    const int pk_slot = ((a.nw * (a.us * kPkTile + 8 * a.sc_rows * 32) + 1023) / 1024) * 1024;
+    const int p_stride = a.us * tok_bytes + pk_slot, o_stride = a.nw * a.us * kWTile;
+    // small tiles leave room for two CTAs per SM: keep each under ~100 KB then
+    const int budget = (pad <= 64 ? 100 : 216) * 1024;
+    a.no = 2;
+    int np = (budget - 2048 - a.no * o_stride) / p_stride;
+    if (np > 12) np = 12;
+    if (np < 2) np = 2;
+    a.np = np;
+    *smem = 1024 + (size_t)a.no * o_stride + (size_t)np * p_stride + (size_t)(2 * np + 2 * a.no + 4) * 8 +
+            kMaxInlineNodes * sizeof(EpNodeDev) + 64;
+    *grid = dim3(col_tiles, tiles, splits);
+    *ws_floats = splits > 1 ? (size_t)col_tiles * tiles * splits * (a.nw * 128) * pad : 0;
+    *n_counters = splits > 1 ? (size_t)col_tiles * tiles : 0;
+}
 
+cudaError_t gemm_tc_launch(GemmTcArgs a, int bf16, dim3 grid, size_t smem, cudaStream_t stream) {
     CUtensorMap tm;
     const cuuint64_t gdim[2] = {(cuuint64_t)a.k, (cuuint64_t)a.m};
     const cuuint64_t gstride[1] = {(cuuint64_t)a.k * 2};
@@ -343,9 +436,9 @@ cudaError_t gemm_tc_launch(GemmTcArgs a, int bf16, int wkind, cudaStream_t strea
                              gstride, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
                              CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
     if (r != CUDA_SUCCESS) return cudaErrorInvalidValue;
-    dim3 grid((a.n + kColsPerCta - 1) / kColsPerCta, tiles);
-    if (bf16) return launch_tc<1, 4>(tm, a, grid, smem, stream);
-    return launch_tc<0, 4>(tm, a, grid, smem, stream);
+    if (smem > 227 * 1024) return cudaErrorInvalidConfiguration;
+    if (bf16) return launch_tc<1>(tm, a, grid, smem, stream);
+    return launch_tc<0>(tm, a, grid, smem, stream);
 }
 
 }  // namespace smeg

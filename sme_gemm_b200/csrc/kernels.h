@@ -62,12 +62,16 @@ struct GemmTcArgs {
     float* c32;                   // if set: raw f32 accumulators instead
     int m, n, k;
     int n16, ku, nb, log2_block;
-    int ntok_tile, ntok_pad, ntok_box, nmma, tmem_cols, sc_rows, ns;   // launcher-filled
+    int ntok_tile, ntok_pad, ntok_box, nmma, tmem_cols, sc_rows;       // planner-filled
+    int np, no, nw, us;           // ring depths (packed / operand), accumulator sets, units per stage
+    float* ws;                    // split-depth workspace [tile][slice][token][column]
+    int* counters;                // one per output tile, zero between launches
     unsigned* status;
     EpParams ep;
 };
 bool gemm_tc_supported(int wkind, int m, int k, int log2_block, const void* a);
-cudaError_t gemm_tc_launch(GemmTcArgs a, int bf16, int wkind, cudaStream_t stream);
+void gemm_tc_plan(GemmTcArgs& a, int sm_count, dim3* grid, size_t* smem, size_t* ws_floats, size_t* n_counters);
+cudaError_t gemm_tc_launch(GemmTcArgs a, int bf16, dim3 grid, size_t smem, cudaStream_t stream);
 
 // ---- element-wise model ops (elementwise.cu) ----
 cudaError_t glu_launch(uint16_t* out, const uint16_t* both, size_t m, size_t n, uint32_t act, cudaStream_t s);

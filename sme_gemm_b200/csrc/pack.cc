@@ -90,6 +90,7 @@ PackedDims make_dims(size_t n, size_t k, size_t block, int unit_depth) {
     PackedDims d;
     d.n = n; d.k = k; d.block = block; d.unit_depth = unit_depth;
     d.n16 = div_up(n, 16);
+    if (unit_depth == kQ4UnitDepth) d.n16 = div_up(d.n16, 8) * 8;   // whole 128-column super-groups
     d.ku = div_up(k, (size_t)unit_depth);
     d.nb_real = div_up(k, block);
     d.nb = std::max(d.nb_real, div_up(d.ku * (size_t)unit_depth, block));
@@ -212,14 +213,17 @@ void q1_quantize_host(const float* w, int layout, size_t n, size_t k, size_t blo
 // ------------------------------------------------------------------ prepack
 
 namespace {
+size_t scale_row(const PackedDims& d, size_t cg, size_t b) {
+    return d.unit_depth == kQ4UnitDepth ? q4_scale_row(cg, b, d.nb) : (cg * d.nb + b) * 16;
+}
 void pack_scales(const uint16_t* scales, const PackedDims& d, std::vector<uint16_t>& sc) {
     sc.assign(d.n16 * d.nb * 16, 0);
     for (size_t j = 0; j < d.n; ++j)
-        for (size_t b = 0; b < d.nb_real; ++b) sc[((j / 16) * d.nb + b) * 16 + scale_slot((int)(j % 16))] = scales[j * d.nb_real + b];
+        for (size_t b = 0; b < d.nb_real; ++b) sc[scale_row(d, j / 16, b) + scale_slot((int)(j % 16))] = scales[j * d.nb_real + b];
 }
 void unpack_scales(const uint16_t* sc, const PackedDims& d, uint16_t* scales) {
     for (size_t j = 0; j < d.n; ++j)
-        for (size_t b = 0; b < d.nb_real; ++b) scales[j * d.nb_real + b] = sc[((j / 16) * d.nb + b) * 16 + scale_slot((int)(j % 16))];
+        for (size_t b = 0; b < d.nb_real; ++b) scales[j * d.nb_real + b] = sc[scale_row(d, j / 16, b) + scale_slot((int)(j % 16))];
 }
 
 struct PackCtx {

@@ -173,9 +173,13 @@ __global__ void __launch_bounds__(kThreads) q4_gemv_kernel(Q4GemvArgs p) {
                 unsigned char* sbase = stages + (size_t)slot * stage_bytes;
                 for (int c = 0; c < ncg; ++c) {
                     const size_t cgi = cg0 + c;
-                    bulk_g2s(sbase + c * code_bytes, p.codes + ((cgi * p.k64 + (size_t)st * kConsumerWarps) * kUnitBytes), cb,
-                             &full[slot]);
-                    bulk_g2s(sbase + CG * code_bytes + c * scale_bytes, p.scales + (cgi * p.nb + blk0) * 16, sb, &full[slot]);
+                    // units of one column group are 4 KB apart (128-column super-group layout)
+                    for (int u = 0; u < units; ++u)
+                        bulk_g2s(sbase + c * code_bytes + u * kUnitBytes,
+                                 p.codes + q4_unit_offset(cgi, (size_t)st * kConsumerWarps + u, p.k64), kUnitBytes, &full[slot]);
+                    for (int r = 0; r < rows; ++r)
+                        bulk_g2s(sbase + CG * code_bytes + c * scale_bytes + r * 32, p.scales + q4_scale_row(cgi, blk0 + r, p.nb), 32,
+                                 &full[slot]);
                 }
             }
         }
