@@ -17,6 +17,7 @@
 #include "../../include/smeg_api.h"
 #include "kernels.h"
 #include "layout.h"
+#include "handles.h"
 #include "pack.h"
 
 using namespace smeg;
@@ -36,12 +37,13 @@ struct DeviceState {
 std::mutex g_mu;
 std::map<int, DeviceState> g_dev;
 int g_trace = -1;
-// Row count above which the tcgen05 kernel runs instead of the warp-level-MMA kernel
+// Row count above which the tcgen05 kernel runs instead of the warp-level-MMA decode kernel
 // (the reference switches kernels at Linear::PANEL_ROWS = 8 rows, src/linear.rs:160).
-// The tensor-core kernel covers every row count; SMEG_TC_MIN_ROWS is a tuning knob.
+// Measured on B200 the decode kernel is faster up to 16 rows.  The tensor-core kernel
+// covers every row count; SMEG_TC_MIN_ROWS is a tuning knob.
 int g_tc_min_rows = []() {
     const char* e = getenv("SMEG_TC_MIN_ROWS");
-    return e ? atoi(e) : 0;
+    return e ? atoi(e) : 16;
 }();
 
 DeviceState* dev_state() {
@@ -230,27 +232,6 @@ struct HostEp {
 // ---------------------------------------------------------------------------
 // handles
 // ---------------------------------------------------------------------------
-struct smeg_q4 {
-    PackedDims d;
-    unsigned char* codes = nullptr;
-    uint16_t* scales = nullptr;
-    size_t code_bytes = 0, scale_elems = 0;
-};
-struct smeg_lowbit {
-    PackedDims d;
-    int bits = 0;
-    uint32_t lut = 0;
-    int8_t codebook[4] = {0, 0, 0, 0};
-    unsigned char* codes = nullptr;
-    uint16_t* scales = nullptr;
-    size_t code_bytes = 0, scale_elems = 0;
-};
-struct smeg_mlp {
-    const smeg_q4* gate_up;
-    const smeg_q4* down;
-    uint32_t act;
-};
-
 extern "C" {
 
 const char* smeg_version(void) { return "sme-gemm-b200 0.1 (sm_100a)"; }

@@ -33,9 +33,21 @@
 
 namespace smeg {
 
+#ifdef SMEG_TC_TIMELINE
+// Debug builds only: per-stage SM-clock timestamps of CTA (0,0,0), [stage][event].
+__device__ long long g_tc_timeline[512 * 12];
+#define SMEG_TL(ev, i)                                                                          \
+    do {                                                                                        \
+        if (blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0 && (i) < 512) g_tc_timeline[(i) * 12 + (ev)] = clock64(); \
+    } while (0)
+#else
+#define SMEG_TL(ev, i) do { } while (0)
+#endif
+
 namespace {
 
-constexpr int kDeqWarps = 8;
+constexpr int kDeqWarps = 16;                    // dequant warps (the first 8 also drain tensor memory)
+constexpr int kDrainWarps = 8;
 constexpr int kTcThreads = 32 * (kDeqWarps + 2);
 constexpr int kStageK = 64;                       // depths per stage (one 128-byte swizzle row)
 constexpr int kWTile = 128 * kStageK * 2;         // one 128-column operand tile per stage: 16 KB
@@ -112,7 +124,7 @@ __device__ __forceinline__ void dequant_unit_q4(unsigned char* tile, int cu, con
 }
 
 template <int BF16>
-__global__ void __launch_bounds__(kTcThreads, 2) gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_tok, GemmTcArgs p) {
+__global__ void __launch_bounds__(kTcThreads, 1) gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_tok, GemmTcArgs p) {
     extern __shared__ unsigned char smem_dyn[];
     // the swizzled operands need 1024-byte aligned tiles: align the window by hand
     unsigned char* smem_raw = smem_dyn + ((1024u - (smem_u32(smem_dyn) & 1023u)) & 1023u);
@@ -176,7 +188,9 @@ __global__ void __launch_bounds__(kTcThreads, 2) gemm_tc_kernel(const __grid_con
         if (lane == 0) {
             for (int i = 0; i < num_stages; ++i) {
                 const int slot = i % P;
+                SMEG_TL(0, i);
                 if (i >= P && !mbar_wait(&p_empty[slot], ((i / P) - 1) & 1, abort_flag, p.status, STATUS_TMEM_TIMEOUT)) break;
+                SMEG_TL(1, i);
                 unsigned char* sb = ring_p + (size_t)slot * p_stride;
                 const int st = st_begin + i;
                 const int u0 = st * US;                                     // first 64-deep unit of the stage
@@ -204,41 +218,51 @@ __global__ void __launch_bounds__(kTcThreads, 2) gemm_tc_kernel(const __grid_con
         }
     } else if (warp == kDeqWarps + 1) {
         // ===================== MMA issuer =====================
-        if (lane == 0) {
-            const uint32_t idesc = umma_idesc(BF16, 128, p.ntok_box);
-            for (int i = 0; i < num_stages; ++i) {
-                const int ps = i % P, os = i % O;
-                if (!mbar_wait(&p_full[ps], (i / P) & 1, abort_flag, p.status, STATUS_TMEM_TIMEOUT)) break;
-                if (!mbar_wait(&o_full[os], (i / O) & 1, abort_flag, p.status, STATUS_TMEM_TIMEOUT)) break;
-                tc_fence_after();
-                const uint32_t tok_addr = smem_u32(ring_p + (size_t)ps * p_stride);
-                const uint32_t w_addr = smem_u32(ring_o + (size_t)os * o_stride);
-                const int units = min(US, p.ku - (st_begin + i) * US);
+        // the whole warp walks the stages (converged); one elected lane issues
+        const uint32_t idesc = umma_idesc(BF16, 128, p.ntok_box);
+        const uint32_t tok_half = (uint32_t)(tok_bytes / 2);
+        for (int i = 0; i < num_stages; ++i) {
+            const int ps = i % P, os = i % O;
+            if (!mbar_wait(&p_full[ps], (i / P) & 1, abort_flag, p.status, STATUS_TMEM_TIMEOUT)) break;
+            if (lane == 0) SMEG_TL(5, i);
+            if (!mbar_wait(&o_full[os], (i / O) & 1, abort_flag, p.status, STATUS_TMEM_TIMEOUT)) break;
+            if (lane == 0) SMEG_TL(6, i);
+            tc_fence_after();
+            const uint32_t tok_addr = smem_u32(ring_p + (size_t)ps * p_stride);
+            const uint32_t w_addr = smem_u32(ring_o + (size_t)os * o_stride);
+            const int units = min(US, p.ku - (st_begin + i) * US);
+            if (elect_one()) {
                 for (int uu = 0; uu < units; ++uu) {
+                    for (int w = 0; w < NW; ++w) {
+                        const uint64_t a_desc0 = umma_desc_sw128(w_addr + (w * US + uu) * kWTile);
+                        for (int h = 0; h < p.nmma; ++h) {
+                            const uint64_t b_desc0 = umma_desc_sw128(tok_addr + uu * tok_bytes + h * tok_half);
+                            const uint32_t d_tmem = tmem_base + (uint32_t)((w * p.nmma + h) * p.ntok_box);
 #pragma unroll
-                    for (int ks = 0; ks < kStageK / 16; ++ks) {
-                        const uint32_t accum = (i > 0 || uu > 0 || ks > 0) ? 1u : 0u;
-                        for (int w = 0; w < NW; ++w) {
-                            const uint64_t a_desc = umma_desc_sw128(w_addr + (w * US + uu) * kWTile) + 2 * ks;
-                            for (int h = 0; h < p.nmma; ++h) {
-                                const uint64_t b_desc = umma_desc_sw128(tok_addr + uu * tok_bytes + h * (tok_bytes / 2)) + 2 * ks;
-                                umma_f16(tmem_base + (uint32_t)((w * p.nmma + h) * p.ntok_box), a_desc, b_desc, idesc, accum);
-                            }
+                            for (int ks = 0; ks < kStageK / 16; ++ks)
+                                umma_f16(d_tmem, a_desc0 + 2 * ks, b_desc0 + 2 * ks, idesc, (i > 0 || uu > 0 || ks > 0) ? 1u : 0u);
                         }
                     }
                 }
+                SMEG_TL(10, i);
                 umma_commit(&o_empty[os]);
                 umma_commit(&p_empty[ps]);
+                SMEG_TL(7, i);
             }
-            umma_commit(acc_full);
+            __syncwarp();
         }
+        if (elect_one()) umma_commit(acc_full);
+        __syncwarp();
     } else {
         // ===================== dequant warps (0..7), then epilogue =====================
         const int g = lane >> 2, t = lane & 3;
         for (int i = 0; i < num_stages; ++i) {
             const int ps = i % P, os = i % O;
+            if (tid == 0) SMEG_TL(2, i);
             if (i >= O && !mbar_wait(&o_empty[os], ((i / O) - 1) & 1, abort_flag, p.status, STATUS_TMEM_TIMEOUT)) break;
+            if (tid == 0) SMEG_TL(8, i);
             if (!mbar_wait(&p_full[ps], (i / P) & 1, abort_flag, p.status, STATUS_TMEM_TIMEOUT)) break;
+            if (tid == 0) SMEG_TL(3, i);
             const int u0 = (st_begin + i) * US;
             const int units = min(US, p.ku - u0);
             const int d0 = u0 * kStageK;
@@ -260,10 +284,13 @@ __global__ void __launch_bounds__(kTcThreads, 2) gemm_tc_kernel(const __grid_con
             mbar_arrive(&o_full[os]);
             __syncwarp();
             if (lane == 0) mbar_arrive(&p_empty[ps]);
+            if (tid == 0) SMEG_TL(4, i);
         }
 
-        // ---- drain: thread = weight column (TMEM lane), registers = tokens ----
+        // ---- drain (warps 0..7): thread = weight column (TMEM lane), registers = tokens ----
+        if (warp < kDrainWarps) {
         if (num_stages > 0) mbar_wait(acc_full, 0, abort_flag, p.status, STATUS_TMEM_TIMEOUT);
+        if (tid == 0) SMEG_TL(9, 0);
         tc_fence_after();
         const int q = warp & 3, half = warp >> 2;              // lane quarter, token half
         const uint32_t lane_base = tmem_base + ((uint32_t)(32 * q) << 16);
@@ -308,13 +335,13 @@ __global__ void __launch_bounds__(kTcThreads, 2) gemm_tc_kernel(const __grid_con
         if (splits > 1) {
             // the last CTA of the tile to arrive adds the slices in slice order and stores
             __threadfence();
-            asm volatile("bar.sync 1, %0;" ::"n"(32 * kDeqWarps));
+            asm volatile("bar.sync 1, %0;" ::"n"(32 * kDrainWarps));
             if (tid == 0) {
                 const int prev = atomicAdd(p.counters + tile_id, 1);
                 *last_flag = (prev == splits - 1) ? 1 : 0;
                 if (prev == splits - 1) p.counters[tile_id] = 0;      // ready for the next launch
             }
-            asm volatile("bar.sync 1, %0;" ::"n"(32 * kDeqWarps));
+            asm volatile("bar.sync 1, %0;" ::"n"(32 * kDrainWarps));
             if (*last_flag) {
                 __threadfence();
                 for (int w = 0; w < NW; ++w) {
@@ -331,6 +358,7 @@ __global__ void __launch_bounds__(kTcThreads, 2) gemm_tc_kernel(const __grid_con
                 }
             }
         }
+        }   // drain warps
     }
     __syncthreads();
     if (warp == kDeqWarps + 1) {
@@ -371,6 +399,12 @@ cudaError_t launch_tc(const CUtensorMap& tm, const GemmTcArgs& a, dim3 grid, siz
 
 }  // namespace
 
+#ifdef SMEG_TC_TIMELINE
+extern "C" int smeg_debug_timeline(long long* host, int n) {
+    return cudaMemcpyFromSymbol(host, g_tc_timeline, sizeof(long long) * n) == cudaSuccess ? 0 : -1;
+}
+#endif
+
 bool gemm_tc_supported(int wkind, int m, int k, int log2_block, const void* a) {
     if (wkind != 4) return false;
     if (k % 8 != 0 || k == 0 || ((uintptr_t)a & 15) != 0) return false;   // TMA: 16-byte aligned rows
@@ -392,7 +426,9 @@ void gemm_tc_plan(GemmTcArgs& a, int sm_count, dim3* grid, size_t* smem, size_t*
     const int col_tiles_1 = (a.n + 127) / 128;
     // two accumulator sets (256 columns per CTA) halve the token traffic when tensor memory has
     // room and there are still enough CTAs to fill the machine
+    static const int env_nw = []() { const char* e = getenv("SMEG_TC_NW"); return e ? atoi(e) : 0; }();
     a.nw = (2 * pad <= 512 && pad >= 64 && col_tiles_1 >= 2 * sm_count * 3 / 4) ? 2 : 1;
+    if ((env_nw == 1 || env_nw == 2) && env_nw * pad <= 512) a.nw = env_nw;
     int cols = 32;
     while (cols < a.nw * pad) cols *= 2;
     a.tmem_cols = cols;
@@ -403,18 +439,37 @@ void gemm_tc_plan(GemmTcArgs& a, int sm_count, dim3* grid, size_t* smem, size_t*
     const int sk = a.us * kStageK;
     a.sc_rows = block >= sk ? 1 : sk / block;
     const int col_tiles = (a.n + 128 * a.nw - 1) / (128 * a.nw);
-    // depth split: only for small token counts, until the grid covers about two CTAs per SM
+    // depth split: one CTA per SM is resident.  Small token tiles (decode) split until the grid
+    // wastes little of its last wave; larger ones only when the column tiles alone cannot fill the
+    // machine (each slice costs a workspace round trip of the whole partial tile)
     const int stages_all = (a.ku + a.us - 1) / a.us;
     int splits = 1;
-    if (pad <= 64) {
-        while (col_tiles * tiles * splits < 2 * sm_count && splits < 16 && stages_all / (splits * 2) >= 4) splits *= 2;
+    {
+        const int base = col_tiles * tiles;
+        if (pad <= 64) {
+            double best = 0.0;
+            for (int s = 1; s <= 16; s *= 2) {
+                if (s > 1 && stages_all / s < 8) break;
+                const int ctas = base * s;
+                const int waves = (ctas + sm_count - 1) / sm_count;
+                double eff = (double)ctas / ((double)waves * sm_count);
+                if (s > 1) eff *= 0.97;
+                if (eff > best + 1e-9) { best = eff; splits = s; }
+            }
+        } else if (pad <= 256) {
+            while (base * splits * 2 <= sm_count && stages_all / (splits * 2) >= 16 && splits < 8) splits *= 2;
+        }
     }
     const int tok_bytes = pad * 128;
     const int pk_slot = ((a.nw * (a.us * kPkTile + 8 * a.sc_rows * 32) + 1023) / 1024) * 1024;
     const int p_stride = a.us * tok_bytes + pk_slot, o_stride = a.nw * a.us * kWTile;
-    // small tiles leave room for two CTAs per SM: keep each under ~100 KB then
-    const int budget = (pad <= 64 ? 100 : 216) * 1024;
-    a.no = 2;
+    const int budget = 216 * 1024;
+    static const int env_no = []() { const char* e = getenv("SMEG_TC_NO"); return e ? atoi(e) : 0; }();
+    // operand ring: three slots let the dequant warps run a stage ahead of the MMAs when the
+    // packed/token ring still keeps at least two stages in flight
+    a.no = a.nw == 2 ? 2 : 3;
+    if ((budget - 2048 - a.no * o_stride) / p_stride < 2) a.no = 2;
+    if (env_no >= 2 && env_no <= 6) a.no = env_no;
     int np = (budget - 2048 - a.no * o_stride) / p_stride;
     if (np > 12) np = 12;
     if (np < 2) np = 2;

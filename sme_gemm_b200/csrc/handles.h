@@ -1,0 +1,27 @@
+// The opaque weight handles of the C ABI (include/smeg_api.h), shared by the
+// translation units that implement entry points.
+#pragma once
+#include <stdint.h>
+
+#include "pack.h"
+
+struct smeg_q4 {
+    smeg::PackedDims d;
+    unsigned char* codes = nullptr;   // device: packed units
+    uint16_t* scales = nullptr;       // device: f16 scale rows
+    size_t code_bytes = 0, scale_elems = 0;
+};
+struct smeg_lowbit {
+    smeg::PackedDims d;
+    int bits = 0;                     // 2 or 1
+    uint32_t lut = 0;                 // 2-bit codebook, byte c = value of code c
+    int8_t codebook[4] = {0, 0, 0, 0};
+    unsigned char* codes = nullptr;
+    uint16_t* scales = nullptr;
+    size_t code_bytes = 0, scale_elems = 0;
+};
+struct smeg_mlp {
+    const smeg_q4* gate_up;
+    const smeg_q4* down;
+    uint32_t act;
+};
