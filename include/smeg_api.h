@@ -184,6 +184,17 @@ int smeg_matmul_lowbit_dev(const smeg_lowbit *w, const uint16_t *a, uint16_t *c,
  * sa (m*ceil(k/block) f32), sums (m*n*ceil(k/block) int32); any may be NULL. */
 int smeg_matmul_lowbit_debug_dev(const smeg_lowbit *w, const uint16_t *a, uint16_t *c, size_t m,
                                  int8_t *q_out, float *sa_out, int32_t *sums_out, void *stream);
+/* No counterpart in the reference.  smeg_matmul_lowbit_dev for callers that cannot allocate
+ * device memory (a serving loop with a frozen memory map, a process that handed all of HBM
+ * to weights and caches, a sandbox without cudaMalloc): the int8-activation scratch lives in
+ * a fixed array inside the library image instead of coming from the allocator.  Holds on
+ * every GPU that loads the library, until exit, about 200 KB.  Limits: m <= 8, depth (padded
+ * to the weight unit) <= 16384, <= 1024 K-blocks per row, <= 16 epilogue nodes; rc = -4 beyond
+ * them.  All calls on a device share the array: calls that overlap on the GPU race, so keep
+ * them on one stream.  The first call on a device resolves the array's address and must come
+ * before any stream capture.  Results are bit-identical to smeg_matmul_lowbit_dev. */
+int smeg_matmul_lowbit_static_dev(const smeg_lowbit *w, const uint16_t *a, uint16_t *c, size_t m,
+                                  const ep_desc16 *ep, void *stream);
 /* neon_glu_f16 / neon_add_f16_to_f32 / neon_act_f16 / converts
  * (csrc/sme_gemm_api.h:216-220; glu: src/linear.rs:804-835; add: src/convert.rs:37-48). */
 int smeg_glu_f16_dev(uint16_t *out, const uint16_t *both, size_t m, size_t n, uint32_t act, void *stream);

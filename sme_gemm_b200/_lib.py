@@ -79,6 +79,7 @@ SIGNATURES = {
     "smeg_matmul_q4_f16_dev": (_i, [_vp, _vp, _vp, _sz, _epp, _vp]),
     "smeg_matmul_q4_bf16_dev": (_i, [_vp, _vp, _vp, _sz, _epp, _vp]),
     "smeg_matmul_lowbit_dev": (_i, [_vp, _vp, _vp, _sz, _epp, _vp]),
+    "smeg_matmul_lowbit_static_dev": (_i, [_vp, _vp, _vp, _sz, _epp, _vp]),
     "smeg_matmul_lowbit_debug_dev": (_i, [_vp, _vp, _vp, _sz, _vp, _vp, _vp, _vp]),
     "smeg_glu_f16_dev": (_i, [_vp, _vp, _sz, _sz, _u32, _vp]),
     "smeg_add_f16_to_f32_dev": (_i, [_vp, _vp, _sz, _vp]),

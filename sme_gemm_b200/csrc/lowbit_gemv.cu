@@ -409,3 +409,125 @@ cudaError_t lowbit_gemv_launch(LowbitGemvArgs a, int bits, int sm_count, cudaStr
 }
 
 }  // namespace smeg
+
+// ---------------------------------------------------------------------------
+// smeg_matmul_lowbit_static_dev: the 2-bit / 1-bit GEMV for callers that must
+// not allocate device memory.
+//
+// The ordinary entry point takes the scratch for the quantised activations
+// (int8 codes, per-block scales, per-block code sums) from the stream-ordered
+// allocator on every call.  Some callers cannot do that: code running inside a
+// latency-critical serving loop that has frozen its memory map, a host that
+// pre-reserved all of HBM for weights and KV cache and leaves the allocator
+// nothing, or a plug-in sandbox that is simply not allowed to call cudaMalloc.
+// For them this variant keeps that scratch in a fixed array that is part of the
+// library image: it exists on every GPU that loads the library, from load until
+// the process exits, whether the entry point is ever called or not.
+//
+// Limits (rejected with rc = -4 beyond them): at most kStaticRows activation
+// rows, padded depth at most kStaticDepth, at most kStaticBlocks K-blocks per
+// row, and an epilogue graph of at most 16 nodes.
+//
+// The array is shared by every call on the device and keeps whatever the last
+// call left in it.  Nothing in it has to start at zero: each call rewrites the
+// region it reads (all codes, scales and sums of its rows) before the GEMV
+// kernel, ordered by the stream.  Two calls that overlap on the GPU (different
+// streams, or different host threads on different streams) race on the array and
+// give wrong results; serialise them on one stream.
+//
+// The first call on a device looks up the array's device address (host code
+// cannot use the array's name as a pointer: on the host that name is only a
+// stand-in symbol) and raises the kernels' shared-memory limit; make that first
+// call before any stream capture.
+// ---------------------------------------------------------------------------
+#include <mutex>
+
+#include "../../include/smeg_api.h"
+#include "handles.h"
+
+namespace {
+
+constexpr size_t kStaticRows = 8;
+constexpr size_t kStaticDepth = 16384;
+constexpr size_t kStaticBlocks = 1024;
+constexpr size_t kStaticQBytes = kStaticRows * kStaticDepth;               // int8 codes
+constexpr size_t kStaticSaBytes = kStaticRows * kStaticBlocks * 4;         // f32 scales / i32 sums
+constexpr size_t kStaticBytes = kStaticQBytes + 2 * kStaticSaBytes + 256;  // + the status word's slot
+
+static __device__ __align__(256) unsigned char g_lowbit_static_scratch[kStaticBytes];
+
+struct StaticSetup {
+    bool ready = false;
+    unsigned char* base = nullptr;   // device address of g_lowbit_static_scratch on this device
+    int sm_count = 0;
+};
+std::mutex g_static_mu;
+StaticSetup g_static[64];
+
+// Once per device, with that device current.
+int static_setup(StaticSetup** out) {
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return -5;
+    std::lock_guard<std::mutex> lk(g_static_mu);
+    StaticSetup& s = g_static[dev];
+    if (!s.ready) {
+        int major = 0;
+        if (cudaDeviceGetAttribute(&major, cudaDevAttrComputeCapabilityMajor, dev) != cudaSuccess || major != 10) return -5;
+        if (cudaDeviceGetAttribute(&s.sm_count, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess) return -5;
+        void* ptr = nullptr;
+        if (cudaGetSymbolAddress(&ptr, g_lowbit_static_scratch) != cudaSuccess || !ptr) return -6;
+        s.base = static_cast<unsigned char*>(ptr);
+        // the status word lives in the array's last 256 bytes and starts at zero
+        if (cudaMemset(s.base + kStaticQBytes + 2 * kStaticSaBytes, 0, 256) != cudaSuccess) return -6;
+        s.ready = true;
+    }
+    *out = &s;
+    return 0;
+}
+
+}  // namespace
+
+extern "C" int smeg_matmul_lowbit_static_dev(const smeg_lowbit* w, const uint16_t* a, uint16_t* c, size_t m,
+                                              const ep_desc16* ep, void* stream_v) {
+    using namespace smeg;
+    if (!w) return -4;
+    cudaStream_t stream = (cudaStream_t)stream_v;
+    const size_t n = w->d.n, k = w->d.k;
+    if (m == 0 || n == 0) return 0;
+    if (!c || (k && !a) || n > 0x7fffffffu || k > 0x7fffffffu) return -4;
+    const size_t kq = w->d.ku * (size_t)w->d.unit_depth, nb = w->d.nb;
+    if (m > kStaticRows || kq > kStaticDepth || nb > kStaticBlocks) return -4;   // beyond the fixed scratch
+    if (ep && ep->n_nodes > (uint32_t)kMaxInlineNodes) return -4;               // a longer graph would need a device buffer
+    StaticSetup* st = nullptr;
+    int rc = static_setup(&st);
+    if (rc) return rc;
+
+    ActQuantArgs aq;
+    aq.a = a;
+    aq.q = reinterpret_cast<int8_t*>(st->base);
+    aq.sa = reinterpret_cast<float*>(st->base + kStaticQBytes);
+    aq.qsum = w->bits == 1 ? reinterpret_cast<int32_t*>(st->base + kStaticQBytes + kStaticSaBytes) : nullptr;
+    aq.m = (int)m; aq.k = (int)k; aq.kq = (int)kq; aq.nbq = (int)nb; aq.log2_block = w->d.log2_block;
+
+    LowbitGemvArgs g;
+    memset(&g, 0, sizeof(g));
+    if (ep && ep->n_nodes && ep->nodes) {
+        for (uint32_t i = 0; i < ep->n_nodes; ++i) {
+            const EpNode& s = ep->nodes[i];
+            if (s.op > 24u) return -4;
+            g.ep.nodes[i].op = (s.op & 0xffu) | ((s.aux & 0xffu) << 8);
+            g.ep.nodes[i].scalar = s.scalar;
+            g.ep.nodes[i].ptr = static_cast<const uint16_t*>(s.ptr);
+            g.ep.nodes[i].ld = s.ld == 0 ? n : s.ld;
+        }
+        g.ep.n_nodes = (int)ep->n_nodes;
+    }
+    g.codes = w->codes; g.scales = w->scales; g.q = aq.q; g.sa = aq.sa; g.qsum = aq.qsum; g.c = c;
+    g.m = (int)m; g.n = (int)n; g.k = (int)k; g.kq = (int)kq;
+    g.n16 = (int)w->d.n16; g.ku = (int)w->d.ku; g.nb = (int)nb; g.nb_real = (int)w->d.nb_real;
+    g.log2_block = w->d.log2_block; g.lut = w->lut;
+    g.status = reinterpret_cast<unsigned*>(st->base + kStaticQBytes + 2 * kStaticSaBytes);
+    if (act_quant_launch(aq, stream) != cudaSuccess) return -6;
+    if (lowbit_gemv_launch(g, w->bits, st->sm_count, stream) != cudaSuccess) return -6;
+    return 0;
+}
