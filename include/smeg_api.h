@@ -180,6 +180,15 @@ int smeg_matmul_q4_bf16_dev(const smeg_q4 *w, const uint16_t *a, uint16_t *c, si
  * quantisation are bit-exact with quantize_row / reference (:354-398). */
 int smeg_matmul_lowbit_dev(const smeg_lowbit *w, const uint16_t *a, uint16_t *c, size_t m,
                            const ep_desc16 *ep, void *stream);
+/* matmul_q2_mopa_ep / matmul_q1_mopa_ep (src/kernels/lowbit/matmul.rs:100-139, mopa_impl
+ * :339-350): the same weights on the f16 path -- f16 activations, no int8 quantisation,
+ * weights f16(scale * value) as Codes::dequant (:178-197) rounds them, f32 accumulation on
+ * the tensor cores.  The first such call on a handle builds a 4-bit twin of the weights on
+ * the device (synchronously; smeg_lowbit_prepare_f16 does it ahead of time, e.g. before a
+ * stream capture).  A 2-bit codebook with a value outside [-8, 7] has no twin: rc = -3. */
+int smeg_lowbit_prepare_f16(const smeg_lowbit *w);
+int smeg_matmul_lowbit_f16_dev(const smeg_lowbit *w, const uint16_t *a, uint16_t *c, size_t m,
+                               const ep_desc16 *ep, void *stream);
 /* Same, also writing the intermediate integers for parity checks: q (m*k int8),
  * sa (m*ceil(k/block) f32), sums (m*n*ceil(k/block) int32); any may be NULL. */
 int smeg_matmul_lowbit_debug_dev(const smeg_lowbit *w, const uint16_t *a, uint16_t *c, size_t m,
@@ -208,6 +217,7 @@ int smeg_f16_to_f32_dev(float *dst, const uint16_t *src, size_t len, void *strea
 int smeg_matmul_q4_f16(const smeg_q4 *w, const uint16_t *a, uint16_t *c, size_t m, const ep_desc16 *ep);
 int smeg_matmul_q4_bf16(const smeg_q4 *w, const uint16_t *a, uint16_t *c, size_t m, const ep_desc16 *ep);
 int smeg_matmul_lowbit(const smeg_lowbit *w, const uint16_t *a, uint16_t *c, size_t m, const ep_desc16 *ep);
+int smeg_matmul_lowbit_f16(const smeg_lowbit *w, const uint16_t *a, uint16_t *c, size_t m, const ep_desc16 *ep);
 
 /* ---- MLP block ---------------------------------------------------------------- */
 
@@ -251,6 +261,12 @@ int gemm_sme_f16_q1(size_t m, size_t n, size_t k, uint16_t *dst, const uint16_t 
 int gemm_sme_f16_q2(size_t m, size_t n, size_t k, uint16_t *dst, const uint16_t *lhs,
                     const uint8_t *codes, const uint16_t *scales, const int8_t *codebook, size_t block,
                     const ep_desc16 *ep);
+/* csrc/sme_gemm_api.h:110-115: the same weights on the f16 path */
+int gemm_sme_f16f16_q1(size_t m, size_t n, size_t k, uint16_t *dst, const uint16_t *lhs,
+                       const uint8_t *signs, const uint16_t *scales, size_t block, const ep_desc16 *ep);
+int gemm_sme_f16f16_q2(size_t m, size_t n, size_t k, uint16_t *dst, const uint16_t *lhs,
+                       const uint8_t *codes, const uint16_t *scales, const int8_t *codebook, size_t block,
+                       const ep_desc16 *ep);
 /* csrc/sme_gemm_api.h:216-220 (host pointers) */
 void neon_glu_f16(uint16_t *out, const uint16_t *in, size_t m, size_t n, uint32_t act);
 void neon_add_f16_to_f32(float *dst, const uint16_t *src, size_t n);

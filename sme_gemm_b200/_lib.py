@@ -79,6 +79,8 @@ SIGNATURES = {
     "smeg_matmul_q4_f16_dev": (_i, [_vp, _vp, _vp, _sz, _epp, _vp]),
     "smeg_matmul_q4_bf16_dev": (_i, [_vp, _vp, _vp, _sz, _epp, _vp]),
     "smeg_matmul_lowbit_dev": (_i, [_vp, _vp, _vp, _sz, _epp, _vp]),
+    "smeg_lowbit_prepare_f16": (_i, [_vp]),
+    "smeg_matmul_lowbit_f16_dev": (_i, [_vp, _vp, _vp, _sz, _epp, _vp]),
     "smeg_matmul_lowbit_static_dev": (_i, [_vp, _vp, _vp, _sz, _epp, _vp]),
     "smeg_matmul_lowbit_debug_dev": (_i, [_vp, _vp, _vp, _sz, _vp, _vp, _vp, _vp]),
     "smeg_glu_f16_dev": (_i, [_vp, _vp, _sz, _sz, _u32, _vp]),
@@ -89,6 +91,7 @@ SIGNATURES = {
     "smeg_matmul_q4_f16": (_i, [_vp, _vp, _vp, _sz, _epp]),
     "smeg_matmul_q4_bf16": (_i, [_vp, _vp, _vp, _sz, _epp]),
     "smeg_matmul_lowbit": (_i, [_vp, _vp, _vp, _sz, _epp]),
+    "smeg_matmul_lowbit_f16": (_i, [_vp, _vp, _vp, _sz, _epp]),
     "smeg_mlp_create": (_i, [_vp, _vp, _u32, _pp]),
     "smeg_mlp_destroy": (None, [_vp]),
     "smeg_mlp_accumulate_dev": (_i, [_vp, _vp, _vp, _sz, _vp]),
@@ -99,6 +102,8 @@ SIGNATURES = {
     "gemm_sme_b16b16_q4": (_i, [_sz, _sz, _sz, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _sz, _epp]),
     "gemm_sme_f16_q1": (_i, [_sz, _sz, _sz, _vp, _vp, _vp, _vp, _sz, _epp]),
     "gemm_sme_f16_q2": (_i, [_sz, _sz, _sz, _vp, _vp, _vp, _vp, _vp, _sz, _epp]),
+    "gemm_sme_f16f16_q1": (_i, [_sz, _sz, _sz, _vp, _vp, _vp, _vp, _sz, _epp]),
+    "gemm_sme_f16f16_q2": (_i, [_sz, _sz, _sz, _vp, _vp, _vp, _vp, _vp, _sz, _epp]),
     "neon_glu_f16": (None, [_vp, _vp, _sz, _sz, _u32]),
     "neon_add_f16_to_f32": (None, [_vp, _vp, _sz]),
     "smeg_forget": (None, [_vp]),

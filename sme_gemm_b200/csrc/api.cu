@@ -422,6 +422,7 @@ int smeg_q1_from_band(const uint8_t* signs, const uint16_t* scales, size_t n, si
 }
 void smeg_lowbit_destroy(smeg_lowbit* w) {
     if (!w) return;
+    smeg_q4_destroy(w->twin.load());
     if (w->codes) cudaFree(w->codes);
     if (w->scales) cudaFree(w->scales);
     delete w;
@@ -620,6 +621,61 @@ int smeg_matmul_lowbit_debug_dev(const smeg_lowbit* w, const uint16_t* a, uint16
     return lowbit_dev(w, a, c, m, nullptr, q_out, sa_out, sums_out, (cudaStream_t)stream);
 }
 
+// The 4-bit twin of a 2-bit / 1-bit weight set (see transcode.cu), built once under the
+// handle's lock; the build synchronises, so it must not first happen inside a stream capture.
+static int lowbit_twin(const smeg_lowbit* w, const smeg_q4** out) {
+    smeg_q4* t = w->twin.load(std::memory_order_acquire);
+    if (t) { *out = t; return 0; }
+    if (w->bits == 2)
+        for (int i = 0; i < 4; ++i)
+            if (w->codebook[i] < -8 || w->codebook[i] > 7) return -3;
+    std::lock_guard<std::mutex> lock(w->twin_lock);
+    t = w->twin.load(std::memory_order_acquire);
+    if (t) { *out = t; return 0; }
+    if (!dev_state()) return -5;
+    smeg_q4* h = new smeg_q4();
+    h->d = make_dims(w->d.n, w->d.k, w->d.block, kQ4UnitDepth);
+    h->code_bytes = h->d.n16 * h->d.ku * kUnitBytes;
+    h->scale_elems = h->d.n16 * h->d.nb * 16;
+    if ((h->code_bytes && cudaMalloc(&h->codes, h->code_bytes) != cudaSuccess) ||
+        (h->scale_elems && cudaMalloc(&h->scales, h->scale_elems * 2) != cudaSuccess)) {
+        smeg_q4_destroy(h);
+        return -2;
+    }
+    LowbitToQ4Args a;
+    a.src = w->codes; a.src_scales = w->scales; a.dst = h->codes; a.dst_scales = h->scales;
+    a.n = w->d.n; a.k = w->d.k;
+    a.ku_src = w->d.ku; a.n16_src = w->d.n16; a.nb_src = w->d.nb;
+    a.ku4 = h->d.ku; a.nb4 = h->d.nb;
+    a.dst_words = h->code_bytes / 4; a.dst_scale_elems = h->scale_elems;
+    a.bits = w->bits; a.lut = w->lut;
+    cudaStream_t s = nullptr;
+    if (cudaStreamCreateWithFlags(&s, cudaStreamNonBlocking) != cudaSuccess) { smeg_q4_destroy(h); return -2; }
+    cudaError_t e = lowbit_to_q4_launch(a, s);
+    if (e == cudaSuccess) e = cudaStreamSynchronize(s);
+    cudaStreamDestroy(s);
+    if (e != cudaSuccess) { smeg_q4_destroy(h); return -6; }
+    w->twin.store(h, std::memory_order_release);
+    *out = h;
+    return 0;
+}
+
+int smeg_lowbit_prepare_f16(const smeg_lowbit* w) {
+    if (!w) return -4;
+    const smeg_q4* t = nullptr;
+    return lowbit_twin(w, &t);
+}
+
+int smeg_matmul_lowbit_f16_dev(const smeg_lowbit* w, const uint16_t* a, uint16_t* c, size_t m, const ep_desc16* ep,
+                               void* stream) {
+    if (!w) return -4;
+    if (m == 0 || w->d.n == 0) return 0;
+    const smeg_q4* t = nullptr;
+    const int rc = lowbit_twin(w, &t);
+    if (rc) return rc;
+    return q4_dev(t, a, c, m, ep, 0, (cudaStream_t)stream);
+}
+
 int smeg_glu_f16_dev(uint16_t* out, const uint16_t* both, size_t m, size_t n, uint32_t act, void* stream) {
     if (act != SMEG_ACT_SILU && act != SMEG_ACT_GELU) return -4;
     return glu_launch(out, both, m, n, act, (cudaStream_t)stream) == cudaSuccess ? 0 : -6;
@@ -701,6 +757,13 @@ int smeg_matmul_lowbit(const smeg_lowbit* w, const uint16_t* a, uint16_t* c, siz
     TraceScope ts(w->bits == 2 ? "matmul_q2" : "matmul_q1", m, w->d.n, w->d.k);
     return host_matmul(m, w->d.n, w->d.k, a, c, ep, [&](const uint16_t* da, uint16_t* dc, const ep_desc16* dep) {
         return lowbit_dev(w, da, dc, m, dep, nullptr, nullptr, nullptr, 0);
+    });
+}
+int smeg_matmul_lowbit_f16(const smeg_lowbit* w, const uint16_t* a, uint16_t* c, size_t m, const ep_desc16* ep) {
+    if (!w) return -4;
+    TraceScope ts(w->bits == 2 ? "matmul_q2_mopa" : "matmul_q1_mopa", m, w->d.n, w->d.k);
+    return host_matmul(m, w->d.n, w->d.k, a, c, ep, [&](const uint16_t* da, uint16_t* dc, const ep_desc16* dep) {
+        return smeg_matmul_lowbit_f16_dev(w, da, dc, m, dep, nullptr);
     });
 }
 
@@ -863,6 +926,24 @@ int gemm_sme_f16_q2(size_t m, size_t n, size_t k, uint16_t* dst, const uint16_t*
     smeg_lowbit* w = cached_lowbit(2, codes, scales, codebook, n, k, block, &rc);
     if (!w) return rc;
     return smeg_matmul_lowbit(w, lhs, dst, m, ep);
+}
+
+int gemm_sme_f16f16_q1(size_t m, size_t n, size_t k, uint16_t* dst, const uint16_t* lhs, const uint8_t* signs,
+                       const uint16_t* scales, size_t block, const ep_desc16* ep) {
+    if (m == 0 || n == 0) return 0;
+    int rc = 0;
+    smeg_lowbit* w = cached_lowbit(1, signs, scales, nullptr, n, k, block, &rc);
+    if (!w) return rc;
+    return smeg_matmul_lowbit_f16(w, lhs, dst, m, ep);
+}
+int gemm_sme_f16f16_q2(size_t m, size_t n, size_t k, uint16_t* dst, const uint16_t* lhs, const uint8_t* codes,
+                       const uint16_t* scales, const int8_t* codebook, size_t block, const ep_desc16* ep) {
+    if (m == 0 || n == 0) return 0;
+    if (!codebook) return -4;
+    int rc = 0;
+    smeg_lowbit* w = cached_lowbit(2, codes, scales, codebook, n, k, block, &rc);
+    if (!w) return rc;
+    return smeg_matmul_lowbit_f16(w, lhs, dst, m, ep);
 }
 
 void neon_glu_f16(uint16_t* out, const uint16_t* in, size_t m, size_t n, uint32_t act) {

@@ -120,9 +120,143 @@ __device__ __forceinline__ uint16_t ep_store_value(const EpParams& ep, float acc
     return f32_to_t<BF16>(x);
 }
 
-// Same, over an explicit node array (shared or global memory).
+// A graph of at most four nodes whose operands are scalars or per-column vectors and
+// whose activations are relu, silu or sigmoid, resolved once per thread for the
+// thread's output column: the per-cell work is then four predictable steps on
+// registers.  Arithmetic is the interpreter's (separately rounded f32 ops on the
+// T-rounded product); silu and sigmoid use the fast exponential and division, whose
+// error (about 1e-6 relative) is three orders below the 16-bit output's rounding.
+struct FastEp {
+    int n;
+    int cls[4];     // 1 add, 2 mul, 3 sub, 4 div, 5 max, 6 min, 8 + kind for an activation
+    float v[4];
+};
+
+// Host-side test: can this resolved graph run as a FastEp?
+inline bool fast_ep_eligible(const EpParams& ep) {
+    if (ep.n_nodes < 1 || ep.n_nodes > 4) return false;
+    for (int q = 0; q < ep.n_nodes; ++q) {
+        const uint32_t op = ep.nodes[q].op & 0xffu, kind = (ep.nodes[q].op >> 8) & 0xffu;
+        const bool scalar = op == 0 || op == 1 || op == 9 || op == 10 || op == 11 || op == 15;
+        const bool col = op == 4 || op == 5 || op == 13 || op == 17 || op == 20 || op == 23;
+        if (!(scalar || col || (op == 8 && (kind == 1 || kind == 3 || kind == 5)))) return false;
+    }
+    return true;
+}
+
 template <int BF16>
-__device__ __forceinline__ uint16_t ep_store_nodes(const EpNodeDev* nodes, int nn, float acc, size_t i, size_t j) {
+__device__ __forceinline__ void fast_ep_build(const EpNodeDev* nodes, int nn, int col, bool col_ok, FastEp& f) {
+    f.n = nn;
+#pragma unroll
+    for (int q = 0; q < 4; ++q) {
+        f.cls[q] = 0;
+        f.v[q] = 0.0f;
+        if (q < nn) {
+            const uint32_t op = nodes[q].op & 0xffu;
+            int cls = 0;
+            switch (op) {
+            case 0: case 4: cls = 1; break;
+            case 1: case 5: cls = 2; break;
+            case 11: case 13: cls = 3; break;
+            case 15: case 17: cls = 4; break;
+            case 9: case 20: cls = 5; break;
+            case 10: case 23: cls = 6; break;
+            case 8: cls = 8 + (int)((nodes[q].op >> 8) & 0xffu); break;
+            default: break;
+            }
+            const bool is_col = op == 4 || op == 5 || op == 13 || op == 17 || op == 20 || op == 23;
+            f.cls[q] = cls;
+            f.v[q] = is_col ? (col_ok ? t_to_f32<BF16>(nodes[q].ptr[col]) : 0.0f) : nodes[q].scalar;
+        }
+    }
+}
+
+// Applies the graph to 16 accumulators of one output column at once.  The walk over the
+// slots is outside the walk over the values: one uniform branch per slot and a straight run
+// of 16 operations under it, so the code stays a few hundred instructions however it is
+// unrolled (a per-value walk of every case, unrolled 16 times, overflowed the instruction
+// cache and made the drain fetch-bound).
+template <int BF16>
+__device__ __forceinline__ void fast_ep_apply16(const FastEp& f, const uint32_t (&acc)[16], uint16_t (&out)[16]) {
+    float x[16];
+#pragma unroll
+    for (int j = 0; j < 16; ++j) x[j] = t_to_f32<BF16>(f32_to_t<BF16>(__uint_as_float(acc[j])));
+#pragma unroll
+    for (int q = 0; q < 4; ++q) {
+        const int cls = f.cls[q];
+        const float o = f.v[q];
+        if (cls == 0) continue;
+        switch (cls) {
+        case 1:
+#pragma unroll
+            for (int j = 0; j < 16; ++j) x[j] = __fadd_rn(x[j], o);
+            break;
+        case 2:
+#pragma unroll
+            for (int j = 0; j < 16; ++j) x[j] = __fmul_rn(x[j], o);
+            break;
+        case 3:
+#pragma unroll
+            for (int j = 0; j < 16; ++j) x[j] = __fsub_rn(x[j], o);
+            break;
+        case 4:
+#pragma unroll 1
+            for (int j = 0; j < 16; ++j) x[j] = __fdiv_rn(x[j], o);
+            break;
+        case 5:
+#pragma unroll
+            for (int j = 0; j < 16; ++j) x[j] = fmaxf(x[j], o);
+            break;
+        case 6:
+#pragma unroll
+            for (int j = 0; j < 16; ++j) x[j] = fminf(x[j], o);
+            break;
+        case 8 + 1:
+#pragma unroll
+            for (int j = 0; j < 16; ++j) x[j] = fmaxf(x[j], 0.0f);
+            break;
+        case 8 + 3:
+#pragma unroll
+            for (int j = 0; j < 16; ++j) x[j] = __fdividef(x[j], 1.0f + __expf(-x[j]));
+            break;
+        case 8 + 5:
+#pragma unroll
+            for (int j = 0; j < 16; ++j) x[j] = __fdividef(1.0f, 1.0f + __expf(-x[j]));
+            break;
+        default: break;
+        }
+    }
+#pragma unroll
+    for (int j = 0; j < 16; ++j) out[j] = f32_to_t<BF16>(x[j]);
+}
+
+template <int BF16>
+__device__ __forceinline__ uint16_t fast_ep_store(const FastEp& f, float acc) {
+    float x = t_to_f32<BF16>(f32_to_t<BF16>(acc));
+#pragma unroll
+    for (int q = 0; q < 4; ++q) {
+        const int cls = f.cls[q];
+        const float o = f.v[q];
+        switch (cls) {
+        case 1: x = __fadd_rn(x, o); break;
+        case 2: x = __fmul_rn(x, o); break;
+        case 3: x = __fsub_rn(x, o); break;
+        case 4: x = __fdiv_rn(x, o); break;
+        case 5: x = fmaxf(x, o); break;
+        case 6: x = fminf(x, o); break;
+        case 8 + 1: x = fmaxf(x, 0.0f); break;
+        case 8 + 3: x = __fdividef(x, 1.0f + __expf(-x)); break;
+        case 8 + 5: x = __fdividef(1.0f, 1.0f + __expf(-x)); break;
+        default: break;
+        }
+    }
+    return f32_to_t<BF16>(x);
+}
+
+// Same, over an explicit node array (shared or global memory).  Out of line: the interpreter
+// with every activation inlined is large, and the callers sit in unrolled loops.
+template <int BF16>
+__device__ __noinline__ uint16_t ep_store_nodes(const EpNodeDev* nodes, int nn, float acc, size_t i, size_t j) {
     uint16_t c = f32_to_t<BF16>(acc);
     if (nn == 0) return c;
     float x = t_to_f32<BF16>(c);

@@ -47,7 +47,6 @@ __device__ long long g_tc_timeline[512 * 12];
 namespace {
 
 constexpr int kDeqWarps = 16;                    // dequant warps (the first 8 also drain tensor memory)
-constexpr int kDrainWarps = 8;
 constexpr int kTcThreads = 32 * (kDeqWarps + 2);
 constexpr int kStageK = 64;                       // depths per stage (one 128-byte swizzle row)
 constexpr int kWTile = 128 * kStageK * 2;         // one 128-column operand tile per stage: 16 KB
@@ -135,6 +134,10 @@ __global__ void __launch_bounds__(kTcThreads, 1) gemm_tc_kernel(const __grid_con
     const int pk_slot = ((NW * (US * kPkTile + 8 * sc_rows * 32) + 1023) / 1024) * 1024;
     const int p_stride = US * tok_bytes + pk_slot;             // ring P slot: [token tiles | packed units | scales]
     const int o_stride = NW * US * kWTile;                     // ring O slot: NW x US operand tiles
+    // a stage holds 8 * NW * US packed units, one per dequant warp: with only 8 of them the 16
+    // warps form two groups that take alternate stages
+    const int deq_groups = (8 * NW * US >= kDeqWarps) ? 1 : 2;
+    const int deq_wpg = kDeqWarps / deq_groups;
 
     unsigned char* ring_o = smem_raw;
     unsigned char* ring_p = smem_raw + (size_t)O * o_stride;
@@ -161,10 +164,10 @@ __global__ void __launch_bounds__(kTcThreads, 1) gemm_tc_kernel(const __grid_con
     if (tid == 0) {
         for (int s = 0; s < P; ++s) {
             mbar_init(&p_full[s], 1);
-            mbar_init(&p_empty[s], kDeqWarps + 1);
+            mbar_init(&p_empty[s], deq_wpg + 1);
         }
         for (int s = 0; s < O; ++s) {
-            mbar_init(&o_full[s], 32 * kDeqWarps);
+            mbar_init(&o_full[s], 32 * deq_wpg);
             mbar_init(&o_empty[s], 1);
         }
         mbar_init(acc_full, 1);
@@ -185,36 +188,44 @@ __global__ void __launch_bounds__(kTcThreads, 1) gemm_tc_kernel(const __grid_con
 
     if (warp == kDeqWarps) {
         // ===================== producer =====================
-        if (lane == 0) {
-            for (int i = 0; i < num_stages; ++i) {
-                const int slot = i % P;
-                SMEG_TL(0, i);
-                if (i >= P && !mbar_wait(&p_empty[slot], ((i / P) - 1) & 1, abort_flag, p.status, STATUS_TMEM_TIMEOUT)) break;
-                SMEG_TL(1, i);
-                unsigned char* sb = ring_p + (size_t)slot * p_stride;
-                const int st = st_begin + i;
-                const int u0 = st * US;                                     // first 64-deep unit of the stage
-                const int units = min(US, p.ku - u0);
-                const int d0 = u0 * kStageK;
-                const int blk0 = d0 >> p.log2_block;
-                const int blk1 = min(p.nb, ((d0 + units * kStageK - 1) >> p.log2_block) + 1);
-                const int rows = blk1 - blk0;
+        // the whole warp walks the stages; after lane 0 has armed the barrier the stage's copies
+        // are issued by one lane each (token tiles: lane 0; packed units: lanes 0-15; scale rows:
+        // lanes 16-31), so their issue cost does not add up on one thread
+        for (int i = 0; i < num_stages; ++i) {
+            const int slot = i % P;
+            if (lane == 0) SMEG_TL(0, i);
+            // the verdict is made warp-uniform so that no lane is left behind at a warp barrier
+            if (i >= P && !__all_sync(0xffffffffu, mbar_wait(&p_empty[slot], ((i / P) - 1) & 1, abort_flag, p.status, STATUS_TMEM_TIMEOUT))) break;
+            if (lane == 0) SMEG_TL(1, i);
+            unsigned char* sb = ring_p + (size_t)slot * p_stride;
+            const int st = st_begin + i;
+            const int u0 = st * US;                                     // first 64-deep unit of the stage
+            const int units = min(US, p.ku - u0);
+            const int d0 = u0 * kStageK;
+            const int blk0 = d0 >> p.log2_block;
+            const int blk1 = min(p.nb, ((d0 + units * kStageK - 1) >> p.log2_block) + 1);
+            const int rows = blk1 - blk0;
+            if (lane == 0) {
                 mbar_expect_tx(&p_full[slot], (unsigned)(units * tok_bytes) + (unsigned)NW * (units * kPkTile + rows * 256u));
                 for (int uu = 0; uu < units; ++uu) {
                     tma_load_2d(sb + uu * tok_bytes, &tmap_tok, d0 + uu * kStageK, tok0, &p_full[slot]);
                     if (p.nmma == 2)
                         tma_load_2d(sb + uu * tok_bytes + tok_bytes / 2, &tmap_tok, d0 + uu * kStageK, tok0 + p.ntok_box, &p_full[slot]);
                 }
-                unsigned char* pkdst = sb + US * tok_bytes;
-                unsigned char* scdst = pkdst + NW * US * kPkTile;
-                for (int w = 0; w < NW; ++w) {
-                    const size_t sg = (size_t)min(sg0 + w, p.n16 / 8 - 1);  // a tail super-group re-reads the last one
-                    // one contiguous run: [unit][8 column groups][512 B]
-                    bulk_g2s(pkdst + w * US * kPkTile, p.codes + (sg * p.ku + (size_t)u0) * kPkTile, units * kPkTile, &p_full[slot]);
-                    // [block][8 column groups][16 slots]
-                    bulk_g2s(scdst + w * sc_rows * 256, p.scales + (sg * p.nb + blk0) * 128, rows * 256, &p_full[slot]);
-                }
             }
+            __syncwarp();
+            unsigned char* pkdst = sb + US * tok_bytes;
+            unsigned char* scdst = pkdst + NW * US * kPkTile;
+            const int c = lane & 15;
+            if (c < 8 * NW) {
+                const size_t cgi = (size_t)min(sg0 * 8 + c, p.n16 - 1);   // a tail group re-reads the last one
+                // [column group][units of the stage][512 B] and [column group][blocks of the stage][16]
+                if (lane < 16)
+                    bulk_g2s(pkdst + (size_t)c * US * kUnitBytes, p.codes + q4_unit_offset(cgi, (size_t)u0, p.ku), units * kUnitBytes, &p_full[slot]);
+                else
+                    bulk_g2s(scdst + (size_t)c * sc_rows * 32, p.scales + q4_scale_row(cgi, blk0, p.nb), rows * 32, &p_full[slot]);
+            }
+            __syncwarp();
         }
     } else if (warp == kDeqWarps + 1) {
         // ===================== MMA issuer =====================
@@ -223,9 +234,9 @@ __global__ void __launch_bounds__(kTcThreads, 1) gemm_tc_kernel(const __grid_con
         const uint32_t tok_half = (uint32_t)(tok_bytes / 2);
         for (int i = 0; i < num_stages; ++i) {
             const int ps = i % P, os = i % O;
-            if (!mbar_wait(&p_full[ps], (i / P) & 1, abort_flag, p.status, STATUS_TMEM_TIMEOUT)) break;
+            if (!__all_sync(0xffffffffu, mbar_wait(&p_full[ps], (i / P) & 1, abort_flag, p.status, STATUS_TMEM_TIMEOUT))) break;
             if (lane == 0) SMEG_TL(5, i);
-            if (!mbar_wait(&o_full[os], (i / O) & 1, abort_flag, p.status, STATUS_TMEM_TIMEOUT)) break;
+            if (!__all_sync(0xffffffffu, mbar_wait(&o_full[os], (i / O) & 1, abort_flag, p.status, STATUS_TMEM_TIMEOUT))) break;
             if (lane == 0) SMEG_TL(6, i);
             tc_fence_after();
             const uint32_t tok_addr = smem_u32(ring_p + (size_t)ps * p_stride);
@@ -256,13 +267,15 @@ __global__ void __launch_bounds__(kTcThreads, 1) gemm_tc_kernel(const __grid_con
     } else {
         // ===================== dequant warps (0..7), then epilogue =====================
         const int g = lane >> 2, t = lane & 3;
+        const int wig = warp % deq_wpg;                        // warp within its group
         for (int i = 0; i < num_stages; ++i) {
+            if (deq_groups == 2 && (i & 1) != (warp >> 3)) continue;
             const int ps = i % P, os = i % O;
-            if (tid == 0) SMEG_TL(2, i);
-            if (i >= O && !mbar_wait(&o_empty[os], ((i / O) - 1) & 1, abort_flag, p.status, STATUS_TMEM_TIMEOUT)) break;
-            if (tid == 0) SMEG_TL(8, i);
-            if (!mbar_wait(&p_full[ps], (i / P) & 1, abort_flag, p.status, STATUS_TMEM_TIMEOUT)) break;
-            if (tid == 0) SMEG_TL(3, i);
+            if (wig == 0 && lane == 0) SMEG_TL(2, i);
+            if (i >= O && !__all_sync(0xffffffffu, mbar_wait(&o_empty[os], ((i / O) - 1) & 1, abort_flag, p.status, STATUS_TMEM_TIMEOUT))) break;
+            if (wig == 0 && lane == 0) SMEG_TL(8, i);
+            if (!__all_sync(0xffffffffu, mbar_wait(&p_full[ps], (i / P) & 1, abort_flag, p.status, STATUS_TMEM_TIMEOUT))) break;
+            if (wig == 0 && lane == 0) SMEG_TL(3, i);
             const int u0 = (st_begin + i) * US;
             const int units = min(US, p.ku - u0);
             const int d0 = u0 * kStageK;
@@ -270,39 +283,43 @@ __global__ void __launch_bounds__(kTcThreads, 1) gemm_tc_kernel(const __grid_con
             const unsigned char* pk = ring_p + (size_t)ps * p_stride + US * tok_bytes;
             const uint16_t* scs = reinterpret_cast<const uint16_t*>(pk + NW * US * kPkTile);
             unsigned char* ob = ring_o + (size_t)os * o_stride;
-            // unit index c = (w * US + uu) * 8 + column group
-            for (int c = warp; c < 8 * NW * US; c += kDeqWarps) {
-                const int cgl = c & 7, wu = c >> 3, uu = wu % US, w = wu / US;
+            // work item c = (w * 8 + column group) * US + uu
+            for (int c = wig; c < 8 * NW * US; c += deq_wpg) {
+                const int uu = c % US, wc = c / US, cgl = wc & 7, w = wc >> 3;
                 if (uu >= units) continue;
                 const int du = d0 + uu * kStageK;
                 const int ra = ((du + 8 * t) >> p.log2_block) - blk0, rb = ((du + 32 + 8 * t) >> p.log2_block) - blk0;
-                const uint4 wv = *reinterpret_cast<const uint4*>(pk + (size_t)wu * kPkTile + cgl * kUnitBytes + lane * 16);
-                // scale rows of this super-group: [block][8 column groups][16 slots]
-                dequant_unit_q4<BF16>(ob + wu * kWTile, cgl, wv, scs + w * sc_rows * 128 + cgl * 16, ra * 8, rb * 8, g, t);
+                const uint4 wv = *reinterpret_cast<const uint4*>(pk + (size_t)c * kUnitBytes + lane * 16);
+                dequant_unit_q4<BF16>(ob + (w * US + uu) * kWTile, cgl, wv, scs + (size_t)wc * sc_rows * 16, ra, rb, g, t);
             }
             fence_proxy_async();
             mbar_arrive(&o_full[os]);
             __syncwarp();
             if (lane == 0) mbar_arrive(&p_empty[ps]);
-            if (tid == 0) SMEG_TL(4, i);
+            if (wig == 0 && lane == 0) SMEG_TL(4, i);
         }
 
-        // ---- drain (warps 0..7): thread = weight column (TMEM lane), registers = tokens ----
-        if (warp < kDrainWarps) {
+        // ---- drain: thread = weight column (TMEM lane), registers = tokens.  A warp reaches the
+        // lane quarter warp % 4; the token columns are split over 4 (or 2) warps per quarter ----
+        const int ntok = p.ntok_pad;                           // a multiple of 32
+        const int parts = (ntok % 64 == 0) ? 4 : 2;            // every part is whole groups of 16 tokens
+        const int drain_threads = 32 * 4 * parts;
+        if (warp < 4 * parts) {
         if (num_stages > 0) mbar_wait(acc_full, 0, abort_flag, p.status, STATUS_TMEM_TIMEOUT);
         if (tid == 0) SMEG_TL(9, 0);
         tc_fence_after();
-        const int q = warp & 3, half = warp >> 2;              // lane quarter, token half
+        const int q = warp & 3, part = warp >> 2;              // lane quarter, token part
         const uint32_t lane_base = tmem_base + ((uint32_t)(32 * q) << 16);
         const EpNodeDev* nodes = p.ep.n_nodes <= kMaxInlineNodes ? ep_nodes : p.ep.ext;
-        const int ntok = p.ntok_pad;                           // a multiple of 32: both halves are whole 16-groups
-        const int j_begin = half * (ntok / 2), j_end = j_begin + ntok / 2;
+        const int j_begin = part * (ntok / parts), j_end = j_begin + ntok / parts;
         const int splits = (int)gridDim.z;
         const int tile_id = blockIdx.y * gridDim.x + blockIdx.x;
         float* ws_tile = p.ws + ((size_t)tile_id * splits) * (size_t)(NW * 128) * ntok;
 
         for (int w = 0; w < NW; ++w) {
             const int col = col0 + 128 * w + 32 * q + lane;
+            FastEp fe;
+            if (p.ep_fast) fast_ep_build<BF16>(nodes, p.ep.n_nodes, col, col < p.n, fe);
             for (int j0 = j_begin; j0 < j_end; j0 += 16) {
                 uint32_t r[16];
                 if (num_stages > 0) {
@@ -313,13 +330,25 @@ __global__ void __launch_bounds__(kTcThreads, 1) gemm_tc_kernel(const __grid_con
                     for (int j = 0; j < 16; ++j) r[j] = 0u;
                 }
                 if (splits == 1) {
+                    if (col < p.n) {
+                        if (p.c32) {
 #pragma unroll
-                    for (int j = 0; j < 16; ++j) {
-                        const int tok = tok0 + j0 + j;
-                        if (tok < p.m && col < p.n) {
-                            const float acc = __uint_as_float(r[j]);
-                            if (p.c32) p.c32[(size_t)tok * p.n + col] = acc;
-                            else p.c[(size_t)tok * p.n + col] = ep_store_nodes<BF16>(nodes, p.ep.n_nodes, acc, (size_t)tok, (size_t)col);
+                            for (int j = 0; j < 16; ++j)
+                                if (tok0 + j0 + j < p.m) p.c32[(size_t)(tok0 + j0 + j) * p.n + col] = __uint_as_float(r[j]);
+                        } else {
+                            uint16_t v[16];
+                            if (p.ep_fast) fast_ep_apply16<BF16>(fe, r, v);
+                            else if (p.ep.n_nodes == 0) {
+#pragma unroll
+                                for (int j = 0; j < 16; ++j) v[j] = f32_to_t<BF16>(__uint_as_float(r[j]));
+                            } else {
+#pragma unroll
+                                for (int j = 0; j < 16; ++j)
+                                    v[j] = (tok0 + j0 + j < p.m) ? ep_store_nodes<BF16>(nodes, p.ep.n_nodes, __uint_as_float(r[j]), (size_t)(tok0 + j0 + j), (size_t)col) : (uint16_t)0;
+                            }
+#pragma unroll
+                            for (int j = 0; j < 16; ++j)
+                                if (tok0 + j0 + j < p.m) p.c[(size_t)(tok0 + j0 + j) * p.n + col] = v[j];
                         }
                     }
                 } else {
@@ -335,24 +364,29 @@ __global__ void __launch_bounds__(kTcThreads, 1) gemm_tc_kernel(const __grid_con
         if (splits > 1) {
             // the last CTA of the tile to arrive adds the slices in slice order and stores
             __threadfence();
-            asm volatile("bar.sync 1, %0;" ::"n"(32 * kDrainWarps));
+            asm volatile("bar.sync 1, %0;" ::"r"(drain_threads));
             if (tid == 0) {
                 const int prev = atomicAdd(p.counters + tile_id, 1);
                 *last_flag = (prev == splits - 1) ? 1 : 0;
                 if (prev == splits - 1) p.counters[tile_id] = 0;      // ready for the next launch
             }
-            asm volatile("bar.sync 1, %0;" ::"n"(32 * kDrainWarps));
+            asm volatile("bar.sync 1, %0;" ::"r"(drain_threads));
             if (*last_flag) {
                 __threadfence();
                 for (int w = 0; w < NW; ++w) {
                     const int col = col0 + 128 * w + 32 * q + lane;
+                    if (col >= p.n) continue;
+                    FastEp fe;
+                    if (p.ep_fast) fast_ep_build<BF16>(nodes, p.ep.n_nodes, col, true, fe);
+#pragma unroll 1
                     for (int j = j_begin; j < j_end; ++j) {
                         const int tok = tok0 + j;
-                        if (tok >= p.m || col >= p.n) continue;
+                        if (tok >= p.m) continue;
                         float acc = 0.0f;
                         for (int z = 0; z < splits; ++z)
                             acc += __ldcg(ws_tile + ((size_t)z * ntok + j) * (NW * 128) + (128 * w + 32 * q + lane));
                         if (p.c32) p.c32[(size_t)tok * p.n + col] = acc;
+                        else if (p.ep_fast) p.c[(size_t)tok * p.n + col] = fast_ep_store<BF16>(fe, acc);
                         else p.c[(size_t)tok * p.n + col] = ep_store_nodes<BF16>(nodes, p.ep.n_nodes, acc, (size_t)tok, (size_t)col);
                     }
                 }
@@ -420,6 +454,7 @@ void gemm_tc_plan(GemmTcArgs& a, int sm_count, dim3* grid, size_t* smem, size_t*
     const int tile = (a.m + tiles - 1) / tiles;
     const int pad = (tile + 31) / 32 * 32;
     a.ntok_tile = pad;
+    a.ep_fast = fast_ep_eligible(a.ep) ? 1 : 0;
     a.ntok_pad = pad;
     a.nmma = pad > 256 ? 2 : 1;
     a.ntok_box = pad / a.nmma;

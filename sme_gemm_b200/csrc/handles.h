@@ -3,6 +3,9 @@
 #pragma once
 #include <stdint.h>
 
+#include <atomic>
+#include <mutex>
+
 #include "pack.h"
 
 struct smeg_q4 {
@@ -19,6 +22,9 @@ struct smeg_lowbit {
     unsigned char* codes = nullptr;
     uint16_t* scales = nullptr;
     size_t code_bytes = 0, scale_elems = 0;
+    // 4-bit twin for the f16 tensor-core path, built on the first such call (transcode.cu)
+    mutable std::mutex twin_lock;
+    mutable std::atomic<smeg_q4*> twin{nullptr};
 };
 struct smeg_mlp {
     const smeg_q4* gate_up;

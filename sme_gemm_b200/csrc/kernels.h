@@ -63,6 +63,7 @@ struct GemmTcArgs {
     int m, n, k;
     int n16, ku, nb, log2_block;
     int ntok_tile, ntok_pad, ntok_box, nmma, tmem_cols, sc_rows;       // planner-filled
+    int ep_fast;                  // the graph runs as a per-thread FastEp (see epilogue.cuh)
     int np, no, nw, us;           // ring depths (packed / operand), accumulator sets, units per stage
     float* ws;                    // split-depth workspace [tile][slice][token][column]
     int* counters;                // one per output tile, zero between launches
@@ -72,6 +73,21 @@ struct GemmTcArgs {
 bool gemm_tc_supported(int wkind, int m, int k, int log2_block, const void* a);
 void gemm_tc_plan(GemmTcArgs& a, int sm_count, dim3* grid, size_t* smem, size_t* ws_floats, size_t* n_counters);
 cudaError_t gemm_tc_launch(GemmTcArgs a, int bf16, dim3 grid, size_t smem, cudaStream_t stream);
+
+// ---- 2-bit / 1-bit weights -> 4-bit plane for the tensor-core GEMM (transcode.cu) ----
+struct LowbitToQ4Args {
+    const unsigned char* src;       // packed 2-bit / 1-bit units
+    const uint16_t* src_scales;     // [n16_src][nb_src][16]
+    unsigned char* dst;             // packed 4-bit units [n16 (padded)][ku4][512]
+    uint16_t* dst_scales;           // [n16 (padded)][nb4][16]
+    size_t n, k;
+    size_t ku_src, n16_src, nb_src; // source units along K, column groups, scale rows
+    size_t ku4, nb4;                // 4-bit plane: units along K, scale rows
+    size_t dst_words, dst_scale_elems;
+    int bits;                       // 2 or 1
+    uint32_t lut;                   // 2-bit codebook, byte c = value of code c
+};
+cudaError_t lowbit_to_q4_launch(const LowbitToQ4Args& a, cudaStream_t s);
 
 // ---- element-wise model ops (elementwise.cu) ----
 cudaError_t glu_launch(uint16_t* out, const uint16_t* both, size_t m, size_t n, uint32_t act, cudaStream_t s);

@@ -30,12 +30,11 @@
 //       d = 256*u + 32*s + 8*t + {0..7}
 //   column c0 + 8*(b & 1), depth d + 4*((b >> 1) & 1) + (b >> 3)
 //
-// Q4 units are stored [super-group of 8 column groups = 128 columns][unit along K][8 groups][512 B],
-// so the 128 columns x 64 depths a tensor-core CTA consumes per stage are one contiguous 4 KB run
-// (and consecutive stages follow each other); Q2 / Q1 units are stored [column group][unit][512 B].
+// Units are stored [column group][unit along K][512 B]: everything one column group needs is one
+// contiguous run along K, so a CTA streams it with a few large bulk copies.  Q4 pads the column
+// groups to a multiple of 8 (128 columns, the tensor-core kernel's tile).
 //
-// Scales: f16 bit patterns in rows of 16 slots per (column group, K-block), stored
-// [super-group][K-block][8 groups][16] for Q4 and [column group][K-block][16] for Q2 / Q1; column
+// Scales: f16 bit patterns in rows of 16 slots, stored [column group][K-block][16]; column
 // c of the group sits in slot 2*(c % 8) + c / 8, so the two columns a lane holds
 // (g and g + 8) are one aligned 32-bit word.
 // Padding columns / depths hold code 0 (Q4), and padded scales are 0; padded
@@ -51,6 +50,12 @@ constexpr int kQ4UnitDepth = 64;
 constexpr int kQ2UnitDepth = 128;
 constexpr int kQ1UnitDepth = 256;
 
+#if defined(__CUDACC__)
+#define SMEG_HD __host__ __device__
+#else
+#define SMEG_HD
+#endif
+
 inline size_t div_up(size_t a, size_t b) { return (a + b - 1) / b; }
 
 // Slot of column c (0..15) of a column group inside a 16-entry scale row.
@@ -63,16 +68,16 @@ inline int scale_slot(int c) { return 2 * (c & 7) + (c >> 3); }
 #if defined(__CUDACC__)
 __host__ __device__
 #endif
-inline size_t q4_scale_row(size_t cg, size_t blk, size_t nb) { return (((cg / 8) * nb + blk) * 8 + cg % 8) * 16; }
+inline size_t q4_scale_row(size_t cg, size_t blk, size_t nb) { return (cg * nb + blk) * 16; }
 #if defined(__CUDACC__)
 __host__ __device__
 #endif
-inline size_t q4_unit_offset(size_t cg, size_t u, size_t k_units) { return (((cg / 8) * k_units + u) * 8 + cg % 8) * 512; }
+inline size_t q4_unit_offset(size_t cg, size_t u, size_t k_units) { return (cg * k_units + u) * 512; }
 
 // --- Q4 ---
 // Position of (depth d, column j) inside the packed code array: byte offset of
 // the 32-bit word and the nibble index within it.
-inline void q4_locate(size_t d, size_t j, size_t k_units, size_t* word_byte, int* nibble) {
+SMEG_HD inline void q4_locate(size_t d, size_t j, size_t k_units, size_t* word_byte, int* nibble) {
     size_t cg = j / 16, c = j % 16, u = d / 64, r = d % 64;
     int g = (int)(c % 8), hi_col = (int)(c / 8);
     int half = (int)(r / 32), rr = (int)(r % 32);
@@ -81,12 +86,12 @@ inline void q4_locate(size_t d, size_t j, size_t k_units, size_t* word_byte, int
     int lane = 4 * g + t;
     // e: 0,1 -> low positions (nibble 0/4 or 2/6); 2,3 -> (1/5 or 3/7)
     int nib = (e & 1) * 4 + (e >> 1) + 2 * hi_col;
-    *word_byte = ((((cg / 8) * k_units + u) * 8 + cg % 8) * 32 + (size_t)lane) * 16 + (size_t)ks * 4;
+    *word_byte = ((cg * k_units + u) * 32 + (size_t)lane) * 16 + (size_t)ks * 4;
     *nibble = nib;
 }
 
 // --- Q2 ---
-inline void q2_locate(size_t d, size_t j, size_t k_units, size_t* word_byte, int* field) {
+SMEG_HD inline void q2_locate(size_t d, size_t j, size_t k_units, size_t* word_byte, int* field) {
     size_t cg = j / 16, c = j % 16, u = d / 128, r = d % 128;
     int g = (int)(c % 8), hi_col = (int)(c / 8);
     int ks = (int)(r / 32), rr = (int)(r % 32);
@@ -97,7 +102,7 @@ inline void q2_locate(size_t d, size_t j, size_t k_units, size_t* word_byte, int
 }
 
 // --- Q1 ---
-inline void q1_locate(size_t d, size_t j, size_t k_units, size_t* word_byte, int* bit) {
+SMEG_HD inline void q1_locate(size_t d, size_t j, size_t k_units, size_t* word_byte, int* bit) {
     size_t cg = j / 16, c = j % 16, u = d / 256, r = d % 256;
     int g = (int)(c % 8), hi_col = (int)(c / 8);
     int s = (int)(r / 32), rr = (int)(r % 32);

@@ -173,13 +173,8 @@ __global__ void __launch_bounds__(kThreads) q4_gemv_kernel(Q4GemvArgs p) {
                 unsigned char* sbase = stages + (size_t)slot * stage_bytes;
                 for (int c = 0; c < ncg; ++c) {
                     const size_t cgi = cg0 + c;
-                    // units of one column group are 4 KB apart (128-column super-group layout)
-                    for (int u = 0; u < units; ++u)
-                        bulk_g2s(sbase + c * code_bytes + u * kUnitBytes,
-                                 p.codes + q4_unit_offset(cgi, (size_t)st * kConsumerWarps + u, p.k64), kUnitBytes, &full[slot]);
-                    for (int r = 0; r < rows; ++r)
-                        bulk_g2s(sbase + CG * code_bytes + c * scale_bytes + r * 32, p.scales + q4_scale_row(cgi, blk0 + r, p.nb), 32,
-                                 &full[slot]);
+                    bulk_g2s(sbase + c * code_bytes, p.codes + q4_unit_offset(cgi, (size_t)st * kConsumerWarps, p.k64), cb, &full[slot]);
+                    bulk_g2s(sbase + CG * code_bytes + c * scale_bytes, p.scales + q4_scale_row(cgi, blk0, p.nb), sb, &full[slot]);
                 }
             }
         }

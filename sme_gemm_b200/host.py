@@ -533,7 +533,7 @@ def matmul_q4_bf16_ep(a, w: Q4Weights, c, m: int, ep: Epilogue) -> None:
     _run_q4(a, w, c, m, ep, True)
 
 
-def _run_lowbit(a, w: _LowbitWeights, c, m: int, ep: Epilogue | None) -> None:
+def _run_lowbit(a, w: _LowbitWeights, c, m: int, ep: Epilogue | None, mopa: bool = False) -> None:
     n, k = w.n(), w.k()
     _check_io(a, c, m, n, k)
     if ep is not None:
@@ -546,14 +546,15 @@ def _run_lowbit(a, w: _LowbitWeights, c, m: int, ep: Epilogue | None) -> None:
         assert a.is_cuda and c.is_cuda and a.is_contiguous() and c.is_contiguous()
         assert a.dtype == torch.float16 and c.dtype == torch.float16
         desc, keep = ep._desc(True) if ep is not None else (None, [])
-        check("smeg_matmul_lowbit_dev",
-              L.smeg_matmul_lowbit_dev(w._h, _ptr(a), _ptr(c), m, C.byref(desc) if desc else None, _stream()))
+        name = "smeg_matmul_lowbit_f16_dev" if mopa else "smeg_matmul_lowbit_dev"
+        check(name, getattr(L, name)(w._h, _ptr(a), _ptr(c), m, C.byref(desc) if desc else None, _stream()))
         del keep
     else:
         ab = _np_bits(a, "a")
         assert isinstance(c, np.ndarray) and c.flags.c_contiguous and c.dtype in (np.float16, np.uint16)
         desc, keep = ep._desc(False) if ep is not None else (None, [])
-        check("smeg_matmul_lowbit", L.smeg_matmul_lowbit(w._h, _ptr(ab), _ptr(c), m, C.byref(desc) if desc else None))
+        name = "smeg_matmul_lowbit_f16" if mopa else "smeg_matmul_lowbit"
+        check(name, getattr(L, name)(w._h, _ptr(ab), _ptr(c), m, C.byref(desc) if desc else None))
         del keep
 
 
@@ -575,6 +576,26 @@ def matmul_q1(a, w: Q1Weights, c, m: int) -> None:
 def matmul_q1_ep(a, w: Q1Weights, c, m: int, ep: Epilogue) -> None:
     """matmul_q1_ep, src/kernels/lowbit/matmul.rs:79-81."""
     _run_lowbit(a, w, c, m, ep)
+
+
+def matmul_q2_mopa(a, w: Q2Weights, c, m: int) -> None:
+    """matmul_q2_mopa, src/kernels/lowbit/matmul.rs:100-102: f16 activations, no int8 step."""
+    _run_lowbit(a, w, c, m, None, mopa=True)
+
+
+def matmul_q2_mopa_ep(a, w: Q2Weights, c, m: int, ep: Epilogue) -> None:
+    """matmul_q2_mopa_ep, src/kernels/lowbit/matmul.rs:108-116."""
+    _run_lowbit(a, w, c, m, ep, mopa=True)
+
+
+def matmul_q1_mopa(a, w: Q1Weights, c, m: int) -> None:
+    """matmul_q1_mopa, src/kernels/lowbit/matmul.rs:123-125."""
+    _run_lowbit(a, w, c, m, None, mopa=True)
+
+
+def matmul_q1_mopa_ep(a, w: Q1Weights, c, m: int, ep: Epilogue) -> None:
+    """matmul_q1_mopa_ep, src/kernels/lowbit/matmul.rs:131-139."""
+    _run_lowbit(a, w, c, m, ep, mopa=True)
 
 
 def matmul_lowbit_debug(a, w: _LowbitWeights, m: int):

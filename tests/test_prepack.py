@@ -118,24 +118,24 @@ def test_q4_unit_layout_is_the_documented_mma_fragment_order():
     quants = (flat[0::2] | (flat[1::2] << 4)).astype(np.uint8)
     scales = np.arange(n * (k // block), dtype=np.uint16)
     codes, sc = host_pack(4, quants, 0, scales, n, k, block)
-    # [128-column super-group][unit][8 column groups][32 lanes][4 words]; n = 32 pads to one super-group
-    words = codes.view(np.uint32).reshape(1, k // 64, 8, 32, 4)
-    assert (codes.view(np.uint32).reshape(1, k // 64, 8, 128)[:, :, 2:] == 0x88888888).all()   # padding = code 0
+    # [column group][unit][32 lanes][4 words]; the 2 real column groups are padded to 8 (128 columns)
+    words = codes.view(np.uint32).reshape(8, k // 64, 32, 4)
+    assert (words[2:] == 0x88888888).all()   # padding = code 0
     for cg in range(n // 16):
         for u in range(k // 64):
             for lane in range(32):
                 g, t = lane >> 2, lane & 3
                 for ks in range(4):
-                    w = int(words[0, u, cg, lane, ks])
+                    w = int(words[cg, u, lane, ks])
                     d = 64 * u + 32 * (ks >> 1) + 8 * t + 4 * (ks & 1)
                     nib = [(w >> (4 * i)) & 0xF for i in range(8)]
                     got_lo = [nib[0] - 8, nib[4] - 8, nib[1] - 8, nib[5] - 8]
                     got_hi = [nib[2] - 8, nib[6] - 8, nib[3] - 8, nib[7] - 8]
                     assert got_lo == list(code[d:d + 4, 16 * cg + g])
                     assert got_hi == list(code[d:d + 4, 16 * cg + g + 8])
-    # scales: [super-group][block][8 column groups][16 slots], column c in slot 2*(c % 8) + c // 8
-    assert sc.reshape(1, k // block, 8, 16)[0, 2, 1, 2 * 5] == scales[(16 + 5) * (k // block) + 2]
-    assert sc.reshape(1, k // block, 8, 16)[0, 1, 0, 2 * 3 + 1] == scales[11 * (k // block) + 1]
+    # scales: [column group][block][16 slots], column c in slot 2*(c % 8) + c // 8
+    assert sc.reshape(8, k // block, 16)[1, 2, 2 * 5] == scales[(16 + 5) * (k // block) + 2]
+    assert sc.reshape(8, k // block, 16)[0, 1, 2 * 3 + 1] == scales[11 * (k // block) + 1]
 
 
 def test_q2_q1_unit_layouts_are_the_documented_fragment_order():
