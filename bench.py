@@ -38,6 +38,9 @@ HIDDEN, INTER, BLOCK = 4096, 14336, 32
 L2_BYTES = 126 * 1024 * 1024
 
 
+GATE_UP_DRAM_BYTES_M256 = 71.64e6   # dram__bytes_read.sum + dram__bytes_write.sum, one launch
+
+
 def measured_peaks():
     path = os.path.join(ROOT, "MEASURED_PEAKS.json")
     if os.path.exists(path):
@@ -185,66 +188,110 @@ def graph_time_us(torch, fn, n_items, reps=20):
     return e0.elapsed_time(e1) * 1e3 / (reps * n_items)
 
 
-def kernel_configs(torch, sg, orc, peaks):
-    """BASELINE.json configs[0..3] as single kernels on one GPU (device-resident, graph replay)."""
-    out = []
+def kernel_cases(torch, sg, orc):
+    """BASELINE.json configs[0..3] as single device-resident kernel calls.  Each entry builds
+    lazily and returns (fn(i), number of rotating weight sets, description dict)."""
     rng = np.random.default_rng(7)
-    hbm = peaks["hbm_gbs"]
+    k = 4096
 
     def sets_for(bytes_per_set):
         return max(2, int(np.ceil(2.2 * L2_BYTES / bytes_per_set)))
 
-    # configs[0]: Q4 decode GEMV 1 x 4096 x 4096
-    n = k = 4096
-    w = (rng.standard_normal(n * k) * 0.02).astype(np.float32)
-    q, s, _ = orc.q4_quantize(w, 0, n, k)
-    ws = [sg.Q4Weights.new(q, s, n, k) for _ in range(sets_for(9.4e6))]
-    a = torch.randn(1, k, device="cuda", dtype=torch.float16)
-    c = torch.zeros(1, n, device="cuda", dtype=torch.float16)
-    us = graph_time_us(torch, lambda i: sg.matmul_q4(a, ws[i], c, 1), len(ws))
-    out.append({"config": "q4_gemv_1x4096x4096", "us": us, "value": 9453568 / us / 1e3, "unit": "GB/s",
-                "frac_of_measured_hbm": 9453568 / us / 1e3 / hbm, "algorithmic_bytes": 9453568})
-    del ws
-    # configs[1]: ternary 2-bit GEMV 1 x 4096 x 11008, block 256
-    n = 11008
-    two = rng.integers(0, 3, k * n).astype(np.uint8)
-    codes = (two[0::4] | (two[1::4] << 2) | (two[2::4] << 4) | (two[3::4] << 6)).astype(np.uint8)
-    sc = orc.f32_to_f16_bits(rng.uniform(0.01, 0.05, n * (k // 256)).astype(np.float32))
-    ws = [sg.Q2Weights.new(codes, sc, n, k) for _ in range(sets_for(11.6e6))]
-    c = torch.zeros(1, n, device="cuda", dtype=torch.float16)
-    us = graph_time_us(torch, lambda i: sg.matmul_q2(a, ws[i], c, 1), len(ws))
-    out.append({"config": "q2_ternary_gemv_1x4096x11008", "us": us, "value": 11654656 / us / 1e3, "unit": "GB/s",
-                "frac_of_measured_hbm": 11654656 / us / 1e3 / hbm, "algorithmic_bytes": 11654656})
-    del ws
-    # configs[2]: 1-bit GEMV batch 8 x 4096 x 14336, block 128, mul_col.add_col
-    n = 14336
-    signs = rng.integers(0, 256, k * n // 8).astype(np.uint8)
-    sc = orc.f32_to_f16_bits(rng.uniform(0.005, 0.03, n * (k // 128)).astype(np.float32))
-    ws = [sg.Q1Weights.new(signs, sc, sg.WeightLayout.OutIn, n, k, 128) for _ in range(sets_for(8.6e6))]
-    a8 = torch.randn(8, k, device="cuda", dtype=torch.float16)
-    c8 = torch.zeros(8, n, device="cuda", dtype=torch.float16)
-    sv = torch.empty(n, device="cuda", dtype=torch.float16).uniform_(0.5, 1.5)
-    bv = torch.randn(n, device="cuda", dtype=torch.float16) * 0.1
-    ep = sg.Epilogue().mul_col(sv).add_col(bv)
-    us = graph_time_us(torch, lambda i: sg.matmul_q1_ep(a8, ws[i], c8, 8, ep), len(ws))
-    out.append({"config": "q1_gemv_8x4096x14336_mulcol_addcol", "us": us, "value": 8609792 / us / 1e3, "unit": "GB/s",
-                "frac_of_measured_hbm": 8609792 / us / 1e3 / hbm, "algorithmic_bytes": 8609792})
-    del ws
-    # configs[3]: Q4 prefill GEMM bf16 512 x 4096 x 14336 + add_col.silu.clamp
-    w = (rng.standard_normal(n * k) * 0.02).astype(np.float32)
-    q, s, _ = orc.q4_quantize(w, 0, n, k)
-    ws = [sg.Q4Weights.new(q, s, n, k) for _ in range(sets_for(33e6))]
-    ab = torch.randn(512, k, device="cuda", dtype=torch.bfloat16)
-    cb = torch.zeros(512, n, device="cuda", dtype=torch.bfloat16)
-    bias = (torch.randn(n, device="cuda") * 0.1).to(torch.bfloat16)
-    ep4 = sg.Epilogue("bf16").add_col(bias).silu().clamp(-6.0, 6.0)
-    us = graph_time_us(torch, lambda i: sg.matmul_q4_bf16_ep(ab, ws[i], cb, 512, ep4), len(ws), reps=10)
-    flops = 2.0 * 512 * k * n
-    out.append({"config": "q4_prefill_gemm_bf16_512x4096x14336_addcol_silu_clamp", "us": us, "value": flops / us / 1e6,
-                "unit": "TFLOP/s", "frac_of_measured_bf16_burst": flops / us / 1e6 / peaks["bf16_tflops"],
-                "frac_of_nominal_2250": flops / us / 1e6 / 2250.0, "algorithmic_flops": flops})
-    del ws
+    def q4_gemv():
+        n = 4096
+        w = (rng.standard_normal(n * k) * 0.02).astype(np.float32)
+        q, s, _ = orc.q4_quantize(w, 0, n, k)
+        ws = [sg.Q4Weights.new(q, s, n, k) for _ in range(sets_for(9.4e6))]
+        a = torch.randn(1, k, device="cuda", dtype=torch.float16)
+        c = torch.zeros(1, n, device="cuda", dtype=torch.float16)
+        return (lambda i: sg.matmul_q4(a, ws[i], c, 1)), len(ws), {"config": "q4_gemv_1x4096x4096", "bytes": 9453568}
+
+    def q2_gemv():
+        n = 11008
+        two = rng.integers(0, 3, k * n).astype(np.uint8)
+        codes = (two[0::4] | (two[1::4] << 2) | (two[2::4] << 4) | (two[3::4] << 6)).astype(np.uint8)
+        sc = orc.f32_to_f16_bits(rng.uniform(0.01, 0.05, n * (k // 256)).astype(np.float32))
+        ws = [sg.Q2Weights.new(codes, sc, n, k) for _ in range(sets_for(11.6e6))]
+        a = torch.randn(1, k, device="cuda", dtype=torch.float16)
+        c = torch.zeros(1, n, device="cuda", dtype=torch.float16)
+        return (lambda i: sg.matmul_q2(a, ws[i], c, 1)), len(ws), {"config": "q2_ternary_gemv_1x4096x11008", "bytes": 11654656}
+
+    def q1_gemv():
+        n = 14336
+        signs = rng.integers(0, 256, k * n // 8).astype(np.uint8)
+        sc = orc.f32_to_f16_bits(rng.uniform(0.005, 0.03, n * (k // 128)).astype(np.float32))
+        ws = [sg.Q1Weights.new(signs, sc, sg.WeightLayout.OutIn, n, k, 128) for _ in range(sets_for(8.6e6))]
+        a8 = torch.randn(8, k, device="cuda", dtype=torch.float16)
+        c8 = torch.zeros(8, n, device="cuda", dtype=torch.float16)
+        sv = torch.empty(n, device="cuda", dtype=torch.float16).uniform_(0.5, 1.5)
+        bv = torch.randn(n, device="cuda", dtype=torch.float16) * 0.1
+        ep = sg.Epilogue().mul_col(sv).add_col(bv)
+        return (lambda i: sg.matmul_q1_ep(a8, ws[i], c8, 8, ep)), len(ws), {"config": "q1_gemv_8x4096x14336_mulcol_addcol", "bytes": 8609792}
+
+    def q4_prefill():
+        n = 14336
+        w = (rng.standard_normal(n * k) * 0.02).astype(np.float32)
+        q, s, _ = orc.q4_quantize(w, 0, n, k)
+        ws = [sg.Q4Weights.new(q, s, n, k) for _ in range(sets_for(33e6))]
+        ab = torch.randn(512, k, device="cuda", dtype=torch.bfloat16)
+        cb = torch.zeros(512, n, device="cuda", dtype=torch.bfloat16)
+        bias = (torch.randn(n, device="cuda") * 0.1).to(torch.bfloat16)
+        ep4 = sg.Epilogue("bf16").add_col(bias).silu().clamp(-6.0, 6.0)
+        return ((lambda i: sg.matmul_q4_bf16_ep(ab, ws[i], cb, 512, ep4)), len(ws),
+                {"config": "q4_prefill_gemm_bf16_512x4096x14336_addcol_silu_clamp", "flops": 2.0 * 512 * k * n})
+
+    return {"q4_gemv": q4_gemv, "q2_gemv": q2_gemv, "q1_gemv": q1_gemv, "q4_prefill": q4_prefill}
+
+
+def kernel_configs(torch, sg, orc, peaks):
+    """The four single-kernel configs on one GPU, timed by CUDA-graph replay."""
+    out = []
+    for name, build in kernel_cases(torch, sg, orc).items():
+        fn, nsets, d = build()
+        us = graph_time_us(torch, fn, nsets, reps=10 if "flops" in d else 20)
+        if "bytes" in d:
+            gbs = d["bytes"] / us / 1e3
+            out.append({"config": d["config"], "us": us, "value": gbs, "unit": "GB/s", "frac_of_measured_hbm": gbs / peaks["hbm_gbs"],
+                        "frac_of_nominal_8000": gbs / 8000.0, "algorithmic_bytes": d["bytes"]})
+        else:
+            tf = d["flops"] / us / 1e6
+            out.append({"config": d["config"], "us": us, "value": tf, "unit": "TFLOP/s",
+                        "frac_of_measured_bf16_burst": tf / peaks["bf16_tflops"], "frac_of_nominal_2250": tf / 2250.0,
+                        "algorithmic_flops": d["flops"]})
+        del fn
     return out
+
+
+def run_profile_case(args):
+    """A few plain launches of one kernel, for a profiler to capture (`--profile-case NAME`):
+    three untimed launches, then three more.  Prints no benchmark number."""
+    import torch
+    import oracle as orc          # input generation only
+    import sme_gemm_b200 as sg
+    torch.cuda.set_device(0)
+    name = args.profile_case
+    if name in ("mlp_gate_up", "mlp_down"):
+        m = args.m
+        wg, wu, wd = mlp_weights_f32(5)
+        if name == "mlp_gate_up":
+            both = sg.interleave_gate_up(wg, wu, sg.WeightLayout.OutIn, INTER, HIDDEN)
+            q, s, _ = orc_quant(sg, both, 1, 2 * INTER, HIDDEN)
+            n, k = 2 * INTER, HIDDEN
+        else:
+            q, s, _ = orc_quant(sg, wd, 0, HIDDEN, INTER)
+            n, k = HIDDEN, INTER
+        ws = [sg.Q4Weights.new(q, s, n, k) for _ in range(3)]
+        a = torch.randn(m, k, device="cuda", dtype=torch.float16)
+        c = torch.zeros(m, n, device="cuda", dtype=torch.float16)
+        fn, nsets = (lambda i: sg.matmul_q4(a, ws[i], c, m)), 3
+    else:
+        fn, nsets, _ = kernel_cases(torch, sg, orc)[name]()
+    for i in range(6):
+        fn(i % nsets)
+    torch.cuda.synchronize()
+    if sg.last_status() != 0:
+        raise SystemExit("a kernel abandoned a bounded wait")
+    print(json.dumps({"profile_case": name, "launches": 6}), flush=True)
 
 
 def run_ours(args):
@@ -323,11 +370,26 @@ def run_ours(args):
     sampler = ClockSampler(local) if rank == 0 else None
     if sampler:
         sampler.start()
-        t_end = time.perf_counter() + 1.0      # at least a second of the same steps before timing
-        while time.perf_counter() < t_end:
-            for i in range(8):
-                step(i)
-            torch.cuda.synchronize()
+
+    def preload(seconds):
+        """The same steps for about `seconds`, so that the clock samples are taken under load.
+        Every rank runs the same number of steps (rank 0's estimate), as the steps hold collectives."""
+        for i in range(4):
+            step(i)
+        sync()
+        t0 = time.perf_counter()
+        for i in range(8):
+            step(i)
+        sync()
+        per = max((time.perf_counter() - t0) / 8, 1e-6)
+        count = torch.tensor([int(min(20000, max(8, seconds / per)))], device="cuda", dtype=torch.int64)
+        if dist:
+            dist.broadcast(count, 0)
+        for i in range(int(count.item())):
+            step(i)
+        sync()
+
+    preload(1.0)
     for i in range(args.warmup):
         step(i)
     ms = timed(step, args.steps)
@@ -344,12 +406,7 @@ def run_ours(args):
         e2e_step(i)
     ms_e2e = timed(e2e_step, args.steps)
     e2e_value = m * args.steps / (ms_e2e * 1e-3)
-    if sampler:
-        t_end = time.perf_counter() + 0.5
-        while time.perf_counter() < t_end:
-            for i in range(8):
-                step(i)
-            torch.cuda.synchronize()
+    preload(0.5)
     clocks = sampler.stop() if sampler else None
 
     status = sg.last_status()
@@ -367,9 +424,14 @@ def run_ours(args):
     us_gu = graph_time_us(torch, lambda i: sg.matmul_q4(x, gu[i], both_out, m), nsets, reps=10)
     flops_gu = 2.0 * m * HIDDEN * 2 * fl
     ach = flops_gu / us_gu / 1e6
+    # DRAM bytes per launch from the profiler capture summarised in
+    # profiles/gemm_tc_kernel_mlp_gate_up_m256.md (M=256, whole matrix); a rank's shard moves its
+    # share of the columns, and traffic is proportional to them
+    traffic = GATE_UP_DRAM_BYTES_M256 / world if m == 256 else None
     roofline = {"kernel": "gemm_tc_kernel (gate/up projection, this rank's shard)", "bound": "tensor", "achieved": ach,
                 "peak": peaks["bf16_tflops"], "unit": "TFLOP/s", "frac": ach / peaks["bf16_tflops"],
-                "peak_source": peaks["source"] + " (burst: kernel timed alone)", "us_per_launch": us_gu, "traffic": None}
+                "peak_source": peaks["source"] + " (burst: kernel timed alone)", "us_per_launch": us_gu, "traffic": traffic,
+                "algorithmic_flops": flops_gu}
 
     # ---- CPU baseline beside it: the oracle block on a bounded row sample, all host cores ----
     cores = orc.max_threads()
@@ -423,10 +485,16 @@ def main():
     ap.add_argument("--steps", type=int, default=20)
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    ap.add_argument("--m", type=int, default=256, help="tokens per step (BASELINE.json: 1 or 256)")
+    ap.add_argument("--tokens", dest="m", type=int, default=256, help="tokens per step (BASELINE.json: 1 or 256)")
     ap.add_argument("--ref-rows", type=int, default=4, help="rows of the batch the CPU arm computes per step")
     ap.add_argument("--no-kernels", action="store_true", help="skip the single-kernel configs")
+    ap.add_argument("--profile-case", default=None,
+                    choices=["q4_gemv", "q2_gemv", "q1_gemv", "q4_prefill", "mlp_gate_up", "mlp_down"],
+                    help="run six plain launches of one kernel and exit (for profiler captures)")
     args = ap.parse_args()
+    if args.profile_case:
+        run_profile_case(args)
+        return
     if args.warmup < 3:
         args.warmup = 3
     if args.impl == "reference":

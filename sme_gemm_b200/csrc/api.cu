@@ -581,26 +581,40 @@ static int lowbit_dev(const smeg_lowbit* w, const uint16_t* a, uint16_t* c, size
     DeviceState* ds = dev_state();
     if (!ds) return -5;
     const size_t kq = w->d.ku * (size_t)w->d.unit_depth, nb = w->d.nb;
-    // scratch: int8 activations, their per-block scales and (1-bit) sums
-    const size_t q_bytes = (m * kq + 255) / 256 * 256, sa_bytes = (m * nb * 4 + 255) / 256 * 256;
-    char* ws = nullptr;
-    if (cudaMallocAsync(&ws, q_bytes + 2 * sa_bytes + 256, stream) != cudaSuccess) return -2;
-    ActQuantArgs aq;
-    aq.a = a; aq.q = (int8_t*)ws; aq.sa = (float*)(ws + q_bytes);
-    aq.qsum = w->bits == 1 ? (int32_t*)(ws + q_bytes + sa_bytes) : nullptr;
-    aq.m = (int)m; aq.k = (int)k; aq.kq = (int)kq; aq.nbq = (int)nb; aq.log2_block = w->d.log2_block;
     LowbitGemvArgs g;
     memset(&g, 0, sizeof(g));
     EpNodeDev* ext = nullptr;
     int rc = make_ep(ep, n, &g.ep, stream, &ext);
+    if (rc) { if (ext) cudaFreeAsync(ext, stream); return rc; }
+    g.codes = w->codes; g.scales = w->scales; g.c = c;
+    g.sums_out = sums_out;
+    g.m = (int)m; g.n = (int)n; g.k = (int)k; g.kq = (int)kq;
+    g.n16 = (int)w->d.n16; g.ku = (int)w->d.ku; g.nb = (int)nb; g.nb_real = (int)w->d.nb_real;
+    g.log2_block = w->d.log2_block; g.lut = w->lut; g.status = ds->status;
     cudaError_t e = cudaSuccess;
-    if (!rc) {
+    char* ws = nullptr;
+    // up to four rows the kernel stages and quantises the activations itself (one launch, no scratch);
+    // above that every CTA would repeat too much work, and a separate pass over the rows is faster
+    static const size_t fuse_max_rows = []() { const char* e = getenv("SMEG_LB_FUSE_MAX_ROWS"); return e ? (size_t)atoi(e) : (size_t)4; }();
+    if (k > 0 && m <= fuse_max_rows && (k % 8 == 0) && ((uintptr_t)a % 16 == 0) && lowbit_gemv_fuses_quant(g, w->bits, ds->sm_count)) {
+        // the kernel quantises the activation rows itself: one launch, no scratch
+        g.a = a;
+        g.a_vec_ok = 1;
+        g.q_out = q_out; g.sa_out = sa_out;
+        e = lowbit_gemv_launch(g, w->bits, ds->sm_count, stream);
+    } else {
+        // blocks longer than the kernel's K chunk: quantise first, into stream-ordered scratch
+        const size_t q_bytes = (m * kq + 255) / 256 * 256, sa_bytes = (m * nb * 4 + 255) / 256 * 256;
+        if (cudaMallocAsync(&ws, q_bytes + 2 * sa_bytes + 256, stream) != cudaSuccess) {
+            if (ext) cudaFreeAsync(ext, stream);
+            return -2;
+        }
+        ActQuantArgs aq;
+        aq.a = a; aq.q = (int8_t*)ws; aq.sa = (float*)(ws + q_bytes);
+        aq.qsum = w->bits == 1 ? (int32_t*)(ws + q_bytes + sa_bytes) : nullptr;
+        aq.m = (int)m; aq.k = (int)k; aq.kq = (int)kq; aq.nbq = (int)nb; aq.log2_block = w->d.log2_block;
         e = act_quant_launch(aq, stream);
-        g.codes = w->codes; g.scales = w->scales; g.q = aq.q; g.sa = aq.sa; g.qsum = aq.qsum; g.c = c;
-        g.sums_out = sums_out;
-        g.m = (int)m; g.n = (int)n; g.k = (int)k; g.kq = (int)kq;
-        g.n16 = (int)w->d.n16; g.ku = (int)w->d.ku; g.nb = (int)nb; g.nb_real = (int)w->d.nb_real;
-        g.log2_block = w->d.log2_block; g.lut = w->lut; g.status = ds->status;
+        g.q = aq.q; g.sa = aq.sa; g.qsum = aq.qsum;
         if (e == cudaSuccess) e = lowbit_gemv_launch(g, w->bits, ds->sm_count, stream);
         if (e == cudaSuccess && q_out)
             e = cudaMemcpy2DAsync(q_out, k, aq.q, kq, k, m, cudaMemcpyDeviceToDevice, stream);
@@ -608,8 +622,7 @@ static int lowbit_dev(const smeg_lowbit* w, const uint16_t* a, uint16_t* c, size
             e = cudaMemcpy2DAsync(sa_out, w->d.nb_real * 4, aq.sa, nb * 4, w->d.nb_real * 4, m, cudaMemcpyDeviceToDevice, stream);
     }
     if (ext) cudaFreeAsync(ext, stream);
-    cudaFreeAsync(ws, stream);
-    if (rc) return rc;
+    if (ws) cudaFreeAsync(ws, stream);
     return e == cudaSuccess ? 0 : -6;
 }
 

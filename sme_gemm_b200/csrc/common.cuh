@@ -27,6 +27,20 @@ __device__ __forceinline__ unsigned long long global_ns() {
     return t;
 }
 
+#ifdef SMEG_TC_TIMELINE
+// Debug builds only: SM-clock stamps of a kernel's phases in its first and last CTA
+// (slots 0-13: clock64; 14 / 15: global timer at entry / exit).  The array is per translation unit.
+#define SMEG_EV_DECL(name) __device__ long long name[2 * 16];
+#define SMEG_EV(name, ev)                                                                                   \
+    do {                                                                                                    \
+        const int b_ = (blockIdx.x == 0 && blockIdx.y == 0) ? 0 : ((blockIdx.x == gridDim.x - 1 && blockIdx.y == 0) ? 1 : -1); \
+        if (b_ >= 0) name[b_ * 16 + (ev)] = ((ev) >= 14) ? (long long)global_ns() : clock64();              \
+    } while (0)
+#else
+#define SMEG_EV_DECL(name)
+#define SMEG_EV(name, ev) do { } while (0)
+#endif
+
 __device__ __forceinline__ uint32_t smem_u32(const void* p) {
     return static_cast<uint32_t>(__cvta_generic_to_shared(p));
 }
@@ -58,6 +72,20 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, unsigned parity) {
         : "memory");
     return ok != 0;
 }
+// Same, letting the hardware suspend the thread for up to `ns` nanoseconds while the phase is
+// pending (it resumes at once when the phase completes): a waiting warp then issues a handful
+// of instructions per microsecond instead of competing with the working warps for issue slots.
+__device__ __forceinline__ bool mbar_try_wait_suspend(uint64_t* bar, unsigned parity, unsigned ns) {
+    unsigned ok;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(ok)
+        : "r"(smem_u32(bar)), "r"(parity), "r"(ns)
+        : "memory");
+    return ok != 0;
+}
 // Bounded wait.  Returns false (and raises `status`) if the barrier never
 // flipped; `abort_flag` in shared memory then short-circuits every later wait
 // of the CTA so the kernel still ends quickly.
@@ -67,7 +95,7 @@ __device__ __forceinline__ bool mbar_wait(uint64_t* bar, unsigned parity, volati
     const unsigned long long t0 = global_ns();
     for (;;) {
         if (*abort_flag) return false;
-        if (mbar_try_wait(bar, parity)) return true;
+        if (mbar_try_wait_suspend(bar, parity, 4000u)) return true;
         if (global_ns() - t0 > kWaitLimitNs) break;
     }
     *abort_flag = 1;

@@ -103,21 +103,27 @@ __device__ __forceinline__ float ep_node(const EpNodeDev& nd, float x, size_t i,
     }
 }
 
-// acc (f32 accumulator) -> stored T bits at output cell (i, j).
+// Same, over an explicit node array (shared or global memory).  Out of line: the interpreter
+// with every activation inlined is large, and the callers sit in unrolled loops.
 template <int BF16>
-__device__ __forceinline__ uint16_t ep_store_value(const EpParams& ep, float acc, size_t i, size_t j) {
+__device__ __noinline__ uint16_t ep_store_nodes(const EpNodeDev* nodes, int nn, float acc, size_t i, size_t j) {
     uint16_t c = f32_to_t<BF16>(acc);
-    const int nn = ep.n_nodes;
     if (nn == 0) return c;
     float x = t_to_f32<BF16>(c);
-    if (nn <= kMaxInlineNodes) {
 #pragma unroll 1
-        for (int q = 0; q < nn; ++q) x = ep_node<BF16>(ep.nodes[q], x, i, j);
-    } else {
-#pragma unroll 1
-        for (int q = 0; q < nn; ++q) x = ep_node<BF16>(ep.ext[q], x, i, j);
-    }
+    for (int q = 0; q < nn; ++q) x = ep_node<BF16>(nodes[q], x, i, j);
     return f32_to_t<BF16>(x);
+}
+
+// acc (f32 accumulator) -> stored T bits at output cell (i, j).  `ep` must be addressable
+// (a __grid_constant__ kernel parameter, or a copy in shared memory): the interpreter is one
+// out-of-line function, so that kernels which store from unrolled loops do not carry a copy of
+// every activation per store.
+template <int BF16>
+__device__ __forceinline__ uint16_t ep_store_value(const EpParams& ep, float acc, size_t i, size_t j) {
+    const int nn = ep.n_nodes;
+    if (nn == 0) return f32_to_t<BF16>(acc);
+    return ep_store_nodes<BF16>(nn <= kMaxInlineNodes ? ep.nodes : ep.ext, nn, acc, i, j);
 }
 
 // A graph of at most four nodes whose operands are scalars or per-column vectors and
@@ -250,18 +256,6 @@ __device__ __forceinline__ uint16_t fast_ep_store(const FastEp& f, float acc) {
         default: break;
         }
     }
-    return f32_to_t<BF16>(x);
-}
-
-// Same, over an explicit node array (shared or global memory).  Out of line: the interpreter
-// with every activation inlined is large, and the callers sit in unrolled loops.
-template <int BF16>
-__device__ __noinline__ uint16_t ep_store_nodes(const EpNodeDev* nodes, int nn, float acc, size_t i, size_t j) {
-    uint16_t c = f32_to_t<BF16>(acc);
-    if (nn == 0) return c;
-    float x = t_to_f32<BF16>(c);
-#pragma unroll 1
-    for (int q = 0; q < nn; ++q) x = ep_node<BF16>(nodes[q], x, i, j);
     return f32_to_t<BF16>(x);
 }
 

@@ -38,20 +38,26 @@ cudaError_t act_quant_launch(const ActQuantArgs& a, cudaStream_t stream);
 struct LowbitGemvArgs {
     const unsigned char* codes;   // packed units [n16][ku][512 B]
     const uint16_t* scales;       // f16 bits [n16][nb][16]
+    const uint16_t* a;            // m x k f16 activations: the kernel quantises them itself (else q / sa / qsum)
+    int a_vec_ok;                 // rows of a are 16-byte aligned
     const int8_t* q;              // m x kq
     const float* sa;              // m x nb
     const int32_t* qsum;          // m x nb (1-bit)
     uint16_t* c;                  // m x n f16 bits
     int32_t* sums_out;            // optional debug: m x n x nb_real exact block sums
+    int8_t* q_out;                // optional debug (with a): m x k int8 codes
+    float* sa_out;                // optional debug (with a): m x nb_real activation scales
     int m, n, k, kq;
     int n16, ku, nb, nb_real;     // column groups, units along K, block rows staged / real
     int log2_block;
     uint32_t lut;                 // 2-bit codebook, byte c = value of code c
-    int ns, cg, kc;               // launcher-filled: ring depth, groups per CTA, K chunk
+    int ns, gpt, kc, kqc;         // launcher-filled: ring depth, column groups per task, fold chunk, staged activation chunk
+    int ntasks, rows_s, u_bytes;  // launcher-filled: tasks along n, rows kept in the shared sums, bytes of the sums / f16-rows region
     unsigned* status;
     EpParams ep;
 };
 cudaError_t lowbit_gemv_launch(LowbitGemvArgs a, int bits, int sm_count, cudaStream_t stream);
+bool lowbit_gemv_fuses_quant(LowbitGemvArgs a, int bits, int sm_count);
 
 // ---- prefill GEMM on tcgen05 (gemm_tc.cu) ----
 struct GemmTcArgs {

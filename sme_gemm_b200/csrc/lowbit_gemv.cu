@@ -22,11 +22,21 @@
 
 namespace smeg {
 
+SMEG_EV_DECL(g_ev_lb)
+#ifdef SMEG_TC_TIMELINE
+__device__ int g_dbg_skip_lb = 0;
+#define SMEG_DBG_SKIP_LB ((g_dbg_skip_lb & 1) != 0)
+#define SMEG_DBG_BIT(b) ((g_dbg_skip_lb & (b)) != 0)
+#else
+#define SMEG_DBG_SKIP_LB false
+#define SMEG_DBG_BIT(b) false
+#endif
+
 namespace {
 
-constexpr int kWarps = 8;
-constexpr int kThreadsLb = 32 * (kWarps + 1);
-constexpr int kMaxOutPerThread = 8;
+constexpr int kWarps = 8;                 // units per stage
+constexpr int kCWarps = 16;               // consumer warps: two per unit, each taking every other column group
+constexpr int kThreadsLb = 32 * (kCWarps + 1);
 
 __device__ __forceinline__ void mma_s8(int (&c)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
     asm volatile("mma.sync.aligned.m16n8k32.row.col.s32.s8.s8.s32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
@@ -96,253 +106,491 @@ __global__ void __launch_bounds__(128) act_quant_kernel(ActQuantArgs p) {
 }
 
 // ---------------------------------------------------------------------------
-// The GEMV.  BITS = 2 or 1, MT = groups of 8 rows per CTA.
+// The GEMV.  BITS = 2 or 1, MT = groups of 8 rows per CTA, NCG = most column groups per task,
+// B16 = 16-deep K-blocks (two per MMA step).
+//
+// One CTA per SM, persistent over TASKS: a task is `gpt` adjacent column groups (16 columns
+// each) over the whole depth.  Everything the CTA reads from global memory goes through the
+// bulk-copy engine, in the order it is needed -- a plain load issued while tens of KB of
+// copies are queued waits behind them: first the activation rows (when the call passes f16
+// activations), then per stage the packed units of the task (8 units = one per consumer warp,
+// for every column group) and, with the first stage of a fold chunk, its scale rows.  The
+// copies of a round of stages are issued from different lanes at once.  The 8 consumer warps
+//   1. quantise the activation rows to int8 in shared memory while the first weights are in
+//      flight (or copy rows that act_quant_kernel prepared, for depths too long to stage),
+//   2. run the int8 MMAs of their unit of each stage and add the exact block sums into a
+//      shared int32 array covering one fold chunk of the depth,
+//   3. after each fold chunk, fold every output cell's blocks in K order (one thread per
+//      cell), and at the end of the task run the epilogue and store.
 // ---------------------------------------------------------------------------
-template <int BITS, int MT>
-__global__ void __launch_bounds__(kThreadsLb) lowbit_gemv_kernel(LowbitGemvArgs p) {
+template <int BITS, int MT, int NCG, int B16, int DP>
+__global__ void __launch_bounds__(kThreadsLb, 1) lowbit_gemv_kernel(const __grid_constant__ LowbitGemvArgs p) {
     constexpr int UD = BITS == 2 ? kQ2UnitDepth : kQ1UnitDepth;   // depths per unit
     constexpr int STEPS = UD / 32;                                 // mma k-steps per unit
     constexpr int SD = UD * kWarps;                                // depths per stage
     extern __shared__ __align__(128) unsigned char smem_raw[];
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int g = lane >> 2, t = lane & 3;
-    const int NS = p.ns, CG = p.cg, KC = p.kc;
+    const int uw = warp & (kWarps - 1), chalf = warp >> 3;         // consumer warp: unit of the stage, half of the column groups
+    const int NS = p.ns, GPT = p.gpt, KC = p.kc, KQ = p.kqc;
     const int block = 1 << p.log2_block;
-    const int bpc = KC >= block ? KC / block : 1;                  // sums rows held per chunk
+    const int bpc = KC >= block ? KC / block : 1;                  // sums rows held per fold chunk
+    const int nbq = (KQ + block - 1) / block;                      // activation-scale rows per staged chunk
     const int code_bytes = kUnitBytes * kWarps;
-    const int stage_bytes = CG * code_bytes;
+    const int stage_bytes = GPT * code_bytes;
     const int rows = 8 * MT;
+    const int row0 = blockIdx.y * rows;
+    const int rows_used = min(rows, p.m - row0);
+    const int RS = p.rows_s;                                       // rows kept in the sums array
+    const bool fused = p.a != nullptr;
 
     uint64_t* full = reinterpret_cast<uint64_t*>(smem_raw);
     uint64_t* empty = full + NS;
-    volatile int* abort_flag = reinterpret_cast<volatile int*>(empty + NS);
+    uint64_t* a_full = empty + NS;
+    uint64_t* s_empty = a_full + 1;                                // [2] scale buffer read by its fold
+    volatile int* abort_flag = reinterpret_cast<volatile int*>(s_empty + 2);
     unsigned char* stages = smem_raw + 256;
-    const int q_stride = KC + 32;                                  // bytes; keeps LDS.64 conflict-free
+    const int q_stride = KQ + 32;                                  // bytes; keeps LDS.64 conflict-free
     int8_t* Qs = reinterpret_cast<int8_t*>(stages + (size_t)NS * stage_bytes);
-    uint16_t* Ss = reinterpret_cast<uint16_t*>(Qs + (size_t)rows * q_stride);          // [CG][bpc][16] scales
-    float* SAs = reinterpret_cast<float*>(Ss + (size_t)CG * bpc * 16);                 // [rows][bpc]
-    int* QSs = reinterpret_cast<int*>(SAs + (size_t)rows * bpc);                       // [rows][bpc]
-    int* sums = QSs + (size_t)rows * bpc;                                              // [bpc][CG][rows][16]
+    uint16_t* Ss = reinterpret_cast<uint16_t*>(Qs + (size_t)rows * q_stride);          // [2][GPT][bpc][16] scales
+    float* SAs = reinterpret_cast<float*>(Ss + (size_t)2 * GPT * bpc * 16);            // [rows][nbq]
+    int* QSs = reinterpret_cast<int*>(SAs + (size_t)rows * nbq);                       // [rows][nbq]
+    int* AMX = QSs + (size_t)rows * nbq;                                               // [rows][nbq] amax bits, then 127/amax
+    // the f16 rows are dead once quantised, before the first block sum is written: same storage
+    int* sums = reinterpret_cast<int*>((reinterpret_cast<uintptr_t>(AMX + (size_t)rows * nbq) + 127) & ~(uintptr_t)127);   // [bpc][GPT][RS][16]
+    const uint16_t* Abuf = reinterpret_cast<const uint16_t*>(sums);                    // [rows_used][KQ] f16
+    // running f32 totals of the task's output cells, [GPT][RS][16], behind whichever of the two is larger
+    float* TOT = reinterpret_cast<float*>(reinterpret_cast<unsigned char*>(sums) + p.u_bytes);
 
-    const int cg0 = blockIdx.x * CG;
-    const int ncg = min(CG, p.n16 - cg0);
-    const int row0 = blockIdx.y * rows;
-    const int num_chunks = (p.kq + KC - 1) / KC;
+    const int num_qchunks = (p.kq + KQ - 1) / KQ;
     const int stages_total = (p.ku + kWarps - 1) / kWarps;
+    const int fc_stages = KC / SD;                                 // stages per fold chunk
+    const int my_tasks = ((int)blockIdx.x < p.ntasks) ? (p.ntasks - 1 - (int)blockIdx.x) / (int)gridDim.x + 1 : 0;
 
+    if (tid == 0) { SMEG_EV(g_ev_lb, 14); SMEG_EV(g_ev_lb, 0); }
     if (tid == 0) {
         for (int s = 0; s < NS; ++s) {
             mbar_init(&full[s], 1);
-            mbar_init(&empty[s], kWarps);
+            mbar_init(&empty[s], kCWarps);
         }
+        mbar_init(a_full, 1);
+        mbar_init(&s_empty[0], kCWarps);
+        mbar_init(&s_empty[1], kCWarps);
         *abort_flag = 0;
         fence_barrier_init();
     }
     __syncthreads();
+    if (tid == 0) SMEG_EV(g_ev_lb, 1);
 
-    if (warp == kWarps) {
+    if (warp == kCWarps) {
         // ================= producer =================
-        if (lane == 0) {
-            int st = 0;
-            for (int ch = 0; ch < num_chunks; ++ch) {
-                const int d0 = ch * KC;
-                const int st_end = min(stages_total, (d0 + KC) / SD);
-                for (; st < st_end; ++st) {
-                    const int slot = st % NS;
-                    if (st >= NS) mbar_wait(&empty[slot], ((st / NS) - 1) & 1, abort_flag, p.status);
-                    const int units = min(kWarps, p.ku - st * kWarps);
-                    mbar_expect_tx(&full[slot], ncg * units * kUnitBytes);
-                    unsigned char* sbase = stages + (size_t)slot * stage_bytes;
-                    for (int c = 0; c < ncg; ++c)
-                        bulk_g2s(sbase + c * code_bytes,
-                                 p.codes + (((size_t)(cg0 + c) * p.ku + (size_t)st * kWarps) * kUnitBytes),
-                                 units * kUnitBytes, &full[slot]);
-                }
+        if (fused) {
+            // the activation rows first: one bulk copy per row, one lane each
+            if (lane == 0) mbar_expect_tx(a_full, (unsigned)rows_used * (unsigned)p.k * 2u);
+            __syncwarp();
+            for (int r = lane; r < rows_used; r += 32)
+                bulk_g2s(const_cast<uint16_t*>(Abuf) + (size_t)r * KQ, p.a + (size_t)(row0 + r) * p.k, (unsigned)p.k * 2u, a_full);
+        }
+        // lane = (stage of the round, copy): copies 0-7 are the code runs of the task's column
+        // groups, 8-15 their scale rows (first stage of a fold chunk only); a round never holds
+        // more stages than the ring has slots
+        const int si = lane >> 4, j = lane & 15;
+        const int round_stages = min(2, NS);
+        const int total_seq = my_tasks * stages_total;
+        for (int seq0 = 0; seq0 < total_seq; seq0 += round_stages) {
+            const int seq = seq0 + si;
+            const bool active = si < round_stages && seq < total_seq;
+            const int ti = active ? seq / stages_total : 0, st = active ? seq % stages_total : 0;
+            const int task = (int)blockIdx.x + ti * (int)gridDim.x;
+            const int cg0 = task * GPT;
+            const int ncg = min(GPT, p.n16 - cg0);
+            const int slot = seq % NS;
+            const int units = min(kWarps, p.ku - st * kWarps);
+            const bool fc_first = st % fc_stages == 0;
+            const int fseq = ti * ((stages_total + fc_stages - 1) / fc_stages) + st / fc_stages;   // fold chunks so far
+            const int blk0 = (st * SD) >> p.log2_block;
+            const int nrows = min(bpc, p.nb - blk0);
+            bool ok = true;
+            if (active && j == 0) {
+                if (seq >= NS) ok = mbar_wait(&empty[slot], ((seq / NS) - 1) & 1, abort_flag, p.status);
+                // the scale buffer of this parity was last read by the fold two chunks back
+                if (ok && fc_first && fseq >= 2) ok = mbar_wait(&s_empty[fseq & 1], ((fseq >> 1) - 1) & 1, abort_flag, p.status);
+                if (ok) mbar_expect_tx(&full[slot], ncg * units * kUnitBytes + (fc_first ? ncg * nrows * 32 : 0));
+            }
+            if (!__all_sync(0xffffffffu, ok)) return;
+            if (active) {
+                if (j < ncg)
+                    bulk_g2s(stages + (size_t)slot * stage_bytes + j * code_bytes,
+                             p.codes + (((size_t)(cg0 + j) * p.ku + (size_t)st * kWarps) * kUnitBytes), units * kUnitBytes, &full[slot]);
+                else if (fc_first && j >= 8 && j - 8 < ncg)
+                    bulk_g2s(Ss + ((size_t)(fseq & 1) * GPT + (j - 8)) * bpc * 16,
+                             p.scales + ((size_t)(cg0 + j - 8) * p.nb + blk0) * 16, nrows * 32, &full[slot]);
             }
         }
+        if (lane == 0) SMEG_EV(g_ev_lb, 2);
         return;
     }
 
     // ================= consumers =================
-    float total[kMaxOutPerThread];
-#pragma unroll
-    for (int i = 0; i < kMaxOutPerThread; ++i) total[i] = 0.0f;
-    const int n_out = CG * 16 * rows;            // output cells of this CTA
-    int acc[4][MT][4];
+    // rows past the batch feed zeros to the MMAs
+    for (int idx = tid; idx < (rows - rows_used) * (q_stride / 4); idx += 32 * kCWarps)
+        reinterpret_cast<uint32_t*>(Qs + (size_t)rows_used * q_stride)[idx] = 0u;
 
-    int st = 0;
-    for (int ch = 0; ch < num_chunks; ++ch) {
-        const int d0 = ch * KC;
-        const int chunk = min(KC, p.kq - d0);
-        const int blk0 = d0 >> p.log2_block;                     // first block (row of scales) of the chunk
-        const bool block_starts = (d0 & (block - 1)) == 0;       // always true when block <= KC
-        asm volatile("bar.sync 1, %0;" ::"n"(32 * kWarps));
-        // ---- stage q, sa, qsum, scales; clear the sums ----
-        {
-            const int vec_per_row = chunk / 16;
-            for (int idx = tid; idx < rows * vec_per_row; idx += 32 * kWarps) {
-                const int r = idx / vec_per_row, v = idx % vec_per_row;
-                uint4 val = make_uint4(0, 0, 0, 0);
-                if (row0 + r < p.m) val = *reinterpret_cast<const uint4*>(p.q + (size_t)(row0 + r) * p.kq + d0 + v * 16);
-                *reinterpret_cast<uint4*>(Qs + (size_t)r * q_stride + v * 16) = val;
-            }
-            const int nblk = min(bpc, p.nb - blk0);
-            for (int idx = tid; idx < rows * bpc; idx += 32 * kWarps) {
-                const int r = idx / bpc, bl = idx % bpc;
-                const bool ok = row0 + r < p.m && bl < nblk;
-                SAs[idx] = ok ? p.sa[(size_t)(row0 + r) * p.nb + blk0 + bl] : 0.0f;
-                QSs[idx] = (ok && p.qsum) ? p.qsum[(size_t)(row0 + r) * p.nb + blk0 + bl] : 0;
-            }
-            for (int idx = tid; idx < CG * bpc * 16; idx += 32 * kWarps) {
-                const int c = idx / (bpc * 16), rem = idx % (bpc * 16);
-                const int bl = rem / 16, col = rem % 16;
-                Ss[idx] = (c < ncg && bl < nblk) ? p.scales[((size_t)(cg0 + c) * p.nb + blk0 + bl) * 16 + col] : (uint16_t)0;
-            }
-            if (block_starts)
-                for (int idx = tid; idx < bpc * n_out; idx += 32 * kWarps) sums[idx] = 0;
-        }
-        asm volatile("bar.sync 1, %0;" ::"n"(32 * kWarps));
+    int acc[NCG / 2][DP ? 2 : MT][4];                                  // DP (= most rows): [column g | g + 8][row]
+    int staged_qc = -1;
+    int seq = 0;                                                   // stage counter of this CTA's ring
+    int fseq = 0;                                                  // fold-chunk counter (scale buffer parity)
 
-        const int st_end = min(stages_total, (d0 + chunk + SD - 1) / SD);
-        for (; st < st_end; ++st) {
-            const int slot = st % NS;
-            mbar_wait(&full[slot], (st / NS) & 1, abort_flag, p.status);
-            const int units = min(kWarps, p.ku - st * kWarps);
-            if (warp < units) {
-                const unsigned char* sbase = stages + (size_t)slot * stage_bytes;
-                const int d_unit = st * SD + warp * UD;             // global depth of this unit
-                const int dl = d_unit - d0;                         // within the staged chunk
-#pragma unroll
-                for (int c = 0; c < 4; ++c)
-#pragma unroll
-                    for (int mt = 0; mt < MT; ++mt)
-#pragma unroll
-                        for (int r = 0; r < 4; ++r) acc[c][mt][r] = 0;
+    for (int ti = 0; ti < my_tasks; ++ti) {
+        const int task = (int)blockIdx.x + ti * (int)gridDim.x;
+        const int cg0 = task * GPT;
+        const int ncg = min(GPT, p.n16 - cg0);
+        const int n_out = ncg * 16 * RS;                           // output cells of this task
+        for (int o = tid; o < n_out; o += 32 * kCWarps) TOT[o] = 0.0f;   // read back by the same thread only
 
-                uint4 wv[4];
+        int st = 0;
+        for (int qc = 0; qc < num_qchunks; ++qc) {
+            const int dq0 = qc * KQ;
+            const int qchunk = min(KQ, p.kq - dq0);
+            const int blkq0 = dq0 >> p.log2_block;                   // first block of the staged chunk
+            // ---- the chunk's activations: int8 codes, per-block scales, per-block code sums ----
+            if (staged_qc != qc) {
+                staged_qc = qc;
+                asm volatile("bar.sync 1, %0;" ::"n"(32 * kCWarps));  // the previous chunk's readers are done
+                if (fused) {
+                    // quantize_row (src/kernels/lowbit/matmul.rs:354-371) over the staged f16 rows (whole depth)
+                    for (int idx = tid; idx < rows * nbq; idx += 32 * kCWarps) { AMX[idx] = 0; QSs[idx] = 0; }
+                    mbar_wait(a_full, 0, abort_flag, p.status);
+                    asm volatile("bar.sync 1, %0;" ::"n"(32 * kCWarps));
+                    // items: 8 consecutive depths of one row; consecutive lanes take consecutive items, so the
+                    // lanes of one K-block are an aligned run of seg = min(32, block / 8) lanes
+                    const int nvec = qchunk / 8;
+                    const int total_items = rows_used * nvec;
+                    const float inv_nvec = 1.0f / (float)nvec;
+                    int seg = min(32, block >> 3);
+                    if (nvec % seg) seg = 16;                        // the staged depth is whole units: a multiple of 16 items
+                    const int iters = (total_items + 32 * kCWarps - 1) / (32 * kCWarps);
+                    for (int it = 0; it < iters; ++it) {
+                        const int idx = tid + it * 32 * kCWarps;
+                        const bool in = idx < total_items;
+                        int r = in ? (int)(((float)idx + 0.5f) * inv_nvec) : 0;
+                        if (r * nvec > idx) --r;
+                        if ((r + 1) * nvec <= idx) ++r;
+                        const int v = idx - r * nvec, d = 8 * v;
+                        int mx = 0;
+                        if (in && d < p.k) {
+                            const uint4 hv = *reinterpret_cast<const uint4*>(Abuf + (size_t)r * KQ + d);
+                            const uint32_t hw[4] = {hv.x, hv.y, hv.z, hv.w};
+                            // |x| as integer bits: ordered like the values, and every NaN is above infinity
 #pragma unroll
-                for (int c = 0; c < 4; ++c)
-                    if (c < ncg) wv[c] = *reinterpret_cast<const uint4*>(sbase + c * code_bytes + warp * kUnitBytes + lane * 16);
-
-#pragma unroll
-                for (int s = 0; s < STEPS; ++s) {
-                    // activation fragment of this 32-deep step: 8 int8 of row g at depth 8t
-                    uint2 bq[MT];
-#pragma unroll
-                    for (int mt = 0; mt < MT; ++mt)
-                        bq[mt] = *reinterpret_cast<const uint2*>(Qs + (size_t)(8 * mt + g) * q_stride + dl + 32 * s + 8 * t);
-#pragma unroll
-                    for (int c = 0; c < 4; ++c) {
-                        if (c >= ncg) break;
-                        uint32_t af[4];
-                        if (BITS == 2) {
-                            const uint32_t w = s == 0 ? wv[c].x : (s == 1 ? wv[c].y : (s == 2 ? wv[c].z : wv[c].w));
-                            const uint32_t e = w & 0x33333333u, o = (w >> 2) & 0x33333333u;
-                            af[0] = prmt(p.lut, e);
-                            af[1] = prmt(p.lut, o);
-                            af[2] = prmt(p.lut, e >> 16);
-                            af[3] = prmt(p.lut, o >> 16);
-                        } else {
-                            const int wd = s >> 1, sh = 4 * (s & 1);
-                            const uint32_t w = wd == 0 ? wv[c].x : (wd == 1 ? wv[c].y : (wd == 2 ? wv[c].z : wv[c].w));
-                            af[0] = (w >> (sh + 0)) & 0x01010101u;
-                            af[1] = (w >> (sh + 1)) & 0x01010101u;
-                            af[2] = (w >> (sh + 2)) & 0x01010101u;
-                            af[3] = (w >> (sh + 3)) & 0x01010101u;
-                        }
-                        if (block >= 32) {
-#pragma unroll
-                            for (int mt = 0; mt < MT; ++mt) mma_s8(acc[c][mt], af, bq[mt].x, bq[mt].y);
-                        } else {
-                            // 16-deep blocks: a step covers two; lanes t < 2 feed the
-                            // first, t >= 2 the second, and each is flushed separately
-#pragma unroll
-                            for (int hb = 0; hb < 2; ++hb) {
-                                const bool mine = (t >> 1) == hb;
-                                int a2[MT][4];
-#pragma unroll
-                                for (int mt = 0; mt < MT; ++mt) {
-#pragma unroll
-                                    for (int r = 0; r < 4; ++r) a2[mt][r] = 0;
-                                    mma_s8(a2[mt], af, mine ? bq[mt].x : 0u, mine ? bq[mt].y : 0u);
-                                    const int bl = ((d_unit + 32 * s + 16 * hb) >> p.log2_block) - blk0;
-                                    int* dst = sums + (((size_t)bl * CG + c) * rows + 8 * mt) * 16;
-                                    atomicAdd(dst + (2 * t) * 16 + g, a2[mt][0]);
-                                    atomicAdd(dst + (2 * t + 1) * 16 + g, a2[mt][1]);
-                                    atomicAdd(dst + (2 * t) * 16 + g + 8, a2[mt][2]);
-                                    atomicAdd(dst + (2 * t + 1) * 16 + g + 8, a2[mt][3]);
-                                }
+                            for (int i = 0; i < 4; ++i) {
+                                const float2 f = __half22float2(*reinterpret_cast<const __half2*>(&hw[i]));
+                                mx = max(mx, max(__float_as_int(fabsf(f.x)), __float_as_int(fabsf(f.y))));
                             }
                         }
+                        // nvec is a multiple of seg, so a run never crosses a row
+                        for (int o = 1; o < seg; o <<= 1) mx = max(mx, __shfl_xor_sync(0xffffffffu, mx, o));
+                        if (in && d < p.k && (lane & (seg - 1)) == 0) atomicMax(&AMX[r * nbq + (d >> p.log2_block)], mx);
                     }
-                    // flush at the end of a block (or of the unit)
-                    if (block >= 32) {
-                        const int d_end = d_unit + 32 * (s + 1);
-                        if ((d_end & (block - 1)) == 0 || s == STEPS - 1) {
-                            const int bl = (block <= KC) ? (((d_end - 1) >> p.log2_block) - blk0) : 0;
+                    asm volatile("bar.sync 1, %0;" ::"n"(32 * kCWarps));
+                    for (int idx = tid; idx < rows_used * nbq; idx += 32 * kCWarps) {
+                        const int r = idx / nbq, bl = idx % nbq;
+                        const int bits = AMX[idx];
+                        const float amax = bits > 0x7f800000 ? __int_as_float(0x7fc00000) : __int_as_float(bits);
+                        const bool real = ((size_t)bl << p.log2_block) < (size_t)p.k;
+                        const float sa = real ? __fdiv_rn(amax, 127.0f) : 0.0f;
+                        SAs[idx] = sa;
+                        AMX[idx] = __float_as_int(amax > 0.0f ? __fdiv_rn(127.0f, amax) : 0.0f);
+                        if (p.sa_out && blockIdx.x == 0 && real) p.sa_out[(size_t)(row0 + r) * p.nb_real + bl] = sa;
+                    }
+                    asm volatile("bar.sync 1, %0;" ::"n"(32 * kCWarps));
+                    for (int it = 0; it < iters; ++it) {
+                        const int idx = tid + it * 32 * kCWarps;
+                        const bool in = idx < total_items;
+                        int r = in ? (int)(((float)idx + 0.5f) * inv_nvec) : 0;
+                        if (r * nvec > idx) --r;
+                        if ((r + 1) * nvec <= idx) ++r;
+                        const int v = idx - r * nvec, d = 8 * v;
+                        uint32_t lo = 0, hi = 0;
+                        int sum = 0;
+                        const int bl = d >> p.log2_block;
+                        if (in && d < p.k) {
+                            const uint4 hv = *reinterpret_cast<const uint4*>(Abuf + (size_t)r * KQ + d);
+                            const uint32_t hw[4] = {hv.x, hv.y, hv.z, hv.w};
+                            const float inv = __int_as_float(AMX[r * nbq + bl]);
+                            int q[8];
 #pragma unroll
-                            for (int c = 0; c < 4; ++c) {
+                            for (int i = 0; i < 4; ++i) {
+                                const float2 f = __half22float2(*reinterpret_cast<const __half2*>(&hw[i]));
+                                // round to nearest even, NaN -> 0, then saturate: round_ties_even(x) as i8
+                                q[2 * i] = max(-128, min(127, __float2int_rn(__fmul_rn(f.x, inv))));
+                                q[2 * i + 1] = max(-128, min(127, __float2int_rn(__fmul_rn(f.y, inv))));
+                            }
+                            lo = __byte_perm(__byte_perm(q[0], q[1], 0x0040), __byte_perm(q[2], q[3], 0x0040), 0x5410);
+                            hi = __byte_perm(__byte_perm(q[4], q[5], 0x0040), __byte_perm(q[6], q[7], 0x0040), 0x5410);
+                            if (BITS == 1) sum = __dp4a((int)lo, 0x01010101, __dp4a((int)hi, 0x01010101, 0));
+                            if (p.q_out && blockIdx.x == 0) *reinterpret_cast<uint2*>(p.q_out + (size_t)(row0 + r) * p.k + d) = make_uint2(lo, hi);
+                        }
+                        if (BITS == 1) {
+                            for (int o = 1; o < seg; o <<= 1) sum += __shfl_xor_sync(0xffffffffu, sum, o);
+                            if (in && d < p.k && (lane & (seg - 1)) == 0 && sum != 0) atomicAdd(&QSs[r * nbq + bl], sum);
+                        }
+                        if (in) *reinterpret_cast<uint2*>(Qs + (size_t)r * q_stride + d) = make_uint2(lo, hi);
+                    }
+                } else {
+                    const int vec_per_row = qchunk / 16;
+                    for (int idx = tid; idx < rows_used * vec_per_row; idx += 32 * kCWarps) {
+                        const int r = idx / vec_per_row, v = idx % vec_per_row;
+                        *reinterpret_cast<uint4*>(Qs + (size_t)r * q_stride + v * 16) =
+                            *reinterpret_cast<const uint4*>(p.q + (size_t)(row0 + r) * p.kq + dq0 + v * 16);
+                    }
+                    const int nblkq = min(nbq, p.nb - blkq0);
+                    for (int idx = tid; idx < rows_used * nbq; idx += 32 * kCWarps) {
+                        const int r = idx / nbq, bl = idx % nbq;
+                        const bool ok = bl < nblkq;
+                        SAs[idx] = ok ? p.sa[(size_t)(row0 + r) * p.nb + blkq0 + bl] : 0.0f;
+                        QSs[idx] = (ok && p.qsum) ? p.qsum[(size_t)(row0 + r) * p.nb + blkq0 + bl] : 0;
+                    }
+                }
+                if (tid == 0 && ti == 0 && qc == 0) SMEG_EV(g_ev_lb, 3);
+            }
+
+            const int st_qend = min(stages_total, (dq0 + qchunk + SD - 1) / SD);
+            while (st < st_qend) {
+                // ---- one fold chunk: KC depths from stage st ----
+                const int d0 = st * SD;
+                const int chunk = min(KC, p.kq - d0);
+                const int blk0 = d0 >> p.log2_block;                     // first block (row of scales) of the fold chunk
+                const int blr = block <= KQ ? blk0 - blkq0 : 0;          // ... relative to the staged activation scales
+                const bool block_starts = (d0 & (block - 1)) == 0;       // always true when block <= KC
+                const uint16_t* Sc = Ss + (size_t)(fseq & 1) * GPT * bpc * 16;
+                asm volatile("bar.sync 1, %0;" ::"n"(32 * kCWarps));      // quantised rows visible; previous fold done
+                if (block_starts)
+                    for (int idx = tid; idx < bpc * GPT * RS * 16; idx += 32 * kCWarps) sums[idx] = 0;
+                asm volatile("bar.sync 1, %0;" ::"n"(32 * kCWarps));
+
+                const int st_end = min(st_qend, st + fc_stages);
+                for (; st < st_end; ++st, ++seq) {
+                    const int slot = seq % NS;
+                    mbar_wait(&full[slot], (seq / NS) & 1, abort_flag, p.status);
+                    if (tid == 0 && seq == 0) SMEG_EV(g_ev_lb, 4);
+                    if (tid == 0 && ti == my_tasks - 1 && st == stages_total - 1) SMEG_EV(g_ev_lb, 9);
+                    const int units = min(kWarps, p.ku - st * kWarps);
+                    if (uw < units && !SMEG_DBG_SKIP_LB) {
+                        const unsigned char* sbase = stages + (size_t)slot * stage_bytes;
+                        const int d_unit = st * SD + uw * UD;             // global depth of this unit
+                        const int dl = d_unit - dq0;                        // within the staged activations
+#pragma unroll
+                        for (int ci = 0; ci < NCG / 2; ++ci)
+#pragma unroll
+                            for (int mt = 0; mt < (DP ? 2 : MT); ++mt)
+#pragma unroll
+                                for (int r = 0; r < 4; ++r) acc[ci][mt][r] = 0;
+
+                        uint4 wv[NCG / 2];
+#pragma unroll
+                        for (int ci = 0; ci < NCG / 2; ++ci)
+                            if (2 * ci + chalf < ncg) wv[ci] = *reinterpret_cast<const uint4*>(sbase + (2 * ci + chalf) * code_bytes + uw * kUnitBytes + lane * 16);
+
+                        // rolled on purpose: the body is large once the column groups are unrolled, and a fully
+                        // unrolled unit did not fit the instruction cache
+#pragma unroll 1
+                        for (int s = 0; s < STEPS; ++s) {
+                            if (DP) {
+                                // at most four rows: dot products on the integer units instead of the tensor cores
+                                // (an int8 mma.sync issues about once per 85 cycles per scheduler on this part).
+                                // The lane's bytes are columns g and g + 8 at depths 8t .. 8t + 7.
+                                uint2 aq[DP ? DP : 1];
+#pragma unroll
+                                for (int r = 0; r < DP; ++r)
+                                    aq[r] = r < RS ? *reinterpret_cast<const uint2*>(Qs + (size_t)r * q_stride + dl + 32 * s + 8 * t) : make_uint2(0u, 0u);
+                                const int wsel = BITS == 2 ? s : (s >> 1);
+                                const int sh = 4 * (s & 1);
+#pragma unroll
+                                for (int ci = 0; ci < NCG / 2; ++ci) {
+                                    const int c = 2 * ci + chalf;
+                                    if (c >= ncg) break;
+                                    uint32_t af[4];
+                                    const uint32_t w = wsel == 0 ? wv[ci].x : (wsel == 1 ? wv[ci].y : (wsel == 2 ? wv[ci].z : wv[ci].w));
+                                    if (BITS == 2) {
+                                        const uint32_t e = w & 0x33333333u, o = (w >> 2) & 0x33333333u;
+                                        af[0] = prmt(p.lut, e);
+                                        af[1] = prmt(p.lut, o);
+                                        af[2] = prmt(p.lut, e >> 16);
+                                        af[3] = prmt(p.lut, o >> 16);
+                                    } else {
+                                        af[0] = (w >> (sh + 0)) & 0x01010101u;
+                                        af[1] = (w >> (sh + 1)) & 0x01010101u;
+                                        af[2] = (w >> (sh + 2)) & 0x01010101u;
+                                        af[3] = (w >> (sh + 3)) & 0x01010101u;
+                                    }
+                                    if (SMEG_DBG_BIT(2)) { acc[ci][0][0] ^= (int)(af[0] + af[1] + af[2] + af[3]); continue; }
+#pragma unroll
+                                    for (int r = 0; r < DP; ++r) {
+                                        acc[ci][0][r] = __dp4a((int)af[0], (int)aq[r].x, acc[ci][0][r]);
+                                        acc[ci][0][r] = __dp4a((int)af[2], (int)aq[r].y, acc[ci][0][r]);
+                                        acc[ci][1][r] = __dp4a((int)af[1], (int)aq[r].x, acc[ci][1][r]);
+                                        acc[ci][1][r] = __dp4a((int)af[3], (int)aq[r].y, acc[ci][1][r]);
+                                    }
+                                }
+                                // flush at the end of a block (or of the unit): the four lanes holding the depth
+                                // slices of a column add into the same cell
+                                const int d_end = d_unit + 32 * (s + 1);
+                                if ((B16 || (d_end & (block - 1)) == 0 || s == STEPS - 1) && !SMEG_DBG_BIT(4)) {
+                                    const int bl = B16 ? (((d_unit + 32 * s + 16 * (t >> 1)) >> p.log2_block) - blk0)
+                                                       : ((block <= KC) ? (((d_end - 1) >> p.log2_block) - blk0) : 0);
+                                    int* dst0 = sums + (size_t)bl * GPT * RS * 16 + g;
+#pragma unroll
+                                    for (int ci = 0; ci < NCG / 2; ++ci) {
+                                        const int c = 2 * ci + chalf;
+                                        if (c >= ncg) break;
+#pragma unroll
+                                        for (int r = 0; r < DP; ++r) {
+                                            if (r < RS) {
+                                                atomicAdd(dst0 + (c * RS + r) * 16, acc[ci][0][r]);
+                                                atomicAdd(dst0 + (c * RS + r) * 16 + 8, acc[ci][1][r]);
+                                            }
+                                            acc[ci][0][r] = 0;
+                                            acc[ci][1][r] = 0;
+                                        }
+                                    }
+                                }
+                                continue;
+                            }
+                            // activation fragment of this 32-deep step: 8 int8 of row g at depth 8t
+                            uint2 bq[MT];
+#pragma unroll
+                            for (int mt = 0; mt < MT; ++mt)
+                                bq[mt] = *reinterpret_cast<const uint2*>(Qs + (size_t)(8 * mt + g) * q_stride + dl + 32 * s + 8 * t);
+                            const int wsel = BITS == 2 ? s : (s >> 1);
+                            const int sh = 4 * (s & 1);
+#pragma unroll
+                            for (int ci = 0; ci < NCG / 2; ++ci) {
+                                const int c = 2 * ci + chalf;
                                 if (c >= ncg) break;
+                                uint32_t af[4];
+                                const uint32_t w = wsel == 0 ? wv[ci].x : (wsel == 1 ? wv[ci].y : (wsel == 2 ? wv[ci].z : wv[ci].w));
+                                if (BITS == 2) {
+                                    const uint32_t e = w & 0x33333333u, o = (w >> 2) & 0x33333333u;
+                                    af[0] = prmt(p.lut, e);
+                                    af[1] = prmt(p.lut, o);
+                                    af[2] = prmt(p.lut, e >> 16);
+                                    af[3] = prmt(p.lut, o >> 16);
+                                } else {
+                                    af[0] = (w >> (sh + 0)) & 0x01010101u;
+                                    af[1] = (w >> (sh + 1)) & 0x01010101u;
+                                    af[2] = (w >> (sh + 2)) & 0x01010101u;
+                                    af[3] = (w >> (sh + 3)) & 0x01010101u;
+                                }
+                                if (!B16) {
 #pragma unroll
-                                for (int mt = 0; mt < MT; ++mt) {
-                                    int* dst = sums + (((size_t)bl * CG + c) * rows + 8 * mt) * 16;
-                                    atomicAdd(dst + (2 * t) * 16 + g, acc[c][mt][0]);
-                                    atomicAdd(dst + (2 * t + 1) * 16 + g, acc[c][mt][1]);
-                                    atomicAdd(dst + (2 * t) * 16 + g + 8, acc[c][mt][2]);
-                                    atomicAdd(dst + (2 * t + 1) * 16 + g + 8, acc[c][mt][3]);
+                                    for (int mt = 0; mt < MT; ++mt) mma_s8(acc[ci][mt], af, bq[mt].x, bq[mt].y);
+                                } else {
+                                    // 16-deep blocks: a step covers two; lanes t < 2 feed the
+                                    // first, t >= 2 the second, and each is flushed separately
+#pragma unroll 1
+                                    for (int hb = 0; hb < 2; ++hb) {
+                                        const bool mine = (t >> 1) == hb;
 #pragma unroll
-                                    for (int r = 0; r < 4; ++r) acc[c][mt][r] = 0;
+                                        for (int mt = 0; mt < MT; ++mt) {
+                                            int a2[4] = {0, 0, 0, 0};
+                                            mma_s8(a2, af, mine ? bq[mt].x : 0u, mine ? bq[mt].y : 0u);
+                                            const int bl = ((d_unit + 32 * s + 16 * hb) >> p.log2_block) - blk0;
+                                            int* dst = sums + ((size_t)bl * GPT + c) * RS * 16;
+                                            const int r0 = 8 * mt + 2 * t;
+                                            if (r0 < RS) {
+                                                atomicAdd(dst + r0 * 16 + g, a2[0]);
+                                                atomicAdd(dst + r0 * 16 + g + 8, a2[2]);
+                                            }
+                                            if (r0 + 1 < RS) {
+                                                atomicAdd(dst + (r0 + 1) * 16 + g, a2[1]);
+                                                atomicAdd(dst + (r0 + 1) * 16 + g + 8, a2[3]);
+                                            }
+                                        }
+                                    }
+                                }
+                            }
+                            // flush at the end of a block (or of the unit)
+                            if (!B16) {
+                                const int d_end = d_unit + 32 * (s + 1);
+                                if ((d_end & (block - 1)) == 0 || s == STEPS - 1) {
+                                    const int bl = (block <= KC) ? (((d_end - 1) >> p.log2_block) - blk0) : 0;
+#pragma unroll
+                                    for (int ci = 0; ci < NCG / 2; ++ci) {
+                                        const int c = 2 * ci + chalf;
+                                        if (c >= ncg) break;
+#pragma unroll
+                                        for (int mt = 0; mt < MT; ++mt) {
+                                            int* dst = sums + ((size_t)bl * GPT + c) * RS * 16;
+                                            const int r0 = 8 * mt + 2 * t;
+                                            if (r0 < RS) {
+                                                atomicAdd(dst + r0 * 16 + g, acc[ci][mt][0]);
+                                                atomicAdd(dst + r0 * 16 + g + 8, acc[ci][mt][2]);
+                                            }
+                                            if (r0 + 1 < RS) {
+                                                atomicAdd(dst + (r0 + 1) * 16 + g, acc[ci][mt][1]);
+                                                atomicAdd(dst + (r0 + 1) * 16 + g + 8, acc[ci][mt][3]);
+                                            }
+#pragma unroll
+                                            for (int r = 0; r < 4; ++r) acc[ci][mt][r] = 0;
+                                        }
+                                    }
                                 }
                             }
                         }
                     }
+                    __syncwarp();
+                    if (lane == 0) mbar_arrive(&empty[slot]);
                 }
-            }
-            __syncwarp();
-            if (lane == 0) mbar_arrive(&empty[slot]);
-        }
-        asm volatile("bar.sync 1, %0;" ::"n"(32 * kWarps));
+                if (tid == 0 && st == stages_total && ti == my_tasks - 1) SMEG_EV(g_ev_lb, 5);
+                asm volatile("bar.sync 1, %0;" ::"n"(32 * kCWarps));
+                if (tid == 0 && st == stages_total && ti == my_tasks - 1) SMEG_EV(g_ev_lb, 6);
 
-        // ---- ordered fold of the blocks completed by this chunk ----
-        const bool block_ends = block <= KC || ((d0 + chunk) & (block - 1)) == 0 || ch == num_chunks - 1;
-        if (block_ends) {
-            const int nblk = block <= KC ? min(bpc, p.nb_real - blk0) : (blk0 < p.nb_real ? 1 : 0);
-#pragma unroll
-            for (int i = 0; i < kMaxOutPerThread; ++i) {
-                const int o = tid + i * 32 * kWarps;
-                if (o >= n_out) break;
-                const int col = o & 15, r = (o >> 4) % rows, c = o / (16 * rows);
-                float tot = total[i];
-                for (int bl = 0; bl < nblk; ++bl) {
-                    int s = sums[(((size_t)bl * CG + c) * rows + r) * 16 + col];
-                    if (BITS == 1) s = 2 * s - QSs[r * bpc + bl];
-                    if (p.sums_out) {
-                        const int gr = row0 + r, gc = (cg0 + c) * 16 + col;
-                        if (c < ncg && gr < p.m && gc < p.n) p.sums_out[((size_t)gr * p.n + gc) * p.nb_real + blk0 + bl] = s;
+                // ---- ordered fold of the blocks completed by this fold chunk ----
+                const bool block_ends = block <= KC || ((d0 + chunk) & (block - 1)) == 0 || st == stages_total;
+                if (block_ends) {
+                    const int nfold = block <= KC ? min(bpc, p.nb_real - blk0) : (blk0 < p.nb_real ? 1 : 0);
+#pragma unroll 1
+                    for (int o = tid; o < n_out; o += 32 * kCWarps) {
+                        const int col = o & 15, r = (o >> 4) % RS, c = o / (16 * RS);
+                        if (r >= rows_used) continue;
+                        float tot = TOT[o];
+#pragma unroll 4
+                        for (int bl = 0; bl < nfold; ++bl) {
+                            int s = sums[(((size_t)bl * GPT + c) * RS + r) * 16 + col];
+                            if (BITS == 1) s = 2 * s - QSs[r * nbq + blr + bl];
+                            if (p.sums_out) {
+                                const int gr = row0 + r, gc = (cg0 + c) * 16 + col;
+                                if (gc < p.n) p.sums_out[((size_t)gr * p.n + gc) * p.nb_real + blk0 + bl] = s;
+                            }
+                            const float sc = __half2float(__ushort_as_half(Sc[(c * bpc + bl) * 16 + scale_slot(col)]));
+                            tot = fmaf((float)s, __fmul_rn(sc, SAs[r * nbq + blr + bl]), tot);
+                        }
+                        TOT[o] = tot;
                     }
-                    const float sc = __half2float(__ushort_as_half(Ss[(c * bpc + bl) * 16 + scale_slot(col)]));
-                    tot = fmaf((float)s, __fmul_rn(sc, SAs[r * bpc + bl]), tot);
                 }
-                total[i] = tot;
+                __syncwarp();
+                if (lane == 0) mbar_arrive(&s_empty[fseq & 1]);
+                ++fseq;
             }
         }
-    }
+        if (tid == 0 && ti == my_tasks - 1) SMEG_EV(g_ev_lb, 10);
 
-    // ---- epilogue + store ----
-#pragma unroll
-    for (int i = 0; i < kMaxOutPerThread; ++i) {
-        const int o = tid + i * 32 * kWarps;
-        if (o >= n_out) break;
-        const int col = o & 15, r = (o >> 4) % rows, c = o / (16 * rows);
-        const int gr = row0 + r, gc = (cg0 + c) * 16 + col;
-        if (c < ncg && gr < p.m && gc < p.n)
-            p.c[(size_t)gr * p.n + gc] = ep_store_value<0>(p.ep, total[i], (size_t)gr, (size_t)gc);
+        // ---- epilogue + store ----
+#pragma unroll 1
+        for (int o = tid; o < n_out; o += 32 * kCWarps) {
+            const int col = o & 15, r = (o >> 4) % RS, c = o / (16 * RS);
+            const int gr = row0 + r, gc = (cg0 + c) * 16 + col;
+            if (r < rows_used && gc < p.n)
+                p.c[(size_t)gr * p.n + gc] = ep_store_value<0>(p.ep, TOT[o], (size_t)gr, (size_t)gc);
+        }
     }
+    if (tid == 0) { SMEG_EV(g_ev_lb, 7); SMEG_EV(g_ev_lb, 15); }
 }
 
-template <int BITS, int MT>
+template <int BITS, int MT, int NCG, int B16, int DP>
 cudaError_t launch_lb(const LowbitGemvArgs& a, dim3 grid, size_t smem, cudaStream_t stream) {
-    auto kern = lowbit_gemv_kernel<BITS, MT>;
+    auto kern = lowbit_gemv_kernel<BITS, MT, NCG, B16, DP>;
     static int attr_dev = -1;   // the opt-in is per device; set it once (to the maximum) per device
     int dev = 0;
     cudaGetDevice(&dev);
@@ -356,15 +604,27 @@ cudaError_t launch_lb(const LowbitGemvArgs& a, dim3 grid, size_t smem, cudaStrea
     return cudaGetLastError();
 }
 
-size_t lowbit_smem(int bits, int ns, int cg, int mt, int kc, int block) {
+// bytes of the region shared by the staged f16 rows and the block sums
+size_t lowbit_u_bytes(int gpt, int rows_s, int kc, int kqc, int block, bool fused) {
+    const int bpc = kc >= block ? kc / block : 1;
+    const size_t sums = (size_t)bpc * gpt * 16 * rows_s * 4;
+    const size_t abuf = fused ? (size_t)rows_s * kqc * 2 : 0;
+    return ((sums > abuf ? sums : abuf) + 127) / 128 * 128;
+}
+size_t lowbit_smem(int ns, int gpt, int mt, int rows_s, int kc, int kqc, int block, bool fused) {
     const int rows = 8 * mt;
     const int bpc = kc >= block ? kc / block : 1;
-    (void)bits;
-    return 256 + (size_t)ns * cg * kUnitBytes * kWarps + (size_t)rows * (kc + 32) + (size_t)cg * bpc * 16 * 2 +
-           (size_t)rows * bpc * 8 + (size_t)bpc * cg * 16 * rows * 4 + 64;
+    const int nbq = (kqc + block - 1) / block;
+    return 256 + (size_t)ns * gpt * kUnitBytes * kWarps + (size_t)rows * (kqc + 32) + (size_t)2 * gpt * bpc * 32 +
+           (size_t)rows * nbq * 12 + 128 + lowbit_u_bytes(gpt, rows_s, kc, kqc, block, fused) + (size_t)gpt * rows_s * 64 + 64;
 }
 
 }  // namespace
+
+#ifdef SMEG_TC_TIMELINE
+extern "C" int smeg_debug_skip_lb(int v) { return cudaMemcpyToSymbol(smeg::g_dbg_skip_lb, &v, sizeof(int)) == cudaSuccess ? 0 : -1; }
+extern "C" int smeg_debug_ev_lb(long long* host) { return cudaMemcpyFromSymbol(host, g_ev_lb, sizeof(long long) * 32) == cudaSuccess ? 0 : -1; }
+#endif
 
 cudaError_t act_quant_launch(const ActQuantArgs& a, cudaStream_t stream) {
     if (a.m == 0 || a.nbq == 0) return cudaSuccess;
@@ -373,39 +633,103 @@ cudaError_t act_quant_launch(const ActQuantArgs& a, cudaStream_t stream) {
     return cudaGetLastError();
 }
 
-cudaError_t lowbit_gemv_launch(LowbitGemvArgs a, int bits, int sm_count, cudaStream_t stream) {
+// Picks rows per CTA, column groups per task, the staged activation chunk, the fold chunk and the
+// ring depth.  `fused`: the kernel stages and quantises the f16 rows itself, which needs the
+// whole depth in one staged chunk; returns false if no configuration fits shared memory.
+bool lowbit_gemv_plan(LowbitGemvArgs& a, int bits, int sm_count, bool fused, dim3* grid, size_t* smem, int* mt_out) {
     const int ud = bits == 2 ? kQ2UnitDepth : kQ1UnitDepth;
     const int sd = ud * kWarps;
     const int block = 1 << a.log2_block;
-    int mt = a.m <= 8 ? 1 : (a.m <= 16 ? 2 : 4);
-    int cg = 4;
-    while (cg > 1 && (a.n16 + cg - 1) / cg < 2 * sm_count) cg >>= 1;
-    // K chunk: a power-of-two number of stages, at most 32 KB of int8 activations
-    int kc = sd;
-    while (kc * 2 <= 4096 / mt * 1 && kc < a.kq) kc *= 2;
-    if (kc < sd) kc = sd;
-    const size_t budget = 200 * 1024;
-    int ns = 4;
-    for (;;) {
-        ns = cg >= 4 ? 3 : (cg == 2 ? 4 : 6);
-        const int n_out = cg * 16 * 8 * mt;
-        if (lowbit_smem(bits, ns, cg, mt, kc, block) <= budget && n_out <= kMaxOutPerThread * 32 * kWarps) break;
-        if (kc > sd) { kc /= 2; continue; }
-        if (cg > 1) { cg >>= 1; continue; }
-        if (mt > 1) { mt >>= 1; continue; }
-        return cudaErrorInvalidConfiguration;
+    const int stages_total = (a.ku + kWarps - 1) / kWarps;
+    const int kq_pad = stages_total * sd;
+    const size_t budget = 212 * 1024;
+    for (int mt = a.m <= 8 ? 1 : (a.m <= 16 ? 2 : 4); mt >= 1; mt >>= 1) {
+        const int ncg_max = mt == 1 ? 8 : 4;
+        const int rows = 8 * mt;
+        const int rows_s = a.m < rows ? a.m : rows;
+        const int row_tiles = (a.m + rows - 1) / rows;
+        const int target_x = sm_count / row_tiles > 0 ? sm_count / row_tiles : 1;   // one CTA per SM
+        int gpt0 = (a.n16 + target_x - 1) / target_x;
+        if (gpt0 > ncg_max) gpt0 = ncg_max;
+        if (gpt0 < 1) gpt0 = 1;
+        // staged activation chunk: the whole depth when its int8 rows fit 72 KB, else a power-of-two number of stages
+        int kqc = kq_pad;
+        if ((size_t)rows * (kq_pad + 32) > 72 * 1024) {
+            if (fused) continue;
+            kqc = sd;
+            while ((size_t)rows * (2 * kqc + 32) <= 64 * 1024 && 2 * kqc < kq_pad) kqc *= 2;
+        }
+        int kc_max = sd;
+        while (kc_max * 2 <= kqc && kc_max < 8192) kc_max *= 2;
+        const int want = stages_total < 8 ? stages_total : 8;
+        const int needs[3] = {want < 4 ? want : 4, want < 2 ? want : 2, 1};
+        for (int gpt = gpt0; gpt >= 1; --gpt) {
+            // a deep ring matters more than a long fold chunk
+            for (int ni = 0; ni < 3; ++ni) {
+                for (int kc = kc_max; kc >= sd; kc /= 2) {
+                    int ns = want;
+                    while (ns >= 1 && lowbit_smem(ns, gpt, mt, rows_s, kc, kqc, block, fused) > budget) --ns;
+                    if (ns < needs[ni] || ns < 1) continue;
+                    a.ns = ns; a.gpt = gpt; a.kc = kc; a.kqc = kqc; a.rows_s = rows_s;
+                    a.u_bytes = (int)lowbit_u_bytes(gpt, rows_s, kc, kqc, block, fused);
+                    a.ntasks = (a.n16 + gpt - 1) / gpt;
+                    *grid = dim3(a.ntasks < target_x ? a.ntasks : target_x, row_tiles);
+                    *smem = lowbit_smem(ns, gpt, mt, rows_s, kc, kqc, block, fused);
+                    *mt_out = mt;
+                    return true;
+                }
+            }
+        }
     }
-    a.ns = ns; a.cg = cg; a.kc = kc;
-    const size_t smem = lowbit_smem(bits, ns, cg, mt, kc, block);
-    dim3 grid((a.n16 + cg - 1) / cg, (a.m + 8 * mt - 1) / (8 * mt));
+    return false;
+}
+
+cudaError_t lowbit_gemv_launch(LowbitGemvArgs a, int bits, int sm_count, cudaStream_t stream) {
+    dim3 grid;
+    size_t smem = 0;
+    int mt = 1;
+    if (!lowbit_gemv_plan(a, bits, sm_count, a.a != nullptr, &grid, &smem, &mt)) return cudaErrorInvalidConfiguration;
+    const bool b16 = a.log2_block < 5;
+#define SMEG_LB(B, M, N)                                                   \
+    do {                                                                   \
+        if (b16) return launch_lb<B, M, N, 1, 0>(a, grid, smem, stream);   \
+        return launch_lb<B, M, N, 0, 0>(a, grid, smem, stream);            \
+    } while (0)
+    // up to four rows: the dot-product path
+#define SMEG_LB_DP(B, D)                                                   \
+    do {                                                                   \
+        if (b16) return launch_lb<B, 1, 8, 1, D>(a, grid, smem, stream);   \
+        return launch_lb<B, 1, 8, 0, D>(a, grid, smem, stream);            \
+    } while (0)
+    if (mt == 1 && a.rows_s <= 4) {
+        if (bits == 2) {
+            if (a.rows_s == 1) SMEG_LB_DP(2, 1);
+            if (a.rows_s == 2) SMEG_LB_DP(2, 2);
+            SMEG_LB_DP(2, 4);
+        }
+        if (a.rows_s == 1) SMEG_LB_DP(1, 1);
+        if (a.rows_s == 2) SMEG_LB_DP(1, 2);
+        SMEG_LB_DP(1, 4);
+    }
+#undef SMEG_LB_DP
     if (bits == 2) {
-        if (mt == 1) return launch_lb<2, 1>(a, grid, smem, stream);
-        if (mt == 2) return launch_lb<2, 2>(a, grid, smem, stream);
-        return launch_lb<2, 4>(a, grid, smem, stream);
+        if (mt == 1) SMEG_LB(2, 1, 8);
+        if (mt == 2) SMEG_LB(2, 2, 4);
+        SMEG_LB(2, 4, 4);
     }
-    if (mt == 1) return launch_lb<1, 1>(a, grid, smem, stream);
-    if (mt == 2) return launch_lb<1, 2>(a, grid, smem, stream);
-    return launch_lb<1, 4>(a, grid, smem, stream);
+    if (mt == 1) SMEG_LB(1, 1, 8);
+    if (mt == 2) SMEG_LB(1, 2, 4);
+    SMEG_LB(1, 4, 4);
+#undef SMEG_LB
+}
+
+// Whether lowbit_gemv_launch can take f16 activations (a.a) for this shape, i.e. stage and quantise
+// them in the kernel; otherwise the caller runs act_quant_kernel first and passes q / sa / qsum.
+bool lowbit_gemv_fuses_quant(LowbitGemvArgs a, int bits, int sm_count) {
+    dim3 grid;
+    size_t smem = 0;
+    int mt = 1;
+    return lowbit_gemv_plan(a, bits, sm_count, true, &grid, &smem, &mt);
 }
 
 }  // namespace smeg

@@ -26,6 +26,8 @@
 
 namespace smeg {
 
+SMEG_EV_DECL(g_ev_q4)
+
 namespace {
 
 constexpr int kConsumerWarps = 8;
@@ -103,7 +105,7 @@ __device__ __forceinline__ void decode_word_scaled(uint32_t w, uint32_t (&a)[4],
 }
 
 template <int BF16, int OPSIDE, int MT>
-__global__ void __launch_bounds__(kThreads) q4_gemv_kernel(Q4GemvArgs p) {
+__global__ void __launch_bounds__(kThreads) q4_gemv_kernel(const __grid_constant__ Q4GemvArgs p) {
     extern __shared__ __align__(128) unsigned char smem_raw[];
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int g = lane >> 2, t = lane & 3;
@@ -134,6 +136,7 @@ __global__ void __launch_bounds__(kThreads) q4_gemv_kernel(Q4GemvArgs p) {
     const int num_stages = (p.k64 + kConsumerWarps - 1) / kConsumerWarps;
     const int stages_per_chunk = p.ka / kStageDepth;
 
+    if (tid == 0) { SMEG_EV(g_ev_q4, 14); SMEG_EV(g_ev_q4, 0); }
     if (tid == 0) {
         for (int s = 0; s < NS; ++s) {
             mbar_init(&full[s], 1);
@@ -147,37 +150,64 @@ __global__ void __launch_bounds__(kThreads) q4_gemv_kernel(Q4GemvArgs p) {
         fence_barrier_init();
     }
     __syncthreads();
+    if (tid == 0) SMEG_EV(g_ev_q4, 1);
 
     if (warp == kConsumerWarps) {
         // ================= producer: stream activations and this CTA's weights =================
-        if (lane == 0) {
-            for (int st = 0; st < num_stages; ++st) {
-                if (p.a_vec_ok && st % stages_per_chunk == 0) {
-                    // the activation chunk that starts with this stage: one bulk copy per row
+        // Issuing a bulk copy costs a few hundred cycles on the issuing thread, so the copies of
+        // a round of stages go out from different lanes at once: lane = (stage of the round,
+        // copy of the stage), the first CG copies of a stage being the code runs of its column
+        // groups and the next CG their scale rows.
+        const int per_stage = 2 * CG;
+        // a round never spans more stages than the ring has slots (its waits are on stages issued
+        // in earlier rounds) nor, with several activation chunks, more than one chunk
+        // two stages per round: the first data lands early and the issue still runs ahead of the consumers
+        int round_stages = min(min(32 / per_stage, NS), 2);
+        if (nchunks > 1) round_stages = min(round_stages, stages_per_chunk);
+        const int si = lane / per_stage, j = lane % per_stage;
+        for (int st0 = 0; st0 < num_stages; st0 += round_stages) {
+            if (p.a_vec_ok) {
+                // activation chunks that start inside this round: one bulk copy per row, one lane each
+                for (int st = st0; st < min(num_stages, st0 + round_stages); ++st) {
+                    if (st % stages_per_chunk != 0) continue;
                     const int ch = st / stages_per_chunk, buf = ch & 1;
-                    if (ch >= 2) mbar_wait(&a_empty[buf], ((ch >> 1) - 1) & 1, abort_flag, p.status);
                     const int ka0 = ch * p.ka;
                     const unsigned bytes = (unsigned)(min(p.ka, p.k - ka0) * 2);
-                    mbar_expect_tx(&a_full[buf], rows_used * bytes);
-                    for (int r = 0; r < rows_used; ++r)
+                    bool ok = true;
+                    if (lane == 0) {
+                        if (ch >= 2) ok = mbar_wait(&a_empty[buf], ((ch >> 1) - 1) & 1, abort_flag, p.status);
+                        if (ok) mbar_expect_tx(&a_full[buf], rows_used * bytes);
+                    }
+                    if (!__all_sync(0xffffffffu, ok)) return;
+                    for (int r = lane; r < rows_used; r += 32)
                         bulk_g2s(As + buf * a_buf_halves + (size_t)r * a_stride, p.a + (size_t)(row0 + r) * p.k + ka0, bytes, &a_full[buf]);
                 }
-                const int slot = st % NS;
-                if (st >= NS) mbar_wait(&empty[slot], ((st / NS) - 1) & 1, abort_flag, p.status);
-                const int units = min(kConsumerWarps, p.k64 - st * kConsumerWarps);
-                const int blk0 = (st * kStageDepth) >> p.log2_block;
-                const int blk1 = min(p.nb, ((st * kStageDepth + units * 64 - 1) >> p.log2_block) + 1);
-                const int rows = blk1 - blk0;
-                const unsigned cb = units * kUnitBytes, sb = rows * 32;
-                mbar_expect_tx(&full[slot], ncg * (cb + sb));
+            }
+            const int st = st0 + si;
+            const bool active = si < round_stages && st < num_stages;
+            const int slot = active ? st % NS : 0;
+            const int units = active ? min(kConsumerWarps, p.k64 - st * kConsumerWarps) : 0;
+            const int blk0 = (st * kStageDepth) >> p.log2_block;
+            const int blk1 = min(p.nb, ((st * kStageDepth + units * 64 - 1) >> p.log2_block) + 1);
+            const unsigned cb = units * kUnitBytes, sb = (unsigned)(blk1 - blk0) * 32;
+            bool ok = true;
+            if (active && j == 0) {
+                if (st >= NS) ok = mbar_wait(&empty[slot], ((st / NS) - 1) & 1, abort_flag, p.status);
+                if (ok) mbar_expect_tx(&full[slot], ncg * (cb + sb));
+            }
+            if (!__all_sync(0xffffffffu, ok)) return;
+            if (active) {
                 unsigned char* sbase = stages + (size_t)slot * stage_bytes;
-                for (int c = 0; c < ncg; ++c) {
+                const int c = j < CG ? j : j - CG;
+                if (c < ncg) {
                     const size_t cgi = cg0 + c;
-                    bulk_g2s(sbase + c * code_bytes, p.codes + q4_unit_offset(cgi, (size_t)st * kConsumerWarps, p.k64), cb, &full[slot]);
-                    bulk_g2s(sbase + CG * code_bytes + c * scale_bytes, p.scales + q4_scale_row(cgi, blk0, p.nb), sb, &full[slot]);
+                    if (j < CG) bulk_g2s(sbase + c * code_bytes, p.codes + q4_unit_offset(cgi, (size_t)st * kConsumerWarps, p.k64), cb, &full[slot]);
+                    else bulk_g2s(sbase + CG * code_bytes + c * scale_bytes, p.scales + q4_scale_row(cgi, blk0, p.nb), sb, &full[slot]);
                 }
             }
+            if (lane == 0 && st0 == 0) SMEG_EV(g_ev_q4, 8);
         }
+        if (lane == 0) SMEG_EV(g_ev_q4, 2);
         return;
     }
 
@@ -205,6 +235,7 @@ __global__ void __launch_bounds__(kThreads) q4_gemv_kernel(Q4GemvArgs p) {
                 asm volatile("bar.sync 1, %0;" ::"n"(32 * kConsumerWarps));
             }
             mbar_wait(&a_full[buf], (ch >> 1) & 1, abort_flag, p.status);
+            if (tid == 0 && ch == 0) SMEG_EV(g_ev_q4, 3);
         } else {
             // rows of A are not 16-byte aligned: cooperative copy (zero padded)
             asm volatile("bar.sync 1, %0;" ::"n"(32 * kConsumerWarps));
@@ -219,6 +250,8 @@ __global__ void __launch_bounds__(kThreads) q4_gemv_kernel(Q4GemvArgs p) {
         for (int st = st_begin; st < st_end; ++st) {
             const int slot = st % NS;
             mbar_wait(&full[slot], (st / NS) & 1, abort_flag, p.status);
+            if (tid == 0 && st == 0) SMEG_EV(g_ev_q4, 4);
+            if (tid == 0 && st == num_stages - 1) SMEG_EV(g_ev_q4, 9);
             const int units = min(kConsumerWarps, p.k64 - st * kConsumerWarps);
             if (warp < units) {
                 const unsigned char* sbase = stages + (size_t)slot * stage_bytes;
@@ -291,6 +324,7 @@ __global__ void __launch_bounds__(kThreads) q4_gemv_kernel(Q4GemvArgs p) {
         if (p.a_vec_ok && lane == 0) mbar_arrive(&a_empty[buf]);
     }
 
+    if (tid == 0) SMEG_EV(g_ev_q4, 5);
     // ---- fixed-order reduction over the 8 warps, epilogue, store ----
     // red[warp][c][mt][r][lane]
 #pragma unroll
@@ -302,6 +336,7 @@ __global__ void __launch_bounds__(kThreads) q4_gemv_kernel(Q4GemvArgs p) {
             for (int r = 0; r < 4; ++r) red[((((size_t)warp * CG + c) * MT + mt) * 4 + r) * 32 + lane] = total[c][mt][r];
     }
     asm volatile("bar.sync 1, %0;" ::"n"(32 * kConsumerWarps));
+    if (tid == 0) SMEG_EV(g_ev_q4, 6);
     const int per_warp = CG * MT * 128;
     for (int o = tid; o < per_warp; o += 32 * kConsumerWarps) {
         float acc = 0.0f;
@@ -315,6 +350,7 @@ __global__ void __launch_bounds__(kThreads) q4_gemv_kernel(Q4GemvArgs p) {
             else p.c[(size_t)row * p.n + col] = ep_store_value<BF16>(p.ep, acc, (size_t)row, (size_t)col);
         }
     }
+    if (tid == 0) { SMEG_EV(g_ev_q4, 7); SMEG_EV(g_ev_q4, 15); }
 }
 
 template <int BF16, int OPSIDE, int MT>
@@ -334,6 +370,10 @@ cudaError_t launch(const Q4GemvArgs& a, dim3 grid, size_t smem, cudaStream_t str
 }
 
 }  // namespace
+
+#ifdef SMEG_TC_TIMELINE
+extern "C" int smeg_debug_ev_q4(long long* host) { return cudaMemcpyFromSymbol(host, g_ev_q4, sizeof(long long) * 32) == cudaSuccess ? 0 : -1; }
+#endif
 
 // Host-side launcher.  Chooses the column groups per CTA so that the grid has
 // at least about two CTAs per SM when the matrix allows it, the ring depth from
