@@ -519,12 +519,19 @@ int smeg_host_q1_quantize(const float* w, int layout, size_t n, size_t k, size_t
 // ---------------------------------------------------------------------------
 // device-pointer compute
 // ---------------------------------------------------------------------------
+// Whether an m-row call on these weights runs on the tensor-core GEMM (else the decode kernel).
+static bool q4_uses_tc(const smeg_q4* w, const uint16_t* a, size_t m) {
+    return (int)m > g_tc_min_rows && gemm_tc_supported(4, (int)m, (int)w->d.k, w->d.log2_block, a);
+}
+
+// glu / yacc: the fused forms of the MLP block (tensor-core GEMM only, see GemmTcArgs).
 static int q4_dev(const smeg_q4* w, const uint16_t* a, uint16_t* c, size_t m, const ep_desc16* ep, int bf16,
-                  cudaStream_t stream, float* c32 = nullptr) {
+                  cudaStream_t stream, float* c32 = nullptr, int glu = 0, float* yacc = nullptr) {
     if (!w) return -4;
     const size_t n = w->d.n, k = w->d.k;
     if (m == 0 || n == 0) return 0;
-    if ((!c && !c32) || (k && !a) || m > 0x7fffffffu || n > 0x7fffffffu || k > 0x7fffffffu) return -4;
+    if ((!c && !c32 && !yacc) || (k && !a) || m > 0x7fffffffu || n > 0x7fffffffu || k > 0x7fffffffu) return -4;
+    if ((glu || yacc) && !q4_uses_tc(w, a, m)) return -4;
     DeviceState* ds = dev_state();
     if (!ds) return -5;
     Q4GemvArgs g;
@@ -539,10 +546,10 @@ static int q4_dev(const smeg_q4* w, const uint16_t* a, uint16_t* c, size_t m, co
     g.a_vec_ok = (k % 8 == 0) && ((uintptr_t)a % 16 == 0);
     g.status = ds->status;
     cudaError_t e;
-    if ((int)m > g_tc_min_rows && gemm_tc_supported(4, (int)m, (int)k, w->d.log2_block, a)) {
+    if (q4_uses_tc(w, a, m)) {
         GemmTcArgs t;
         memset(&t, 0, sizeof(t));
-        t.codes = w->codes; t.scales = w->scales; t.a = a; t.c = c; t.c32 = c32;
+        t.codes = w->codes; t.scales = w->scales; t.a = a; t.c = c; t.c32 = c32; t.glu = glu; t.yacc = yacc;
         t.m = (int)m; t.n = (int)n; t.k = (int)k;
         t.n16 = (int)w->d.n16; t.ku = (int)w->d.ku; t.nb = (int)w->d.nb; t.log2_block = w->d.log2_block;
         t.status = ds->status;
@@ -804,18 +811,29 @@ static int mlp_run(smeg_mlp* mlp, const uint16_t* x, float* y, float* partial, s
     char* ws = nullptr;
     const size_t both_bytes = (m * 2 * h * 2 + 255) / 256 * 256, hid_bytes = (m * h * 2 + 255) / 256 * 256;
     const size_t out_bytes = (m * d_out * 2 + 255) / 256 * 256;
-    if (cudaMallocAsync(&ws, both_bytes + hid_bytes + out_bytes, stream) != cudaSuccess) return -2;
-    uint16_t* both = (uint16_t*)ws;
-    uint16_t* hid = (uint16_t*)(ws + both_bytes);
-    uint16_t* out = (uint16_t*)(ws + both_bytes + hid_bytes);
-    int rc = q4_dev(mlp->gate_up, x, both, m, nullptr, 0, stream);
-    if (!rc) rc = glu_launch(hid, both, m, h, mlp->act, stream) == cudaSuccess ? 0 : -6;
-    if (!rc) {
-        if (partial) {
-            rc = q4_dev(mlp->down, hid, nullptr, m, nullptr, 0, stream, partial);
-        } else {
-            rc = q4_dev(mlp->down, hid, out, m, nullptr, 0, stream);
-            if (!rc) rc = add_f16_to_f32_launch(y, out, m * d_out, stream) == cudaSuccess ? 0 : -6;
+    // prefill-sized batches: the gated product is formed in the gate/up GEMM's drain and the residual add in the
+    // down GEMM's, with the arithmetic of the separate passes (two launches instead of four)
+    const bool fuse = m > 64 && h % 32 == 0 && mlp->gate_up->d.n == 2 * h && q4_uses_tc(mlp->gate_up, x, m) &&
+                      mlp->down->d.k % 8 == 0 && (int)m > g_tc_min_rows && mlp->down->d.log2_block >= 3;
+    if (cudaMallocAsync(&ws, (fuse ? 0 : both_bytes) + hid_bytes + out_bytes, stream) != cudaSuccess) return -2;
+    uint16_t* hid = (uint16_t*)ws;
+    uint16_t* out = (uint16_t*)(ws + hid_bytes);
+    uint16_t* both = (uint16_t*)(ws + hid_bytes + out_bytes);
+    int rc;
+    if (fuse) {
+        rc = q4_dev(mlp->gate_up, x, hid, m, nullptr, 0, stream, nullptr, (int)mlp->act);
+        if (!rc) rc = partial ? q4_dev(mlp->down, hid, nullptr, m, nullptr, 0, stream, partial)
+                              : q4_dev(mlp->down, hid, nullptr, m, nullptr, 0, stream, nullptr, 0, y);
+    } else {
+        rc = q4_dev(mlp->gate_up, x, both, m, nullptr, 0, stream);
+        if (!rc) rc = glu_launch(hid, both, m, h, mlp->act, stream) == cudaSuccess ? 0 : -6;
+        if (!rc) {
+            if (partial) {
+                rc = q4_dev(mlp->down, hid, nullptr, m, nullptr, 0, stream, partial);
+            } else {
+                rc = q4_dev(mlp->down, hid, out, m, nullptr, 0, stream);
+                if (!rc) rc = add_f16_to_f32_launch(y, out, m * d_out, stream) == cudaSuccess ? 0 : -6;
+            }
         }
     }
     cudaFreeAsync(ws, stream);

@@ -290,7 +290,15 @@ __global__ void __launch_bounds__(kTcThreads, 1) gemm_tc_kernel(const __grid_con
                 const int du = d0 + uu * kStageK;
                 const int ra = ((du + 8 * t) >> p.log2_block) - blk0, rb = ((du + 32 + 8 * t) >> p.log2_block) - blk0;
                 const uint4 wv = *reinterpret_cast<const uint4*>(pk + (size_t)c * kUnitBytes + lane * 16);
-                dequant_unit_q4<BF16>(ob + (w * US + uu) * kWTile, cgl, wv, scs + (size_t)wc * sc_rows * 16, ra, rb, g, t);
+                // gate/up matrix: gate column groups go to operand tile 0 and the matching up groups to tile 1,
+                // so that a thread of the drain holds both values of one hidden unit
+                int tw = w, rg = cgl;
+                if (p.glu) {
+                    const int gi = 8 * w + cgl;                    // group within the CTA; chunks of [2 gate | 2 up] groups
+                    tw = (gi >> 1) & 1;
+                    rg = ((gi >> 2) << 1) | (gi & 1);
+                }
+                dequant_unit_q4<BF16>(ob + (tw * US + uu) * kWTile, rg, wv, scs + (size_t)wc * sc_rows * 16, ra, rb, g, t);
             }
             fence_proxy_async();
             mbar_arrive(&o_full[os]);
@@ -316,6 +324,30 @@ __global__ void __launch_bounds__(kTcThreads, 1) gemm_tc_kernel(const __grid_con
         const int tile_id = blockIdx.y * gridDim.x + blockIdx.x;
         float* ws_tile = p.ws + ((size_t)tile_id * splits) * (size_t)(NW * 128) * ntok;
 
+        if (p.glu && splits == 1) {
+            // accumulator set 0 = gate, set 1 = up of hidden unit hcol (glu, src/linear.rs:804-835)
+            const int hn = p.n >> 1, hcol = blockIdx.x * 128 + 32 * q + lane;
+            for (int j0 = j_begin; j0 < j_end; j0 += 16) {
+                uint32_t rg[16], ru[16];
+                tmem_ld16(lane_base + (uint32_t)j0, rg);
+                tmem_ld16(lane_base + (uint32_t)(ntok + j0), ru);
+                tmem_ld_wait();
+                if (hcol < hn) {
+#pragma unroll
+                    for (int j = 0; j < 16; ++j) {
+                        const float gv = t_to_f32<BF16>(f32_to_t<BF16>(__uint_as_float(rg[j])));
+                        const float uv = t_to_f32<BF16>(f32_to_t<BF16>(__uint_as_float(ru[j])));
+                        float a;
+                        if (p.glu == 3) a = __fdiv_rn(gv, __fadd_rn(1.0f, expf(-gv)));
+                        else {
+                            const float g3 = __fmul_rn(__fmul_rn(__fmul_rn(0.044715f, gv), gv), gv);
+                            a = __fmul_rn(__fmul_rn(0.5f, gv), __fadd_rn(1.0f, tanhf(__fmul_rn(0.7978846f, __fadd_rn(gv, g3)))));
+                        }
+                        if (tok0 + j0 + j < p.m) p.c[(size_t)(tok0 + j0 + j) * hn + hcol] = f32_to_t<BF16>(__fmul_rn(a, uv));
+                    }
+                }
+            }
+        } else
         for (int w = 0; w < NW; ++w) {
             const int col = col0 + 128 * w + 32 * q + lane;
             FastEp fe;
@@ -335,6 +367,14 @@ __global__ void __launch_bounds__(kTcThreads, 1) gemm_tc_kernel(const __grid_con
 #pragma unroll
                             for (int j = 0; j < 16; ++j)
                                 if (tok0 + j0 + j < p.m) p.c32[(size_t)(tok0 + j0 + j) * p.n + col] = __uint_as_float(r[j]);
+                        } else if (p.yacc) {
+                            float yv[16];
+#pragma unroll
+                            for (int j = 0; j < 16; ++j) yv[j] = (tok0 + j0 + j < p.m) ? p.yacc[(size_t)(tok0 + j0 + j) * p.n + col] : 0.0f;
+#pragma unroll
+                            for (int j = 0; j < 16; ++j)
+                                if (tok0 + j0 + j < p.m)
+                                    p.yacc[(size_t)(tok0 + j0 + j) * p.n + col] = __fadd_rn(yv[j], t_to_f32<BF16>(f32_to_t<BF16>(__uint_as_float(r[j]))));
                         } else {
                             uint16_t v[16];
                             if (p.ep_fast) fast_ep_apply16<BF16>(fe, r, v);
@@ -371,7 +411,43 @@ __global__ void __launch_bounds__(kTcThreads, 1) gemm_tc_kernel(const __grid_con
                 if (prev == splits - 1) p.counters[tile_id] = 0;      // ready for the next launch
             }
             asm volatile("bar.sync 1, %0;" ::"r"(drain_threads));
-            if (*last_flag) {
+            // eight tokens at a time: their loads are independent, so the reduce is bound by
+            // bandwidth and not by one memory latency per token
+            if (*last_flag && p.glu) {
+                __threadfence();
+                const int hn = p.n >> 1, hcol = blockIdx.x * 128 + 32 * q + lane;
+                if (hcol < hn) {
+#pragma unroll 1
+                    for (int j0 = j_begin; j0 < j_end; j0 += 8) {
+                        float ag[8], au[8];
+#pragma unroll
+                        for (int jj = 0; jj < 8; ++jj) ag[jj] = au[jj] = 0.0f;
+                        for (int z = 0; z < splits; ++z) {
+                            const float* src = ws_tile + ((size_t)z * ntok + j0) * (NW * 128) + (32 * q + lane);
+                            float vg[8], vu[8];
+#pragma unroll
+                            for (int jj = 0; jj < 8; ++jj) {
+                                vg[jj] = __ldcg(src + (size_t)jj * (NW * 128));
+                                vu[jj] = __ldcg(src + (size_t)jj * (NW * 128) + 128);
+                            }
+#pragma unroll
+                            for (int jj = 0; jj < 8; ++jj) { ag[jj] += vg[jj]; au[jj] += vu[jj]; }
+                        }
+#pragma unroll
+                        for (int jj = 0; jj < 8; ++jj) {
+                            const int tok = tok0 + j0 + jj;
+                            const float gv = t_to_f32<BF16>(f32_to_t<BF16>(ag[jj])), uv = t_to_f32<BF16>(f32_to_t<BF16>(au[jj]));
+                            float a;
+                            if (p.glu == 3) a = __fdiv_rn(gv, __fadd_rn(1.0f, expf(-gv)));
+                            else {
+                                const float g3 = __fmul_rn(__fmul_rn(__fmul_rn(0.044715f, gv), gv), gv);
+                                a = __fmul_rn(__fmul_rn(0.5f, gv), __fadd_rn(1.0f, tanhf(__fmul_rn(0.7978846f, __fadd_rn(gv, g3)))));
+                            }
+                            if (tok < p.m) p.c[(size_t)tok * hn + hcol] = f32_to_t<BF16>(__fmul_rn(a, uv));
+                        }
+                    }
+                }
+            } else if (*last_flag) {
                 __threadfence();
                 for (int w = 0; w < NW; ++w) {
                     const int col = col0 + 128 * w + 32 * q + lane;
@@ -379,15 +455,31 @@ __global__ void __launch_bounds__(kTcThreads, 1) gemm_tc_kernel(const __grid_con
                     FastEp fe;
                     if (p.ep_fast) fast_ep_build<BF16>(nodes, p.ep.n_nodes, col, true, fe);
 #pragma unroll 1
-                    for (int j = j_begin; j < j_end; ++j) {
-                        const int tok = tok0 + j;
-                        if (tok >= p.m) continue;
-                        float acc = 0.0f;
-                        for (int z = 0; z < splits; ++z)
-                            acc += __ldcg(ws_tile + ((size_t)z * ntok + j) * (NW * 128) + (128 * w + 32 * q + lane));
-                        if (p.c32) p.c32[(size_t)tok * p.n + col] = acc;
-                        else if (p.ep_fast) p.c[(size_t)tok * p.n + col] = fast_ep_store<BF16>(fe, acc);
-                        else p.c[(size_t)tok * p.n + col] = ep_store_nodes<BF16>(nodes, p.ep.n_nodes, acc, (size_t)tok, (size_t)col);
+                    for (int j0 = j_begin; j0 < j_end; j0 += 8) {
+                        float acc[8], yv[8];
+#pragma unroll
+                        for (int jj = 0; jj < 8; ++jj) acc[jj] = 0.0f;
+                        if (p.yacc) {
+#pragma unroll
+                            for (int jj = 0; jj < 8; ++jj) yv[jj] = (tok0 + j0 + jj < p.m) ? p.yacc[(size_t)(tok0 + j0 + jj) * p.n + col] : 0.0f;
+                        }
+                        for (int z = 0; z < splits; ++z) {
+                            const float* src = ws_tile + ((size_t)z * ntok + j0) * (NW * 128) + (128 * w + 32 * q + lane);
+                            float v[8];
+#pragma unroll
+                            for (int jj = 0; jj < 8; ++jj) v[jj] = __ldcg(src + (size_t)jj * (NW * 128));
+#pragma unroll
+                            for (int jj = 0; jj < 8; ++jj) acc[jj] += v[jj];
+                        }
+#pragma unroll
+                        for (int jj = 0; jj < 8; ++jj) {
+                            const int tok = tok0 + j0 + jj;
+                            if (tok >= p.m) continue;
+                            if (p.c32) p.c32[(size_t)tok * p.n + col] = acc[jj];
+                            else if (p.yacc) p.yacc[(size_t)tok * p.n + col] = __fadd_rn(yv[jj], t_to_f32<BF16>(f32_to_t<BF16>(acc[jj])));
+                            else if (p.ep_fast) p.c[(size_t)tok * p.n + col] = fast_ep_store<BF16>(fe, acc[jj]);
+                            else p.c[(size_t)tok * p.n + col] = ep_store_nodes<BF16>(nodes, p.ep.n_nodes, acc[jj], (size_t)tok, (size_t)col);
+                        }
                     }
                 }
             }
@@ -450,7 +542,8 @@ bool gemm_tc_supported(int wkind, int m, int k, int log2_block, const void* a) {
 void gemm_tc_plan(GemmTcArgs& a, int sm_count, dim3* grid, size_t* smem, size_t* ws_floats, size_t* n_counters) {
     // token tiling: equal tiles of at most 512 tokens, padded so that both token halves of the
     // drain (and both MMA halves above 256) are whole groups of 16
-    const int tiles = (a.m + 511) / 512;
+    // the fused gate/up form keeps both values of a hidden unit in one CTA: two accumulator sets, at most 256 tokens
+    const int tiles = a.glu ? (a.m + 255) / 256 : (a.m + 511) / 512;
     const int tile = (a.m + tiles - 1) / tiles;
     const int pad = (tile + 31) / 32 * 32;
     a.ntok_tile = pad;
@@ -464,6 +557,7 @@ void gemm_tc_plan(GemmTcArgs& a, int sm_count, dim3* grid, size_t* smem, size_t*
     static const int env_nw = []() { const char* e = getenv("SMEG_TC_NW"); return e ? atoi(e) : 0; }();
     a.nw = (2 * pad <= 512 && pad >= 64 && col_tiles_1 >= 2 * sm_count * 3 / 4) ? 2 : 1;
     if ((env_nw == 1 || env_nw == 2) && env_nw * pad <= 512) a.nw = env_nw;
+    if (a.glu) a.nw = 2;
     int cols = 32;
     while (cols < a.nw * pad) cols *= 2;
     a.tmem_cols = cols;
@@ -481,7 +575,7 @@ void gemm_tc_plan(GemmTcArgs& a, int sm_count, dim3* grid, size_t* smem, size_t*
     int splits = 1;
     {
         const int base = col_tiles * tiles;
-        if (pad <= 64) {
+        if (pad <= 64 && !a.glu) {
             double best = 0.0;
             for (int s = 1; s <= 16; s *= 2) {
                 if (s > 1 && stages_all / s < 8) break;
@@ -492,7 +586,7 @@ void gemm_tc_plan(GemmTcArgs& a, int sm_count, dim3* grid, size_t* smem, size_t*
                 if (eff > best + 1e-9) { best = eff; splits = s; }
             }
         } else if (pad <= 256) {
-            while (base * splits * 2 <= sm_count && stages_all / (splits * 2) >= 16 && splits < 8) splits *= 2;
+            while (base * splits * 2 <= sm_count && stages_all / (splits * 2) >= 7 && splits < 8) splits *= 2;
         }
     }
     const int tok_bytes = pad * 128;

@@ -66,6 +66,9 @@ struct GemmTcArgs {
     const uint16_t* a;            // tokens, row-major m x k (T bits), 16-byte aligned rows
     uint16_t* c;                  // m x n (T bits)
     float* c32;                   // if set: raw f32 accumulators instead
+    float* yacc;                  // if set: y[m][n] += f32(T(acc)) instead of storing C (the MLP's residual add)
+    int glu;                      // 0, or SMEG_ACT_SILU / _GELU: W is a gate/up matrix interleaved 32 columns at a time and
+                                  // C (m x n/2) receives T(act(T(gate)) * T(up))
     int m, n, k;
     int n16, ku, nb, log2_block;
     int ntok_tile, ntok_pad, ntok_box, nmma, tmem_cols, sc_rows;       // planner-filled

@@ -184,6 +184,49 @@ def test_mlp_equals_its_three_calls_and_the_oracle(m):
     assert torch.equal(y4, y)
 
 
+@pytest.mark.parametrize("m,d,f", [(65, 256, 1152), (130, 192, 2048), (300, 512, 1024)])
+def test_prefill_mlp_with_fused_gate_and_residual_equals_its_three_calls(m, d, f):
+    """Above 64 rows the block runs as two tensor-core GEMMs -- the gated product formed in the
+    gate/up GEMM's store, the residual add in the down GEMM's -- and must give the bits of the
+    three separate calls plus add_f16 (tests/correctness/model.rs:447-510), also through the
+    tensor-parallel partial / finish pair."""
+    rng = np.random.default_rng(m)
+    wg = (rng.standard_normal(f * d) * 0.05).astype(np.float32)
+    wu = (rng.standard_normal(f * d) * 0.05).astype(np.float32)
+    wd = (rng.standard_normal(d * f) * 0.05).astype(np.float32)
+    up = sg.GatedLinear.quantize(wg, wu, sg.WeightLayout.OutIn, f, d, sg.Gate.Silu)
+    down = sg.Linear.quantize(wd, sg.WeightLayout.OutIn, d, f)
+    mlp = sg.Mlp.gated(up, down)
+    x = torch.from_numpy(rng.standard_normal((m, d)).astype(np.float16)).cuda()
+    y0 = rng.standard_normal((m, d)).astype(np.float32)
+    y = torch.from_numpy(y0.copy()).cuda()
+    mlp.accumulate(x, y, m)
+    hid = torch.zeros((m, f), dtype=torch.float16, device="cuda")
+    out = torch.zeros((m, d), dtype=torch.float16, device="cuda")
+    up.forward(x, hid, m)
+    down.forward(hid, out, m)
+    y3 = torch.from_numpy(y0.copy()).cuda()
+    assert sg.lib().smeg_add_f16_to_f32_dev(y3.data_ptr(), out.data_ptr(), m * d, 0) == 0
+    torch.cuda.synchronize()
+    assert sg.last_status() == 0
+    assert torch.equal(y, y3)
+    part = torch.zeros((m, d), dtype=torch.float32, device="cuda")
+    mlp.partial(x, part, m)
+    y4 = torch.from_numpy(y0.copy()).cuda()
+    sg.Mlp.finish(y4, part)
+    torch.cuda.synchronize()
+    assert torch.equal(y4, y)
+    # sampled rows against the oracle block
+    both_w = sg.interleave_gate_up(wg, wu, sg.WeightLayout.OutIn, f, d)
+    guq, gus, _ = orc.q4_quantize(both_w, 1, 2 * f, d)
+    dq, ds, _ = orc.q4_quantize(wd, 0, d, f)
+    xs = x.cpu().numpy()
+    for r0 in (0, m // 2, m - 1):
+        want = y0[r0:r0 + 1].copy()
+        orc.mlp_accumulate(xs[r0:r0 + 1], want, 1, d, f, guq, gus, dq, ds)
+        assert max_rel(y.cpu().numpy()[r0:r0 + 1] - y0[r0:r0 + 1], want - y0[r0:r0 + 1]) <= 1e-2
+
+
 def test_concurrent_host_threads_share_weights_bit_identically():
     """tests/concurrency.rs:130-180: 4 threads x 4 repetitions on shared weights."""
     import threading
