@@ -10,19 +10,24 @@
 //
 // One CTA owns NW x 128 weight columns (the MMA's M dimension; NW = 1 or 2 accumulator sets) x a
 // tile of up to 512 tokens (the MMA's N dimension, one or two instructions of N <= 256) over a
-// slice of the depth.  Roles (320 threads):
-//   warp 8 (producer)   streams 64-deep stages through a ring of P slots: the token tile by TMA
-//                       (tensor map, 128-byte swizzle) and the CTA's packed weight units + scales
-//                       by bulk copies.  P sets the bytes in flight.
-//   warps 0-7 (dequant) expand packed units into the K-major, 128-byte-swizzled MMA operand in a
-//                       second, shallower ring of O slots: a lane's 16-byte vector becomes four
-//                       16-byte chunks of 8 consecutive depths.
-//   warp 9 (MMA)        one thread issues the stage's tcgen05.mma (K = 16 each) and commits the
-//                       stage back to both rings.
-// After the last stage warps 0-7 drain tensor memory (thread = weight column, registers =
-// tokens).  With the depth split (grid.z > 1) each CTA leaves its f32 partial tile in a global
-// workspace; the CTA that finishes a tile last adds the slices in slice order (so the result does
-// not depend on arrival order), runs the epilogue graph on the rounded product and stores C.
+// slice of the depth, walked in 64-deep stages.  Roles (608 threads):
+//   warp 16 (tokens)    one TMA tile load per stage (tensor map, 128-byte swizzle) into the
+//                       token ring.
+//   warp 18 (weights)   the packed units and scale rows of the CTA's column groups into the
+//                       packed ring.  A slot covers several stages: a bulk copy costs a couple
+//                       of hundred cycles to issue whatever its size, and a column group's
+//                       units are contiguous along K, so one copy carries them for all of them.
+//   warps 0-15 (dequant) expand the stage's packed units into the K-major, 128-byte-swizzled
+//                       MMA operand in the operand ring: a lane's 16-byte vector becomes four
+//                       16-byte chunks of 8 consecutive depths.  With one accumulator set the
+//                       two halves of the warps take alternate stages.
+//   warp 17 (MMA)       one elected thread issues the stage's tcgen05.mma (K = 16 each) and
+//                       commits the stage back to the token and operand rings.
+// After the last stage the dequant warps drain tensor memory (thread = weight column, registers
+// = tokens): the epilogue graph on the rounded product, or -- for the MLP block -- the gated
+// product of a gate/up pair, or the residual add.  With the depth split (grid.z > 1) each CTA
+// leaves its f32 partial tile in a global workspace; the CTA that finishes a tile last adds the
+// slices in slice order (so the result does not depend on arrival order) and stores.
 // Every wait is bounded; a timed-out wait raises the status word and the kernel drains and exits.
 #include "epilogue.cuh"
 #include "kernels.h"
@@ -47,10 +52,9 @@ __device__ long long g_tc_timeline[512 * 12];
 namespace {
 
 constexpr int kDeqWarps = 16;                    // dequant warps (the first 8 also drain tensor memory)
-constexpr int kTcThreads = 32 * (kDeqWarps + 2);
+constexpr int kTcThreads = 32 * (kDeqWarps + 3);   // + token producer, MMA issuer, packed-weight producer
 constexpr int kStageK = 64;                       // depths per stage (one 128-byte swizzle row)
 constexpr int kWTile = 128 * kStageK * 2;         // one 128-column operand tile per stage: 16 KB
-constexpr int kPkTile = 8 * kUnitBytes;           // packed Q4 units of 128 columns x 64 depths: 4 KB
 
 __device__ __forceinline__ uint32_t swz_off(int row, int chunk) {
     // byte offset of 16-byte chunk `chunk` (0..7) of row `row` in a 128B-swizzled K-major tile
@@ -128,23 +132,26 @@ __global__ void __launch_bounds__(kTcThreads, 1) gemm_tc_kernel(const __grid_con
     // the swizzled operands need 1024-byte aligned tiles: align the window by hand
     unsigned char* smem_raw = smem_dyn + ((1024u - (smem_u32(smem_dyn) & 1023u)) & 1023u);
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-    const int P = p.np, O = p.no, NW = p.nw, US = p.us;
-    const int tok_bytes = p.ntok_pad * 128;                    // token operand per 64-deep unit
-    const int sc_rows = p.sc_rows;                             // scale rows (blocks) staged per stage
-    const int pk_slot = ((NW * (US * kPkTile + 8 * sc_rows * 32) + 1023) / 1024) * 1024;
-    const int p_stride = US * tok_bytes + pk_slot;             // ring P slot: [token tiles | packed units | scales]
-    const int o_stride = NW * US * kWTile;                     // ring O slot: NW x US operand tiles
-    // a stage holds 8 * NW * US packed units, one per dequant warp: with only 8 of them the 16
+    const int NT = p.nt, NK = p.nk, O = p.no, NW = p.nw, PU = p.pu;
+    const int tok_bytes = p.ntok_pad * 128;                    // token operand per 64-deep stage
+    const int rpg = p.rpg;                                     // scale rows (blocks) staged per packed slot
+    const int k_code = PU * kUnitBytes;                        // packed slot: [8 NW groups][PU units] then [8 NW groups][rpg rows]
+    const int k_stride = ((8 * NW * (k_code + rpg * 32) + 1023) / 1024) * 1024;
+    const int o_stride = NW * kWTile;                          // ring O slot: NW operand tiles
+    // a stage holds 8 * NW packed units, one per dequant warp: with only 8 of them the 16
     // warps form two groups that take alternate stages
-    const int deq_groups = (8 * NW * US >= kDeqWarps) ? 1 : 2;
+    const int deq_groups = (8 * NW >= kDeqWarps) ? 1 : 2;
     const int deq_wpg = kDeqWarps / deq_groups;
 
     unsigned char* ring_o = smem_raw;
-    unsigned char* ring_p = smem_raw + (size_t)O * o_stride;
-    uint64_t* bars = reinterpret_cast<uint64_t*>(ring_p + (size_t)P * p_stride);
-    uint64_t* p_full = bars;                 // [P] tokens + packed landed
-    uint64_t* p_empty = bars + P;            // [P] released: 8 dequant warps + the MMA commit
-    uint64_t* o_full = bars + 2 * P;         // [O] operand written (256 arrivals)
+    unsigned char* ring_t = ring_o + (size_t)O * o_stride;
+    unsigned char* ring_k = ring_t + (size_t)NT * tok_bytes;
+    uint64_t* bars = reinterpret_cast<uint64_t*>(ring_k + (size_t)NK * k_stride);
+    uint64_t* t_full = bars;                 // [NT] token tile landed
+    uint64_t* t_empty = t_full + NT;         // [NT] the stage's MMAs retired
+    uint64_t* k_full = t_empty + NT;         // [NK] packed units + scale rows landed
+    uint64_t* k_empty = k_full + NK;         // [NK] every dequant warp is past the slot's stages
+    uint64_t* o_full = k_empty + NK;         // [O] operand written
     uint64_t* o_empty = o_full + O;          // [O] MMAs of the stage retired
     uint64_t* acc_full = o_empty + O;        // all MMAs retired
     uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(acc_full + 1);
@@ -155,16 +162,21 @@ __global__ void __launch_bounds__(kTcThreads, 1) gemm_tc_kernel(const __grid_con
     const int sg0 = blockIdx.x * NW;                           // first 128-column super-group
     const int col0 = blockIdx.x * 128 * NW;
     const int tok0 = blockIdx.y * p.ntok_tile;
-    const int stages_all = (p.ku + US - 1) / US;
+    const int stages_all = p.ku;
     const int per_split = (stages_all + (int)gridDim.z - 1) / (int)gridDim.z;
     const int st_begin = blockIdx.z * per_split;
     const int st_end = min(stages_all, st_begin + per_split);
     const int num_stages = max(0, st_end - st_begin);
+    const int num_groups = (num_stages + PU - 1) / PU;         // packed-ring slots this CTA consumes
 
     if (tid == 0) {
-        for (int s = 0; s < P; ++s) {
-            mbar_init(&p_full[s], 1);
-            mbar_init(&p_empty[s], deq_wpg + 1);
+        for (int s = 0; s < NT; ++s) {
+            mbar_init(&t_full[s], 1);
+            mbar_init(&t_empty[s], 1);
+        }
+        for (int s = 0; s < NK; ++s) {
+            mbar_init(&k_full[s], 1);
+            mbar_init(&k_empty[s], kDeqWarps);
         }
         for (int s = 0; s < O; ++s) {
             mbar_init(&o_full[s], 32 * deq_wpg);
@@ -187,43 +199,44 @@ __global__ void __launch_bounds__(kTcThreads, 1) gemm_tc_kernel(const __grid_con
     const uint32_t tmem_base = *tmem_slot;
 
     if (warp == kDeqWarps) {
-        // ===================== producer =====================
-        // the whole warp walks the stages; after lane 0 has armed the barrier the stage's copies
-        // are issued by one lane each (token tiles: lane 0; packed units: lanes 0-15; scale rows:
-        // lanes 16-31), so their issue cost does not add up on one thread
-        for (int i = 0; i < num_stages; ++i) {
-            const int slot = i % P;
-            if (lane == 0) SMEG_TL(0, i);
-            // the verdict is made warp-uniform so that no lane is left behind at a warp barrier
-            if (i >= P && !__all_sync(0xffffffffu, mbar_wait(&p_empty[slot], ((i / P) - 1) & 1, abort_flag, p.status, STATUS_TMEM_TIMEOUT))) break;
-            if (lane == 0) SMEG_TL(1, i);
-            unsigned char* sb = ring_p + (size_t)slot * p_stride;
-            const int st = st_begin + i;
-            const int u0 = st * US;                                     // first 64-deep unit of the stage
-            const int units = min(US, p.ku - u0);
+        // ===================== token producer =====================
+        if (lane == 0) {
+            for (int i = 0; i < num_stages; ++i) {
+                const int slot = i % NT;
+                SMEG_TL(0, i);
+                if (i >= NT && !mbar_wait(&t_empty[slot], ((i / NT) - 1) & 1, abort_flag, p.status, STATUS_TMEM_TIMEOUT)) break;
+                SMEG_TL(1, i);
+                unsigned char* sb = ring_t + (size_t)slot * tok_bytes;
+                const int d0 = (st_begin + i) * kStageK;
+                mbar_expect_tx(&t_full[slot], (unsigned)tok_bytes);
+                tma_load_2d(sb, &tmap_tok, d0, tok0, &t_full[slot]);
+                if (p.nmma == 2) tma_load_2d(sb + tok_bytes / 2, &tmap_tok, d0, tok0 + p.ntok_box, &t_full[slot]);
+            }
+        }
+    } else if (warp == kDeqWarps + 2) {
+        // ===================== packed-weight producer =====================
+        // One slot covers PU stages: issuing a bulk copy costs a couple of hundred cycles whatever its
+        // size, so a column group's units of PU stages (contiguous along K) travel as one copy, and so do
+        // its scale rows.  Lanes 0-15 issue the code runs, lanes 16-31 the scale rows.
+        for (int gq = 0; gq < num_groups; ++gq) {
+            const int slot = gq % NK;
+            if (gq >= NK && !__all_sync(0xffffffffu, mbar_wait(&k_empty[slot], ((gq / NK) - 1) & 1, abort_flag, p.status, STATUS_TMEM_TIMEOUT))) break;
+            unsigned char* sb = ring_k + (size_t)slot * k_stride;
+            const int u0 = st_begin + gq * PU;                          // first 64-deep unit of the slot
+            const int units = min(PU, st_end - u0);
             const int d0 = u0 * kStageK;
             const int blk0 = d0 >> p.log2_block;
             const int blk1 = min(p.nb, ((d0 + units * kStageK - 1) >> p.log2_block) + 1);
             const int rows = blk1 - blk0;
-            if (lane == 0) {
-                mbar_expect_tx(&p_full[slot], (unsigned)(units * tok_bytes) + (unsigned)NW * (units * kPkTile + rows * 256u));
-                for (int uu = 0; uu < units; ++uu) {
-                    tma_load_2d(sb + uu * tok_bytes, &tmap_tok, d0 + uu * kStageK, tok0, &p_full[slot]);
-                    if (p.nmma == 2)
-                        tma_load_2d(sb + uu * tok_bytes + tok_bytes / 2, &tmap_tok, d0 + uu * kStageK, tok0 + p.ntok_box, &p_full[slot]);
-                }
-            }
+            if (lane == 0) mbar_expect_tx(&k_full[slot], (unsigned)(8 * NW) * (unsigned)(units * kUnitBytes + rows * 32));
             __syncwarp();
-            unsigned char* pkdst = sb + US * tok_bytes;
-            unsigned char* scdst = pkdst + NW * US * kPkTile;
             const int c = lane & 15;
             if (c < 8 * NW) {
                 const size_t cgi = (size_t)min(sg0 * 8 + c, p.n16 - 1);   // a tail group re-reads the last one
-                // [column group][units of the stage][512 B] and [column group][blocks of the stage][16]
                 if (lane < 16)
-                    bulk_g2s(pkdst + (size_t)c * US * kUnitBytes, p.codes + q4_unit_offset(cgi, (size_t)u0, p.ku), units * kUnitBytes, &p_full[slot]);
+                    bulk_g2s(sb + (size_t)c * k_code, p.codes + q4_unit_offset(cgi, (size_t)u0, p.ku), units * kUnitBytes, &k_full[slot]);
                 else
-                    bulk_g2s(scdst + (size_t)c * sc_rows * 32, p.scales + q4_scale_row(cgi, blk0, p.nb), rows * 32, &p_full[slot]);
+                    bulk_g2s(sb + (size_t)8 * NW * k_code + (size_t)c * rpg * 32, p.scales + q4_scale_row(cgi, blk0, p.nb), rows * 32, &k_full[slot]);
             }
             __syncwarp();
         }
@@ -233,31 +246,28 @@ __global__ void __launch_bounds__(kTcThreads, 1) gemm_tc_kernel(const __grid_con
         const uint32_t idesc = umma_idesc(BF16, 128, p.ntok_box);
         const uint32_t tok_half = (uint32_t)(tok_bytes / 2);
         for (int i = 0; i < num_stages; ++i) {
-            const int ps = i % P, os = i % O;
-            if (!__all_sync(0xffffffffu, mbar_wait(&p_full[ps], (i / P) & 1, abort_flag, p.status, STATUS_TMEM_TIMEOUT))) break;
+            const int ts = i % NT, os = i % O;
+            if (!__all_sync(0xffffffffu, mbar_wait(&t_full[ts], (i / NT) & 1, abort_flag, p.status, STATUS_TMEM_TIMEOUT))) break;
             if (lane == 0) SMEG_TL(5, i);
             if (!__all_sync(0xffffffffu, mbar_wait(&o_full[os], (i / O) & 1, abort_flag, p.status, STATUS_TMEM_TIMEOUT))) break;
             if (lane == 0) SMEG_TL(6, i);
             tc_fence_after();
-            const uint32_t tok_addr = smem_u32(ring_p + (size_t)ps * p_stride);
+            const uint32_t tok_addr = smem_u32(ring_t + (size_t)ts * tok_bytes);
             const uint32_t w_addr = smem_u32(ring_o + (size_t)os * o_stride);
-            const int units = min(US, p.ku - (st_begin + i) * US);
             if (elect_one()) {
-                for (int uu = 0; uu < units; ++uu) {
-                    for (int w = 0; w < NW; ++w) {
-                        const uint64_t a_desc0 = umma_desc_sw128(w_addr + (w * US + uu) * kWTile);
-                        for (int h = 0; h < p.nmma; ++h) {
-                            const uint64_t b_desc0 = umma_desc_sw128(tok_addr + uu * tok_bytes + h * tok_half);
-                            const uint32_t d_tmem = tmem_base + (uint32_t)((w * p.nmma + h) * p.ntok_box);
+                for (int w = 0; w < NW; ++w) {
+                    const uint64_t a_desc0 = umma_desc_sw128(w_addr + w * kWTile);
+                    for (int h = 0; h < p.nmma; ++h) {
+                        const uint64_t b_desc0 = umma_desc_sw128(tok_addr + h * tok_half);
+                        const uint32_t d_tmem = tmem_base + (uint32_t)((w * p.nmma + h) * p.ntok_box);
 #pragma unroll
-                            for (int ks = 0; ks < kStageK / 16; ++ks)
-                                umma_f16(d_tmem, a_desc0 + 2 * ks, b_desc0 + 2 * ks, idesc, (i > 0 || uu > 0 || ks > 0) ? 1u : 0u);
-                        }
+                        for (int ks = 0; ks < kStageK / 16; ++ks)
+                            umma_f16(d_tmem, a_desc0 + 2 * ks, b_desc0 + 2 * ks, idesc, (i > 0 || ks > 0) ? 1u : 0u);
                     }
                 }
                 SMEG_TL(10, i);
                 umma_commit(&o_empty[os]);
-                umma_commit(&p_empty[ps]);
+                umma_commit(&t_empty[ts]);
                 SMEG_TL(7, i);
             }
             __syncwarp();
@@ -265,45 +275,52 @@ __global__ void __launch_bounds__(kTcThreads, 1) gemm_tc_kernel(const __grid_con
         if (elect_one()) umma_commit(acc_full);
         __syncwarp();
     } else {
-        // ===================== dequant warps (0..7), then epilogue =====================
+        // ===================== dequant warps (0..15), then epilogue =====================
         const int g = lane >> 2, t = lane & 3;
         const int wig = warp % deq_wpg;                        // warp within its group
         for (int i = 0; i < num_stages; ++i) {
-            if (deq_groups == 2 && (i & 1) != (warp >> 3)) continue;
-            const int ps = i % P, os = i % O;
+            const int gq = i / PU, ks = gq % NK;
+            const bool last_of_slot = (i % PU == PU - 1) || (i == num_stages - 1);
+            if (deq_groups == 2 && (i & 1) != (warp >> 3)) {
+                // not this group's stage; a warp that walks past the end of a packed slot still releases it
+                if (last_of_slot) {
+                    __syncwarp();
+                    if (lane == 0) mbar_arrive(&k_empty[ks]);
+                }
+                continue;
+            }
+            const int os = i % O;
             if (wig == 0 && lane == 0) SMEG_TL(2, i);
             if (i >= O && !__all_sync(0xffffffffu, mbar_wait(&o_empty[os], ((i / O) - 1) & 1, abort_flag, p.status, STATUS_TMEM_TIMEOUT))) break;
             if (wig == 0 && lane == 0) SMEG_TL(8, i);
-            if (!__all_sync(0xffffffffu, mbar_wait(&p_full[ps], (i / P) & 1, abort_flag, p.status, STATUS_TMEM_TIMEOUT))) break;
+            if (!__all_sync(0xffffffffu, mbar_wait(&k_full[ks], (gq / NK) & 1, abort_flag, p.status, STATUS_TMEM_TIMEOUT))) break;
             if (wig == 0 && lane == 0) SMEG_TL(3, i);
-            const int u0 = (st_begin + i) * US;
-            const int units = min(US, p.ku - u0);
-            const int d0 = u0 * kStageK;
-            const int blk0 = d0 >> p.log2_block;
-            const unsigned char* pk = ring_p + (size_t)ps * p_stride + US * tok_bytes;
-            const uint16_t* scs = reinterpret_cast<const uint16_t*>(pk + NW * US * kPkTile);
+            const int uq = i % PU;                                  // unit within the packed slot
+            const int du = (st_begin + i) * kStageK;                // depth of the stage
+            const int blk0 = ((st_begin + gq * PU) * kStageK) >> p.log2_block;   // first scale row of the slot
+            const unsigned char* pk = ring_k + (size_t)ks * k_stride;
+            const uint16_t* scs = reinterpret_cast<const uint16_t*>(pk + (size_t)8 * NW * k_code);
             unsigned char* ob = ring_o + (size_t)os * o_stride;
-            // work item c = (w * 8 + column group) * US + uu
-            for (int c = wig; c < 8 * NW * US; c += deq_wpg) {
-                const int uu = c % US, wc = c / US, cgl = wc & 7, w = wc >> 3;
-                if (uu >= units) continue;
-                const int du = d0 + uu * kStageK;
-                const int ra = ((du + 8 * t) >> p.log2_block) - blk0, rb = ((du + 32 + 8 * t) >> p.log2_block) - blk0;
-                const uint4 wv = *reinterpret_cast<const uint4*>(pk + (size_t)c * kUnitBytes + lane * 16);
+            const int ra = ((du + 8 * t) >> p.log2_block) - blk0, rb = ((du + 32 + 8 * t) >> p.log2_block) - blk0;
+            // work item c = w * 8 + column group
+            for (int c = wig; c < 8 * NW; c += deq_wpg) {
+                const int cgl = c & 7, w = c >> 3;
+                const uint4 wv = *reinterpret_cast<const uint4*>(pk + (size_t)c * k_code + uq * kUnitBytes + lane * 16);
                 // gate/up matrix: gate column groups go to operand tile 0 and the matching up groups to tile 1,
                 // so that a thread of the drain holds both values of one hidden unit
                 int tw = w, rg = cgl;
                 if (p.glu) {
-                    const int gi = 8 * w + cgl;                    // group within the CTA; chunks of [2 gate | 2 up] groups
-                    tw = (gi >> 1) & 1;
-                    rg = ((gi >> 2) << 1) | (gi & 1);
+                    tw = (c >> 1) & 1;                             // chunks of [2 gate | 2 up] groups
+                    rg = ((c >> 2) << 1) | (c & 1);
                 }
-                dequant_unit_q4<BF16>(ob + (tw * US + uu) * kWTile, rg, wv, scs + (size_t)wc * sc_rows * 16, ra, rb, g, t);
+                dequant_unit_q4<BF16>(ob + tw * kWTile, rg, wv, scs + (size_t)c * rpg * 16, ra, rb, g, t);
             }
             fence_proxy_async();
             mbar_arrive(&o_full[os]);
-            __syncwarp();
-            if (lane == 0) mbar_arrive(&p_empty[ps]);
+            if (last_of_slot) {
+                __syncwarp();
+                if (lane == 0) mbar_arrive(&k_empty[ks]);
+            }
             if (wig == 0 && lane == 0) SMEG_TL(4, i);
         }
 
@@ -562,16 +579,11 @@ void gemm_tc_plan(GemmTcArgs& a, int sm_count, dim3* grid, size_t* smem, size_t*
     while (cols < a.nw * pad) cols *= 2;
     a.tmem_cols = cols;
     const int block = 1 << a.log2_block;
-    static const int env_us = []() { const char* e = getenv("SMEG_TC_US"); return e ? atoi(e) : 0; }();
-    a.us = pad <= 64 ? 2 : 1;                                    // 64-deep units per stage
-    if (env_us == 1 || env_us == 2 || env_us == 4) a.us = env_us;
-    const int sk = a.us * kStageK;
-    a.sc_rows = block >= sk ? 1 : sk / block;
     const int col_tiles = (a.n + 128 * a.nw - 1) / (128 * a.nw);
     // depth split: one CTA per SM is resident.  Small token tiles (decode) split until the grid
     // wastes little of its last wave; larger ones only when the column tiles alone cannot fill the
     // machine (each slice costs a workspace round trip of the whole partial tile)
-    const int stages_all = (a.ku + a.us - 1) / a.us;
+    const int stages_all = a.ku;
     int splits = 1;
     {
         const int base = col_tiles * tiles;
@@ -589,22 +601,37 @@ void gemm_tc_plan(GemmTcArgs& a, int sm_count, dim3* grid, size_t* smem, size_t*
             while (base * splits * 2 <= sm_count && stages_all / (splits * 2) >= 7 && splits < 8) splits *= 2;
         }
     }
-    const int tok_bytes = pad * 128;
-    const int pk_slot = ((a.nw * (a.us * kPkTile + 8 * a.sc_rows * 32) + 1023) / 1024) * 1024;
-    const int p_stride = a.us * tok_bytes + pk_slot, o_stride = a.nw * a.us * kWTile;
-    const int budget = 216 * 1024;
+    // shared memory: operand ring (NW x 16 KB per slot), token ring (pad x 128 B per slot) and the packed-weight
+    // ring, whose slots cover PU stages each so that one bulk copy moves a column group's units of PU stages
+    const int tok_bytes = pad * 128, o_stride = a.nw * kWTile;
+    const int budget = 214 * 1024;
     static const int env_no = []() { const char* e = getenv("SMEG_TC_NO"); return e ? atoi(e) : 0; }();
-    // operand ring: three slots let the dequant warps run a stage ahead of the MMAs when the
-    // packed/token ring still keeps at least two stages in flight
-    a.no = a.nw == 2 ? 2 : 3;
-    if ((budget - 2048 - a.no * o_stride) / p_stride < 2) a.no = 2;
-    if (env_no >= 2 && env_no <= 6) a.no = env_no;
-    int np = (budget - 2048 - a.no * o_stride) / p_stride;
-    if (np > 12) np = 12;
-    if (np < 2) np = 2;
-    a.np = np;
-    *smem = 1024 + (size_t)a.no * o_stride + (size_t)np * p_stride + (size_t)(2 * np + 2 * a.no + 4) * 8 +
-            kMaxInlineNodes * sizeof(EpNodeDev) + 64;
+    static const int env_pu = []() { const char* e = getenv("SMEG_TC_PU"); return e ? atoi(e) : 0; }();
+    const int per_cta_stages = (stages_all + splits - 1) / splits;
+    int best_score = -1;
+    for (int pu = 8; pu >= 1; pu /= 2) {
+        if (env_pu && pu != env_pu) continue;
+        const int rpg = block <= kStageK ? pu * kStageK / block : pu * kStageK / block + 1;
+        const int k_stride = ((8 * a.nw * (pu * kUnitBytes + rpg * 32) + 1023) / 1024) * 1024;
+        for (int no = 3; no >= 2; --no) {
+            if (env_no >= 2 && env_no <= 3 && no != env_no) continue;
+            for (int nk = 4; nk >= 2; --nk) {
+                const int left = budget - 2048 - no * o_stride - nk * k_stride;
+                if (left < 2 * tok_bytes) continue;
+                int nt = left / tok_bytes;
+                if (nt > 8) nt = 8;
+                // prefer: at least three token slots, then few copies per stage (large PU), then depth
+                const int score = (nt >= 3 ? 1000 : 0) + (pu > per_cta_stages ? 0 : pu * 50) + (no == 3 ? 20 : 0) + nk * 5 + nt;
+                if (score > best_score) {
+                    best_score = score;
+                    a.pu = pu; a.rpg = rpg; a.no = no; a.nk = nk; a.nt = nt;
+                }
+            }
+        }
+    }
+    const int k_stride = ((8 * a.nw * (a.pu * kUnitBytes + a.rpg * 32) + 1023) / 1024) * 1024;
+    *smem = 1024 + (size_t)a.no * o_stride + (size_t)a.nt * tok_bytes + (size_t)a.nk * k_stride +
+            (size_t)(2 * a.nt + 2 * a.nk + 2 * a.no + 4) * 8 + kMaxInlineNodes * sizeof(EpNodeDev) + 64;
     *grid = dim3(col_tiles, tiles, splits);
     *ws_floats = splits > 1 ? (size_t)col_tiles * tiles * splits * (a.nw * 128) * pad : 0;
     *n_counters = splits > 1 ? (size_t)col_tiles * tiles : 0;

@@ -71,9 +71,11 @@ struct GemmTcArgs {
                                   // C (m x n/2) receives T(act(T(gate)) * T(up))
     int m, n, k;
     int n16, ku, nb, log2_block;
-    int ntok_tile, ntok_pad, ntok_box, nmma, tmem_cols, sc_rows;       // planner-filled
+    int ntok_tile, ntok_pad, ntok_box, nmma, tmem_cols;                // planner-filled
     int ep_fast;                  // the graph runs as a per-thread FastEp (see epilogue.cuh)
-    int np, no, nw, us;           // ring depths (packed / operand), accumulator sets, units per stage
+    int nt, nk, no, nw;           // ring depths (tokens / packed / operand), accumulator sets per CTA
+    int pu;                       // 64-deep stages covered by one packed-ring slot
+    int rpg;                      // scale rows staged per packed-ring slot
     float* ws;                    // split-depth workspace [tile][slice][token][column]
     int* counters;                // one per output tile, zero between launches
     unsigned* status;
