@@ -89,6 +89,7 @@ void smeg_trace(int on);
 typedef struct smeg_q4 smeg_q4;          /* Q4Weights, src/kernels/q4/weights.rs:26-37 */
 typedef struct smeg_lowbit smeg_lowbit;  /* Q2Weights / Q1Weights, src/kernels/lowbit/q2.rs:31-38, q1.rs:23-30 */
 typedef struct smeg_mlp smeg_mlp;        /* Mlp (gated), src/mlp.rs:56-92 */
+typedef struct smeg_dense smeg_dense;    /* Packed<f16> / Packed<bf16>, src/element.rs */
 
 #define SMEG_LAYOUT_OUT_IN 0             /* WeightLayout::OutIn: w[j*k + d] */
 #define SMEG_LAYOUT_IN_OUT 1             /* WeightLayout::InOut: w[d*n + j] */
@@ -218,6 +219,23 @@ int smeg_matmul_q4_f16(const smeg_q4 *w, const uint16_t *a, uint16_t *c, size_t 
 int smeg_matmul_q4_bf16(const smeg_q4 *w, const uint16_t *a, uint16_t *c, size_t m, const ep_desc16 *ep);
 int smeg_matmul_lowbit(const smeg_lowbit *w, const uint16_t *a, uint16_t *c, size_t m, const ep_desc16 *ep);
 int smeg_matmul_lowbit_f16(const smeg_lowbit *w, const uint16_t *a, uint16_t *c, size_t m, const ep_desc16 *ep);
+
+/* ---- dense 16-bit weights: the Gemm builder --------------------------------------- */
+
+/* prepack_f16 / prepack_bf16 (src/kernels/f16.rs:212, src/kernels/bf16.rs): b is k x n row-major
+ * T bits; the handle keeps it K-major on the device. */
+int smeg_dense_create(const uint16_t *b, size_t n, size_t k, int bf16, smeg_dense **out);
+void smeg_dense_destroy(smeg_dense *w);
+size_t smeg_dense_n(const smeg_dense *w);
+size_t smeg_dense_k(const smeg_dense *w);
+/* Gemm::run (src/exec/builder.rs:803-813 -> packed_ep_impl, src/exec/macros.rs:98-200):
+ * C = ep( T(beta * (A @ B)) ), C row-major m x n or, with col_major, c[i + j * m].  Replaces
+ * gemm_sme_f16f16_run_packed / gemm_sme_b16b16_run_packed (csrc/sme_gemm_api.h) for this use.
+ * k must be a multiple of 8 and a 16-byte aligned (rc = -3 otherwise). */
+int smeg_gemm_dense_dev(const smeg_dense *w, const uint16_t *a, uint16_t *c, size_t m, uint16_t beta_bits,
+                        int col_major, const ep_desc16 *ep, void *stream);
+int smeg_gemm_dense(const smeg_dense *w, const uint16_t *a, uint16_t *c, size_t m, uint16_t beta_bits,
+                    int col_major, const ep_desc16 *ep);
 
 /* ---- MLP block ---------------------------------------------------------------- */
 

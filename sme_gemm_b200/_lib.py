@@ -92,6 +92,12 @@ SIGNATURES = {
     "smeg_matmul_q4_bf16": (_i, [_vp, _vp, _vp, _sz, _epp]),
     "smeg_matmul_lowbit": (_i, [_vp, _vp, _vp, _sz, _epp]),
     "smeg_matmul_lowbit_f16": (_i, [_vp, _vp, _vp, _sz, _epp]),
+    "smeg_dense_create": (_i, [_vp, _sz, _sz, _i, _pp]),
+    "smeg_dense_destroy": (None, [_vp]),
+    "smeg_dense_n": (_sz, [_vp]),
+    "smeg_dense_k": (_sz, [_vp]),
+    "smeg_gemm_dense_dev": (_i, [_vp, _vp, _vp, _sz, C.c_uint16, _i, _epp, _vp]),
+    "smeg_gemm_dense": (_i, [_vp, _vp, _vp, _sz, C.c_uint16, _i, _epp]),
     "smeg_mlp_create": (_i, [_vp, _vp, _u32, _pp]),
     "smeg_mlp_destroy": (None, [_vp]),
     "smeg_mlp_accumulate_dev": (_i, [_vp, _vp, _vp, _sz, _vp]),

@@ -132,6 +132,7 @@ struct TraceScope {
     }
 };
 
+float __uint_as_float_host(uint32_t u) { float f; memcpy(&f, &u, 4); return f; }
 bool is_pow2(size_t x) { return x != 0 && (x & (x - 1)) == 0; }
 bool mul_overflows(size_t a, size_t b) { return a != 0 && b > (size_t)-1 / a; }
 
@@ -696,6 +697,68 @@ int smeg_matmul_lowbit_f16_dev(const smeg_lowbit* w, const uint16_t* a, uint16_t
     return q4_dev(t, a, c, m, ep, 0, (cudaStream_t)stream);
 }
 
+// ---- dense 16-bit weights: prepack_f16 / prepack_bf16 + the Gemm builder's run ----
+int smeg_dense_create(const uint16_t* b, size_t n, size_t k, int bf16, smeg_dense** out) {
+    if (!out) return -4;
+    *out = nullptr;
+    if (mul_overflows(n, k) || ((n != 0 && k != 0) && !b)) return -4;
+    if (!dev_state()) return -5;
+    smeg_dense* h = new smeg_dense();
+    h->n = n; h->k = k; h->kd = (k + 7) / 8 * 8; h->bf16 = bf16 ? 1 : 0;
+    // b is k x n row-major (prepack_f16, src/kernels/f16.rs:212); the tensor cores take K-major rows
+    std::vector<uint16_t> w(n * h->kd, 0);
+    for (size_t d = 0; d < k; ++d)
+        for (size_t j = 0; j < n; ++j) w[j * h->kd + d] = b[d * n + j];
+    if (upload(w, &h->w)) { smeg_dense_destroy(h); return -2; }
+    *out = h;
+    return 0;
+}
+void smeg_dense_destroy(smeg_dense* w) {
+    if (!w) return;
+    if (w->w) cudaFree(w->w);
+    delete w;
+}
+size_t smeg_dense_n(const smeg_dense* w) { return w->n; }
+size_t smeg_dense_k(const smeg_dense* w) { return w->k; }
+
+int smeg_gemm_dense_dev(const smeg_dense* w, const uint16_t* a, uint16_t* c, size_t m, uint16_t beta_bits, int col_major,
+                        const ep_desc16* ep, void* stream_v) {
+    if (!w) return -4;
+    cudaStream_t stream = (cudaStream_t)stream_v;
+    const size_t n = w->n, k = w->k;
+    if (m == 0 || n == 0) return 0;
+    if (!c || (k && !a) || m > 0x7fffffffu || n > 0x7fffffffu || k > 0x7fffffffu) return -4;
+    // the token tile travels by TMA: rows of 16-byte multiples at a 16-byte aligned base
+    if (k == 0 || k % 8 != 0 || ((uintptr_t)a & 15) != 0) return -3;
+    DeviceState* ds = dev_state();
+    if (!ds) return -5;
+    if (!gemm_tc_supported(16, (int)m, (int)k, 5, a)) return -3;
+    GemmTcArgs t;
+    memset(&t, 0, sizeof(t));
+    EpNodeDev* ext = nullptr;
+    int rc = make_ep(ep, n, &t.ep, stream, &ext);
+    if (rc) { if (ext) cudaFreeAsync(ext, stream); return rc; }
+    t.wdense = w->w; t.kd = (int)w->kd; t.a = a; t.c = c;
+    t.beta = w->bf16 ? __uint_as_float_host((uint32_t)beta_bits << 16) : h2f(beta_bits);
+    t.col_major = col_major ? 1 : 0;
+    t.m = (int)m; t.n = (int)n; t.k = (int)k;
+    t.n16 = (int)((n + 15) / 16); t.ku = (int)((k + 63) / 64); t.nb = 0; t.log2_block = 5;
+    t.status = ds->status;
+    dim3 grid;
+    size_t smem = 0, ws_floats = 0, ncounters = 0;
+    gemm_tc_plan(t, ds->sm_count, &grid, &smem, &ws_floats, &ncounters);
+    TcScratch sc;
+    if (ws_floats && tc_scratch(stream, ws_floats, ncounters, &sc)) {
+        if (ext) cudaFreeAsync(ext, stream);
+        return -2;
+    }
+    t.ws = sc.ws;
+    t.counters = sc.counters;
+    cudaError_t e = gemm_tc_launch(t, w->bf16, grid, smem, stream);
+    if (ext) cudaFreeAsync(ext, stream);
+    return e == cudaSuccess ? 0 : -6;
+}
+
 int smeg_glu_f16_dev(uint16_t* out, const uint16_t* both, size_t m, size_t n, uint32_t act, void* stream) {
     if (act != SMEG_ACT_SILU && act != SMEG_ACT_GELU) return -4;
     return glu_launch(out, both, m, n, act, (cudaStream_t)stream) == cudaSuccess ? 0 : -6;
@@ -784,6 +847,14 @@ int smeg_matmul_lowbit_f16(const smeg_lowbit* w, const uint16_t* a, uint16_t* c,
     TraceScope ts(w->bits == 2 ? "matmul_q2_mopa" : "matmul_q1_mopa", m, w->d.n, w->d.k);
     return host_matmul(m, w->d.n, w->d.k, a, c, ep, [&](const uint16_t* da, uint16_t* dc, const ep_desc16* dep) {
         return smeg_matmul_lowbit_f16_dev(w, da, dc, m, dep, nullptr);
+    });
+}
+int smeg_gemm_dense(const smeg_dense* w, const uint16_t* a, uint16_t* c, size_t m, uint16_t beta_bits, int col_major,
+                    const ep_desc16* ep) {
+    if (!w) return -4;
+    TraceScope ts(w->bf16 ? "gemm_bf16_packed" : "gemm_f16_packed", m, w->n, w->k);
+    return host_matmul(m, w->n, w->k, a, c, ep, [&](const uint16_t* da, uint16_t* dc, const ep_desc16* dep) {
+        return smeg_gemm_dense_dev(w, da, dc, m, beta_bits, col_major, dep, nullptr);
     });
 }
 

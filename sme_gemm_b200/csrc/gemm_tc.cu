@@ -127,7 +127,7 @@ __device__ __forceinline__ void dequant_unit_q4(unsigned char* tile, int cu, con
 }
 
 template <int BF16>
-__global__ void __launch_bounds__(kTcThreads, 1) gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_tok, GemmTcArgs p) {
+__global__ void __launch_bounds__(kTcThreads, 1) gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_tok, const __grid_constant__ CUtensorMap tmap_w, GemmTcArgs p) {
     extern __shared__ unsigned char smem_dyn[];
     // the swizzled operands need 1024-byte aligned tiles: align the window by hand
     unsigned char* smem_raw = smem_dyn + ((1024u - (smem_u32(smem_dyn) & 1023u)) & 1023u);
@@ -146,7 +146,8 @@ __global__ void __launch_bounds__(kTcThreads, 1) gemm_tc_kernel(const __grid_con
     unsigned char* ring_o = smem_raw;
     unsigned char* ring_t = ring_o + (size_t)O * o_stride;
     unsigned char* ring_k = ring_t + (size_t)NT * tok_bytes;
-    uint64_t* bars = reinterpret_cast<uint64_t*>(ring_k + (size_t)NK * k_stride);
+    const bool dense = p.wdense != nullptr;                    // then there is no packed ring
+    uint64_t* bars = reinterpret_cast<uint64_t*>(ring_k + (dense ? (size_t)0 : (size_t)NK * k_stride));
     uint64_t* t_full = bars;                 // [NT] token tile landed
     uint64_t* t_empty = t_full + NT;         // [NT] the stage's MMAs retired
     uint64_t* k_full = t_empty + NT;         // [NK] packed units + scale rows landed
@@ -179,7 +180,7 @@ __global__ void __launch_bounds__(kTcThreads, 1) gemm_tc_kernel(const __grid_con
             mbar_init(&k_empty[s], kDeqWarps);
         }
         for (int s = 0; s < O; ++s) {
-            mbar_init(&o_full[s], 32 * deq_wpg);
+            mbar_init(&o_full[s], p.wdense ? 1 : 32 * deq_wpg);
             mbar_init(&o_empty[s], 1);
         }
         mbar_init(acc_full, 1);
@@ -218,6 +219,20 @@ __global__ void __launch_bounds__(kTcThreads, 1) gemm_tc_kernel(const __grid_con
         // One slot covers PU stages: issuing a bulk copy costs a couple of hundred cycles whatever its
         // size, so a column group's units of PU stages (contiguous along K) travel as one copy, and so do
         // its scale rows.  Lanes 0-15 issue the code runs, lanes 16-31 the scale rows.
+        if (dense) {
+            // dense 16-bit weights need no expansion: their K-major tiles go straight into the operand ring
+            if (lane == 0) {
+                tma_prefetch_desc(&tmap_w);
+                for (int i = 0; i < num_stages; ++i) {
+                    const int os = i % O;
+                    if (i >= O && !mbar_wait(&o_empty[os], ((i / O) - 1) & 1, abort_flag, p.status, STATUS_TMEM_TIMEOUT)) break;
+                    unsigned char* ob = ring_o + (size_t)os * o_stride;
+                    mbar_expect_tx(&o_full[os], (unsigned)(NW * kWTile));
+                    for (int w = 0; w < NW; ++w)
+                        tma_load_2d(ob + w * kWTile, &tmap_w, (st_begin + i) * kStageK, col0 + 128 * w, &o_full[os]);
+                }
+            }
+        } else
         for (int gq = 0; gq < num_groups; ++gq) {
             const int slot = gq % NK;
             if (gq >= NK && !__all_sync(0xffffffffu, mbar_wait(&k_empty[slot], ((gq / NK) - 1) & 1, abort_flag, p.status, STATUS_TMEM_TIMEOUT))) break;
@@ -278,7 +293,7 @@ __global__ void __launch_bounds__(kTcThreads, 1) gemm_tc_kernel(const __grid_con
         // ===================== dequant warps (0..15), then epilogue =====================
         const int g = lane >> 2, t = lane & 3;
         const int wig = warp % deq_wpg;                        // warp within its group
-        for (int i = 0; i < num_stages; ++i) {
+        for (int i = 0; i < (dense ? 0 : num_stages); ++i) {
             const int gq = i / PU, ks = gq % NK;
             const bool last_of_slot = (i % PU == PU - 1) || (i == num_stages - 1);
             if (deq_groups == 2 && (i & 1) != (warp >> 3)) {
@@ -379,6 +394,10 @@ __global__ void __launch_bounds__(kTcThreads, 1) gemm_tc_kernel(const __grid_con
                     for (int j = 0; j < 16; ++j) r[j] = 0u;
                 }
                 if (splits == 1) {
+                    if (p.beta != 1.0f) {
+#pragma unroll
+                        for (int j = 0; j < 16; ++j) r[j] = __float_as_uint(__fmul_rn(p.beta, __uint_as_float(r[j])));
+                    }
                     if (col < p.n) {
                         if (p.c32) {
 #pragma unroll
@@ -405,7 +424,7 @@ __global__ void __launch_bounds__(kTcThreads, 1) gemm_tc_kernel(const __grid_con
                             }
 #pragma unroll
                             for (int j = 0; j < 16; ++j)
-                                if (tok0 + j0 + j < p.m) p.c[(size_t)(tok0 + j0 + j) * p.n + col] = v[j];
+                                if (tok0 + j0 + j < p.m) p.c[p.col_major ? (size_t)col * p.m + (tok0 + j0 + j) : (size_t)(tok0 + j0 + j) * p.n + col] = v[j];
                         }
                     }
                 } else {
@@ -492,10 +511,12 @@ __global__ void __launch_bounds__(kTcThreads, 1) gemm_tc_kernel(const __grid_con
                         for (int jj = 0; jj < 8; ++jj) {
                             const int tok = tok0 + j0 + jj;
                             if (tok >= p.m) continue;
+                            if (p.beta != 1.0f) acc[jj] = __fmul_rn(p.beta, acc[jj]);
+                            const size_t ci = p.col_major ? (size_t)col * p.m + tok : (size_t)tok * p.n + col;
                             if (p.c32) p.c32[(size_t)tok * p.n + col] = acc[jj];
                             else if (p.yacc) p.yacc[(size_t)tok * p.n + col] = __fadd_rn(yv[jj], t_to_f32<BF16>(f32_to_t<BF16>(acc[jj])));
-                            else if (p.ep_fast) p.c[(size_t)tok * p.n + col] = fast_ep_store<BF16>(fe, acc[jj]);
-                            else p.c[(size_t)tok * p.n + col] = ep_store_nodes<BF16>(nodes, p.ep.n_nodes, acc[jj], (size_t)tok, (size_t)col);
+                            else if (p.ep_fast) p.c[ci] = fast_ep_store<BF16>(fe, acc[jj]);
+                            else p.c[ci] = ep_store_nodes<BF16>(nodes, p.ep.n_nodes, acc[jj], (size_t)tok, (size_t)col);
                         }
                     }
                 }
@@ -526,7 +547,7 @@ EncodeTiledFn encode_fn() {
 }
 
 template <int BF16>
-cudaError_t launch_tc(const CUtensorMap& tm, const GemmTcArgs& a, dim3 grid, size_t smem, cudaStream_t stream) {
+cudaError_t launch_tc(const CUtensorMap& tm, const CUtensorMap& tw, const GemmTcArgs& a, dim3 grid, size_t smem, cudaStream_t stream) {
     auto kern = gemm_tc_kernel<BF16>;
     static int attr_dev = -1;
     int dev = 0;
@@ -536,7 +557,7 @@ cudaError_t launch_tc(const CUtensorMap& tm, const GemmTcArgs& a, dim3 grid, siz
         if (e != cudaSuccess) return e;
         attr_dev = dev;
     }
-    kern<<<grid, kTcThreads, smem, stream>>>(tm, a);
+    kern<<<grid, kTcThreads, smem, stream>>>(tm, tw, a);
     return cudaGetLastError();
 }
 
@@ -549,7 +570,7 @@ extern "C" int smeg_debug_timeline(long long* host, int n) {
 #endif
 
 bool gemm_tc_supported(int wkind, int m, int k, int log2_block, const void* a) {
-    if (wkind != 4) return false;
+    if (wkind != 4 && wkind != 16) return false;
     if (k % 8 != 0 || k == 0 || ((uintptr_t)a & 15) != 0) return false;   // TMA: 16-byte aligned rows
     if (log2_block < 3) return false;                                      // one scale per 8-depth chunk
     if (m < 1) return false;
@@ -616,7 +637,7 @@ void gemm_tc_plan(GemmTcArgs& a, int sm_count, dim3* grid, size_t* smem, size_t*
         for (int no = 3; no >= 2; --no) {
             if (env_no >= 2 && env_no <= 3 && no != env_no) continue;
             for (int nk = 4; nk >= 2; --nk) {
-                const int left = budget - 2048 - no * o_stride - nk * k_stride;
+                const int left = budget - 2048 - no * o_stride - (a.wdense ? 0 : nk * k_stride);
                 if (left < 2 * tok_bytes) continue;
                 int nt = left / tok_bytes;
                 if (nt > 8) nt = 8;
@@ -630,7 +651,7 @@ void gemm_tc_plan(GemmTcArgs& a, int sm_count, dim3* grid, size_t* smem, size_t*
         }
     }
     const int k_stride = ((8 * a.nw * (a.pu * kUnitBytes + a.rpg * 32) + 1023) / 1024) * 1024;
-    *smem = 1024 + (size_t)a.no * o_stride + (size_t)a.nt * tok_bytes + (size_t)a.nk * k_stride +
+    *smem = 1024 + (size_t)a.no * o_stride + (size_t)a.nt * tok_bytes + (a.wdense ? 0 : (size_t)a.nk * k_stride) +
             (size_t)(2 * a.nt + 2 * a.nk + 2 * a.no + 4) * 8 + kMaxInlineNodes * sizeof(EpNodeDev) + 64;
     *grid = dim3(col_tiles, tiles, splits);
     *ws_floats = splits > 1 ? (size_t)col_tiles * tiles * splits * (a.nw * 128) * pad : 0;
@@ -648,8 +669,19 @@ cudaError_t gemm_tc_launch(GemmTcArgs a, int bf16, dim3 grid, size_t smem, cudaS
                              CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
     if (r != CUDA_SUCCESS) return cudaErrorInvalidValue;
     if (smem > 227 * 1024) return cudaErrorInvalidConfiguration;
-    if (bf16) return launch_tc<1>(tm, a, grid, smem, stream);
-    return launch_tc<0>(tm, a, grid, smem, stream);
+    CUtensorMap tw = tm;                                         // unused unless the weights are dense
+    if (a.wdense) {
+        const cuuint64_t wdim[2] = {(cuuint64_t)a.kd, (cuuint64_t)a.n};
+        const cuuint64_t wstride[1] = {(cuuint64_t)a.kd * 2};
+        const cuuint32_t wbox[2] = {(cuuint32_t)kStageK, 128};
+        r = encode_fn()(&tw, bf16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, (void*)a.wdense, wdim,
+                        wstride, wbox, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                        CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+        if (r != CUDA_SUCCESS) return cudaErrorInvalidValue;
+    }
+    if (a.beta == 0.0f && !a.wdense) a.beta = 1.0f;
+    if (bf16) return launch_tc<1>(tm, tw, a, grid, smem, stream);
+    return launch_tc<0>(tm, tw, a, grid, smem, stream);
 }
 
 }  // namespace smeg

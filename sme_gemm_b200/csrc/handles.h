@@ -26,6 +26,12 @@ struct smeg_lowbit {
     mutable std::mutex twin_lock;
     mutable std::atomic<smeg_q4*> twin{nullptr};
 };
+// Dense 16-bit weights for the Gemm builder: W[n][kd], K-major, kd = k padded to a multiple of 8.
+struct smeg_dense {
+    size_t n = 0, k = 0, kd = 0;
+    int bf16 = 0;
+    uint16_t* w = nullptr;            // device
+};
 struct smeg_mlp {
     const smeg_q4* gate_up;
     const smeg_q4* down;

@@ -69,6 +69,10 @@ struct GemmTcArgs {
     float* yacc;                  // if set: y[m][n] += f32(T(acc)) instead of storing C (the MLP's residual add)
     int glu;                      // 0, or SMEG_ACT_SILU / _GELU: W is a gate/up matrix interleaved 32 columns at a time and
                                   // C (m x n/2) receives T(act(T(gate)) * T(up))
+    const uint16_t* wdense;       // if set: dense weights W[n][kd] (T bits, K-major, kd = k padded to 8) instead of codes / scales
+    int kd;                       // row length of wdense
+    float beta;                   // the product is scaled by beta before the store rounding (dense builder; 1 elsewhere)
+    int col_major;                // store C column-major: c[i + j * m]
     int m, n, k;
     int n16, ku, nb, log2_block;
     int ntok_tile, ntok_pad, ntok_box, nmma, tmem_cols;                // planner-filled

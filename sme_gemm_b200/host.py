@@ -578,6 +578,102 @@ def matmul_q1_ep(a, w: Q1Weights, c, m: int, ep: Epilogue) -> None:
     _run_lowbit(a, w, c, m, ep)
 
 
+# --------------------------------------------------------------------------- dense weights: the Gemm builder
+
+class Packed:
+    """Pre-packed dense weights (Packed<f16> / Packed<bf16>): B is k x n row-major in the element
+    type; the device copy is K-major for the tensor cores.  Built by prepack_f16 / prepack_bf16."""
+
+    def __init__(self, h, n, k, dtype):
+        self._h, self.n, self.k, self.dtype = h, n, k, dtype
+
+    def __del__(self):
+        try:
+            if self._h:
+                lib().smeg_dense_destroy(self._h)
+                self._h = None
+        except Exception:
+            pass
+
+
+def _prepack(b, n: int, k: int, dtype: str) -> Packed:
+    bits = _np_bits(b, "b")
+    assert bits.size == k * n, "b is k*n (row-major)"
+    h = C.c_void_p()
+    check("smeg_dense_create", lib().smeg_dense_create(_ptr(bits), n, k, 1 if dtype == "bf16" else 0, C.byref(h)))
+    return Packed(h, n, k, dtype)
+
+
+def prepack_f16(b, n: int, k: int) -> Packed:
+    """prepack_f16, src/kernels/f16.rs:212: b is the k x n row-major f16 matrix."""
+    return _prepack(b, n, k, "f16")
+
+
+def prepack_bf16(b, n: int, k: int) -> Packed:
+    """prepack_bf16, src/kernels/bf16.rs: b holds bf16 bit patterns (uint16), k x n row-major."""
+    return _prepack(b, n, k, "bf16")
+
+
+class Gemm:
+    """Gemm::new(a, &packed, m).add_col(bias).gelu().run(&mut c) (src/exec/builder.rs:220-227,
+    428-813): C = ep( T(beta * (A @ B)) ).  Every op method of Epilogue is available with the same
+    meaning (and the same trailing-activation rule), plus beta(), col_major_output() and run()."""
+
+    def __init__(self, a, packed: Packed, m: int):
+        self._a, self._p, self._m = a, packed, m
+        self._beta = 1.0
+        self._col_major = False
+        self._ep = Epilogue(packed.dtype)
+
+    @staticmethod
+    def new(a, packed: Packed, m: int) -> "Gemm":
+        return Gemm(a, packed, m)
+
+    def __getattr__(self, name):
+        fn = getattr(Epilogue, name, None)
+        if fn is None or name.startswith("_") or name in ("new", "resolved", "validate", "with_leading"):
+            raise AttributeError(name)
+
+        def forward(*args):
+            getattr(self._ep, name)(*args)
+            return self
+        return forward
+
+    def beta(self, beta: float) -> "Gemm":
+        self._beta = _round_scalar(beta, self._p.dtype)
+        return self
+
+    def col_major_output(self) -> "Gemm":
+        self._col_major = True
+        return self
+
+    def run(self, c) -> None:
+        m, n, k = self._m, self._p.n, self._p.k
+        _check_io(self._a, c, m, n, k)
+        self._ep.validate(m, n)
+        if m == 0 or n == 0:
+            return
+        if self._p.dtype == "bf16":
+            beta_bits = int(np.asarray([self._beta], np.float32).view(np.uint32)[0] >> 16)
+        else:
+            beta_bits = int(np.asarray([self._beta], np.float16).view(np.uint16)[0])
+        L = lib()
+        has_ep = bool(self._ep.nodes) or self._ep.act is not None
+        if _is_torch(self._a):
+            a = self._a
+            assert a.is_cuda and c.is_cuda and a.is_contiguous() and c.is_contiguous()
+            desc, keep = self._ep._desc(True) if has_ep else (None, [])
+            check("smeg_gemm_dense_dev", L.smeg_gemm_dense_dev(self._p._h, _ptr(a), _ptr(c), m, beta_bits, int(self._col_major),
+                                                               C.byref(desc) if desc else None, _stream()))
+            del keep
+        else:
+            ab = _np_bits(self._a, "a")
+            desc, keep = self._ep._desc(False) if has_ep else (None, [])
+            check("smeg_gemm_dense", L.smeg_gemm_dense(self._p._h, _ptr(ab), _ptr(c), m, beta_bits, int(self._col_major),
+                                                       C.byref(desc) if desc else None))
+            del keep
+
+
 def matmul_q2_mopa(a, w: Q2Weights, c, m: int) -> None:
     """matmul_q2_mopa, src/kernels/lowbit/matmul.rs:100-102: f16 activations, no int8 step."""
     _run_lowbit(a, w, c, m, None, mopa=True)
