@@ -127,7 +127,7 @@ __device__ __forceinline__ uint16_t ep_store_value(const EpParams& ep, float acc
 }
 
 // A graph of at most four nodes whose operands are scalars or per-column vectors and
-// whose activations are relu, silu or sigmoid, resolved once per thread for the
+// whose activations are the five named kinds, resolved once per thread for the
 // thread's output column: the per-cell work is then four predictable steps on
 // registers.  Arithmetic is the interpreter's (separately rounded f32 ops on the
 // T-rounded product); silu and sigmoid use the fast exponential and division, whose
@@ -145,7 +145,7 @@ inline bool fast_ep_eligible(const EpParams& ep) {
         const uint32_t op = ep.nodes[q].op & 0xffu, kind = (ep.nodes[q].op >> 8) & 0xffu;
         const bool scalar = op == 0 || op == 1 || op == 9 || op == 10 || op == 11 || op == 15;
         const bool col = op == 4 || op == 5 || op == 13 || op == 17 || op == 20 || op == 23;
-        if (!(scalar || col || (op == 8 && (kind == 1 || kind == 3 || kind == 5)))) return false;
+        if (!(scalar || col || (op == 8 && kind >= 1 && kind <= 5))) return false;
     }
     return true;
 }
@@ -206,8 +206,8 @@ __device__ __forceinline__ void fast_ep_apply16(const FastEp& f, const uint32_t 
             for (int j = 0; j < 16; ++j) x[j] = __fsub_rn(x[j], o);
             break;
         case 4:
-#pragma unroll 1
-            for (int j = 0; j < 16; ++j) x[j] = __fdiv_rn(x[j], o);
+#pragma unroll
+            for (int j = 0; j < 16; ++j) x[j] = __fdiv_rn(x[j], o);   // unrolled: a rolled loop would index x[] and push it to local memory
             break;
         case 5:
 #pragma unroll
@@ -220,6 +220,14 @@ __device__ __forceinline__ void fast_ep_apply16(const FastEp& f, const uint32_t 
         case 8 + 1:
 #pragma unroll
             for (int j = 0; j < 16; ++j) x[j] = fmaxf(x[j], 0.0f);
+            break;
+        case 8 + 2:
+#pragma unroll
+            for (int j = 0; j < 16; ++j) x[j] = act_apply(2u, x[j], 0.0f);
+            break;
+        case 8 + 4:
+#pragma unroll
+            for (int j = 0; j < 16; ++j) x[j] = act_apply(4u, x[j], 0.0f);
             break;
         case 8 + 3:
 #pragma unroll
@@ -251,6 +259,8 @@ __device__ __forceinline__ uint16_t fast_ep_store(const FastEp& f, float acc) {
         case 5: x = fmaxf(x, o); break;
         case 6: x = fminf(x, o); break;
         case 8 + 1: x = fmaxf(x, 0.0f); break;
+        case 8 + 2: x = act_apply(2u, x, 0.0f); break;
+        case 8 + 4: x = act_apply(4u, x, 0.0f); break;
         case 8 + 3: x = __fdividef(x, 1.0f + __expf(-x)); break;
         case 8 + 5: x = __fdividef(1.0f, 1.0f + __expf(-x)); break;
         default: break;
