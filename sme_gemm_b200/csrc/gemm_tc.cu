@@ -126,26 +126,27 @@ __device__ __forceinline__ void dequant_unit_q4(unsigned char* tile, int cu, con
     *reinterpret_cast<uint4*>(tile + swz_off(row_hi, cb)) = (g & 1) ? v_hi_a : v_hi_b;
 }
 
-template <int BF16>
+template <int BF16, int US>
 __global__ void __launch_bounds__(kTcThreads, 1) gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_tok, const __grid_constant__ CUtensorMap tmap_w, GemmTcArgs p) {
     extern __shared__ unsigned char smem_dyn[];
     // the swizzled operands need 1024-byte aligned tiles: align the window by hand
     unsigned char* smem_raw = smem_dyn + ((1024u - (smem_u32(smem_dyn) & 1023u)) & 1023u);
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int NT = p.nt, NK = p.nk, O = p.no, NW = p.nw, PU = p.pu;
-    const int tok_bytes = p.ntok_pad * 128;                    // token operand per 64-deep stage
+    const int tok_bytes = p.ntok_pad * 128;                    // token operand per 64-deep unit (a stage is US units)
     const int rpg = p.rpg;                                     // scale rows (blocks) staged per packed slot
-    const int k_code = PU * kUnitBytes;                        // packed slot: [8 NW groups][PU units] then [8 NW groups][rpg rows]
+    const int k_code = PU * US * kUnitBytes;                   // packed slot: [8 NW groups][PU * US units] then [8 NW groups][rpg rows]
     const int k_stride = ((8 * NW * (k_code + rpg * 32) + 1023) / 1024) * 1024;
-    const int o_stride = NW * kWTile;                          // ring O slot: NW operand tiles
+    const int o_stride = NW * US * kWTile;                     // ring O slot: NW x US operand tiles
+    const int t_stride = US * tok_bytes;                       // ring T slot: US token tiles
     // a stage holds 8 * NW packed units, one per dequant warp: with only 8 of them the 16
     // warps form two groups that take alternate stages
-    const int deq_groups = (8 * NW >= kDeqWarps) ? 1 : 2;
+    const int deq_groups = (8 * NW * US >= kDeqWarps) ? 1 : 2;
     const int deq_wpg = kDeqWarps / deq_groups;
 
     unsigned char* ring_o = smem_raw;
     unsigned char* ring_t = ring_o + (size_t)O * o_stride;
-    unsigned char* ring_k = ring_t + (size_t)NT * tok_bytes;
+    unsigned char* ring_k = ring_t + (size_t)NT * t_stride;
     const bool dense = p.wdense != nullptr;                    // then there is no packed ring
     uint64_t* bars = reinterpret_cast<uint64_t*>(ring_k + (dense ? (size_t)0 : (size_t)NK * k_stride));
     uint64_t* t_full = bars;                 // [NT] token tile landed
@@ -163,7 +164,7 @@ __global__ void __launch_bounds__(kTcThreads, 1) gemm_tc_kernel(const __grid_con
     const int sg0 = blockIdx.x * NW;                           // first 128-column super-group
     const int col0 = blockIdx.x * 128 * NW;
     const int tok0 = blockIdx.y * p.ntok_tile;
-    const int stages_all = p.ku;
+    const int stages_all = (p.ku + US - 1) / US;
     const int per_split = (stages_all + (int)gridDim.z - 1) / (int)gridDim.z;
     const int st_begin = blockIdx.z * per_split;
     const int st_end = min(stages_all, st_begin + per_split);
@@ -207,11 +208,15 @@ __global__ void __launch_bounds__(kTcThreads, 1) gemm_tc_kernel(const __grid_con
                 SMEG_TL(0, i);
                 if (i >= NT && !mbar_wait(&t_empty[slot], ((i / NT) - 1) & 1, abort_flag, p.status, STATUS_TMEM_TIMEOUT)) break;
                 SMEG_TL(1, i);
-                unsigned char* sb = ring_t + (size_t)slot * tok_bytes;
-                const int d0 = (st_begin + i) * kStageK;
-                mbar_expect_tx(&t_full[slot], (unsigned)tok_bytes);
-                tma_load_2d(sb, &tmap_tok, d0, tok0, &t_full[slot]);
-                if (p.nmma == 2) tma_load_2d(sb + tok_bytes / 2, &tmap_tok, d0, tok0 + p.ntok_box, &t_full[slot]);
+                unsigned char* sb = ring_t + (size_t)slot * t_stride;
+                const int u0 = (st_begin + i) * US;
+                const int units = min(US, p.ku - u0);
+                mbar_expect_tx(&t_full[slot], (unsigned)(units * tok_bytes));
+                for (int uu = 0; uu < units; ++uu) {
+                    const int d0 = (u0 + uu) * kStageK;
+                    tma_load_2d(sb + uu * tok_bytes, &tmap_tok, d0, tok0, &t_full[slot]);
+                    if (p.nmma == 2) tma_load_2d(sb + uu * tok_bytes + tok_bytes / 2, &tmap_tok, d0, tok0 + p.ntok_box, &t_full[slot]);
+                }
             }
         }
     } else if (warp == kDeqWarps + 2) {
@@ -227,9 +232,12 @@ __global__ void __launch_bounds__(kTcThreads, 1) gemm_tc_kernel(const __grid_con
                     const int os = i % O;
                     if (i >= O && !mbar_wait(&o_empty[os], ((i / O) - 1) & 1, abort_flag, p.status, STATUS_TMEM_TIMEOUT)) break;
                     unsigned char* ob = ring_o + (size_t)os * o_stride;
-                    mbar_expect_tx(&o_full[os], (unsigned)(NW * kWTile));
+                    const int u0 = (st_begin + i) * US;
+                    const int units = min(US, p.ku - u0);
+                    mbar_expect_tx(&o_full[os], (unsigned)(NW * units * kWTile));
                     for (int w = 0; w < NW; ++w)
-                        tma_load_2d(ob + w * kWTile, &tmap_w, (st_begin + i) * kStageK, col0 + 128 * w, &o_full[os]);
+                        for (int uu = 0; uu < units; ++uu)
+                            tma_load_2d(ob + (w * US + uu) * kWTile, &tmap_w, (u0 + uu) * kStageK, col0 + 128 * w, &o_full[os]);
                 }
             }
         } else
@@ -237,8 +245,8 @@ __global__ void __launch_bounds__(kTcThreads, 1) gemm_tc_kernel(const __grid_con
             const int slot = gq % NK;
             if (gq >= NK && !__all_sync(0xffffffffu, mbar_wait(&k_empty[slot], ((gq / NK) - 1) & 1, abort_flag, p.status, STATUS_TMEM_TIMEOUT))) break;
             unsigned char* sb = ring_k + (size_t)slot * k_stride;
-            const int u0 = st_begin + gq * PU;                          // first 64-deep unit of the slot
-            const int units = min(PU, st_end - u0);
+            const int u0 = (st_begin + gq * PU) * US;                   // first 64-deep unit of the slot
+            const int units = min(PU * US, min(st_end * US, p.ku) - u0);
             const int d0 = u0 * kStageK;
             const int blk0 = d0 >> p.log2_block;
             const int blk1 = min(p.nb, ((d0 + units * kStageK - 1) >> p.log2_block) + 1);
@@ -267,17 +275,20 @@ __global__ void __launch_bounds__(kTcThreads, 1) gemm_tc_kernel(const __grid_con
             if (!__all_sync(0xffffffffu, mbar_wait(&o_full[os], (i / O) & 1, abort_flag, p.status, STATUS_TMEM_TIMEOUT))) break;
             if (lane == 0) SMEG_TL(6, i);
             tc_fence_after();
-            const uint32_t tok_addr = smem_u32(ring_t + (size_t)ts * tok_bytes);
+            const uint32_t tok_addr = smem_u32(ring_t + (size_t)ts * t_stride);
             const uint32_t w_addr = smem_u32(ring_o + (size_t)os * o_stride);
+            const int units = min(US, p.ku - (st_begin + i) * US);
             if (elect_one()) {
-                for (int w = 0; w < NW; ++w) {
-                    const uint64_t a_desc0 = umma_desc_sw128(w_addr + w * kWTile);
-                    for (int h = 0; h < p.nmma; ++h) {
-                        const uint64_t b_desc0 = umma_desc_sw128(tok_addr + h * tok_half);
-                        const uint32_t d_tmem = tmem_base + (uint32_t)((w * p.nmma + h) * p.ntok_box);
+                for (int uu = 0; uu < units; ++uu) {
+                    for (int w = 0; w < NW; ++w) {
+                        const uint64_t a_desc0 = umma_desc_sw128(w_addr + (w * US + uu) * kWTile);
+                        for (int h = 0; h < p.nmma; ++h) {
+                            const uint64_t b_desc0 = umma_desc_sw128(tok_addr + uu * tok_bytes + h * tok_half);
+                            const uint32_t d_tmem = tmem_base + (uint32_t)((w * p.nmma + h) * p.ntok_box);
 #pragma unroll
-                        for (int ks = 0; ks < kStageK / 16; ++ks)
-                            umma_f16(d_tmem, a_desc0 + 2 * ks, b_desc0 + 2 * ks, idesc, (i > 0 || ks > 0) ? 1u : 0u);
+                            for (int ks = 0; ks < kStageK / 16; ++ks)
+                                umma_f16(d_tmem, a_desc0 + 2 * ks, b_desc0 + 2 * ks, idesc, (i > 0 || uu > 0 || ks > 0) ? 1u : 0u);
+                        }
                     }
                 }
                 SMEG_TL(10, i);
@@ -310,17 +321,20 @@ __global__ void __launch_bounds__(kTcThreads, 1) gemm_tc_kernel(const __grid_con
             if (wig == 0 && lane == 0) SMEG_TL(8, i);
             if (!__all_sync(0xffffffffu, mbar_wait(&k_full[ks], (gq / NK) & 1, abort_flag, p.status, STATUS_TMEM_TIMEOUT))) break;
             if (wig == 0 && lane == 0) SMEG_TL(3, i);
-            const int uq = i % PU;                                  // unit within the packed slot
-            const int du = (st_begin + i) * kStageK;                // depth of the stage
-            const int blk0 = ((st_begin + gq * PU) * kStageK) >> p.log2_block;   // first scale row of the slot
+            const int uq = (i % PU) * US;                           // first unit of the stage within the packed slot
+            const int u0 = (st_begin + i) * US;                     // first unit of the stage
+            const int units = min(US, p.ku - u0);
+            const int blk0 = ((st_begin + gq * PU) * US * kStageK) >> p.log2_block;   // first scale row of the slot
             const unsigned char* pk = ring_k + (size_t)ks * k_stride;
             const uint16_t* scs = reinterpret_cast<const uint16_t*>(pk + (size_t)8 * NW * k_code);
             unsigned char* ob = ring_o + (size_t)os * o_stride;
-            const int ra = ((du + 8 * t) >> p.log2_block) - blk0, rb = ((du + 32 + 8 * t) >> p.log2_block) - blk0;
-            // work item c = w * 8 + column group
-            for (int c = wig; c < 8 * NW; c += deq_wpg) {
-                const int cgl = c & 7, w = c >> 3;
-                const uint4 wv = *reinterpret_cast<const uint4*>(pk + (size_t)c * k_code + uq * kUnitBytes + lane * 16);
+            // work item = (w * 8 + column group) * US + unit of the stage
+            for (int it = wig; it < 8 * NW * US; it += deq_wpg) {
+                const int uu = it % US, c = it / US, cgl = c & 7, w = c >> 3;
+                if (uu >= units) continue;
+                const int du = (u0 + uu) * kStageK;                 // depth of the unit
+                const int ra = ((du + 8 * t) >> p.log2_block) - blk0, rb = ((du + 32 + 8 * t) >> p.log2_block) - blk0;
+                const uint4 wv = *reinterpret_cast<const uint4*>(pk + (size_t)c * k_code + (uq + uu) * kUnitBytes + lane * 16);
                 // gate/up matrix: gate column groups go to operand tile 0 and the matching up groups to tile 1,
                 // so that a thread of the drain holds both values of one hidden unit
                 int tw = w, rg = cgl;
@@ -328,7 +342,7 @@ __global__ void __launch_bounds__(kTcThreads, 1) gemm_tc_kernel(const __grid_con
                     tw = (c >> 1) & 1;                             // chunks of [2 gate | 2 up] groups
                     rg = ((c >> 2) << 1) | (c & 1);
                 }
-                dequant_unit_q4<BF16>(ob + tw * kWTile, rg, wv, scs + (size_t)c * rpg * 16, ra, rb, g, t);
+                dequant_unit_q4<BF16>(ob + (tw * US + uu) * kWTile, rg, wv, scs + (size_t)c * rpg * 16, ra, rb, g, t);
             }
             fence_proxy_async();
             mbar_arrive(&o_full[os]);
@@ -437,7 +451,7 @@ __global__ void __launch_bounds__(kTcThreads, 1) gemm_tc_kernel(const __grid_con
         }
         tc_fence_before();
 
-        if (splits > 1) {
+        if (splits > 1 && !p.defer) {
             // the last CTA of the tile to arrive adds the slices in slice order and stores
             __threadfence();
             asm volatile("bar.sync 1, %0;" ::"r"(drain_threads));
@@ -531,6 +545,80 @@ __global__ void __launch_bounds__(kTcThreads, 1) gemm_tc_kernel(const __grid_con
     }
 }
 
+// Adds the depth slices of a split GEMM in slice order and stores, for splits deep enough that one CTA per
+// tile would spend longer adding than the GEMM spent multiplying.  One block = all columns of a tile x 8 tokens;
+// a thread owns one column (for a gate/up matrix: one hidden unit, i.e. a gate and an up column).
+template <int BF16>
+__global__ void __launch_bounds__(256) splitk_reduce_kernel(const __grid_constant__ GemmTcArgs p, int splits, int col_tiles) {
+    const int NW = p.nw, ntok = p.ntok_pad;
+    const int tile_id = blockIdx.x, bx = tile_id % col_tiles, by = tile_id / col_tiles;
+    const int tok0 = by * p.ntok_tile, j0 = blockIdx.y * 8;
+    const int cl = threadIdx.x;                                  // column within the CTA tile
+    const float* ws_tile = p.ws + ((size_t)tile_id * splits) * (size_t)(NW * 128) * ntok;
+    const EpNodeDev* nodes = p.ep.n_nodes <= kMaxInlineNodes ? p.ep.nodes : p.ep.ext;
+    if (p.glu) {
+        const int hn = p.n >> 1, hcol = bx * 128 + cl;
+        if (cl >= 128 || hcol >= hn) return;
+        float ag[8], au[8];
+#pragma unroll
+        for (int jj = 0; jj < 8; ++jj) ag[jj] = au[jj] = 0.0f;
+        for (int z = 0; z < splits; ++z) {
+            const float* src = ws_tile + ((size_t)z * ntok + j0) * (NW * 128) + cl;
+            float vg[8], vu[8];
+#pragma unroll
+            for (int jj = 0; jj < 8; ++jj) {
+                vg[jj] = __ldcg(src + (size_t)jj * (NW * 128));
+                vu[jj] = __ldcg(src + (size_t)jj * (NW * 128) + 128);
+            }
+#pragma unroll
+            for (int jj = 0; jj < 8; ++jj) { ag[jj] += vg[jj]; au[jj] += vu[jj]; }
+        }
+#pragma unroll
+        for (int jj = 0; jj < 8; ++jj) {
+            const int tok = tok0 + j0 + jj;
+            const float gv = t_to_f32<BF16>(f32_to_t<BF16>(ag[jj])), uv = t_to_f32<BF16>(f32_to_t<BF16>(au[jj]));
+            float a;
+            if (p.glu == 3) a = __fdiv_rn(gv, __fadd_rn(1.0f, expf(-gv)));
+            else {
+                const float g3 = __fmul_rn(__fmul_rn(__fmul_rn(0.044715f, gv), gv), gv);
+                a = __fmul_rn(__fmul_rn(0.5f, gv), __fadd_rn(1.0f, tanhf(__fmul_rn(0.7978846f, __fadd_rn(gv, g3)))));
+            }
+            if (tok < p.m) p.c[(size_t)tok * hn + hcol] = f32_to_t<BF16>(__fmul_rn(a, uv));
+        }
+        return;
+    }
+    const int col = bx * 128 * NW + cl;
+    if (cl >= NW * 128 || col >= p.n) return;
+    float acc[8], yv[8];
+#pragma unroll
+    for (int jj = 0; jj < 8; ++jj) acc[jj] = 0.0f;
+    if (p.yacc) {
+#pragma unroll
+        for (int jj = 0; jj < 8; ++jj) yv[jj] = (tok0 + j0 + jj < p.m) ? p.yacc[(size_t)(tok0 + j0 + jj) * p.n + col] : 0.0f;
+    }
+    for (int z = 0; z < splits; ++z) {
+        const float* src = ws_tile + ((size_t)z * ntok + j0) * (NW * 128) + cl;
+        float v[8];
+#pragma unroll
+        for (int jj = 0; jj < 8; ++jj) v[jj] = __ldcg(src + (size_t)jj * (NW * 128));
+#pragma unroll
+        for (int jj = 0; jj < 8; ++jj) acc[jj] += v[jj];
+    }
+    FastEp fe;
+    if (p.ep_fast) fast_ep_build<BF16>(nodes, p.ep.n_nodes, col, true, fe);
+#pragma unroll
+    for (int jj = 0; jj < 8; ++jj) {
+        const int tok = tok0 + j0 + jj;
+        if (tok >= p.m) continue;
+        if (p.beta != 1.0f) acc[jj] = __fmul_rn(p.beta, acc[jj]);
+        const size_t ci = p.col_major ? (size_t)col * p.m + tok : (size_t)tok * p.n + col;
+        if (p.c32) p.c32[(size_t)tok * p.n + col] = acc[jj];
+        else if (p.yacc) p.yacc[(size_t)tok * p.n + col] = __fadd_rn(yv[jj], t_to_f32<BF16>(f32_to_t<BF16>(acc[jj])));
+        else if (p.ep_fast) p.c[ci] = fast_ep_store<BF16>(fe, acc[jj]);
+        else p.c[ci] = ep_store_nodes<BF16>(nodes, p.ep.n_nodes, acc[jj], (size_t)tok, (size_t)col);
+    }
+}
+
 typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
                                   const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
                                   CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
@@ -546,9 +634,9 @@ EncodeTiledFn encode_fn() {
     return fn;
 }
 
-template <int BF16>
+template <int BF16, int US>
 cudaError_t launch_tc(const CUtensorMap& tm, const CUtensorMap& tw, const GemmTcArgs& a, dim3 grid, size_t smem, cudaStream_t stream) {
-    auto kern = gemm_tc_kernel<BF16>;
+    auto kern = gemm_tc_kernel<BF16, US>;
     static int attr_dev = -1;
     int dev = 0;
     cudaGetDevice(&dev);
@@ -604,7 +692,8 @@ void gemm_tc_plan(GemmTcArgs& a, int sm_count, dim3* grid, size_t* smem, size_t*
     // depth split: one CTA per SM is resident.  Small token tiles (decode) split until the grid
     // wastes little of its last wave; larger ones only when the column tiles alone cannot fill the
     // machine (each slice costs a workspace round trip of the whole partial tile)
-    const int stages_all = a.ku;
+    a.us = (pad <= 64 && !a.wdense) ? 2 : 1;                        // small token tiles: two 64-deep units per stage halve the per-stage hand-offs
+    const int stages_all = (a.ku + a.us - 1) / a.us;
     int splits = 1;
     {
         const int base = col_tiles * tiles;
@@ -618,13 +707,13 @@ void gemm_tc_plan(GemmTcArgs& a, int sm_count, dim3* grid, size_t* smem, size_t*
                 if (s > 1) eff *= 0.97;
                 if (eff > best + 1e-9) { best = eff; splits = s; }
             }
-        } else if (pad <= 256) {
+        } else {
             while (base * splits * 2 <= sm_count && stages_all / (splits * 2) >= 7 && splits < 8) splits *= 2;
         }
     }
     // shared memory: operand ring (NW x 16 KB per slot), token ring (pad x 128 B per slot) and the packed-weight
     // ring, whose slots cover PU stages each so that one bulk copy moves a column group's units of PU stages
-    const int tok_bytes = pad * 128, o_stride = a.nw * kWTile;
+    const int tok_bytes = a.us * pad * 128, o_stride = a.nw * a.us * kWTile;
     const int budget = 214 * 1024;
     static const int env_no = []() { const char* e = getenv("SMEG_TC_NO"); return e ? atoi(e) : 0; }();
     static const int env_pu = []() { const char* e = getenv("SMEG_TC_PU"); return e ? atoi(e) : 0; }();
@@ -632,8 +721,9 @@ void gemm_tc_plan(GemmTcArgs& a, int sm_count, dim3* grid, size_t* smem, size_t*
     int best_score = -1;
     for (int pu = 8; pu >= 1; pu /= 2) {
         if (env_pu && pu != env_pu) continue;
-        const int rpg = block <= kStageK ? pu * kStageK / block : pu * kStageK / block + 1;
-        const int k_stride = ((8 * a.nw * (pu * kUnitBytes + rpg * 32) + 1023) / 1024) * 1024;
+        const int sdepth = pu * a.us * kStageK;                       // depths covered by a packed slot
+        const int rpg = block <= kStageK ? sdepth / block : sdepth / block + 1;
+        const int k_stride = ((8 * a.nw * (pu * a.us * kUnitBytes + rpg * 32) + 1023) / 1024) * 1024;
         for (int no = 3; no >= 2; --no) {
             if (env_no >= 2 && env_no <= 3 && no != env_no) continue;
             for (int nk = 4; nk >= 2; --nk) {
@@ -650,9 +740,10 @@ void gemm_tc_plan(GemmTcArgs& a, int sm_count, dim3* grid, size_t* smem, size_t*
             }
         }
     }
-    const int k_stride = ((8 * a.nw * (a.pu * kUnitBytes + a.rpg * 32) + 1023) / 1024) * 1024;
+    const int k_stride = ((8 * a.nw * (a.pu * a.us * kUnitBytes + a.rpg * 32) + 1023) / 1024) * 1024;
     *smem = 1024 + (size_t)a.no * o_stride + (size_t)a.nt * tok_bytes + (a.wdense ? 0 : (size_t)a.nk * k_stride) +
             (size_t)(2 * a.nt + 2 * a.nk + 2 * a.no + 4) * 8 + kMaxInlineNodes * sizeof(EpNodeDev) + 64;
+    a.defer = splits >= 2 ? 1 : 0;
     *grid = dim3(col_tiles, tiles, splits);
     *ws_floats = splits > 1 ? (size_t)col_tiles * tiles * splits * (a.nw * 128) * pad : 0;
     *n_counters = splits > 1 ? (size_t)col_tiles * tiles : 0;
@@ -680,8 +771,13 @@ cudaError_t gemm_tc_launch(GemmTcArgs a, int bf16, dim3 grid, size_t smem, cudaS
         if (r != CUDA_SUCCESS) return cudaErrorInvalidValue;
     }
     if (a.beta == 0.0f && !a.wdense) a.beta = 1.0f;
-    if (bf16) return launch_tc<1>(tm, tw, a, grid, smem, stream);
-    return launch_tc<0>(tm, tw, a, grid, smem, stream);
+    cudaError_t e = a.us == 2 ? (bf16 ? launch_tc<1, 2>(tm, tw, a, grid, smem, stream) : launch_tc<0, 2>(tm, tw, a, grid, smem, stream))
+                              : (bf16 ? launch_tc<1, 1>(tm, tw, a, grid, smem, stream) : launch_tc<0, 1>(tm, tw, a, grid, smem, stream));
+    if (e != cudaSuccess || !a.defer || grid.z < 2) return e;
+    const dim3 rgrid(grid.x * grid.y, a.ntok_pad / 8);
+    if (bf16) splitk_reduce_kernel<1><<<rgrid, 256, 0, stream>>>(a, (int)grid.z, (int)grid.x);
+    else splitk_reduce_kernel<0><<<rgrid, 256, 0, stream>>>(a, (int)grid.z, (int)grid.x);
+    return cudaGetLastError();
 }
 
 }  // namespace smeg

@@ -78,8 +78,10 @@ struct GemmTcArgs {
     int ntok_tile, ntok_pad, ntok_box, nmma, tmem_cols;                // planner-filled
     int ep_fast;                  // the graph runs as a per-thread FastEp (see epilogue.cuh)
     int nt, nk, no, nw;           // ring depths (tokens / packed / operand), accumulator sets per CTA
-    int pu;                       // 64-deep stages covered by one packed-ring slot
+    int us;                       // 64-deep units per stage (2 for small token tiles)
+    int pu;                       // stages covered by one packed-ring slot
     int rpg;                      // scale rows staged per packed-ring slot
+    int defer;                    // the depth slices are added by splitk_reduce_kernel after the GEMM instead of by the last CTA
     float* ws;                    // split-depth workspace [tile][slice][token][column]
     int* counters;                // one per output tile, zero between launches
     unsigned* status;
