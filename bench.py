@@ -15,9 +15,18 @@ device copies to exceed twice the L2, so every step streams its weights from HBM
 portable scalar path; the reference itself is Rust and cannot be built here) on
 the host cores with the same metric, on a bounded row sample of the same batch.
 
+`value` is device time (CUDA events, max over ranks) with the inputs resident in
+HBM.  `e2e` is the same step through the same public call with host buffers: every
+step copies its tokens from pinned host memory and its result back to pinned host
+memory inside the timed region, the copies running on their own streams with two
+buffers each way so that they overlap the neighbouring steps' compute.  `roofline`
+is the gate/up projection's GEMM timed alone against the measured tensor peak.
+
 The extra "kernels" list reports the single-kernel configs of BASELINE.json
 (Q4 / 2-bit / 1-bit decode GEMV in GB/s, Q4 prefill GEMM in TFLOP/s) measured on
-rank 0 at N = 1.
+rank 0 at N = 1 (`--no-kernels` skips it).  `--profile-case NAME` runs six plain
+launches of one kernel and exits, for profiler captures; `--tokens M` changes the
+batch (BASELINE.json also names M = 1).
 """
 from __future__ import annotations
 

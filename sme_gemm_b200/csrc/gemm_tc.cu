@@ -669,7 +669,13 @@ void gemm_tc_plan(GemmTcArgs& a, int sm_count, dim3* grid, size_t* smem, size_t*
     // token tiling: equal tiles of at most 512 tokens, padded so that both token halves of the
     // drain (and both MMA halves above 256) are whole groups of 16
     // the fused gate/up form keeps both values of a hidden unit in one CTA: two accumulator sets, at most 256 tokens
-    const int tiles = a.glu ? (a.m + 255) / 256 : (a.m + 511) / 512;
+    // Above 256 tokens a CTA takes 128 columns x up to 512 tokens (two MMA halves share one expanded weight tile).
+    // 256 columns x 256 tokens would ingest less per flop but expands twice the weights per flop and streams them
+    // once per token tile: measured 15-20 % slower at 512 tokens.  The fused gate/up form needs both accumulator
+    // sets for the gate and up columns and therefore tiles by 256 tokens.
+    static const int env_tt = []() { const char* e = getenv("SMEG_TC_TOKEN_TILE"); return e ? atoi(e) : 0; }();
+    const bool wide = a.glu != 0 || env_tt == 256;
+    const int tiles = wide ? (a.m + 255) / 256 : (a.m + 511) / 512;
     const int tile = (a.m + tiles - 1) / tiles;
     const int pad = (tile + 31) / 32 * 32;
     a.ntok_tile = pad;
@@ -683,7 +689,7 @@ void gemm_tc_plan(GemmTcArgs& a, int sm_count, dim3* grid, size_t* smem, size_t*
     static const int env_nw = []() { const char* e = getenv("SMEG_TC_NW"); return e ? atoi(e) : 0; }();
     a.nw = (2 * pad <= 512 && pad >= 64 && col_tiles_1 >= 2 * sm_count * 3 / 4) ? 2 : 1;
     if ((env_nw == 1 || env_nw == 2) && env_nw * pad <= 512) a.nw = env_nw;
-    if (a.glu) a.nw = 2;
+    if (wide && 2 * pad <= 512) a.nw = 2;
     int cols = 32;
     while (cols < a.nw * pad) cols *= 2;
     a.tmem_cols = cols;
