@@ -177,6 +177,17 @@ __device__ __forceinline__ void fast_ep_build(const EpNodeDev* nodes, int nn, in
     }
 }
 
+// The long cases (IEEE division, gelu, tanh) as one out-of-line routine over a 16-value array in
+// local memory: inlined and unrolled they cost the calling kernel registers in its main loop
+// and a few thousand instructions of code, for graphs that few callers build.
+static __device__ __noinline__ void fast_ep_rare16(int cls, float o, float* t) {
+#pragma unroll 1
+    for (int j = 0; j < 16; ++j) {
+        const float v = t[j];
+        t[j] = cls == 4 ? __fdiv_rn(v, o) : act_apply(cls == 8 + 2 ? 2u : 4u, v, 0.0f);
+    }
+}
+
 // Applies the graph to 16 accumulators of one output column at once.  The walk over the
 // slots is outside the walk over the values: one uniform branch per slot and a straight run
 // of 16 operations under it, so the code stays a few hundred instructions however it is
@@ -205,10 +216,15 @@ __device__ __forceinline__ void fast_ep_apply16(const FastEp& f, const uint32_t 
 #pragma unroll
             for (int j = 0; j < 16; ++j) x[j] = __fsub_rn(x[j], o);
             break;
-        case 4:
+        case 4: case 8 + 2: case 8 + 4: {
+            float t[16];   // a copy: x[] itself must never be indexed or have its address taken, or it leaves the registers
 #pragma unroll
-            for (int j = 0; j < 16; ++j) x[j] = __fdiv_rn(x[j], o);   // unrolled: a rolled loop would index x[] and push it to local memory
+            for (int j = 0; j < 16; ++j) t[j] = x[j];
+            fast_ep_rare16(cls, o, t);
+#pragma unroll
+            for (int j = 0; j < 16; ++j) x[j] = t[j];
             break;
+        }
         case 5:
 #pragma unroll
             for (int j = 0; j < 16; ++j) x[j] = fmaxf(x[j], o);
@@ -220,14 +236,6 @@ __device__ __forceinline__ void fast_ep_apply16(const FastEp& f, const uint32_t 
         case 8 + 1:
 #pragma unroll
             for (int j = 0; j < 16; ++j) x[j] = fmaxf(x[j], 0.0f);
-            break;
-        case 8 + 2:
-#pragma unroll
-            for (int j = 0; j < 16; ++j) x[j] = act_apply(2u, x[j], 0.0f);
-            break;
-        case 8 + 4:
-#pragma unroll
-            for (int j = 0; j < 16; ++j) x[j] = act_apply(4u, x[j], 0.0f);
             break;
         case 8 + 3:
 #pragma unroll

@@ -126,8 +126,13 @@ __device__ __forceinline__ void dequant_unit_q4(unsigned char* tile, int cu, con
     *reinterpret_cast<uint4*>(tile + swz_off(row_hi, cb)) = (g & 1) ? v_hi_a : v_hi_b;
 }
 
-template <int BF16, int US>
-__global__ void __launch_bounds__(kTcThreads, 1) gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_tok, const __grid_constant__ CUtensorMap tmap_w, GemmTcArgs p) {
+// The kernel's tensor maps: the token matrix, and for dense weights the weight matrix as well.
+template <int DENSE> struct TcMaps { CUtensorMap tok; CUtensorMap w; };
+template <> struct TcMaps<0> { CUtensorMap tok; };
+
+template <int BF16, int US, int DENSE>
+__global__ void __launch_bounds__(kTcThreads, 1) gemm_tc_kernel(const __grid_constant__ TcMaps<DENSE> maps, GemmTcArgs p) {
+    const CUtensorMap& tmap_tok = maps.tok;
     extern __shared__ unsigned char smem_dyn[];
     // the swizzled operands need 1024-byte aligned tiles: align the window by hand
     unsigned char* smem_raw = smem_dyn + ((1024u - (smem_u32(smem_dyn) & 1023u)) & 1023u);
@@ -147,7 +152,7 @@ __global__ void __launch_bounds__(kTcThreads, 1) gemm_tc_kernel(const __grid_con
     unsigned char* ring_o = smem_raw;
     unsigned char* ring_t = ring_o + (size_t)O * o_stride;
     unsigned char* ring_k = ring_t + (size_t)NT * t_stride;
-    const bool dense = p.wdense != nullptr;                    // then there is no packed ring
+    constexpr bool dense = DENSE != 0;                         // dense 16-bit weights: no packed ring, no expansion
     uint64_t* bars = reinterpret_cast<uint64_t*>(ring_k + (dense ? (size_t)0 : (size_t)NK * k_stride));
     uint64_t* t_full = bars;                 // [NT] token tile landed
     uint64_t* t_empty = t_full + NT;         // [NT] the stage's MMAs retired
@@ -181,7 +186,7 @@ __global__ void __launch_bounds__(kTcThreads, 1) gemm_tc_kernel(const __grid_con
             mbar_init(&k_empty[s], kDeqWarps);
         }
         for (int s = 0; s < O; ++s) {
-            mbar_init(&o_full[s], p.wdense ? 1 : 32 * deq_wpg);
+            mbar_init(&o_full[s], dense ? 1 : 32 * deq_wpg);
             mbar_init(&o_empty[s], 1);
         }
         mbar_init(acc_full, 1);
@@ -224,10 +229,10 @@ __global__ void __launch_bounds__(kTcThreads, 1) gemm_tc_kernel(const __grid_con
         // One slot covers PU stages: issuing a bulk copy costs a couple of hundred cycles whatever its
         // size, so a column group's units of PU stages (contiguous along K) travel as one copy, and so do
         // its scale rows.  Lanes 0-15 issue the code runs, lanes 16-31 the scale rows.
-        if (dense) {
+        if constexpr (DENSE != 0) {
             // dense 16-bit weights need no expansion: their K-major tiles go straight into the operand ring
             if (lane == 0) {
-                tma_prefetch_desc(&tmap_w);
+                tma_prefetch_desc(&maps.w);
                 for (int i = 0; i < num_stages; ++i) {
                     const int os = i % O;
                     if (i >= O && !mbar_wait(&o_empty[os], ((i / O) - 1) & 1, abort_flag, p.status, STATUS_TMEM_TIMEOUT)) break;
@@ -237,7 +242,7 @@ __global__ void __launch_bounds__(kTcThreads, 1) gemm_tc_kernel(const __grid_con
                     mbar_expect_tx(&o_full[os], (unsigned)(NW * units * kWTile));
                     for (int w = 0; w < NW; ++w)
                         for (int uu = 0; uu < units; ++uu)
-                            tma_load_2d(ob + (w * US + uu) * kWTile, &tmap_w, (u0 + uu) * kStageK, col0 + 128 * w, &o_full[os]);
+                            tma_load_2d(ob + (w * US + uu) * kWTile, &maps.w, (u0 + uu) * kStageK, col0 + 128 * w, &o_full[os]);
                 }
             }
         } else
@@ -277,9 +282,11 @@ __global__ void __launch_bounds__(kTcThreads, 1) gemm_tc_kernel(const __grid_con
             tc_fence_after();
             const uint32_t tok_addr = smem_u32(ring_t + (size_t)ts * t_stride);
             const uint32_t w_addr = smem_u32(ring_o + (size_t)os * o_stride);
-            const int units = min(US, p.ku - (st_begin + i) * US);
+            const int units = US == 1 ? 1 : min(US, p.ku - (st_begin + i) * US);
             if (elect_one()) {
-                for (int uu = 0; uu < units; ++uu) {
+#pragma unroll
+                for (int uu = 0; uu < US; ++uu) {
+                    if (uu >= units) break;
                     for (int w = 0; w < NW; ++w) {
                         const uint64_t a_desc0 = umma_desc_sw128(w_addr + (w * US + uu) * kWTile);
                         for (int h = 0; h < p.nmma; ++h) {
@@ -328,6 +335,23 @@ __global__ void __launch_bounds__(kTcThreads, 1) gemm_tc_kernel(const __grid_con
             const unsigned char* pk = ring_k + (size_t)ks * k_stride;
             const uint16_t* scs = reinterpret_cast<const uint16_t*>(pk + (size_t)8 * NW * k_code);
             unsigned char* ob = ring_o + (size_t)os * o_stride;
+            if (US == 1) {
+                // work item c = w * 8 + column group
+                const int du = u0 * kStageK;                        // depth of the stage
+                const int ra = ((du + 8 * t) >> p.log2_block) - blk0, rb = ((du + 32 + 8 * t) >> p.log2_block) - blk0;
+                for (int c = wig; c < 8 * NW; c += deq_wpg) {
+                    const int cgl = c & 7, w = c >> 3;
+                    const uint4 wv = *reinterpret_cast<const uint4*>(pk + (size_t)c * k_code + uq * kUnitBytes + lane * 16);
+                    // gate/up matrix: gate column groups go to operand tile 0 and the matching up groups to tile 1,
+                    // so that a thread of the drain holds both values of one hidden unit
+                    int tw = w, rg = cgl;
+                    if (p.glu) {
+                        tw = (c >> 1) & 1;                         // chunks of [2 gate | 2 up] groups
+                        rg = ((c >> 2) << 1) | (c & 1);
+                    }
+                    dequant_unit_q4<BF16>(ob + tw * kWTile, rg, wv, scs + (size_t)c * rpg * 16, ra, rb, g, t);
+                }
+            } else {
             // work item = (w * 8 + column group) * US + unit of the stage
             for (int it = wig; it < 8 * NW * US; it += deq_wpg) {
                 const int uu = it % US, c = it / US, cgl = c & 7, w = c >> 3;
@@ -343,6 +367,7 @@ __global__ void __launch_bounds__(kTcThreads, 1) gemm_tc_kernel(const __grid_con
                     rg = ((c >> 2) << 1) | (c & 1);
                 }
                 dequant_unit_q4<BF16>(ob + (tw * US + uu) * kWTile, rg, wv, scs + (size_t)c * rpg * 16, ra, rb, g, t);
+            }
             }
             fence_proxy_async();
             mbar_arrive(&o_full[os]);
@@ -408,7 +433,7 @@ __global__ void __launch_bounds__(kTcThreads, 1) gemm_tc_kernel(const __grid_con
                     for (int j = 0; j < 16; ++j) r[j] = 0u;
                 }
                 if (splits == 1) {
-                    if (p.beta != 1.0f) {
+                    if (DENSE && p.beta != 1.0f) {
 #pragma unroll
                         for (int j = 0; j < 16; ++j) r[j] = __float_as_uint(__fmul_rn(p.beta, __uint_as_float(r[j])));
                     }
@@ -438,7 +463,10 @@ __global__ void __launch_bounds__(kTcThreads, 1) gemm_tc_kernel(const __grid_con
                             }
 #pragma unroll
                             for (int j = 0; j < 16; ++j)
-                                if (tok0 + j0 + j < p.m) p.c[p.col_major ? (size_t)col * p.m + (tok0 + j0 + j) : (size_t)(tok0 + j0 + j) * p.n + col] = v[j];
+                                if (tok0 + j0 + j < p.m) {
+                                    if (!DENSE || !p.col_major) p.c[(size_t)(tok0 + j0 + j) * p.n + col] = v[j];
+                                    else p.c[(size_t)col * p.m + (tok0 + j0 + j)] = v[j];
+                                }
                         }
                     }
                 } else {
@@ -525,8 +553,8 @@ __global__ void __launch_bounds__(kTcThreads, 1) gemm_tc_kernel(const __grid_con
                         for (int jj = 0; jj < 8; ++jj) {
                             const int tok = tok0 + j0 + jj;
                             if (tok >= p.m) continue;
-                            if (p.beta != 1.0f) acc[jj] = __fmul_rn(p.beta, acc[jj]);
-                            const size_t ci = p.col_major ? (size_t)col * p.m + tok : (size_t)tok * p.n + col;
+                            if (DENSE && p.beta != 1.0f) acc[jj] = __fmul_rn(p.beta, acc[jj]);
+                            const size_t ci = (DENSE && p.col_major) ? (size_t)col * p.m + tok : (size_t)tok * p.n + col;
                             if (p.c32) p.c32[(size_t)tok * p.n + col] = acc[jj];
                             else if (p.yacc) p.yacc[(size_t)tok * p.n + col] = __fadd_rn(yv[jj], t_to_f32<BF16>(f32_to_t<BF16>(acc[jj])));
                             else if (p.ep_fast) p.c[ci] = fast_ep_store<BF16>(fe, acc[jj]);
@@ -634,9 +662,9 @@ EncodeTiledFn encode_fn() {
     return fn;
 }
 
-template <int BF16, int US>
+template <int BF16, int US, int DENSE>
 cudaError_t launch_tc(const CUtensorMap& tm, const CUtensorMap& tw, const GemmTcArgs& a, dim3 grid, size_t smem, cudaStream_t stream) {
-    auto kern = gemm_tc_kernel<BF16, US>;
+    auto kern = gemm_tc_kernel<BF16, US, DENSE>;
     static int attr_dev = -1;
     int dev = 0;
     cudaGetDevice(&dev);
@@ -645,7 +673,10 @@ cudaError_t launch_tc(const CUtensorMap& tm, const CUtensorMap& tw, const GemmTc
         if (e != cudaSuccess) return e;
         attr_dev = dev;
     }
-    kern<<<grid, kTcThreads, smem, stream>>>(tm, tw, a);
+    TcMaps<DENSE> maps;
+    maps.tok = tm;
+    if constexpr (DENSE) maps.w = tw;
+    kern<<<grid, kTcThreads, smem, stream>>>(maps, a);
     return cudaGetLastError();
 }
 
@@ -777,8 +808,10 @@ cudaError_t gemm_tc_launch(GemmTcArgs a, int bf16, dim3 grid, size_t smem, cudaS
         if (r != CUDA_SUCCESS) return cudaErrorInvalidValue;
     }
     if (a.beta == 0.0f && !a.wdense) a.beta = 1.0f;
-    cudaError_t e = a.us == 2 ? (bf16 ? launch_tc<1, 2>(tm, tw, a, grid, smem, stream) : launch_tc<0, 2>(tm, tw, a, grid, smem, stream))
-                              : (bf16 ? launch_tc<1, 1>(tm, tw, a, grid, smem, stream) : launch_tc<0, 1>(tm, tw, a, grid, smem, stream));
+    cudaError_t e;
+    if (a.wdense) e = bf16 ? launch_tc<1, 1, 1>(tm, tw, a, grid, smem, stream) : launch_tc<0, 1, 1>(tm, tw, a, grid, smem, stream);
+    else if (a.us == 2) e = bf16 ? launch_tc<1, 2, 0>(tm, tw, a, grid, smem, stream) : launch_tc<0, 2, 0>(tm, tw, a, grid, smem, stream);
+    else e = bf16 ? launch_tc<1, 1, 0>(tm, tw, a, grid, smem, stream) : launch_tc<0, 1, 0>(tm, tw, a, grid, smem, stream);
     if (e != cudaSuccess || !a.defer || grid.z < 2) return e;
     const dim3 rgrid(grid.x * grid.y, a.ntok_pad / 8);
     if (bf16) splitk_reduce_kernel<1><<<rgrid, 256, 0, stream>>>(a, (int)grid.z, (int)grid.x);
