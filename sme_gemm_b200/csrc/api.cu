@@ -567,6 +567,17 @@ static int q4_dev(const smeg_q4* w, const uint16_t* a, uint16_t* c, size_t m, co
         t.counters = sc.counters;
         e = gemm_tc_launch(t, bf16, grid, smem, stream);
     } else {
+        size_t ws_floats = 0, ncounters = 0;
+        q4_gemv_stream_plan(g, bf16, ds->sm_count, &ws_floats, &ncounters);
+        if (g.sgrid) {
+            TcScratch sc;
+            if (tc_scratch(stream, ws_floats, ncounters, &sc)) {
+                if (ext) cudaFreeAsync(ext, stream);
+                return -2;
+            }
+            g.ws = sc.ws;
+            g.counters = sc.counters;
+        }
         e = q4_gemv_launch(g, bf16, ds->sm_count, stream);
     }
     if (ext) cudaFreeAsync(ext, stream);

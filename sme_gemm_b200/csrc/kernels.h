@@ -20,9 +20,19 @@ struct Q4GemvArgs {
     int log2_block;
     int ns, cg, rps, ka, a_rows;  // filled in by the launcher
     int a_vec_ok;                 // rows of `a` are 16-byte aligned (k % 8 == 0 and base aligned)
+    // streaming form (q4_gemv_stream_plan): the (column group, 16-unit stage) list is cut into one
+    // contiguous range per CTA; a column group cut by a range boundary is summed through ws
+    int sgrid;                    // CTAs of the streaming kernel; 0 = the column-group-per-CTA kernel runs
+    int spc, stotal, spieces;     // stages per column group, stages in all, most CTAs one column group spans
+    int sns, sslot, srps, supw;   // ring slots, bytes per slot, scale rows staged per slot, units per warp and stage
+    float* ws;                    // [n16][spieces][8 * MT rows][16] partial sums of cut column groups
+    int* counters;                // one per column group, zero between launches
     unsigned* status;
     EpParams ep;
 };
+// Chooses the streaming form when the call fits it (fills the s* fields; *ws_floats / *ncounters = the
+// scratch the caller must provide in ws / counters).  Leaves sgrid = 0 otherwise.
+void q4_gemv_stream_plan(Q4GemvArgs& a, int bf16, int sm_count, size_t* ws_floats, size_t* ncounters);
 cudaError_t q4_gemv_launch(Q4GemvArgs a, int bf16, int sm_count, cudaStream_t stream);
 
 // ---- activation int8 quantisation + 2-bit / 1-bit GEMV (lowbit_gemv.cu) ----

@@ -20,6 +20,8 @@
 //     weight is dequantised to exactly the reference's rounded value first;
 //   * warps' partial sums are added in a fixed order through shared memory, the
 //     epilogue graph runs on the rounded product, C is stored once.
+#include <algorithm>
+#include <cstdlib>
 #include "epilogue.cuh"
 #include "kernels.h"
 #include "layout.h"
@@ -36,13 +38,13 @@ constexpr int kThreads = 32 * (kConsumerWarps + 1);
 
 __device__ __forceinline__ void mma_f16(float (&d)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1,
                                         const float (&c)[4]) {
-    asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%10,%11,%12,%13};"
+    asm("mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%10,%11,%12,%13};"
                  : "=f"(d[0]), "=f"(d[1]), "=f"(d[2]), "=f"(d[3])
                  : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1), "f"(c[0]), "f"(c[1]), "f"(c[2]), "f"(c[3]));
 }
 __device__ __forceinline__ void mma_bf16(float (&d)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1,
                                          const float (&c)[4]) {
-    asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%10,%11,%12,%13};"
+    asm("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%10,%11,%12,%13};"
                  : "=f"(d[0]), "=f"(d[1]), "=f"(d[2]), "=f"(d[3])
                  : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1), "f"(c[0]), "f"(c[1]), "f"(c[2]), "f"(c[3]));
 }
@@ -353,6 +355,294 @@ __global__ void __launch_bounds__(kThreads) q4_gemv_kernel(const __grid_constant
     if (tid == 0) { SMEG_EV(g_ev_q4, 7); SMEG_EV(g_ev_q4, 15); }
 }
 
+// ---------------------------------------------------------------------------------------------
+// Streaming form for decode-sized calls (m <= 16, all of A in shared memory).
+//
+// The packed codes are one linear stream of 512-byte units in (column group, depth) order.  The
+// list of 16-unit stages -- never crossing a column group -- is cut into one contiguous range per
+// CTA, one CTA per SM, so that every SM streams the same number of bytes (within one stage)
+// whatever n and k are, through a ring as deep as shared memory allows.  16 consumer warps take one
+// unit of each stage; when a column group (or this CTA's share of it) ends they hand their partial
+// sums to a store warp through a double-buffered exchange and go on with the next column group,
+// so the ring never drains between column groups.  A column group cut by a range boundary is
+// summed through global scratch: every CTA of it writes its share, the one that arrives last
+// (an atomic counter per column group, left at zero again) adds the shares in range order and
+// stores.  No CTA waits for another.
+constexpr int kSWarps = 16;
+constexpr int kSThreads = 32 * (kSWarps + 2);   // + producer warp + store warp
+// UPW = units of a stage each consumer warp takes (1 or 2): a stage is 16 * UPW units.  Two units
+// per warp halve the barrier traffic per byte and give the scheduler two independent chains; one
+// keeps the ranges balanced when a CTA only gets a handful of stages.
+
+// UPW units of one stage at once, the walk over the units innermost: their chains are independent,
+// so the instruction stream alternates between them.
+template <int BF16, int OPSIDE, int MT, int UPW>
+__device__ __forceinline__ void consume_units(const uint4 (&wv)[UPW], const uint16_t* sc, const uint4 (&alo)[UPW][MT],
+                                              const uint4 (&ahi)[UPW][MT], int g, int t, const int (&d_unit)[UPW], int blk0,
+                                              int log2_block, float (&total)[MT][4]) {
+    const float zero4[4] = {0.f, 0.f, 0.f, 0.f};
+    if (OPSIDE) {
+#pragma unroll
+        for (int ks = 0; ks < 4; ++ks) {
+#pragma unroll
+            for (int u = 0; u < UPW; ++u) {
+                const uint32_t word = ks == 0 ? wv[u].x : (ks == 1 ? wv[u].y : (ks == 2 ? wv[u].z : wv[u].w));
+                uint32_t af[4];
+                const int d_word = d_unit[u] + 32 * (ks >> 1) + 8 * t + 4 * (ks & 1);
+                decode_word_scaled<BF16>(word, af, sc, g, d_word - (blk0 << log2_block), log2_block);
+#pragma unroll
+                for (int mt = 0; mt < MT; ++mt) {
+                    const uint4& av = (ks >> 1) ? ahi[u][mt] : alo[u][mt];
+                    const uint32_t b0 = (ks & 1) ? av.z : av.x, b1 = (ks & 1) ? av.w : av.y;
+                    if (BF16) mma_bf16(total[mt], af, b0, b1, total[mt]);
+                    else mma_f16(total[mt], af, b0, b1, total[mt]);
+                }
+            }
+        }
+    } else {
+#pragma unroll
+        for (int h = 0; h < 2; ++h) {
+            float part[UPW][MT][4];
+            float2 sf[UPW];
+#pragma unroll
+            for (int u = 0; u < UPW; ++u) {
+                uint32_t af0[4], af1[4];
+                decode_word_f16(h ? wv[u].z : wv[u].x, af0);
+                decode_word_f16(h ? wv[u].w : wv[u].y, af1);
+                const int row = ((d_unit[u] + 32 * h) >> log2_block) - blk0;
+                // one 32-bit read: the scales of columns g and g+8 sit side by side
+                const uint32_t sp = *reinterpret_cast<const uint32_t*>(sc + row * 16 + 2 * g);
+                sf[u] = __half22float2(*reinterpret_cast<const __half2*>(&sp));
+#pragma unroll
+                for (int mt = 0; mt < MT; ++mt) {
+                    const uint4& av = h ? ahi[u][mt] : alo[u][mt];
+                    mma_f16(part[u][mt], af0, av.x, av.y, zero4);
+                    mma_f16(part[u][mt], af1, av.z, av.w, part[u][mt]);
+                }
+            }
+#pragma unroll
+            for (int u = 0; u < UPW; ++u)
+#pragma unroll
+                for (int mt = 0; mt < MT; ++mt) {
+                    total[mt][0] = fmaf(part[u][mt][0], sf[u].x, total[mt][0]);
+                    total[mt][1] = fmaf(part[u][mt][1], sf[u].x, total[mt][1]);
+                    total[mt][2] = fmaf(part[u][mt][2], sf[u].y, total[mt][2]);
+                    total[mt][3] = fmaf(part[u][mt][3], sf[u].y, total[mt][3]);
+                }
+        }
+    }
+}
+
+// First stage of CTA b's range, and the CTA whose range holds stage s.
+__device__ __forceinline__ int srange_begin(int b, int total, int grid) { return (int)((long long)b * total / grid); }
+__device__ __forceinline__ int srange_owner(int s, int total, int grid) {
+    return (int)((((long long)s + 1) * grid - 1) / total);
+}
+
+template <int BF16, int OPSIDE, int MT, int UPW>
+__global__ void __launch_bounds__(kSThreads, 1) q4_gemv_stream_kernel(const __grid_constant__ Q4GemvArgs p) {
+    constexpr int kSU = kSWarps * UPW;                               // units per stage
+    constexpr int kSCodeBytes = kSU * kUnitBytes;
+    extern __shared__ __align__(128) unsigned char smem_raw[];
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const int g = lane >> 2, t = lane & 3;
+    const int NS = p.sns, spc = p.spc;
+
+    uint64_t* full = reinterpret_cast<uint64_t*>(smem_raw);         // [NS] stage landed
+    uint64_t* empty = full + NS;                                     // [NS] stage released by the 16 consumer warps
+    uint64_t* r_full = empty + NS;                                   // [2] partial sums handed to the store warp
+    uint64_t* r_empty = r_full + 2;                                  // [2] ... and read by it
+    uint64_t* a_full = r_empty + 2;                                  // activations landed
+    volatile int* abort_flag = reinterpret_cast<volatile int*>(a_full + 1);
+    unsigned char* ring = smem_raw + 1024;
+    const int a_stride = p.k64 * 64 + 8;                             // halves; +16 B keeps LDS.128 conflict-free
+    uint16_t* As = reinterpret_cast<uint16_t*>(ring + (size_t)NS * p.sslot);
+    float* red = reinterpret_cast<float*>(reinterpret_cast<unsigned char*>(As) + (size_t)p.a_rows * a_stride * 2);
+    constexpr int kVals = 4 * MT;                                    // values per lane of one column group's tile
+
+    const int s_begin = srange_begin(blockIdx.x, p.stotal, gridDim.x);
+    const int s_end = srange_begin(blockIdx.x + 1, p.stotal, gridDim.x);
+
+    if (tid == 0) {
+        for (int s = 0; s < NS; ++s) {
+            mbar_init(&full[s], 1);
+            mbar_init(&empty[s], kSWarps);
+        }
+        for (int b = 0; b < 2; ++b) {
+            mbar_init(&r_full[b], kSWarps);
+            mbar_init(&r_empty[b], 1);
+        }
+        mbar_init(a_full, 1);
+        *abort_flag = 0;
+        fence_barrier_init();
+    }
+    // depths past k: the bulk copies write [0, k) of each row only
+    {
+        const int pad = p.k64 * 64 - p.k;
+        for (int idx = tid; idx < p.a_rows * pad; idx += kSThreads) As[(size_t)(idx / pad) * a_stride + p.k + idx % pad] = 0;
+    }
+    __syncthreads();
+
+    if (warp == kSWarps) {
+        // ================= producer =================
+        if (lane == 0) mbar_expect_tx(a_full, (unsigned)(p.a_rows * p.k * 2));
+        __syncwarp();
+        for (int r = lane; r < p.a_rows; r += 32) bulk_g2s(As + (size_t)r * a_stride, p.a + (size_t)r * p.k, (unsigned)(p.k * 2), a_full);
+        // a round of four stages, two lanes each: codes and scale rows go out in parallel
+        constexpr int kRound = 4;
+        const int si = lane >> 1, j = lane & 1;
+        for (int st0 = s_begin; st0 < s_end; st0 += kRound) {
+            const int st = st0 + si;
+            const bool active = si < kRound && st < s_end;
+            const int i = st - s_begin, slot = active ? i % NS : 0;
+            const int cg = active ? st / spc : 0;
+            const int u0 = active ? (st - cg * spc) * kSU : 0;
+            const int units = active ? min(kSU, p.k64 - u0) : 0;
+            const int blk0 = (u0 * 64) >> p.log2_block;
+            const int blk1 = min(p.nb, (((u0 + units) * 64 - 1) >> p.log2_block) + 1);
+            const unsigned cb = units * kUnitBytes, sb = (unsigned)max(blk1 - blk0, 0) * 32;
+            bool ok = true;
+            if (active && j == 0) {
+                if (i >= NS) ok = mbar_wait(&empty[slot], ((i / NS) - 1) & 1, abort_flag, p.status);
+                if (ok) mbar_expect_tx(&full[slot], cb + sb);
+            }
+            if (!__all_sync(0xffffffffu, ok)) return;
+            if (active) {
+                unsigned char* sbase = ring + (size_t)slot * p.sslot;
+                if (j == 0) bulk_g2s(sbase, p.codes + q4_unit_offset((size_t)cg, (size_t)u0, p.k64), cb, &full[slot]);
+                else if (sb) bulk_g2s(sbase + kSCodeBytes, p.scales + q4_scale_row((size_t)cg, blk0, p.nb), sb, &full[slot]);
+            }
+        }
+        return;
+    }
+
+    if (warp == kSWarps + 1) {
+        // ================= store warp =================
+        int tix = 0;
+        for (int st = s_begin; st < s_end; ++tix) {
+            const int cg = st / spc;
+            const int cg_first = cg * spc, cg_last = cg_first + spc;      // this column group's stages
+            const int piece_end = min(s_end, cg_last);
+            const int par = tix & 1;
+            if (!mbar_wait(&r_full[par], (tix >> 1) & 1, abort_flag, p.status)) return;
+            float v[kVals];
+            const float* rb = red + (size_t)par * kSWarps * kVals * 32;
+#pragma unroll
+            for (int q = 0; q < kVals; ++q) {
+                float acc = 0.0f;
+#pragma unroll
+                for (int w = 0; w < kSWarps; ++w) acc += rb[(w * kVals + q) * 32 + lane];
+                v[q] = acc;
+            }
+            __syncwarp();
+            if (lane == 0) mbar_arrive(&r_empty[par]);
+            bool store = true;
+            if (st != cg_first || piece_end != cg_last) {
+                // a cut column group: publish this share; the last CTA to arrive adds them in range order
+                const int first_cta = srange_owner(cg_first, p.stotal, gridDim.x);
+                const int last_cta = srange_owner(cg_last - 1, p.stotal, gridDim.x);
+                const int np = last_cta - first_cta + 1;
+                float* mine = p.ws + ((size_t)cg * p.spieces + (blockIdx.x - first_cta)) * (kVals * 32);
+#pragma unroll
+                for (int q = 0; q < kVals; ++q) mine[q * 32 + lane] = v[q];
+                __threadfence();
+                __syncwarp();
+                int old = 0;
+                if (lane == 0) old = atomicAdd(&p.counters[cg], 1);
+                old = __shfl_sync(0xffffffffu, old, 0);
+                store = old == np - 1;
+                if (store) {
+                    __threadfence();
+                    const float* base = p.ws + (size_t)cg * p.spieces * (kVals * 32);
+#pragma unroll
+                    for (int q = 0; q < kVals; ++q) v[q] = 0.0f;
+                    for (int pc = 0; pc < np; ++pc) {
+#pragma unroll
+                        for (int q = 0; q < kVals; ++q) v[q] += __ldcg(base + (size_t)pc * (kVals * 32) + q * 32 + lane);
+                    }
+                    if (lane == 0) p.counters[cg] = 0;
+                }
+            }
+            if (store) {
+#pragma unroll
+                for (int q = 0; q < kVals; ++q) {
+                    const int mt = q >> 2, r = q & 3;
+                    const int col = cg * 16 + g + 8 * (r >> 1);
+                    const int row = 8 * mt + 2 * t + (r & 1);
+                    if (col < p.n && row < p.m) {
+                        if (p.c32) p.c32[(size_t)row * p.n + col] = v[q];
+                        else p.c[(size_t)row * p.n + col] = ep_store_value<BF16>(p.ep, v[q], (size_t)row, (size_t)col);
+                    }
+                }
+            }
+            st = piece_end;
+        }
+        return;
+    }
+
+    // ================= consumers =================
+    float total[MT][4];
+#pragma unroll
+    for (int mt = 0; mt < MT; ++mt)
+#pragma unroll
+        for (int r = 0; r < 4; ++r) total[mt][r] = 0.0f;
+    if (!mbar_wait(a_full, 0, abort_flag, p.status)) return;
+    int tix = 0;
+    int sl = s_begin % spc;
+    int slot = 0;
+    unsigned phase = 0;
+    for (int st = s_begin; st < s_end; ++st) {
+        if (!mbar_wait(&full[slot], phase, abort_flag, p.status)) return;
+        const int u0 = sl * kSU;
+        const int units = min(kSU, p.k64 - u0);
+        const unsigned char* sbase = ring + (size_t)slot * p.sslot;
+        const int blk0 = (u0 * 64) >> p.log2_block;
+        // a unit past the end of a short stage is computed as zero weights at the first unit's depth
+        uint4 wv[UPW], alo[UPW][MT], ahi[UPW][MT];
+        int d_unit[UPW];
+#pragma unroll
+        for (int uu = 0; uu < UPW; ++uu) {
+            const int ul = warp + uu * kSWarps;
+            const bool valid = ul < units;
+            d_unit[uu] = (u0 + (valid ? ul : 0)) * 64;
+            wv[uu] = make_uint4(0x88888888u, 0x88888888u, 0x88888888u, 0x88888888u);
+            if (valid) wv[uu] = *reinterpret_cast<const uint4*>(sbase + ul * kUnitBytes + lane * 16);
+#pragma unroll
+            for (int mt = 0; mt < MT; ++mt) {
+                alo[uu][mt] = make_uint4(0, 0, 0, 0);
+                ahi[uu][mt] = make_uint4(0, 0, 0, 0);
+                if (8 * mt + g < p.a_rows) {
+                    const uint16_t* ar = As + (size_t)(8 * mt + g) * a_stride + d_unit[uu] + 8 * t;
+                    alo[uu][mt] = *reinterpret_cast<const uint4*>(ar);
+                    ahi[uu][mt] = *reinterpret_cast<const uint4*>(ar + 32);
+                }
+            }
+        }
+        if (warp < units)
+            consume_units<BF16, OPSIDE, MT, UPW>(wv, reinterpret_cast<const uint16_t*>(sbase + kSCodeBytes), alo, ahi, g, t, d_unit,
+                                                 blk0, p.log2_block, total);
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&empty[slot]);
+        if (sl == spc - 1 || st == s_end - 1) {
+            const int par = tix & 1;
+            if (tix >= 2 && !mbar_wait(&r_empty[par], ((tix >> 1) - 1) & 1, abort_flag, p.status)) return;
+            float* rb = red + ((size_t)par * kSWarps + warp) * kVals * 32;
+#pragma unroll
+            for (int mt = 0; mt < MT; ++mt)
+#pragma unroll
+                for (int r = 0; r < 4; ++r) {
+                    rb[(mt * 4 + r) * 32 + lane] = total[mt][r];
+                    total[mt][r] = 0.0f;
+                }
+            __syncwarp();
+            if (lane == 0) mbar_arrive(&r_full[par]);
+            ++tix;
+        }
+        if (++sl == spc) sl = 0;
+        if (++slot == NS) { slot = 0; phase ^= 1u; }
+    }
+}
+
 template <int BF16, int OPSIDE, int MT>
 cudaError_t launch(const Q4GemvArgs& a, dim3 grid, size_t smem, cudaStream_t stream) {
     auto kern = q4_gemv_kernel<BF16, OPSIDE, MT>;
@@ -378,8 +668,76 @@ extern "C" int smeg_debug_ev_q4(long long* host) { return cudaMemcpyFromSymbol(h
 // Host-side launcher.  Chooses the column groups per CTA so that the grid has
 // at least about two CTAs per SM when the matrix allows it, the ring depth from
 // the shared-memory budget, and the activation chunk from the row count.
+void q4_gemv_stream_plan(Q4GemvArgs& a, int bf16, int sm_count, size_t* ws_floats, size_t* ncounters) {
+    (void)bf16;
+    a.sgrid = 0;
+    *ws_floats = 0;
+    *ncounters = 0;
+    // tuning knob, read per call: 0 keeps every call on the column-group-per-CTA kernel, 2 streams small matrices too
+    const char* knob = getenv("SMEG_Q4_STREAM");
+    const int enabled = knob ? atoi(knob) : 1;
+    if (!enabled || !a.a_vec_ok || a.m > 16 || a.k64 <= 0 || a.n16 <= 0 || sm_count <= 0) return;
+    const int mt = a.m <= 8 ? 1 : 2;
+    // two units per warp and stage when every CTA still gets a dozen stages or more
+    const int upw = (long long)a.n16 * ((a.k64 + 2 * kSWarps - 1) / (2 * kSWarps)) >= 12ll * sm_count ? 2 : 1;
+    // smaller matrices (under about 200 KB of codes per SM) stay on the column-group-per-CTA kernel: its two
+    // CTAs per SM start and finish faster than one deep ring does (SMEG_Q4_STREAM=2 streams them too)
+    if (upw == 1 && enabled != 2) return;
+    const int su = kSWarps * upw;
+    const int block = 1 << a.log2_block, stage_depth = 64 * su;
+    a.supw = upw;
+    a.srps = block < stage_depth ? stage_depth / block : 1;
+    a.sslot = (su * kUnitBytes + a.srps * 32 + 127) / 128 * 128;
+    const size_t a_bytes = (size_t)a.m * ((size_t)a.k64 * 64 + 8) * 2;
+    const size_t red_bytes = (size_t)2 * kSWarps * 4 * mt * 32 * sizeof(float);
+    const size_t budget = 227 * 1024;
+    if (1024 + a_bytes + red_bytes + (size_t)8 * a.sslot > budget) return;     // the ring needs at least 8 slots
+    a.sns = (int)std::min<size_t>((budget - 1024 - a_bytes - red_bytes) / a.sslot, 48);
+    a.spc = (a.k64 + su - 1) / su;
+    const long long total = (long long)a.n16 * a.spc;
+    if (total > 0x3fffffff) return;
+    a.stotal = (int)total;
+    const int grid = (int)std::min<long long>(sm_count, total);
+    const int minlen = a.stotal / grid;                                         // shortest range, >= 1
+    a.spieces = (a.spc + minlen - 1) / minlen + 1;
+    a.a_rows = a.m;
+    a.sgrid = grid;
+    *ws_floats = (size_t)a.n16 * a.spieces * 128 * mt;
+    *ncounters = (size_t)a.n16;
+}
+
+template <int BF16, int OPSIDE, int MT, int UPW>
+static cudaError_t launch_stream_u(const Q4GemvArgs& a, cudaStream_t stream) {
+    auto kern = q4_gemv_stream_kernel<BF16, OPSIDE, MT, UPW>;
+    static int attr_dev = -1;
+    int dev = 0;
+    cudaGetDevice(&dev);
+    if (attr_dev != dev) {
+        cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024);
+        if (e != cudaSuccess) return e;
+        attr_dev = dev;
+    }
+    const size_t smem = 1024 + (size_t)a.sns * a.sslot + (size_t)a.a_rows * ((size_t)a.k64 * 64 + 8) * 2 +
+                        (size_t)2 * kSWarps * 4 * MT * 32 * sizeof(float);
+    if (smem > 227 * 1024) return cudaErrorInvalidConfiguration;
+    kern<<<a.sgrid, kSThreads, smem, stream>>>(a);
+    return cudaGetLastError();
+}
+
+template <int BF16, int OPSIDE, int MT>
+static cudaError_t launch_stream(const Q4GemvArgs& a, cudaStream_t stream) {
+    return a.supw == 2 ? launch_stream_u<BF16, OPSIDE, MT, 2>(a, stream) : launch_stream_u<BF16, OPSIDE, MT, 1>(a, stream);
+}
+
 cudaError_t q4_gemv_launch(Q4GemvArgs a, int bf16, int sm_count, cudaStream_t stream) {
     const int opside = bf16 || a.log2_block < 5;
+    if (a.sgrid > 0) {
+        if (!a.ws || !a.counters) return cudaErrorInvalidValue;
+        const int smt = a.m <= 8 ? 1 : 2;
+        if (!bf16 && !opside) return smt == 1 ? launch_stream<0, 0, 1>(a, stream) : launch_stream<0, 0, 2>(a, stream);
+        if (!bf16) return smt == 1 ? launch_stream<0, 1, 1>(a, stream) : launch_stream<0, 1, 2>(a, stream);
+        return smt == 1 ? launch_stream<1, 1, 1>(a, stream) : launch_stream<1, 1, 2>(a, stream);
+    }
     const int mt = a.m <= 8 ? 1 : (a.m <= 16 ? 2 : 4);
     int cg = 4;
     while (cg > 1 && (a.n16 + cg - 1) / cg < 2 * sm_count) cg >>= 1;

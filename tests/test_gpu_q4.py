@@ -136,6 +136,62 @@ def test_empty_graph_equals_plain_call_bit_for_bit():
     assert torch.equal(c1.view(torch.int16), c2.view(torch.int16))
 
 
+@pytest.fixture
+def stream_every_size(monkeypatch):
+    """The streaming decode kernel normally takes only matrices of a few hundred KB per SM; the tuning
+    knob (read per call by the library) sends every call that fits it there."""
+    monkeypatch.setenv("SMEG_Q4_STREAM", "2")
+
+
+# k % 8 == 0 (rows of A travel by bulk copy); n and k chosen so that column groups are cut by the
+# per-CTA ranges, stages end short, and the last column group is partly outside the matrix
+STREAM_SHAPES = [(1, 33, 256), (1, 4109, 4096), (3, 1030, 2056), (4, 100, 72), (7, 2000, 1032), (8, 160, 11008),
+                 (9, 389, 1024), (16, 1100, 2048), (2, 16, 14336)]
+
+
+@pytest.mark.parametrize("m,n,k", STREAM_SHAPES)
+@pytest.mark.parametrize("block", [16, 32, 128])
+def test_q4_streaming_decode_kernel_matches_oracle(stream_every_size, m, n, k, block):
+    g, w, _ = run_q4(m, n, k, block)
+    assert max_rel(g, w) <= TOL, f"{m}x{n}x{k} block {block}"
+    g, w, _ = run_q4(m, n, k, block, ep_builder=bias_relu)
+    assert max_rel(g, w) <= TOL
+    if block != 16:
+        g, w, _ = run_q4(m, n, k, block, bf16=True)
+        assert max_rel(g, w) <= TOL
+
+
+@pytest.mark.parametrize("block", [8, 4096])
+def test_q4_streaming_decode_kernel_block_extremes(stream_every_size, block):
+    g, w, _ = run_q4(3, 200, 8192 if block == 4096 else 264, block, from_f32=False)
+    assert max_rel(g, w) <= TOL
+
+
+def test_q4_streaming_decode_kernel_is_repeatable_and_leaves_its_counters_clear(stream_every_size):
+    """Column groups cut between CTAs are summed in range order by whichever CTA arrives last: the result
+    does not depend on which one that is, and the arrival counters are zero again for the next call."""
+    m, n, k = 2, 1200, 4096
+    rng = np.random.default_rng(11)
+    q, s = q4_logical(rng, n, k, 32)
+    w = sg.Q4Weights.new(q, s, n, k)
+    a = torch.from_numpy(rng.standard_normal((m, k)).astype(np.float16)).cuda()
+    outs = []
+    for _ in range(5):
+        c = torch.zeros((m, n), dtype=torch.float16, device="cuda")
+        sg.matmul_q4(a, w, c, m)
+        outs.append(c)
+    torch.cuda.synchronize()
+    assert sg.last_status() == 0
+    for c in outs[1:]:
+        assert torch.equal(c.view(torch.int16), outs[0].view(torch.int16))
+
+
+def test_q4_streaming_decode_kernel_at_the_size_that_selects_it():
+    """Down projection of the MLP block at two rows: large enough to stream without the knob."""
+    g, w, _ = run_q4(2, 4096, 14336, 32, seed=2)
+    assert max_rel(g, w) <= TOL
+
+
 def test_config1_decode_gemv_full_size():
     """M=1, K=4096, N=4096, A ~ N(0,1) f16, W ~ N(0,0.02) -> Q4_0 block 32."""
     g, w, _ = run_q4(1, 4096, 4096, 32, seed=1)
