@@ -46,6 +46,18 @@ int g_tc_min_rows = []() {
     return e ? atoi(e) : 16;
 }();
 
+}  // namespace
+namespace smeg {
+bool pdl_enabled() {
+    static const bool on = []() {
+        const char* e = getenv("SMEG_PDL");
+        return !(e && e[0] == '0');
+    }();
+    return on;
+}
+}  // namespace smeg
+namespace {
+
 DeviceState* dev_state() {
     int dev = 0;
     if (cudaGetDevice(&dev) != cudaSuccess) return nullptr;

@@ -13,6 +13,8 @@ namespace {
 // gate and up interleaved 32 columns at a time (last chunk w < 32 wide).
 __global__ void glu_kernel(uint16_t* __restrict__ out, const uint16_t* __restrict__ both, size_t m, size_t n,
                            uint32_t act) {
+    pdl_launch_dependents();
+    pdl_wait();
     const size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
     if (idx >= m * n) return;
     const size_t i = idx / n, col = idx % n;
@@ -31,6 +33,8 @@ __global__ void glu_kernel(uint16_t* __restrict__ out, const uint16_t* __restric
 }
 
 __global__ void add_f16_to_f32_kernel(float* __restrict__ dst, const uint16_t* __restrict__ src, size_t n) {
+    pdl_launch_dependents();
+    pdl_wait();
     const size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
     if (idx < n) dst[idx] = __fadd_rn(dst[idx], __half2float(__ushort_as_half(src[idx])));
 }
@@ -62,13 +66,11 @@ inline unsigned blocks_for(size_t n) { return (unsigned)((n + 255) / 256); }
 
 cudaError_t glu_launch(uint16_t* out, const uint16_t* both, size_t m, size_t n, uint32_t act, cudaStream_t s) {
     if (m * n == 0) return cudaSuccess;
-    glu_kernel<<<blocks_for(m * n), 256, 0, s>>>(out, both, m, n, act);
-    return cudaGetLastError();
+    return launch_pdl(glu_kernel, dim3(blocks_for(m * n)), dim3(256), 0, s, out, both, m, n, act);
 }
 cudaError_t add_f16_to_f32_launch(float* dst, const uint16_t* src, size_t n, cudaStream_t s) {
     if (n == 0) return cudaSuccess;
-    add_f16_to_f32_kernel<<<blocks_for(n), 256, 0, s>>>(dst, src, n);
-    return cudaGetLastError();
+    return launch_pdl(add_f16_to_f32_kernel, dim3(blocks_for(n)), dim3(256), 0, s, dst, src, n);
 }
 cudaError_t round_add_f32_launch(float* y, const float* sum, size_t n, cudaStream_t s) {
     if (n == 0) return cudaSuccess;

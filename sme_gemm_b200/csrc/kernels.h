@@ -35,6 +35,28 @@ struct Q4GemvArgs {
 void q4_gemv_stream_plan(Q4GemvArgs& a, int bf16, int sm_count, size_t* ws_floats, size_t* ncounters);
 cudaError_t q4_gemv_launch(Q4GemvArgs a, int bf16, int sm_count, cudaStream_t stream);
 
+// Launch with programmatic stream serialisation allowed: when the kernel ahead in the stream has let
+// its dependents go (griddepcontrol.launch_dependents in every CTA, or its end), this kernel's CTAs
+// may start while that one drains.  Every kernel launched this way executes griddepcontrol.wait
+// (pdl_wait) in every thread before its first access to memory another kernel may have written, and
+// before its first store; what it does earlier (barrier set-up, weight prefetch) overlaps the tail of
+// its predecessor.  SMEG_PDL=0 launches plainly.
+bool pdl_enabled();
+template <typename... KArgs, typename... Args>
+inline cudaError_t launch_pdl(void (*kern)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream, Args&&... args) {
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = grid;
+    cfg.blockDim = block;
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = pdl_enabled() ? 1 : 0;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    return cudaLaunchKernelEx(&cfg, kern, KArgs(args)...);
+}
+
 // ---- activation int8 quantisation + 2-bit / 1-bit GEMV (lowbit_gemv.cu) ----
 struct ActQuantArgs {
     const uint16_t* a;    // m x k f16 bits

@@ -54,6 +54,8 @@ __device__ __forceinline__ uint32_t prmt(uint32_t lut, uint32_t sel) {
 // quantize_row, src/kernels/lowbit/matmul.rs:354-371.
 // ---------------------------------------------------------------------------
 __global__ void __launch_bounds__(128) act_quant_kernel(ActQuantArgs p) {
+    pdl_launch_dependents();
+    pdl_wait();
     __shared__ float s_max[4];
     __shared__ int s_nan[4];
     __shared__ int s_sum[4];
@@ -180,17 +182,21 @@ __global__ void __launch_bounds__(kThreadsLb, 1) lowbit_gemv_kernel(const __grid
         fence_barrier_init();
     }
     __syncthreads();
+    pdl_launch_dependents();
     if (tid == 0) SMEG_EV(g_ev_lb, 1);
 
     if (warp == kCWarps) {
         // ================= producer =================
-        if (fused) {
-            // the activation rows first: one bulk copy per row, one lane each
+        // The first round of weights goes out at once (it does not depend on the kernel ahead in the stream);
+        // the activation rows follow when that kernel's memory is visible: one bulk copy per row, one lane each.
+        auto send_a = [&]() {
+            pdl_wait();
+            if (!fused) return;
             if (lane == 0) mbar_expect_tx(a_full, (unsigned)rows_used * (unsigned)p.k * 2u);
             __syncwarp();
             for (int r = lane; r < rows_used; r += 32)
                 bulk_g2s(const_cast<uint16_t*>(Abuf) + (size_t)r * KQ, p.a + (size_t)(row0 + r) * p.k, (unsigned)p.k * 2u, a_full);
-        }
+        };
         // lane = (stage of the round, copy): copies 0-7 are the code runs of the task's column
         // groups, 8-15 their scale rows (first stage of a fold chunk only); a round never holds
         // more stages than the ring has slots
@@ -226,12 +232,15 @@ __global__ void __launch_bounds__(kThreadsLb, 1) lowbit_gemv_kernel(const __grid
                     bulk_g2s(Ss + ((size_t)(fseq & 1) * GPT + (j - 8)) * bpc * 16,
                              p.scales + ((size_t)(cg0 + j - 8) * p.nb + blk0) * 16, nrows * 32, &full[slot]);
             }
+            if (seq0 == 0) send_a();
         }
+        if (total_seq == 0) send_a();
         if (lane == 0) SMEG_EV(g_ev_lb, 2);
         return;
     }
 
     // ================= consumers =================
+    pdl_wait();
     // rows past the batch feed zeros to the MMAs
     for (int idx = tid; idx < (rows - rows_used) * (q_stride / 4); idx += 32 * kCWarps)
         reinterpret_cast<uint32_t*>(Qs + (size_t)rows_used * q_stride)[idx] = 0u;
@@ -600,8 +609,7 @@ cudaError_t launch_lb(const LowbitGemvArgs& a, dim3 grid, size_t smem, cudaStrea
         attr_dev = dev;
     }
     if (smem > 227 * 1024) return cudaErrorInvalidConfiguration;
-    kern<<<grid, kThreadsLb, smem, stream>>>(a);
-    return cudaGetLastError();
+    return launch_pdl(kern, grid, dim3(kThreadsLb), smem, stream, a);
 }
 
 // bytes of the region shared by the staged f16 rows and the block sums
@@ -629,8 +637,7 @@ extern "C" int smeg_debug_ev_lb(long long* host) { return cudaMemcpyFromSymbol(h
 cudaError_t act_quant_launch(const ActQuantArgs& a, cudaStream_t stream) {
     if (a.m == 0 || a.nbq == 0) return cudaSuccess;
     dim3 grid(a.nbq, a.m);
-    act_quant_kernel<<<grid, 128, 0, stream>>>(a);
-    return cudaGetLastError();
+    return launch_pdl(act_quant_kernel, grid, dim3(128), 0, stream, a);
 }
 
 // Picks rows per CTA, column groups per task, the staged activation chunk, the fold chunk and the

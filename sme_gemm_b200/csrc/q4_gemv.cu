@@ -152,6 +152,7 @@ __global__ void __launch_bounds__(kThreads) q4_gemv_kernel(const __grid_constant
         fence_barrier_init();
     }
     __syncthreads();
+    pdl_launch_dependents();
     if (tid == 0) SMEG_EV(g_ev_q4, 1);
 
     if (warp == kConsumerWarps) {
@@ -167,24 +168,29 @@ __global__ void __launch_bounds__(kThreads) q4_gemv_kernel(const __grid_constant
         int round_stages = min(min(32 / per_stage, NS), 2);
         if (nchunks > 1) round_stages = min(round_stages, stages_per_chunk);
         const int si = lane / per_stage, j = lane % per_stage;
-        for (int st0 = 0; st0 < num_stages; st0 += round_stages) {
-            if (p.a_vec_ok) {
-                // activation chunks that start inside this round: one bulk copy per row, one lane each
-                for (int st = st0; st < min(num_stages, st0 + round_stages); ++st) {
-                    if (st % stages_per_chunk != 0) continue;
-                    const int ch = st / stages_per_chunk, buf = ch & 1;
-                    const int ka0 = ch * p.ka;
-                    const unsigned bytes = (unsigned)(min(p.ka, p.k - ka0) * 2);
-                    bool ok = true;
-                    if (lane == 0) {
-                        if (ch >= 2) ok = mbar_wait(&a_empty[buf], ((ch >> 1) - 1) & 1, abort_flag, p.status);
-                        if (ok) mbar_expect_tx(&a_full[buf], rows_used * bytes);
-                    }
-                    if (!__all_sync(0xffffffffu, ok)) return;
-                    for (int r = lane; r < rows_used; r += 32)
-                        bulk_g2s(As + buf * a_buf_halves + (size_t)r * a_stride, p.a + (size_t)(row0 + r) * p.k + ka0, bytes, &a_full[buf]);
+        // activation chunks that start inside the round at st0: one bulk copy per row, one lane each
+        auto send_a = [&](int st0) -> bool {
+            if (!p.a_vec_ok) return true;
+            for (int st = st0; st < min(num_stages, st0 + round_stages); ++st) {
+                if (st % stages_per_chunk != 0) continue;
+                const int ch = st / stages_per_chunk, buf = ch & 1;
+                const int ka0 = ch * p.ka;
+                const unsigned bytes = (unsigned)(min(p.ka, p.k - ka0) * 2);
+                bool ok = true;
+                if (lane == 0) {
+                    if (ch >= 2) ok = mbar_wait(&a_empty[buf], ((ch >> 1) - 1) & 1, abort_flag, p.status);
+                    if (ok) mbar_expect_tx(&a_full[buf], rows_used * bytes);
                 }
+                if (!__all_sync(0xffffffffu, ok)) return false;
+                for (int r = lane; r < rows_used; r += 32)
+                    bulk_g2s(As + buf * a_buf_halves + (size_t)r * a_stride, p.a + (size_t)(row0 + r) * p.k + ka0, bytes, &a_full[buf]);
             }
+            return true;
+        };
+        for (int st0 = 0; st0 < num_stages; st0 += round_stages) {
+            // The first round's weights go out before anything else: they do not depend on the kernel ahead in
+            // the stream; the activations may, and follow once that kernel's memory is visible.
+            if (st0 != 0 && !send_a(st0)) return;
             const int st = st0 + si;
             const bool active = si < round_stages && st < num_stages;
             const int slot = active ? st % NS : 0;
@@ -207,6 +213,10 @@ __global__ void __launch_bounds__(kThreads) q4_gemv_kernel(const __grid_constant
                     else bulk_g2s(sbase + CG * code_bytes + c * scale_bytes, p.scales + q4_scale_row(cgi, blk0, p.nb), sb, &full[slot]);
                 }
             }
+            if (st0 == 0) {
+                pdl_wait();
+                if (!send_a(0)) return;
+            }
             if (lane == 0 && st0 == 0) SMEG_EV(g_ev_q4, 8);
         }
         if (lane == 0) SMEG_EV(g_ev_q4, 2);
@@ -214,6 +224,7 @@ __global__ void __launch_bounds__(kThreads) q4_gemv_kernel(const __grid_constant
     }
 
     // ================= consumers =================
+    pdl_wait();
     float total[4][MT][4];
 #pragma unroll
     for (int c = 0; c < 4; ++c)
@@ -482,16 +493,26 @@ __global__ void __launch_bounds__(kSThreads, 1) q4_gemv_stream_kernel(const __gr
         for (int idx = tid; idx < p.a_rows * pad; idx += kSThreads) As[(size_t)(idx / pad) * a_stride + p.k + idx % pad] = 0;
     }
     __syncthreads();
+    pdl_launch_dependents();
 
     if (warp == kSWarps) {
         // ================= producer =================
-        if (lane == 0) mbar_expect_tx(a_full, (unsigned)(p.a_rows * p.k * 2));
-        __syncwarp();
-        for (int r = lane; r < p.a_rows; r += 32) bulk_g2s(As + (size_t)r * a_stride, p.a + (size_t)r * p.k, (unsigned)(p.k * 2), a_full);
+        // The weights do not depend on the kernel ahead in the stream: the ring is filled first, and the
+        // activations follow once that kernel's memory is visible (before the first wait on a ring slot).
+        bool a_sent = false;
+        auto send_a = [&]() {
+            pdl_wait();
+            if (lane == 0) mbar_expect_tx(a_full, (unsigned)(p.a_rows * p.k * 2));
+            __syncwarp();
+            for (int r = lane; r < p.a_rows; r += 32)
+                bulk_g2s(As + (size_t)r * a_stride, p.a + (size_t)r * p.k, (unsigned)(p.k * 2), a_full);
+            a_sent = true;
+        };
         // a round of four stages, two lanes each: codes and scale rows go out in parallel
         constexpr int kRound = 4;
         const int si = lane >> 1, j = lane & 1;
         for (int st0 = s_begin; st0 < s_end; st0 += kRound) {
+            if (!a_sent && st0 - s_begin + kRound > NS) send_a();
             const int st = st0 + si;
             const bool active = si < kRound && st < s_end;
             const int i = st - s_begin, slot = active ? i % NS : 0;
@@ -513,11 +534,13 @@ __global__ void __launch_bounds__(kSThreads, 1) q4_gemv_stream_kernel(const __gr
                 else if (sb) bulk_g2s(sbase + kSCodeBytes, p.scales + q4_scale_row((size_t)cg, blk0, p.nb), sb, &full[slot]);
             }
         }
+        if (!a_sent) send_a();
         return;
     }
 
     if (warp == kSWarps + 1) {
         // ================= store warp =================
+        pdl_wait();
         int tix = 0;
         for (int st = s_begin; st < s_end; ++tix) {
             const int cg = st / spc;
@@ -586,6 +609,7 @@ __global__ void __launch_bounds__(kSThreads, 1) q4_gemv_stream_kernel(const __gr
     for (int mt = 0; mt < MT; ++mt)
 #pragma unroll
         for (int r = 0; r < 4; ++r) total[mt][r] = 0.0f;
+    pdl_wait();
     if (!mbar_wait(a_full, 0, abort_flag, p.status)) return;
     int tix = 0;
     int sl = s_begin % spc;
@@ -655,8 +679,7 @@ cudaError_t launch(const Q4GemvArgs& a, dim3 grid, size_t smem, cudaStream_t str
         attr_dev = dev;
     }
     if (smem > 227 * 1024) return cudaErrorInvalidConfiguration;
-    kern<<<grid, kThreads, smem, stream>>>(a);
-    return cudaGetLastError();
+    return launch_pdl(kern, grid, dim3(kThreads), smem, stream, a);
 }
 
 }  // namespace
@@ -691,7 +714,7 @@ void q4_gemv_stream_plan(Q4GemvArgs& a, int bf16, int sm_count, size_t* ws_float
     const size_t a_bytes = (size_t)a.m * ((size_t)a.k64 * 64 + 8) * 2;
     const size_t red_bytes = (size_t)2 * kSWarps * 4 * mt * 32 * sizeof(float);
     const size_t budget = 227 * 1024;
-    if (1024 + a_bytes + red_bytes + (size_t)8 * a.sslot > budget) return;     // the ring needs at least 8 slots
+    if (1024 + a_bytes + red_bytes + (size_t)4 * a.sslot > budget) return;     // the ring needs at least 4 slots (64 KB in flight)
     a.sns = (int)std::min<size_t>((budget - 1024 - a_bytes - red_bytes) / a.sslot, 48);
     a.spc = (a.k64 + su - 1) / su;
     const long long total = (long long)a.n16 * a.spc;
@@ -720,8 +743,7 @@ static cudaError_t launch_stream_u(const Q4GemvArgs& a, cudaStream_t stream) {
     const size_t smem = 1024 + (size_t)a.sns * a.sslot + (size_t)a.a_rows * ((size_t)a.k64 * 64 + 8) * 2 +
                         (size_t)2 * kSWarps * 4 * MT * 32 * sizeof(float);
     if (smem > 227 * 1024) return cudaErrorInvalidConfiguration;
-    kern<<<a.sgrid, kSThreads, smem, stream>>>(a);
-    return cudaGetLastError();
+    return launch_pdl(kern, dim3(a.sgrid), dim3(kSThreads), smem, stream, a);
 }
 
 template <int BF16, int OPSIDE, int MT>
