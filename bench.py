@@ -47,7 +47,7 @@ HIDDEN, INTER, BLOCK = 4096, 14336, 32
 L2_BYTES = 126 * 1024 * 1024
 
 
-GATE_UP_DRAM_BYTES_M256 = 71.44e6   # dram__bytes_read.sum + dram__bytes_write.sum, one launch
+GATE_UP_DRAM_BYTES_M256 = 71.28e6   # dram__bytes_read.sum + dram__bytes_write.sum, one launch
 
 
 def measured_peaks():
