@@ -472,6 +472,14 @@ def run_ours(args):
                 "peak": peaks["bf16_tflops"], "unit": "TFLOP/s", "frac": ach / peaks["bf16_tflops"],
                 "peak_source": peaks["source"] + " (burst: kernel timed alone)", "us_per_launch": us_gu, "traffic": traffic,
                 "algorithmic_flops": flops_gu}
+    if m <= 16:
+        # decode-sized steps run the gate/up projection on the decode kernels, which stream the packed weights
+        # once: codes + one f16 scale per 32-deep block and column, the activations and the output, each once
+        bytes_gu = HIDDEN * 2 * fl * 0.5625 + m * HIDDEN * 2 + m * 2 * fl * 2
+        gbs = bytes_gu / us_gu / 1e3
+        roofline = {"kernel": "q4_gemv_stream_kernel / q4_gemv_kernel (gate/up projection, this rank's shard)", "bound": "hbm",
+                    "achieved": gbs, "peak": peaks["hbm_gbs"], "unit": "GB/s", "frac": gbs / peaks["hbm_gbs"],
+                    "peak_source": peaks["source"], "us_per_launch": us_gu, "traffic": None, "algorithmic_bytes": bytes_gu}
 
     # ---- CPU baseline beside it: the oracle block on a bounded row sample, all host cores ----
     cores = orc.max_threads()
