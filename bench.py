@@ -168,6 +168,8 @@ def workload_config(args, sets):
     return {"workload": f"Q4 SwiGLU MLP block (BASELINE.json configs[4]): hidden {HIDDEN}, intermediate {INTER}, Q4_0 block {BLOCK}, "
                         f"M={args.m} tokens per step, f16 activations, f32 residual",
             "tokens_per_step": args.m, "parallelism": f"tp{args.gpus}",
+            **({"collective": "sum + f16 rounding + residual add in one kernel of this library over NVLink peer memory"
+                if getattr(args, "collective", "peer") == "peer" else "NCCL all-reduce + finishing pass"} if args.gpus > 1 else {}),
             "l2": f"weights rotate over {sets} distinct device copies per rank (> 2x L2) between steps"}
 
 
@@ -344,6 +346,12 @@ def run_ours(args):
     x = torch.randn(m, HIDDEN, device="cuda", dtype=torch.float16, generator=gen)
     y = torch.zeros(m, HIDDEN, device="cuda", dtype=torch.float32)
     partial = torch.zeros(m, HIDDEN, device="cuda", dtype=torch.float32)
+    # N > 1: the ranks' partials are summed, rounded and added to the residual stream by one kernel of this
+    # library over peer memory (--collective peer, the default), or by an NCCL all-reduce plus the finishing pass
+    peer = None
+    if world > 1 and args.collective == "peer":
+        from sme_gemm_b200.tp import PeerReduce
+        peer = PeerReduce(m, HIDDEN)
     x_host = x.cpu().pin_memory()
     y_host = torch.zeros(m, HIDDEN, dtype=torch.float32).pin_memory()
 
@@ -354,9 +362,13 @@ def run_ours(args):
         if world == 1:
             mlp.accumulate(xb, yb, m)
         else:
-            mlp.partial(xb, partial, m)
-            dist.all_reduce(partial)
-            sg.Mlp.finish(yb, partial)
+            if peer is not None:
+                mlp.partial(xb, peer.partial, m)
+                peer.finish(yb)
+            else:
+                mlp.partial(xb, partial, m)
+                dist.all_reduce(partial)
+                sg.Mlp.finish(yb, partial)
 
     def sync():
         if dist:
@@ -539,6 +551,8 @@ def main():
     ap.add_argument("--tokens", dest="m", type=int, default=256, help="tokens per step (BASELINE.json: 1 or 256)")
     ap.add_argument("--ref-rows", type=int, default=4, help="rows of the batch the CPU arm computes per step")
     ap.add_argument("--no-kernels", action="store_true", help="skip the single-kernel configs")
+    ap.add_argument("--collective", default="peer", choices=["peer", "nccl"],
+                    help="N > 1: fused sum + finish over peer memory (this library's kernel) or NCCL all-reduce + finishing pass")
     ap.add_argument("--profile-case", default=None,
                     choices=["q4_gemv", "q2_gemv", "q1_gemv", "q4_prefill", "mlp_gate_up", "mlp_down"],
                     help="run six plain launches of one kernel and exit (for profiler captures)")

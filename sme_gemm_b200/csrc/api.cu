@@ -943,6 +943,24 @@ int smeg_mlp_partial_dev(smeg_mlp* mlp, const uint16_t* x, float* partial, size_
 int smeg_mlp_finish_dev(float* y, const float* sum, size_t len, void* stream) {
     return round_add_f32_launch(y, sum, len, (cudaStream_t)stream) == cudaSuccess ? 0 : -6;
 }
+int smeg_mlp_reduce_finish_dev(float* y, const uint64_t* buf_ptrs, const uint64_t* flag_ptrs, int rank, int world,
+                               size_t len, uint32_t seq, int oneshot, void* stream) {
+    if (len == 0) return 0;
+    if (!y || !buf_ptrs || !flag_ptrs || world < 1 || rank < 0 || rank >= world) return -4;
+    if (world > 8 || len % 4 != 0 || ((uintptr_t)y & 15) != 0) return -3;
+    DeviceState* ds = dev_state();
+    if (!ds) return -5;
+    TpReduceArgs a;
+    memset(&a, 0, sizeof(a));
+    for (int s = 0; s < world; ++s) {
+        if (!buf_ptrs[s] || !flag_ptrs[s] || (buf_ptrs[s] & 15) != 0 || (flag_ptrs[s] & 3) != 0) return -4;
+        a.bufs[s] = reinterpret_cast<float*>(buf_ptrs[s]);
+        a.flags[s] = reinterpret_cast<uint32_t*>(flag_ptrs[s]);
+    }
+    a.y = y; a.rank = rank; a.world = world; a.len = len; a.seq = seq; a.status = ds->status;
+    a.oneshot = oneshot ? 1 : 0;
+    return tp_reduce_finish_launch(a, ds->sm_count, (cudaStream_t)stream) == cudaSuccess ? 0 : -6;
+}
 int smeg_mlp_accumulate(smeg_mlp* mlp, const uint16_t* x, float* y, size_t m) {
     if (!mlp) return -4;
     if (m == 0) return 0;

@@ -146,4 +146,17 @@ cudaError_t f32_to_f16_launch(uint16_t* dst, const float* src, size_t n, cudaStr
 cudaError_t f16_to_f32_launch(float* dst, const uint16_t* src, size_t n, cudaStream_t s);
 cudaError_t round_add_f32_launch(float* y, const float* partial_sum, size_t n, cudaStream_t s);
 
+// ---- tensor-parallel sum + f16 rounding + residual add over peer memory (tp_reduce.cu) ----
+struct TpReduceArgs {
+    float* bufs[8];        // every rank's partial buffer, peer-mapped into this process (len floats each)
+    uint32_t* flags[8];    // every rank's flag array (16 words: "ready" from rank s at [s], "done" from owner s at [8 + s])
+    float* y;              // this rank's residual stream, len floats
+    int rank, world;       // world <= 8
+    size_t len;            // multiple of 4
+    uint32_t seq;          // call number, the same on every rank, growing by one per call from 1
+    int oneshot;           // every rank sums everything itself (short vectors; the caller double-buffers bufs)
+    unsigned* status;
+};
+cudaError_t tp_reduce_finish_launch(const TpReduceArgs& a, int sm_count, cudaStream_t stream);
+
 }  // namespace smeg

@@ -35,12 +35,63 @@ def shard_weights(w_gate, w_up, w_down, rank: int, world: int):
             np.ascontiguousarray(w_down[:, lo:hi]))
 
 
+class PeerReduce:
+    """The ranks' partial buffers and flag arrays in memory every rank can address (torch symmetric
+    memory: CUDA peer mappings over NVLink), and the one-kernel sum + f16 rounding + residual add over
+    them (smeg_mlp_reduce_finish_dev).  Collective to construct; every rank then calls `finish` once
+    per step, in the same order."""
+
+    def __init__(self, m: int, d: int, group=None):
+        import torch
+        import torch.distributed as dist
+        import torch.distributed._symmetric_memory as symm
+        group = group if group is not None else dist.group.WORLD
+        dev = torch.device("cuda", torch.cuda.current_device())
+        self.rank, self.world = dist.get_rank(group), dist.get_world_size(group)
+        assert self.world <= 8 and (m * d) % 4 == 0
+        # two buffers, taken in turn from step to step (the one-shot form of the kernel needs that)
+        self._both = symm.empty((2, m, d), dtype=torch.float32, device=dev)
+        self.flags = symm.empty((16,), dtype=torch.int32, device=dev)
+        self.flags.zero_()
+        self._both.zero_()
+        torch.cuda.synchronize()
+        self._hp = symm.rendezvous(self._both, group)
+        self._hf = symm.rendezvous(self.flags, group)
+        dist.barrier(group)                      # every rank's flags are zero before anyone's first call
+        import ctypes as C
+        self._C = C
+        self._base = [int(p) for p in self._hp.buffer_ptrs]
+        self._flags = (C.c_uint64 * self.world)(*[int(p) for p in self._hf.buffer_ptrs])
+        self._len = m * d
+        # short vectors: every rank sums everything itself, one flag round instead of two
+        self.oneshot = 1 if self._len * 4 <= 128 * 1024 else 0
+        self.seq = 0
+
+    @property
+    def partial(self):
+        """The buffer this rank's partial product of the coming step goes into."""
+        return self._both[(self.seq + 1) & 1]
+
+    def finish(self, y) -> None:
+        """y += f32(f16(sum over ranks of their `partial`)), on every rank."""
+        from ._lib import check, lib
+        from .host import _ptr, _stream
+        self.seq += 1
+        off = (self.seq & 1) * self._len * 4
+        bufs = (self._C.c_uint64 * self.world)(*[b + off for b in self._base])
+        check("smeg_mlp_reduce_finish_dev",
+              lib().smeg_mlp_reduce_finish_dev(_ptr(y), bufs, self._flags, self.rank, self.world, y.numel(),
+                                               self.seq & 0xffffffff, self.oneshot, _stream()))
+
+
 class TpMlp:
     """One rank's shard of a gated MLP plus the collective.  `group` is a
-    torch.distributed process group (None = the default group)."""
+    torch.distributed process group (None = the default group).  With `peer` (a PeerReduce for the
+    step's m x d) the sum over ranks, the rounding and the residual add run as one kernel over peer
+    memory; without it an all-reduce of the library behind torch.distributed and the finishing pass."""
 
-    def __init__(self, mlp: Mlp, world: int, group=None):
-        self.mlp, self.world, self.group = mlp, world, group
+    def __init__(self, mlp: Mlp, world: int, group=None, peer: "PeerReduce | None" = None):
+        self.mlp, self.world, self.group, self.peer = mlp, world, group, peer
 
     @staticmethod
     def quantize(w_gate, w_up, w_down, rank: int, world: int, gate: Gate = Gate.Silu, p: Q4Params | None = None,
@@ -58,6 +109,10 @@ class TpMlp:
         import torch.distributed as dist
         if self.world == 1:
             self.mlp.accumulate(x, y, m)
+            return
+        if self.peer is not None:
+            self.mlp.partial(x, self.peer.partial, m)
+            self.peer.finish(y)
             return
         if partial is None:
             partial = torch.empty_like(y)
