@@ -6,7 +6,9 @@
 Headline line (one JSON object on stdout, printed by rank 0): tokens/s of the
 Q4 SwiGLU MLP block of BASELINE.json configs[4] (hidden 4096, intermediate
 14336, M = 256 tokens per step), tensor parallel over N GPUs (gate/up sharded by
-hidden unit, down by the same rows, one all-reduce of the f32 partials).  A step
+hidden unit, down by the same rows; the ranks' f32 partials are summed, rounded and
+added to the residual stream by one kernel of this library over NVLink peer memory,
+or with `--collective nccl` by an NCCL all-reduce and a finishing pass).  A step
 is one Mlp::accumulate pass over one synthetic batch.  Total work is fixed as N
 grows ("strong" scaling).  Between steps the weights rotate over enough distinct
 device copies to exceed twice the L2, so every step streams its weights from HBM.
@@ -351,7 +353,16 @@ def run_ours(args):
     peer = None
     if world > 1 and args.collective == "peer":
         from sme_gemm_b200.tp import PeerReduce
-        peer = PeerReduce(m, HIDDEN)
+        try:
+            peer = PeerReduce(m, HIDDEN)
+        except Exception as e:           # no peer mapping on this box: say so and time the NCCL form
+            print(f"rank {rank}: peer memory unavailable ({type(e).__name__}: {e})", file=sys.stderr, flush=True)
+            peer = None
+        agreed = torch.tensor([1 if peer is not None else 0], device="cuda")
+        dist.all_reduce(agreed, op=dist.ReduceOp.MIN)
+        if int(agreed.item()) == 0:
+            peer = None
+            args.collective = "nccl"
     x_host = x.cpu().pin_memory()
     y_host = torch.zeros(m, HIDDEN, dtype=torch.float32).pin_memory()
 
