@@ -61,3 +61,45 @@ def test_peer_reduce_finish_equals_gathered_sum_bit_for_bit(tmp_path):
                           "--master-addr", "127.0.0.1", "--master-port", "29731", str(script)],
                          capture_output=True, text=True, timeout=280, env=env, cwd=os.getcwd())
     assert "PEER_REDUCE_OK" in out.stdout, out.stdout[-2000:] + out.stderr[-2000:]
+
+
+def _call(y, bufs, flags, rank, world, seq, oneshot):
+    import ctypes as C
+    from sme_gemm_b200._lib import check, lib
+    b = (C.c_uint64 * world)(*[t.data_ptr() for t in bufs])
+    f = (C.c_uint64 * world)(*[t.data_ptr() for t in flags])
+    check("smeg_mlp_reduce_finish_dev",
+          lib().smeg_mlp_reduce_finish_dev(y.data_ptr(), b, f, rank, world, y.numel(), seq, oneshot,
+                                           torch.cuda.current_stream().cuda_stream))
+
+
+@pytest.mark.parametrize("oneshot", [0, 1])
+@pytest.mark.parametrize("m,d", [(1, 4096), (64, 4096), (3, 20)])
+def test_single_rank_reduce_finish_is_the_rounding_and_the_residual_add(m, d, oneshot):
+    """world = 1: the kernel's own flags, slice and add; y += f32(f16(partial)) exactly."""
+    import sme_gemm_b200 as sg
+    g = torch.Generator(device="cuda").manual_seed(5)
+    y = torch.randn(m, d, device="cuda", generator=g)
+    flags = torch.zeros(16, dtype=torch.int32, device="cuda")
+    for seq in (1, 2, 3):
+        part = torch.randn(m, d, device="cuda", generator=g) * 5.0
+        want = y + part.half().float()
+        _call(y, [part], [flags], 0, 1, seq, oneshot)
+        torch.cuda.synchronize()
+        assert sg.last_status() == 0
+        assert torch.equal(y, want)
+
+
+def test_a_peer_that_never_arrives_ends_the_wait_with_the_status_raised_and_y_untouched():
+    """Two ranks' buffers and flags stand on this one GPU and the second rank never runs: nothing sets its
+    "ready" flag, the bounded wait (one second) runs out, the kernel returns, the status word says so."""
+    import sme_gemm_b200 as sg
+    y = torch.ones(2, 64, device="cuda")
+    bufs = [torch.full((2, 64), 3.0, device="cuda") for _ in range(2)]
+    flags = [torch.zeros(16, dtype=torch.int32, device="cuda") for _ in range(2)]
+    _call(y, bufs, flags, 0, 2, 1, 0)
+    torch.cuda.synchronize()
+    assert sg.last_status() & 4          # STATUS_PEER_TIMEOUT; reading clears the word
+    assert sg.last_status() == 0
+    assert torch.equal(y, torch.ones_like(y))
+    assert int(flags[1][0].item()) == 1  # rank 0 did announce its partial to the absent rank
