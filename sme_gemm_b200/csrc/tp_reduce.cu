@@ -14,7 +14,7 @@
 // Flags carry the call's sequence number and only grow, so nothing is reset between calls.  A rank
 // leaves the kernel only after every owner has finished reading its buffer, so the next step may
 // overwrite the buffer at once.  Short vectors take a one-shot form instead (every rank adds all the
-// partials itself after round 0; see the kernel).  Every wait is bounded: after a second it raises the
+// partials itself after the "ready" flags; see the kernel).  Every wait is bounded: after a second it raises the
 // status word and the kernel returns without touching y.
 #include "common.cuh"
 #include "kernels.h"
