@@ -258,13 +258,16 @@ int smeg_mlp_finish_dev(float *y, const float *sum, size_t len, void *stream);
 /* The sum over ranks and finish in one kernel over peer memory (no counterpart in the
  * reference, whose Mlp::accumulate, src/mlp.rs:124-146, runs on one device): every rank
  * has left its partial in a buffer all ranks can address (buf_ptrs[s] = rank s's buffer as
- * mapped into this process, len floats, len % 4 == 0) and owns a zero-initialised array of
- * 16 uint32 flags (flag_ptrs[s], likewise mapped).  Each rank calls this once per step with
+ * mapped into this process: len floats of partial sums followed by room for len f16 results,
+ * i.e. 6 * len bytes; len % 4 == 0) and owns a zero-initialised array of SMEG_TP_FLAG_WORDS
+ * uint32 flags (flag_ptrs[s], likewise mapped).  Each rank calls this once per step with
  * the same seq (1, 2, 3, ... per step); on return of the kernel y += f32(f16(sum over ranks,
  * added in rank order)) on every rank and the buffers may be overwritten.  world <= 8.
  * oneshot != 0 (short vectors): every rank adds all partials itself and no second flag
  * round runs; the caller must then alternate between two buffers from step to step.
- * A peer that never arrives ends the wait after a second: rc -7 at the next status read. */
+ * A peer that never arrives ends the wait after a second: rc -7 at the next status read;
+ * y is untouched when that happens in the first flag round. */
+#define SMEG_TP_FLAG_WORDS 1288
 int smeg_mlp_reduce_finish_dev(float *y, const uint64_t *buf_ptrs, const uint64_t *flag_ptrs, int rank, int world,
                                size_t len, uint32_t seq, int oneshot, void *stream);
 

@@ -46,7 +46,17 @@ int g_tc_min_rows = []() {
     return e ? atoi(e) : 16;
 }();
 
+// Rows up to which the decode calls take the direct kernels of gemv_direct.cu (plain loads, packed
+// f16 / dp4a arithmetic); 0 keeps them on the ring-staged kernels.  SMEG_DIRECT_ROWS is a tuning knob.
+int g_direct_rows = []() {
+    const char* e = getenv("SMEG_DIRECT_ROWS");
+    const int v = e ? atoi(e) : 4;
+    return v < 0 ? 0 : (v > 4 ? 4 : v);
+}();
+
 }  // namespace
+// status word of the allocation-free entry point (lowbit_gemv.cu): read and cleared, 0 if never set up
+unsigned smeg_static_take_status();
 namespace smeg {
 bool pdl_enabled() {
     static const bool on = []() {
@@ -86,10 +96,12 @@ DeviceState* dev_state() {
     return &s;
 }
 
-// Scratch of the depth-split tensor-core GEMM: per-slice partial tiles and one arrival
-// counter per output tile (zero between launches).  One block per stream, so launches
-// that may overlap never share it; grown on demand (a synchronous allocation, so the
-// first call of a new size on a stream must not be inside a stream capture).
+// Scratch of the depth-split tensor-core GEMM (per-slice partial tiles) and of the streaming
+// decode kernel (shares of cut column groups plus one arrival counter per column group, zero
+// between launches).  One block per (device, stream), so launches that may overlap never share
+// it; grown on demand (a synchronous allocation, so the first call of a new size on a stream must
+// not be inside a stream capture).  A block that is outgrown is kept until the process ends:
+// another host thread may have read its address for a launch it has not issued yet.
 struct TcScratch {
     float* ws = nullptr;
     size_t floats = 0;
@@ -97,6 +109,7 @@ struct TcScratch {
     size_t ncounters = 0;
 };
 std::map<std::pair<int, cudaStream_t>, TcScratch> g_tc_scratch;
+std::vector<void*> g_retired;        // outgrown blocks, never freed
 
 int tc_scratch(cudaStream_t stream, size_t floats, size_t ncounters, TcScratch* out) {
     int dev = 0;
@@ -104,22 +117,30 @@ int tc_scratch(cudaStream_t stream, size_t floats, size_t ncounters, TcScratch* 
     std::lock_guard<std::mutex> lk(g_mu);
     TcScratch& s = g_tc_scratch[{dev, stream}];
     if (s.floats < floats) {
-        if (s.ws) cudaFree(s.ws);
-        s.ws = nullptr;
-        s.floats = 0;
-        if (cudaMalloc(&s.ws, floats * sizeof(float)) != cudaSuccess) return -2;
+        float* fresh = nullptr;
+        if (cudaMalloc(&fresh, floats * sizeof(float)) != cudaSuccess) return -2;
+        if (s.ws) g_retired.push_back(s.ws);
+        s.ws = fresh;
         s.floats = floats;
     }
     if (s.ncounters < ncounters) {
-        if (s.counters) cudaFree(s.counters);
-        s.counters = nullptr;
-        s.ncounters = 0;
-        if (cudaMalloc(&s.counters, ncounters * sizeof(int)) != cudaSuccess) return -2;
-        if (cudaMemset(s.counters, 0, ncounters * sizeof(int)) != cudaSuccess) return -2;
+        int* fresh = nullptr;
+        if (cudaMalloc(&fresh, ncounters * sizeof(int)) != cudaSuccess) return -2;
+        if (cudaMemset(fresh, 0, ncounters * sizeof(int)) != cudaSuccess) { cudaFree(fresh); return -2; }
+        if (s.counters) g_retired.push_back(s.counters);
+        s.counters = fresh;
         s.ncounters = ncounters;
     }
     *out = s;
     return 0;
+}
+
+// After a kernel gave up on a bounded wait its arrival counters may be left non-zero: clear every
+// counter block of the device (the device is idle: the caller has just synchronised it).
+void reset_counters_after_timeout(int dev) {
+    std::lock_guard<std::mutex> lk(g_mu);
+    for (auto& kv : g_tc_scratch)
+        if (kv.first.first == dev && kv.second.counters) cudaMemset(kv.second.counters, 0, kv.second.ncounters * sizeof(int));
 }
 
 bool tracing() {
@@ -264,6 +285,8 @@ unsigned smeg_last_status(void) {
     if (cudaDeviceSynchronize() != cudaSuccess) return ~0u;
     cudaMemcpy(&v, s->status, sizeof(v), cudaMemcpyDeviceToHost);
     if (v) cudaMemset(s->status, 0, sizeof(unsigned));
+    v |= smeg_static_take_status();
+    if (v) reset_counters_after_timeout(s->device);
     return v;
 }
 
@@ -578,6 +601,8 @@ static int q4_dev(const smeg_q4* w, const uint16_t* a, uint16_t* c, size_t m, co
         t.ws = sc.ws;
         t.counters = sc.counters;
         e = gemm_tc_launch(t, bf16, grid, smem, stream);
+    } else if (g_direct_rows > 0 && (int)m <= g_direct_rows && q4_direct_supported(g, bf16)) {
+        e = q4_direct_launch(g, ds->sm_count, stream);
     } else {
         size_t ws_floats = 0, ncounters = 0;
         q4_gemv_stream_plan(g, bf16, ds->sm_count, &ws_floats, &ncounters);
@@ -627,7 +652,12 @@ static int lowbit_dev(const smeg_lowbit* w, const uint16_t* a, uint16_t* c, size
     // up to four rows the kernel stages and quantises the activations itself (one launch, no scratch);
     // above that every CTA would repeat too much work, and a separate pass over the rows is faster
     static const size_t fuse_max_rows = []() { const char* e = getenv("SMEG_LB_FUSE_MAX_ROWS"); return e ? (size_t)atoi(e) : (size_t)4; }();
-    if (k > 0 && m <= fuse_max_rows && (k % 8 == 0) && ((uintptr_t)a % 16 == 0) && lowbit_gemv_fuses_quant(g, w->bits, ds->sm_count)) {
+    g.a_vec_ok = (k % 8 == 0) && ((uintptr_t)a % 16 == 0);
+    if (k > 0 && (int)m <= g_direct_rows && m <= 2 && (g.a = a, lowbit_direct_supported(g, true))) {
+        // one or two rows: the direct kernel quantises the rows itself in every CTA
+        g.q_out = q_out; g.sa_out = sa_out;
+        e = lowbit_direct_launch(g, w->bits, ds->sm_count, stream);
+    } else if (g.a = nullptr, k > 0 && m <= fuse_max_rows && (k % 8 == 0) && ((uintptr_t)a % 16 == 0) && lowbit_gemv_fuses_quant(g, w->bits, ds->sm_count)) {
         // the kernel quantises the activation rows itself: one launch, no scratch
         g.a = a;
         g.a_vec_ok = 1;
@@ -646,7 +676,10 @@ static int lowbit_dev(const smeg_lowbit* w, const uint16_t* a, uint16_t* c, size
         aq.m = (int)m; aq.k = (int)k; aq.kq = (int)kq; aq.nbq = (int)nb; aq.log2_block = w->d.log2_block;
         e = act_quant_launch(aq, stream);
         g.q = aq.q; g.sa = aq.sa; g.qsum = aq.qsum;
-        if (e == cudaSuccess) e = lowbit_gemv_launch(g, w->bits, ds->sm_count, stream);
+        if (e == cudaSuccess) {
+            if ((int)m <= g_direct_rows && lowbit_direct_supported(g, false)) e = lowbit_direct_launch(g, w->bits, ds->sm_count, stream);
+            else e = lowbit_gemv_launch(g, w->bits, ds->sm_count, stream);
+        }
         if (e == cudaSuccess && q_out)
             e = cudaMemcpy2DAsync(q_out, k, aq.q, kq, k, m, cudaMemcpyDeviceToDevice, stream);
         if (e == cudaSuccess && sa_out)
@@ -817,6 +850,7 @@ int finish_sync(DeviceState* ds) {
     if (cudaMemcpy(&v, ds->status, sizeof(v), cudaMemcpyDeviceToHost) != cudaSuccess) return -6;
     if (v) {
         cudaMemset(ds->status, 0, sizeof(unsigned));
+        reset_counters_after_timeout(ds->device);
         return -7;
     }
     return 0;

@@ -27,20 +27,6 @@ __device__ __forceinline__ unsigned long long global_ns() {
     return t;
 }
 
-#ifdef SMEG_TC_TIMELINE
-// Debug builds only: SM-clock stamps of a kernel's phases in its first and last CTA
-// (slots 0-13: clock64; 14 / 15: global timer at entry / exit).  The array is per translation unit.
-#define SMEG_EV_DECL(name) __device__ long long name[2 * 16];
-#define SMEG_EV(name, ev)                                                                                   \
-    do {                                                                                                    \
-        const int b_ = (blockIdx.x == 0 && blockIdx.y == 0) ? 0 : ((blockIdx.x == gridDim.x - 1 && blockIdx.y == 0) ? 1 : -1); \
-        if (b_ >= 0) name[b_ * 16 + (ev)] = ((ev) >= 14) ? (long long)global_ns() : clock64();              \
-    } while (0)
-#else
-#define SMEG_EV_DECL(name)
-#define SMEG_EV(name, ev) do { } while (0)
-#endif
-
 __device__ __forceinline__ uint32_t smem_u32(const void* p) {
     return static_cast<uint32_t>(__cvta_generic_to_shared(p));
 }

@@ -26,8 +26,8 @@
 // After the last stage the dequant warps drain tensor memory (thread = weight column, registers
 // = tokens): the epilogue graph on the rounded product, or -- for the MLP block -- the gated
 // product of a gate/up pair, or the residual add.  With the depth split (grid.z > 1) each CTA
-// leaves its f32 partial tile in a global workspace; the CTA that finishes a tile last adds the
-// slices in slice order (so the result does not depend on arrival order) and stores.
+// leaves its f32 partial tile in a global workspace and splitk_reduce_kernel, launched right
+// behind, adds the slices in slice order (so the result does not depend on arrival order) and stores.
 // Every wait is bounded; a timed-out wait raises the status word and the kernel drains and exits.
 #include "epilogue.cuh"
 #include "kernels.h"
@@ -37,17 +37,6 @@
 #include <stdlib.h>
 
 namespace smeg {
-
-#ifdef SMEG_TC_TIMELINE
-// Debug builds only: per-stage SM-clock timestamps of CTA (0,0,0), [stage][event].
-__device__ long long g_tc_timeline[512 * 12];
-#define SMEG_TL(ev, i)                                                                          \
-    do {                                                                                        \
-        if (blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0 && (i) < 512) g_tc_timeline[(i) * 12 + (ev)] = clock64(); \
-    } while (0)
-#else
-#define SMEG_TL(ev, i) do { } while (0)
-#endif
 
 namespace {
 
@@ -163,7 +152,6 @@ __global__ void __launch_bounds__(kTcThreads, 1) gemm_tc_kernel(const __grid_con
     uint64_t* acc_full = o_empty + O;        // all MMAs retired
     uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(acc_full + 1);
     volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
-    int* last_flag = const_cast<int*>(abort_flag) + 1;
     EpNodeDev* ep_nodes = reinterpret_cast<EpNodeDev*>(acc_full + 4);
 
     const int sg0 = blockIdx.x * NW;                           // first 128-column super-group
@@ -191,7 +179,6 @@ __global__ void __launch_bounds__(kTcThreads, 1) gemm_tc_kernel(const __grid_con
         }
         mbar_init(acc_full, 1);
         *abort_flag = 0;
-        *last_flag = 0;
         fence_barrier_init();
     }
     if (tid < p.ep.n_nodes && p.ep.n_nodes <= kMaxInlineNodes) ep_nodes[tid] = p.ep.nodes[tid];
@@ -210,9 +197,7 @@ __global__ void __launch_bounds__(kTcThreads, 1) gemm_tc_kernel(const __grid_con
         if (lane == 0) {
             for (int i = 0; i < num_stages; ++i) {
                 const int slot = i % NT;
-                SMEG_TL(0, i);
                 if (i >= NT && !mbar_wait(&t_empty[slot], ((i / NT) - 1) & 1, abort_flag, p.status, STATUS_TMEM_TIMEOUT)) break;
-                SMEG_TL(1, i);
                 unsigned char* sb = ring_t + (size_t)slot * t_stride;
                 const int u0 = (st_begin + i) * US;
                 const int units = min(US, p.ku - u0);
@@ -276,9 +261,7 @@ __global__ void __launch_bounds__(kTcThreads, 1) gemm_tc_kernel(const __grid_con
         for (int i = 0; i < num_stages; ++i) {
             const int ts = i % NT, os = i % O;
             if (!__all_sync(0xffffffffu, mbar_wait(&t_full[ts], (i / NT) & 1, abort_flag, p.status, STATUS_TMEM_TIMEOUT))) break;
-            if (lane == 0) SMEG_TL(5, i);
             if (!__all_sync(0xffffffffu, mbar_wait(&o_full[os], (i / O) & 1, abort_flag, p.status, STATUS_TMEM_TIMEOUT))) break;
-            if (lane == 0) SMEG_TL(6, i);
             tc_fence_after();
             const uint32_t tok_addr = smem_u32(ring_t + (size_t)ts * t_stride);
             const uint32_t w_addr = smem_u32(ring_o + (size_t)os * o_stride);
@@ -298,10 +281,8 @@ __global__ void __launch_bounds__(kTcThreads, 1) gemm_tc_kernel(const __grid_con
                         }
                     }
                 }
-                SMEG_TL(10, i);
                 umma_commit(&o_empty[os]);
                 umma_commit(&t_empty[ts]);
-                SMEG_TL(7, i);
             }
             __syncwarp();
         }
@@ -323,11 +304,8 @@ __global__ void __launch_bounds__(kTcThreads, 1) gemm_tc_kernel(const __grid_con
                 continue;
             }
             const int os = i % O;
-            if (wig == 0 && lane == 0) SMEG_TL(2, i);
             if (i >= O && !__all_sync(0xffffffffu, mbar_wait(&o_empty[os], ((i / O) - 1) & 1, abort_flag, p.status, STATUS_TMEM_TIMEOUT))) break;
-            if (wig == 0 && lane == 0) SMEG_TL(8, i);
             if (!__all_sync(0xffffffffu, mbar_wait(&k_full[ks], (gq / NK) & 1, abort_flag, p.status, STATUS_TMEM_TIMEOUT))) break;
-            if (wig == 0 && lane == 0) SMEG_TL(3, i);
             const int uq = (i % PU) * US;                           // first unit of the stage within the packed slot
             const int u0 = (st_begin + i) * US;                     // first unit of the stage
             const int units = min(US, p.ku - u0);
@@ -375,17 +353,14 @@ __global__ void __launch_bounds__(kTcThreads, 1) gemm_tc_kernel(const __grid_con
                 __syncwarp();
                 if (lane == 0) mbar_arrive(&k_empty[ks]);
             }
-            if (wig == 0 && lane == 0) SMEG_TL(4, i);
         }
 
         // ---- drain: thread = weight column (TMEM lane), registers = tokens.  A warp reaches the
         // lane quarter warp % 4; the token columns are split over 4 (or 2) warps per quarter ----
         const int ntok = p.ntok_pad;                           // a multiple of 32
         const int parts = (ntok % 64 == 0) ? 4 : 2;            // every part is whole groups of 16 tokens
-        const int drain_threads = 32 * 4 * parts;
         if (warp < 4 * parts) {
         if (num_stages > 0) mbar_wait(acc_full, 0, abort_flag, p.status, STATUS_TMEM_TIMEOUT);
-        if (tid == 0) SMEG_TL(9, 0);
         tc_fence_after();
         const int q = warp & 3, part = warp >> 2;              // lane quarter, token part
         const uint32_t lane_base = tmem_base + ((uint32_t)(32 * q) << 16);
@@ -479,91 +454,6 @@ __global__ void __launch_bounds__(kTcThreads, 1) gemm_tc_kernel(const __grid_con
         }
         tc_fence_before();
 
-        if (splits > 1 && !p.defer) {
-            // the last CTA of the tile to arrive adds the slices in slice order and stores
-            __threadfence();
-            asm volatile("bar.sync 1, %0;" ::"r"(drain_threads));
-            if (tid == 0) {
-                const int prev = atomicAdd(p.counters + tile_id, 1);
-                *last_flag = (prev == splits - 1) ? 1 : 0;
-                if (prev == splits - 1) p.counters[tile_id] = 0;      // ready for the next launch
-            }
-            asm volatile("bar.sync 1, %0;" ::"r"(drain_threads));
-            // eight tokens at a time: their loads are independent, so the reduce is bound by
-            // bandwidth and not by one memory latency per token
-            if (*last_flag && p.glu) {
-                __threadfence();
-                const int hn = p.n >> 1, hcol = blockIdx.x * 128 + 32 * q + lane;
-                if (hcol < hn) {
-#pragma unroll 1
-                    for (int j0 = j_begin; j0 < j_end; j0 += 8) {
-                        float ag[8], au[8];
-#pragma unroll
-                        for (int jj = 0; jj < 8; ++jj) ag[jj] = au[jj] = 0.0f;
-                        for (int z = 0; z < splits; ++z) {
-                            const float* src = ws_tile + ((size_t)z * ntok + j0) * (NW * 128) + (32 * q + lane);
-                            float vg[8], vu[8];
-#pragma unroll
-                            for (int jj = 0; jj < 8; ++jj) {
-                                vg[jj] = __ldcg(src + (size_t)jj * (NW * 128));
-                                vu[jj] = __ldcg(src + (size_t)jj * (NW * 128) + 128);
-                            }
-#pragma unroll
-                            for (int jj = 0; jj < 8; ++jj) { ag[jj] += vg[jj]; au[jj] += vu[jj]; }
-                        }
-#pragma unroll
-                        for (int jj = 0; jj < 8; ++jj) {
-                            const int tok = tok0 + j0 + jj;
-                            const float gv = t_to_f32<BF16>(f32_to_t<BF16>(ag[jj])), uv = t_to_f32<BF16>(f32_to_t<BF16>(au[jj]));
-                            float a;
-                            if (p.glu == 3) a = __fdiv_rn(gv, __fadd_rn(1.0f, expf(-gv)));
-                            else {
-                                const float g3 = __fmul_rn(__fmul_rn(__fmul_rn(0.044715f, gv), gv), gv);
-                                a = __fmul_rn(__fmul_rn(0.5f, gv), __fadd_rn(1.0f, tanhf(__fmul_rn(0.7978846f, __fadd_rn(gv, g3)))));
-                            }
-                            if (tok < p.m) p.c[(size_t)tok * hn + hcol] = f32_to_t<BF16>(__fmul_rn(a, uv));
-                        }
-                    }
-                }
-            } else if (*last_flag) {
-                __threadfence();
-                for (int w = 0; w < NW; ++w) {
-                    const int col = col0 + 128 * w + 32 * q + lane;
-                    if (col >= p.n) continue;
-                    FastEp fe;
-                    if (p.ep_fast) fast_ep_build<BF16>(nodes, p.ep.n_nodes, col, true, fe);
-#pragma unroll 1
-                    for (int j0 = j_begin; j0 < j_end; j0 += 8) {
-                        float acc[8], yv[8];
-#pragma unroll
-                        for (int jj = 0; jj < 8; ++jj) acc[jj] = 0.0f;
-                        if (p.yacc) {
-#pragma unroll
-                            for (int jj = 0; jj < 8; ++jj) yv[jj] = (tok0 + j0 + jj < p.m) ? p.yacc[(size_t)(tok0 + j0 + jj) * p.n + col] : 0.0f;
-                        }
-                        for (int z = 0; z < splits; ++z) {
-                            const float* src = ws_tile + ((size_t)z * ntok + j0) * (NW * 128) + (128 * w + 32 * q + lane);
-                            float v[8];
-#pragma unroll
-                            for (int jj = 0; jj < 8; ++jj) v[jj] = __ldcg(src + (size_t)jj * (NW * 128));
-#pragma unroll
-                            for (int jj = 0; jj < 8; ++jj) acc[jj] += v[jj];
-                        }
-#pragma unroll
-                        for (int jj = 0; jj < 8; ++jj) {
-                            const int tok = tok0 + j0 + jj;
-                            if (tok >= p.m) continue;
-                            if (DENSE && p.beta != 1.0f) acc[jj] = __fmul_rn(p.beta, acc[jj]);
-                            const size_t ci = (DENSE && p.col_major) ? (size_t)col * p.m + tok : (size_t)tok * p.n + col;
-                            if (p.c32) p.c32[(size_t)tok * p.n + col] = acc[jj];
-                            else if (p.yacc) p.yacc[(size_t)tok * p.n + col] = __fadd_rn(yv[jj], t_to_f32<BF16>(f32_to_t<BF16>(acc[jj])));
-                            else if (p.ep_fast) p.c[ci] = fast_ep_store<BF16>(fe, acc[jj]);
-                            else p.c[ci] = ep_store_nodes<BF16>(nodes, p.ep.n_nodes, acc[jj], (size_t)tok, (size_t)col);
-                        }
-                    }
-                }
-            }
-        }
         }   // drain warps
     }
     __syncthreads();
@@ -681,12 +571,6 @@ cudaError_t launch_tc(const CUtensorMap& tm, const CUtensorMap& tw, const GemmTc
 }
 
 }  // namespace
-
-#ifdef SMEG_TC_TIMELINE
-extern "C" int smeg_debug_timeline(long long* host, int n) {
-    return cudaMemcpyFromSymbol(host, g_tc_timeline, sizeof(long long) * n) == cudaSuccess ? 0 : -1;
-}
-#endif
 
 bool gemm_tc_supported(int wkind, int m, int k, int log2_block, const void* a) {
     if (wkind != 4 && wkind != 16) return false;

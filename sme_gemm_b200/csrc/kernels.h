@@ -19,6 +19,7 @@ struct Q4GemvArgs {
     int n16, k64, nb;             // column groups, 64-deep units, staged scale rows per group
     int log2_block;
     int ns, cg, rps, ka, a_rows;  // filled in by the launcher
+    int dq, dr, dupw;             // direct kernel: column groups per CTA (quotient, remainder), units per warp
     int a_vec_ok;                 // rows of `a` are 16-byte aligned (k % 8 == 0 and base aligned)
     // streaming form (q4_gemv_stream_plan): the (column group, 16-unit stage) list is cut into one
     // contiguous range per CTA; a column group cut by a range boundary is summed through ws
@@ -34,6 +35,9 @@ struct Q4GemvArgs {
 // scratch the caller must provide in ws / counters).  Leaves sgrid = 0 otherwise.
 void q4_gemv_stream_plan(Q4GemvArgs& a, int bf16, int sm_count, size_t* ws_floats, size_t* ncounters);
 cudaError_t q4_gemv_launch(Q4GemvArgs a, int bf16, int sm_count, cudaStream_t stream);
+// One to four rows, f16, K-blocks of 32 and up: plain 128-bit loads, packed f16 multiply-adds (gemv_direct.cu).
+bool q4_direct_supported(const Q4GemvArgs& a, int bf16);
+cudaError_t q4_direct_launch(Q4GemvArgs a, int sm_count, cudaStream_t stream);
 
 // Launch with programmatic stream serialisation allowed: when the kernel ahead in the stream has let
 // its dependents go (griddepcontrol.launch_dependents in every CTA, or its end), this kernel's CTAs
@@ -85,11 +89,16 @@ struct LowbitGemvArgs {
     uint32_t lut;                 // 2-bit codebook, byte c = value of code c
     int ns, gpt, kc, kqc;         // launcher-filled: ring depth, column groups per task, fold chunk, staged activation chunk
     int ntasks, rows_s, u_bytes;  // launcher-filled: tasks along n, rows kept in the shared sums, bytes of the sums / f16-rows region
+    int dq, dr, dupw, dsc;        // direct kernel: column groups per CTA (quotient, remainder), units per warp, scales staged in shared memory
     unsigned* status;
     EpParams ep;
 };
 cudaError_t lowbit_gemv_launch(LowbitGemvArgs a, int bits, int sm_count, cudaStream_t stream);
 bool lowbit_gemv_fuses_quant(LowbitGemvArgs a, int bits, int sm_count);
+// One to four rows: plain 128-bit loads and dp4a (gemv_direct.cu).  fused: the kernel quantises the f16 rows
+// itself (a.a set, at most two rows); otherwise a.q / a.sa / a.qsum come from act_quant_kernel.
+bool lowbit_direct_supported(const LowbitGemvArgs& a, bool fused);
+cudaError_t lowbit_direct_launch(LowbitGemvArgs a, int bits, int sm_count, cudaStream_t stream);
 
 // ---- prefill GEMM on tcgen05 (gemm_tc.cu) ----
 struct GemmTcArgs {
@@ -147,9 +156,12 @@ cudaError_t f16_to_f32_launch(float* dst, const uint16_t* src, size_t n, cudaStr
 cudaError_t round_add_f32_launch(float* y, const float* partial_sum, size_t n, cudaStream_t s);
 
 // ---- tensor-parallel sum + f16 rounding + residual add over peer memory (tp_reduce.cu) ----
+constexpr int kTpReadyWords = 8;                                   // "ready" from rank s at [s]
+constexpr int kTpMaxGrid = 160;                                    // most CTAs of the kernel
+constexpr int kTpFlagWords = kTpReadyWords + 8 * kTpMaxGrid;       // "done" from owner s, CTA b at [8 + s * kTpMaxGrid + b]
 struct TpReduceArgs {
-    float* bufs[8];        // every rank's partial buffer, peer-mapped into this process (len floats each)
-    uint32_t* flags[8];    // every rank's flag array (16 words: "ready" from rank s at [s], "done" from owner s at [8 + s])
+    float* bufs[8];        // every rank's buffer, peer-mapped into this process: len f32 partial sums, then len f16 results
+    uint32_t* flags[8];    // every rank's flag array (kTpFlagWords words, zero before the first call)
     float* y;              // this rank's residual stream, len floats
     int rank, world;       // world <= 8
     size_t len;            // multiple of 4

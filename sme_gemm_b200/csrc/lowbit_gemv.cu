@@ -22,16 +22,6 @@
 
 namespace smeg {
 
-SMEG_EV_DECL(g_ev_lb)
-#ifdef SMEG_TC_TIMELINE
-__device__ int g_dbg_skip_lb = 0;
-#define SMEG_DBG_SKIP_LB ((g_dbg_skip_lb & 1) != 0)
-#define SMEG_DBG_BIT(b) ((g_dbg_skip_lb & (b)) != 0)
-#else
-#define SMEG_DBG_SKIP_LB false
-#define SMEG_DBG_BIT(b) false
-#endif
-
 namespace {
 
 constexpr int kWarps = 8;                 // units per stage
@@ -169,7 +159,6 @@ __global__ void __launch_bounds__(kThreadsLb, 1) lowbit_gemv_kernel(const __grid
     const int fc_stages = KC / SD;                                 // stages per fold chunk
     const int my_tasks = ((int)blockIdx.x < p.ntasks) ? (p.ntasks - 1 - (int)blockIdx.x) / (int)gridDim.x + 1 : 0;
 
-    if (tid == 0) { SMEG_EV(g_ev_lb, 14); SMEG_EV(g_ev_lb, 0); }
     if (tid == 0) {
         for (int s = 0; s < NS; ++s) {
             mbar_init(&full[s], 1);
@@ -183,7 +172,6 @@ __global__ void __launch_bounds__(kThreadsLb, 1) lowbit_gemv_kernel(const __grid
     }
     __syncthreads();
     pdl_launch_dependents();
-    if (tid == 0) SMEG_EV(g_ev_lb, 1);
 
     if (warp == kCWarps) {
         // ================= producer =================
@@ -235,7 +223,6 @@ __global__ void __launch_bounds__(kThreadsLb, 1) lowbit_gemv_kernel(const __grid
             if (seq0 == 0) send_a();
         }
         if (total_seq == 0) send_a();
-        if (lane == 0) SMEG_EV(g_ev_lb, 2);
         return;
     }
 
@@ -361,7 +348,6 @@ __global__ void __launch_bounds__(kThreadsLb, 1) lowbit_gemv_kernel(const __grid
                         QSs[idx] = (ok && p.qsum) ? p.qsum[(size_t)(row0 + r) * p.nb + blkq0 + bl] : 0;
                     }
                 }
-                if (tid == 0 && ti == 0 && qc == 0) SMEG_EV(g_ev_lb, 3);
             }
 
             const int st_qend = min(stages_total, (dq0 + qchunk + SD - 1) / SD);
@@ -382,10 +368,8 @@ __global__ void __launch_bounds__(kThreadsLb, 1) lowbit_gemv_kernel(const __grid
                 for (; st < st_end; ++st, ++seq) {
                     const int slot = seq % NS;
                     mbar_wait(&full[slot], (seq / NS) & 1, abort_flag, p.status);
-                    if (tid == 0 && seq == 0) SMEG_EV(g_ev_lb, 4);
-                    if (tid == 0 && ti == my_tasks - 1 && st == stages_total - 1) SMEG_EV(g_ev_lb, 9);
                     const int units = min(kWarps, p.ku - st * kWarps);
-                    if (uw < units && !SMEG_DBG_SKIP_LB) {
+                    if (uw < units) {
                         const unsigned char* sbase = stages + (size_t)slot * stage_bytes;
                         const int d_unit = st * SD + uw * UD;             // global depth of this unit
                         const int dl = d_unit - dq0;                        // within the staged activations
@@ -433,7 +417,6 @@ __global__ void __launch_bounds__(kThreadsLb, 1) lowbit_gemv_kernel(const __grid
                                         af[2] = (w >> (sh + 2)) & 0x01010101u;
                                         af[3] = (w >> (sh + 3)) & 0x01010101u;
                                     }
-                                    if (SMEG_DBG_BIT(2)) { acc[ci][0][0] ^= (int)(af[0] + af[1] + af[2] + af[3]); continue; }
 #pragma unroll
                                     for (int r = 0; r < DP; ++r) {
                                         acc[ci][0][r] = __dp4a((int)af[0], (int)aq[r].x, acc[ci][0][r]);
@@ -445,7 +428,7 @@ __global__ void __launch_bounds__(kThreadsLb, 1) lowbit_gemv_kernel(const __grid
                                 // flush at the end of a block (or of the unit): the four lanes holding the depth
                                 // slices of a column add into the same cell
                                 const int d_end = d_unit + 32 * (s + 1);
-                                if ((B16 || (d_end & (block - 1)) == 0 || s == STEPS - 1) && !SMEG_DBG_BIT(4)) {
+                                if (B16 || (d_end & (block - 1)) == 0 || s == STEPS - 1) {
                                     const int bl = B16 ? (((d_unit + 32 * s + 16 * (t >> 1)) >> p.log2_block) - blk0)
                                                        : ((block <= KC) ? (((d_end - 1) >> p.log2_block) - blk0) : 0);
                                     int* dst0 = sums + (size_t)bl * GPT * RS * 16 + g;
@@ -551,9 +534,7 @@ __global__ void __launch_bounds__(kThreadsLb, 1) lowbit_gemv_kernel(const __grid
                     __syncwarp();
                     if (lane == 0) mbar_arrive(&empty[slot]);
                 }
-                if (tid == 0 && st == stages_total && ti == my_tasks - 1) SMEG_EV(g_ev_lb, 5);
                 asm volatile("bar.sync 1, %0;" ::"n"(32 * kCWarps));
-                if (tid == 0 && st == stages_total && ti == my_tasks - 1) SMEG_EV(g_ev_lb, 6);
 
                 // ---- ordered fold of the blocks completed by this fold chunk ----
                 const bool block_ends = block <= KC || ((d0 + chunk) & (block - 1)) == 0 || st == stages_total;
@@ -583,7 +564,6 @@ __global__ void __launch_bounds__(kThreadsLb, 1) lowbit_gemv_kernel(const __grid
                 ++fseq;
             }
         }
-        if (tid == 0 && ti == my_tasks - 1) SMEG_EV(g_ev_lb, 10);
 
         // ---- epilogue + store ----
 #pragma unroll 1
@@ -594,7 +574,6 @@ __global__ void __launch_bounds__(kThreadsLb, 1) lowbit_gemv_kernel(const __grid
                 p.c[(size_t)gr * p.n + gc] = ep_store_value<0>(p.ep, TOT[o], (size_t)gr, (size_t)gc);
         }
     }
-    if (tid == 0) { SMEG_EV(g_ev_lb, 7); SMEG_EV(g_ev_lb, 15); }
 }
 
 template <int BITS, int MT, int NCG, int B16, int DP>
@@ -628,11 +607,6 @@ size_t lowbit_smem(int ns, int gpt, int mt, int rows_s, int kc, int kqc, int blo
 }
 
 }  // namespace
-
-#ifdef SMEG_TC_TIMELINE
-extern "C" int smeg_debug_skip_lb(int v) { return cudaMemcpyToSymbol(smeg::g_dbg_skip_lb, &v, sizeof(int)) == cudaSuccess ? 0 : -1; }
-extern "C" int smeg_debug_ev_lb(long long* host) { return cudaMemcpyFromSymbol(host, g_ev_lb, sizeof(long long) * 32) == cudaSuccess ? 0 : -1; }
-#endif
 
 cudaError_t act_quant_launch(const ActQuantArgs& a, cudaStream_t stream) {
     if (a.m == 0 || a.nbq == 0) return cudaSuccess;
@@ -817,6 +791,24 @@ int static_setup(StaticSetup** out) {
 }
 
 }  // namespace
+
+// Reads and clears the status word of the fixed array on the current device (0 if the entry point
+// was never used there).  Called by smeg_last_status after it has synchronised the device; allocates nothing.
+unsigned smeg_static_take_status() {
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return 0;
+    unsigned char* base = nullptr;
+    {
+        std::lock_guard<std::mutex> lk(g_static_mu);
+        if (!g_static[dev].ready) return 0;
+        base = g_static[dev].base;
+    }
+    unsigned v = 0;
+    unsigned char* word = base + kStaticQBytes + 2 * kStaticSaBytes;
+    if (cudaMemcpy(&v, word, sizeof(v), cudaMemcpyDeviceToHost) != cudaSuccess) return ~0u;
+    if (v) cudaMemset(word, 0, sizeof(unsigned));
+    return v;
+}
 
 extern "C" int smeg_matmul_lowbit_static_dev(const smeg_lowbit* w, const uint16_t* a, uint16_t* c, size_t m,
                                               const ep_desc16* ep, void* stream_v) {

@@ -28,8 +28,6 @@
 
 namespace smeg {
 
-SMEG_EV_DECL(g_ev_q4)
-
 namespace {
 
 constexpr int kConsumerWarps = 8;
@@ -138,7 +136,6 @@ __global__ void __launch_bounds__(kThreads) q4_gemv_kernel(const __grid_constant
     const int num_stages = (p.k64 + kConsumerWarps - 1) / kConsumerWarps;
     const int stages_per_chunk = p.ka / kStageDepth;
 
-    if (tid == 0) { SMEG_EV(g_ev_q4, 14); SMEG_EV(g_ev_q4, 0); }
     if (tid == 0) {
         for (int s = 0; s < NS; ++s) {
             mbar_init(&full[s], 1);
@@ -153,7 +150,6 @@ __global__ void __launch_bounds__(kThreads) q4_gemv_kernel(const __grid_constant
     }
     __syncthreads();
     pdl_launch_dependents();
-    if (tid == 0) SMEG_EV(g_ev_q4, 1);
 
     if (warp == kConsumerWarps) {
         // ================= producer: stream activations and this CTA's weights =================
@@ -217,9 +213,7 @@ __global__ void __launch_bounds__(kThreads) q4_gemv_kernel(const __grid_constant
                 pdl_wait();
                 if (!send_a(0)) return;
             }
-            if (lane == 0 && st0 == 0) SMEG_EV(g_ev_q4, 8);
         }
-        if (lane == 0) SMEG_EV(g_ev_q4, 2);
         return;
     }
 
@@ -248,7 +242,6 @@ __global__ void __launch_bounds__(kThreads) q4_gemv_kernel(const __grid_constant
                 asm volatile("bar.sync 1, %0;" ::"n"(32 * kConsumerWarps));
             }
             mbar_wait(&a_full[buf], (ch >> 1) & 1, abort_flag, p.status);
-            if (tid == 0 && ch == 0) SMEG_EV(g_ev_q4, 3);
         } else {
             // rows of A are not 16-byte aligned: cooperative copy (zero padded)
             asm volatile("bar.sync 1, %0;" ::"n"(32 * kConsumerWarps));
@@ -263,8 +256,6 @@ __global__ void __launch_bounds__(kThreads) q4_gemv_kernel(const __grid_constant
         for (int st = st_begin; st < st_end; ++st) {
             const int slot = st % NS;
             mbar_wait(&full[slot], (st / NS) & 1, abort_flag, p.status);
-            if (tid == 0 && st == 0) SMEG_EV(g_ev_q4, 4);
-            if (tid == 0 && st == num_stages - 1) SMEG_EV(g_ev_q4, 9);
             const int units = min(kConsumerWarps, p.k64 - st * kConsumerWarps);
             if (warp < units) {
                 const unsigned char* sbase = stages + (size_t)slot * stage_bytes;
@@ -337,7 +328,6 @@ __global__ void __launch_bounds__(kThreads) q4_gemv_kernel(const __grid_constant
         if (p.a_vec_ok && lane == 0) mbar_arrive(&a_empty[buf]);
     }
 
-    if (tid == 0) SMEG_EV(g_ev_q4, 5);
     // ---- fixed-order reduction over the 8 warps, epilogue, store ----
     // red[warp][c][mt][r][lane]
 #pragma unroll
@@ -349,7 +339,6 @@ __global__ void __launch_bounds__(kThreads) q4_gemv_kernel(const __grid_constant
             for (int r = 0; r < 4; ++r) red[((((size_t)warp * CG + c) * MT + mt) * 4 + r) * 32 + lane] = total[c][mt][r];
     }
     asm volatile("bar.sync 1, %0;" ::"n"(32 * kConsumerWarps));
-    if (tid == 0) SMEG_EV(g_ev_q4, 6);
     const int per_warp = CG * MT * 128;
     for (int o = tid; o < per_warp; o += 32 * kConsumerWarps) {
         float acc = 0.0f;
@@ -363,7 +352,6 @@ __global__ void __launch_bounds__(kThreads) q4_gemv_kernel(const __grid_constant
             else p.c[(size_t)row * p.n + col] = ep_store_value<BF16>(p.ep, acc, (size_t)row, (size_t)col);
         }
     }
-    if (tid == 0) { SMEG_EV(g_ev_q4, 7); SMEG_EV(g_ev_q4, 15); }
 }
 
 // ---------------------------------------------------------------------------------------------
@@ -683,10 +671,6 @@ cudaError_t launch(const Q4GemvArgs& a, dim3 grid, size_t smem, cudaStream_t str
 }
 
 }  // namespace
-
-#ifdef SMEG_TC_TIMELINE
-extern "C" int smeg_debug_ev_q4(long long* host) { return cudaMemcpyFromSymbol(host, g_ev_q4, sizeof(long long) * 32) == cudaSuccess ? 0 : -1; }
-#endif
 
 // Host-side launcher.  Chooses the column groups per CTA so that the grid has
 // at least about two CTAs per SM when the matrix allows it, the ring depth from

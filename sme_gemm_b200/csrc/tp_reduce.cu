@@ -3,26 +3,31 @@
 // stream -- the all-reduce and the last two passes of Mlp::accumulate (src/mlp.rs:124-146: out = f16(down(hid));
 // y += f32(out)) fused.
 //
-// Every rank holds its partial product in a buffer that all ranks can address (NVLink peer mapping) and
-// a small flag array.  Two-shot scheme, one launch per rank, no host round trip:
-//   0. a rank tells every peer that its partial is complete (flag "ready");
-//   1. rank r owns slice r of the output: it reads that slice from every rank's buffer, adds the
-//      values in rank order 0..W-1 (so every element has one summation order whatever the timing),
-//      rounds to f16 and writes the result back into slice r of every rank's buffer;
-//   2. when all of a rank's CTAs have done that, it tells every peer (flag "done"); a rank that has
-//      all W "done" flags adds its own buffer, now holding the reduced values, to its residual stream.
-// Flags carry the call's sequence number and only grow, so nothing is reset between calls.  A rank
-// leaves the kernel only after every owner has finished reading its buffer, so the next step may
-// overwrite the buffer at once.  Short vectors take a one-shot form instead (every rank adds all the
-// partials itself after the "ready" flags; see the kernel).  Every wait is bounded: after a second it raises the
-// status word and the kernel returns without touching y.
+// Every rank holds, in memory all ranks can address (NVLink peer mapping), a buffer of len f32
+// partial sums followed by len f16 results, and an array of kTpFlagWords flag words.  Two-shot
+// scheme, one launch per rank, no host round trip; all ranks launch the same grid:
+//   0. a rank tells every peer that its partial is complete (flag "ready"), and waits for theirs;
+//   1. rank r owns slice r of the output.  CTA b takes part b of it: a thread loads its vectors from
+//      every rank's buffer -- all loads issued before the first add, so a thread has up to
+//      4 x world 16-byte peer loads in flight instead of one NVLink round trip after another -- adds
+//      them in rank order 0..W-1 (one summation order per element whatever the timing: every rank ends
+//      with the same bits), rounds to f16, adds the values to its own residual stream straight from
+//      registers and stores the f16 values into the result area of the other ranks;
+//   2. CTA b then raises its own "done" flag on every peer (one flag per owner and CTA: no counter
+//      shared by the CTAs of a grid, nothing to reset, nothing a timed-out launch can leave behind,
+//      and no CTA waits for another CTA of its own grid);
+//   3. CTA b waits for the "done" flags of part b from the other owners and adds their f16 results,
+//      now in its own memory, to its residual stream.
+// Flags carry the call's sequence number and only grow.  A rank's kernel ends only after every owner
+// has finished reading its buffer, so the next step may overwrite the buffer at once.  Short vectors
+// take a one-shot form instead (every rank adds all the partials itself after the "ready" flags).
+// Every wait is bounded: after a second it raises the status word and the CTA returns; when that
+// happens in round 0 the residual stream is untouched.
 #include "common.cuh"
 #include "kernels.h"
 
 namespace smeg {
 namespace {
-
-__device__ unsigned g_ar_ctas_done;   // CTAs of this device's launch that finished their slice; zero at rest
 
 __device__ __forceinline__ void st_release_sys(uint32_t* p, uint32_t v) {
     asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
@@ -32,13 +37,20 @@ __device__ __forceinline__ uint32_t ld_acquire_sys(const uint32_t* p) {
     asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
     return v;
 }
+// Peer loads and stores: relaxed at system scope, and -- unlike a volatile access -- free to be
+// issued back to back; the flag rounds order them.
 __device__ __forceinline__ float4 ld_sys_f4(const float* p) {
     float4 v;
-    asm volatile("ld.relaxed.sys.global.v4.f32 {%0,%1,%2,%3}, [%4];" : "=f"(v.x), "=f"(v.y), "=f"(v.z), "=f"(v.w) : "l"(p) : "memory");
+    asm("ld.relaxed.sys.global.v4.f32 {%0,%1,%2,%3}, [%4];" : "=f"(v.x), "=f"(v.y), "=f"(v.z), "=f"(v.w) : "l"(p));
     return v;
 }
-__device__ __forceinline__ void st_sys_f4(float* p, float4 v) {
-    asm volatile("st.relaxed.sys.global.v4.f32 [%0], {%1,%2,%3,%4};" ::"l"(p), "f"(v.x), "f"(v.y), "f"(v.z), "f"(v.w) : "memory");
+__device__ __forceinline__ uint2 ld_sys_u2(const void* p) {
+    uint2 v;
+    asm("ld.relaxed.sys.global.v2.u32 {%0,%1}, [%2];" : "=r"(v.x), "=r"(v.y) : "l"(p));
+    return v;
+}
+__device__ __forceinline__ void st_sys_u2(void* p, uint2 v) {
+    asm volatile("st.relaxed.sys.global.v2.u32 [%0], {%1,%2};" ::"l"(p), "r"(v.x), "r"(v.y) : "memory");
 }
 __device__ __forceinline__ float round_f16(float x) { return __half2float(__float2half_rn(x)); }
 
@@ -48,18 +60,40 @@ __device__ __forceinline__ bool wait_flag(const uint32_t* flag, uint32_t seq) {
     for (;;) {
         if ((int)(ld_acquire_sys(flag) - seq) >= 0) return true;
         if (global_ns() - t0 > 1000000000ull) return false;
-        __nanosleep(200);
+        __nanosleep(100);
     }
 }
 
+// Sum over ranks in rank order of vector v; every load is issued before the first add.
+__device__ __forceinline__ float4 sum_ranks(const TpReduceArgs& p, size_t v) {
+    float4 x[8];
+#pragma unroll
+    for (int s = 0; s < 8; ++s)
+        if (s < p.world) x[s] = ld_sys_f4(p.bufs[s] + 4 * v);
+    float4 acc = x[0];
+#pragma unroll
+    for (int s = 1; s < 8; ++s)
+        if (s < p.world) {
+            acc.x = __fadd_rn(acc.x, x[s].x); acc.y = __fadd_rn(acc.y, x[s].y);
+            acc.z = __fadd_rn(acc.z, x[s].z); acc.w = __fadd_rn(acc.w, x[s].w);
+        }
+    return acc;
+}
+
+__device__ __forceinline__ void add_into(float* y, size_t v, float4 a) {
+    float4 t = reinterpret_cast<float4*>(y)[v];
+    t.x = __fadd_rn(t.x, a.x); t.y = __fadd_rn(t.y, a.y); t.z = __fadd_rn(t.z, a.z); t.w = __fadd_rn(t.w, a.w);
+    reinterpret_cast<float4*>(y)[v] = t;
+}
+
 __global__ void __launch_bounds__(256) tp_reduce_finish_kernel(const __grid_constant__ TpReduceArgs p) {
-    __shared__ int s_fail, s_last;
-    const int tid = threadIdx.x, W = p.world, r = p.rank;
-    if (tid == 0) { s_fail = 0; s_last = 0; }
+    __shared__ int s_fail;
+    const int tid = threadIdx.x, W = p.world, r = p.rank, G = (int)gridDim.x, b = (int)blockIdx.x;
+    if (tid == 0) s_fail = 0;
     __syncthreads();
 
     // ---- 0: my partial (written by the kernel ahead in the stream) is complete: tell every rank ----
-    if (blockIdx.x == 0 && tid < W) {
+    if (b == 0 && tid < W) {
         __threadfence_system();
         st_release_sys(p.flags[tid] + r, p.seq);
     }
@@ -75,72 +109,75 @@ __global__ void __launch_bounds__(256) tp_reduce_finish_kernel(const __grid_cons
         // Short vectors: every rank adds all the partials itself (same rank order, so the same bits everywhere) and
         // needs no second flag round.  The caller alternates between two buffers: a rank overwrites the buffer of
         // step n in step n + 2, after step n + 1's "ready" flags told it that every peer had finished step n.
-        for (size_t v = (size_t)blockIdx.x * blockDim.x + tid; v < nvec; v += (size_t)gridDim.x * blockDim.x) {
-            float4 acc = ld_sys_f4(p.bufs[0] + 4 * v);
-            for (int s = 1; s < W; ++s) {
-                const float4 x = ld_sys_f4(p.bufs[s] + 4 * v);
-                acc.x = __fadd_rn(acc.x, x.x); acc.y = __fadd_rn(acc.y, x.y);
-                acc.z = __fadd_rn(acc.z, x.z); acc.w = __fadd_rn(acc.w, x.w);
-            }
-            float4 y = reinterpret_cast<float4*>(p.y)[v];
-            y.x = __fadd_rn(y.x, round_f16(acc.x)); y.y = __fadd_rn(y.y, round_f16(acc.y));
-            y.z = __fadd_rn(y.z, round_f16(acc.z)); y.w = __fadd_rn(y.w, round_f16(acc.w));
-            reinterpret_cast<float4*>(p.y)[v] = y;
+        for (size_t v = (size_t)b * blockDim.x + tid; v < nvec; v += (size_t)G * blockDim.x) {
+            float4 acc = sum_ranks(p, v);
+            acc.x = round_f16(acc.x); acc.y = round_f16(acc.y); acc.z = round_f16(acc.z); acc.w = round_f16(acc.w);
+            add_into(p.y, v, acc);
         }
         return;
     }
 
-    // ---- 1: my slice, in float4 ----
-    const size_t per = (nvec + W - 1) / W;
-    const size_t v0 = per * r, v1 = min(nvec, v0 + per);
-    for (size_t v = v0 + (size_t)blockIdx.x * blockDim.x + tid; v < v1; v += (size_t)gridDim.x * blockDim.x) {
-        float4 acc = ld_sys_f4(p.bufs[0] + 4 * v);
-        for (int s = 1; s < W; ++s) {
-            const float4 x = ld_sys_f4(p.bufs[s] + 4 * v);
-            acc.x = __fadd_rn(acc.x, x.x); acc.y = __fadd_rn(acc.y, x.y);
-            acc.z = __fadd_rn(acc.z, x.z); acc.w = __fadd_rn(acc.w, x.w);
+    // ---- 1: part b of my slice ----
+    const size_t per = (nvec + W - 1) / W;                         // vectors per slice
+    const size_t cper = (per + G - 1) / G;                         // vectors per CTA and slice
+    {
+        const size_t v0 = per * r + cper * b, v1 = min(min(nvec, per * (r + 1)), v0 + cper);
+        constexpr int UN = 4;                                      // independent vectors per thread and pass
+        for (size_t vb = v0 + tid; vb < v1; vb += (size_t)UN * blockDim.x) {
+            float4 acc[UN];
+#pragma unroll
+            for (int u = 0; u < UN; ++u) {
+                const size_t v = vb + (size_t)u * blockDim.x;
+                if (v < v1) acc[u] = sum_ranks(p, v);
+            }
+#pragma unroll
+            for (int u = 0; u < UN; ++u) {
+                const size_t v = vb + (size_t)u * blockDim.x;
+                if (v >= v1) continue;
+                const __half2 lo = __floats2half2_rn(acc[u].x, acc[u].y), hi = __floats2half2_rn(acc[u].z, acc[u].w);
+                const uint2 h = make_uint2(*reinterpret_cast<const uint32_t*>(&lo), *reinterpret_cast<const uint32_t*>(&hi));
+                for (int s = 0; s < W; ++s)
+                    if (s != r) st_sys_u2(reinterpret_cast<unsigned char*>(p.bufs[s] + p.len) + 8 * v, h);
+                const float2 f0 = __half22float2(lo), f1 = __half22float2(hi);
+                add_into(p.y, v, make_float4(f0.x, f0.y, f1.x, f1.y));
+            }
         }
-        acc.x = round_f16(acc.x); acc.y = round_f16(acc.y); acc.z = round_f16(acc.z); acc.w = round_f16(acc.w);
-        for (int s = 0; s < W; ++s) st_sys_f4(p.bufs[s] + 4 * v, acc);
     }
+    // ---- 2: this CTA's part is written everywhere ----
     __threadfence_system();
     __syncthreads();
-    if (tid == 0) {
-        const unsigned old = atomicAdd(&g_ar_ctas_done, 1u);
-        s_last = old == gridDim.x - 1;
-    }
-    __syncthreads();
-    if (s_last) {
-        // ---- 2: every CTA of this rank has written its part of slice r everywhere ----
-        __threadfence_system();
-        if (tid < W) st_release_sys(p.flags[tid] + 8 + r, p.seq);
-        if (tid == 0) g_ar_ctas_done = 0;
-    }
-    if (tid < W && !wait_flag(p.flags[r] + 8 + tid, p.seq)) s_fail = 1;
+    if (tid < W && tid != r) st_release_sys(p.flags[tid] + kTpReadyWords + r * kTpMaxGrid + b, p.seq);
+
+    // ---- 3: the other owners' part b, from my own result area ----
+    if (tid < W && tid != r && !wait_flag(p.flags[r] + kTpReadyWords + tid * kTpMaxGrid + b, p.seq)) s_fail = 1;
     __syncthreads();
     if (s_fail) {
         if (tid == 0 && p.status) atomicOr(p.status, STATUS_PEER_TIMEOUT);
         return;
     }
-
-    // ---- residual add from my own buffer, which now holds the reduced, rounded values ----
-    const float* mine = p.bufs[r];
-    for (size_t v = (size_t)blockIdx.x * blockDim.x + tid; v < nvec; v += (size_t)gridDim.x * blockDim.x) {
-        const float4 s = ld_sys_f4(mine + 4 * v);
-        float4 y = reinterpret_cast<float4*>(p.y)[v];
-        y.x = __fadd_rn(y.x, s.x); y.y = __fadd_rn(y.y, s.y); y.z = __fadd_rn(y.z, s.z); y.w = __fadd_rn(y.w, s.w);
-        reinterpret_cast<float4*>(p.y)[v] = y;
+    const unsigned char* mine = reinterpret_cast<const unsigned char*>(p.bufs[r] + p.len);
+    for (int s = 0; s < W; ++s) {
+        if (s == r) continue;
+        const size_t v0 = per * s + cper * b, v1 = min(min(nvec, per * (s + 1)), v0 + cper);
+        for (size_t v = v0 + tid; v < v1; v += blockDim.x) {
+            const uint2 h = ld_sys_u2(mine + 8 * v);
+            const float2 f0 = __half22float2(*reinterpret_cast<const __half2*>(&h.x));
+            const float2 f1 = __half22float2(*reinterpret_cast<const __half2*>(&h.y));
+            add_into(p.y, v, make_float4(f0.x, f0.y, f1.x, f1.y));
+        }
     }
 }
 
 }  // namespace
 
 cudaError_t tp_reduce_finish_launch(const TpReduceArgs& a, int sm_count, cudaStream_t stream) {
-    // at most one CTA per SM: the CTAs of a rank meet at the "done" round, so all of them must be resident
+    (void)sm_count;
+    // the same grid on every rank (it depends on the length and the world size only): one vector per
+    // thread of an owner's slice where the slice is that long, at most kTpMaxGrid CTAs
     const size_t nvec = a.len / 4;
-    size_t ctas = ((a.oneshot ? nvec : nvec / a.world) + 255) / 256;
+    size_t ctas = ((a.oneshot ? nvec : (nvec + a.world - 1) / a.world) + 255) / 256;
     if (ctas < 1) ctas = 1;
-    if (ctas > (size_t)sm_count) ctas = (size_t)sm_count;
+    if (ctas > (size_t)kTpMaxGrid) ctas = (size_t)kTpMaxGrid;
     tp_reduce_finish_kernel<<<(unsigned)ctas, 256, 0, stream>>>(a);
     return cudaGetLastError();
 }

@@ -15,6 +15,8 @@ import numpy as np
 
 from .host import Gate, GatedLinear, Linear, Mlp, Q4Params, WeightLayout
 
+FLAG_WORDS = 1288      # SMEG_TP_FLAG_WORDS of include/smeg_api.h
+
 
 def shard_bounds(hidden_units: int, rank: int, world: int):
     """Hidden units [lo, hi) owned by `rank`: whole 32-unit chunks, sizes differing by at most one chunk."""
@@ -49,11 +51,15 @@ class PeerReduce:
         dev = torch.device("cuda", torch.cuda.current_device())
         self.rank, self.world = dist.get_rank(group), dist.get_world_size(group)
         assert self.world <= 8 and (m * d) % 4 == 0
-        # two buffers, taken in turn from step to step (the one-shot form of the kernel needs that)
-        self._both = symm.empty((2, m, d), dtype=torch.float32, device=dev)
-        self.flags = symm.empty((16,), dtype=torch.int32, device=dev)
+        # two buffers, taken in turn from step to step (the one-shot form of the kernel needs that); each holds
+        # the f32 partial sums followed by the f16 results the owners of the other slices write back
+        self._len = m * d
+        self._stride = self._len + self._len // 2             # floats per buffer (len % 4 == 0)
+        self._both = symm.empty((2, self._stride), dtype=torch.float32, device=dev)
+        self.flags = symm.empty((FLAG_WORDS,), dtype=torch.int32, device=dev)
         self.flags.zero_()
         self._both.zero_()
+        self._m, self._d = m, d
         torch.cuda.synchronize()
         self._hp = symm.rendezvous(self._both, group)
         self._hf = symm.rendezvous(self.flags, group)
@@ -62,7 +68,6 @@ class PeerReduce:
         self._C = C
         self._base = [int(p) for p in self._hp.buffer_ptrs]
         self._flags = (C.c_uint64 * self.world)(*[int(p) for p in self._hf.buffer_ptrs])
-        self._len = m * d
         # short vectors: every rank sums everything itself, one flag round instead of two
         self.oneshot = 1 if self._len * 4 <= 128 * 1024 else 0
         self.seq = 0
@@ -70,14 +75,14 @@ class PeerReduce:
     @property
     def partial(self):
         """The buffer this rank's partial product of the coming step goes into."""
-        return self._both[(self.seq + 1) & 1]
+        return self._both[(self.seq + 1) & 1][: self._len].view(self._m, self._d)
 
     def finish(self, y) -> None:
         """y += f32(f16(sum over ranks of their `partial`)), on every rank."""
         from ._lib import check, lib
         from .host import _ptr, _stream
         self.seq += 1
-        off = (self.seq & 1) * self._len * 4
+        off = (self.seq & 1) * self._stride * 4
         bufs = (self._C.c_uint64 * self.world)(*[b + off for b in self._base])
         check("smeg_mlp_reduce_finish_dev",
               lib().smeg_mlp_reduce_finish_dev(_ptr(y), bufs, self._flags, self.rank, self.world, y.numel(),

@@ -73,18 +73,29 @@ def _call(y, bufs, flags, rank, world, seq, oneshot):
                                            torch.cuda.current_stream().cuda_stream))
 
 
+FLAG_WORDS = 1288      # SMEG_TP_FLAG_WORDS
+
+
+def _buffer(part):
+    """A rank's buffer as the kernel wants it: the f32 partial followed by room for as many f16 results."""
+    n = part.numel()
+    buf = torch.zeros(n + n // 2 + 2, dtype=torch.float32, device="cuda")
+    buf[:n].copy_(part.reshape(-1))
+    return buf
+
+
 @pytest.mark.parametrize("oneshot", [0, 1])
-@pytest.mark.parametrize("m,d", [(1, 4096), (64, 4096), (3, 20)])
+@pytest.mark.parametrize("m,d", [(1, 4096), (64, 4096), (3, 20), (300, 4096)])
 def test_single_rank_reduce_finish_is_the_rounding_and_the_residual_add(m, d, oneshot):
     """world = 1: the kernel's own flags, slice and add; y += f32(f16(partial)) exactly."""
     import sme_gemm_b200 as sg
     g = torch.Generator(device="cuda").manual_seed(5)
     y = torch.randn(m, d, device="cuda", generator=g)
-    flags = torch.zeros(16, dtype=torch.int32, device="cuda")
+    flags = torch.zeros(FLAG_WORDS, dtype=torch.int32, device="cuda")
     for seq in (1, 2, 3):
         part = torch.randn(m, d, device="cuda", generator=g) * 5.0
         want = y + part.half().float()
-        _call(y, [part], [flags], 0, 1, seq, oneshot)
+        _call(y, [_buffer(part)], [flags], 0, 1, seq, oneshot)
         torch.cuda.synchronize()
         assert sg.last_status() == 0
         assert torch.equal(y, want)
@@ -92,14 +103,22 @@ def test_single_rank_reduce_finish_is_the_rounding_and_the_residual_add(m, d, on
 
 def test_a_peer_that_never_arrives_ends_the_wait_with_the_status_raised_and_y_untouched():
     """Two ranks' buffers and flags stand on this one GPU and the second rank never runs: nothing sets its
-    "ready" flag, the bounded wait (one second) runs out, the kernel returns, the status word says so."""
+    "ready" flag, the bounded wait (one second) runs out, the kernel returns, the status word says so.
+    The kernel keeps no state of its own between calls, so a call after the timed-out one works."""
     import sme_gemm_b200 as sg
     y = torch.ones(2, 64, device="cuda")
-    bufs = [torch.full((2, 64), 3.0, device="cuda") for _ in range(2)]
-    flags = [torch.zeros(16, dtype=torch.int32, device="cuda") for _ in range(2)]
+    part = torch.full((2, 64), 3.0, device="cuda")
+    bufs = [_buffer(part) for _ in range(2)]
+    flags = [torch.zeros(FLAG_WORDS, dtype=torch.int32, device="cuda") for _ in range(2)]
     _call(y, bufs, flags, 0, 2, 1, 0)
     torch.cuda.synchronize()
     assert sg.last_status() & 4          # STATUS_PEER_TIMEOUT; reading clears the word
     assert sg.last_status() == 0
     assert torch.equal(y, torch.ones_like(y))
     assert int(flags[1][0].item()) == 1  # rank 0 did announce its partial to the absent rank
+    # the next call, alone in its group, is unaffected
+    fresh = torch.zeros(FLAG_WORDS, dtype=torch.int32, device="cuda")
+    _call(y, [bufs[0]], [fresh], 0, 1, 1, 0)
+    torch.cuda.synchronize()
+    assert sg.last_status() == 0
+    assert torch.equal(y, torch.full_like(y, 4.0))
