@@ -89,6 +89,25 @@ __device__ __forceinline__ bool mbar_wait(uint64_t* bar, unsigned parity, volati
     return false;
 }
 
+// Bounded wait for the hand-offs of a fine-grained pipeline (a stage every few hundred cycles): polls
+// with the plain try_wait, whose own suspension is short, so the waiter resumes as soon as the
+// phase completes.
+__device__ __forceinline__ bool mbar_wait_poll(uint64_t* bar, unsigned parity, volatile int* abort_flag,
+                                               unsigned* status, unsigned code = STATUS_MBAR_TIMEOUT) {
+    if (mbar_try_wait(bar, parity)) return true;
+    const unsigned long long t0 = global_ns();
+    for (unsigned spins = 0;; ++spins) {
+        if (mbar_try_wait(bar, parity)) return true;
+        if ((spins & 63u) == 63u) {
+            if (*abort_flag) return false;
+            if (global_ns() - t0 > kWaitLimitNs) break;
+        }
+    }
+    *abort_flag = 1;
+    if (status) atomicOr(status, code);
+    return false;
+}
+
 // One contiguous global -> shared copy on the bulk-copy (TMA) engine.  Both
 // addresses 16-byte aligned, bytes a multiple of 16.
 __device__ __forceinline__ void bulk_g2s(void* smem_dst, const void* gsrc, unsigned bytes, uint64_t* bar) {

@@ -537,21 +537,6 @@ __global__ void __launch_bounds__(256) splitk_reduce_kernel(const __grid_constan
     }
 }
 
-typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
-                                  const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
-                                  CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
-EncodeTiledFn encode_fn() {
-    static EncodeTiledFn fn = nullptr;
-    if (!fn) {
-        void* ptr = nullptr;
-        cudaDriverEntryPointQueryResult qres;
-        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &ptr, cudaEnableDefault, &qres) == cudaSuccess &&
-            qres == cudaDriverEntryPointSuccess)
-            fn = (EncodeTiledFn)ptr;
-    }
-    return fn;
-}
-
 template <int BF16, int US, int DENSE>
 cudaError_t launch_tc(const CUtensorMap& tm, const CUtensorMap& tw, const GemmTcArgs& a, dim3 grid, size_t smem, cudaStream_t stream) {
     auto kern = gemm_tc_kernel<BF16, US, DENSE>;
@@ -572,12 +557,24 @@ cudaError_t launch_tc(const CUtensorMap& tm, const CUtensorMap& tw, const GemmTc
 
 }  // namespace
 
+TensorMapEncodeFn tensor_map_encoder() {
+    static TensorMapEncodeFn fn = nullptr;
+    if (!fn) {
+        void* ptr = nullptr;
+        cudaDriverEntryPointQueryResult qres;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &ptr, cudaEnableDefault, &qres) == cudaSuccess &&
+            qres == cudaDriverEntryPointSuccess)
+            fn = (TensorMapEncodeFn)ptr;
+    }
+    return fn;
+}
+
 bool gemm_tc_supported(int wkind, int m, int k, int log2_block, const void* a) {
     if (wkind != 4 && wkind != 16) return false;
     if (k % 8 != 0 || k == 0 || ((uintptr_t)a & 15) != 0) return false;   // TMA: 16-byte aligned rows
     if (log2_block < 3) return false;                                      // one scale per 8-depth chunk
     if (m < 1) return false;
-    return encode_fn() != nullptr;
+    return tensor_map_encoder() != nullptr;
 }
 
 void gemm_tc_plan(GemmTcArgs& a, int sm_count, dim3* grid, size_t* smem, size_t* ws_floats, size_t* n_counters) {
@@ -676,7 +673,7 @@ cudaError_t gemm_tc_launch(GemmTcArgs a, int bf16, dim3 grid, size_t smem, cudaS
     const cuuint64_t gstride[1] = {(cuuint64_t)a.k * 2};
     const cuuint32_t box[2] = {(cuuint32_t)kStageK, (cuuint32_t)a.ntok_box};
     const cuuint32_t estr[2] = {1, 1};
-    CUresult r = encode_fn()(&tm, bf16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, (void*)a.a, gdim,
+    CUresult r = tensor_map_encoder()(&tm, bf16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, (void*)a.a, gdim,
                              gstride, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
                              CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
     if (r != CUDA_SUCCESS) return cudaErrorInvalidValue;
@@ -686,7 +683,7 @@ cudaError_t gemm_tc_launch(GemmTcArgs a, int bf16, dim3 grid, size_t smem, cudaS
         const cuuint64_t wdim[2] = {(cuuint64_t)a.kd, (cuuint64_t)a.n};
         const cuuint64_t wstride[1] = {(cuuint64_t)a.kd * 2};
         const cuuint32_t wbox[2] = {(cuuint32_t)kStageK, 128};
-        r = encode_fn()(&tw, bf16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, (void*)a.wdense, wdim,
+        r = tensor_map_encoder()(&tw, bf16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, (void*)a.wdense, wdim,
                         wstride, wbox, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
                         CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
         if (r != CUDA_SUCCESS) return cudaErrorInvalidValue;

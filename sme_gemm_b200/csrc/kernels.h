@@ -1,5 +1,6 @@
 // Internal launch interfaces between the C-ABI layer (api.cu) and the kernels.
 #pragma once
+#include <cuda.h>
 #include <cuda_runtime.h>
 #include <stddef.h>
 #include <stdint.h>
@@ -68,6 +69,9 @@ struct ActQuantArgs {
     float* sa;            // m x nbq per-block activation scales (amax / 127), padded blocks 0
     int32_t* qsum;        // m x nbq per-block sums of q (1-bit path only; may be null)
     int m, k, kq, nbq, log2_block;
+    float* sa_t;          // optional: the same scales as nbq x mpad (block-major), for the tensor-core kernel
+    int32_t* qsum_t;      // optional: the same sums as nbq x mpad
+    int mpad;
 };
 cudaError_t act_quant_launch(const ActQuantArgs& a, cudaStream_t stream);
 
@@ -99,6 +103,32 @@ bool lowbit_gemv_fuses_quant(LowbitGemvArgs a, int bits, int sm_count);
 // itself (a.a set, at most two rows); otherwise a.q / a.sa / a.qsum come from act_quant_kernel.
 bool lowbit_direct_supported(const LowbitGemvArgs& a, bool fused);
 cudaError_t lowbit_direct_launch(LowbitGemvArgs a, int bits, int sm_count, cudaStream_t stream);
+
+// ---- 2-bit / 1-bit x int8 activations on tcgen05 kind::i8 (lowbit_tc.cu) ----
+struct LowbitTcArgs {
+    const unsigned char* codes;   // packed units [n16][ku][512 B]
+    const uint16_t* scales;       // f16 bits [n16][nb][16]
+    const int8_t* q;              // m x kq int8 activation codes (act_quant_kernel)
+    const float* sa_t;            // nb x mpad activation scales, block-major
+    const int32_t* qsum_t;        // nb x mpad per-block sums of q (read for 1-bit weights only)
+    int mpad;                     // m rounded up to a multiple of 64
+    uint16_t* c;                  // m x n f16 bits
+    int32_t* sums_out;            // optional debug: m x n x nb_real exact block sums
+    int m, n, k, kq;
+    int n16, ku, nb, nb_real;
+    int log2_block, bits;
+    uint32_t lut;                 // 2-bit codebook, byte c = value of code c
+    unsigned* status;
+    EpParams ep;
+};
+bool lowbit_tc_supported(int bits, int m, int k, int log2_block);
+cudaError_t lowbit_tc_launch(LowbitTcArgs a, cudaStream_t stream);
+
+// cuTensorMapEncodeTiled through the runtime's driver entry point lookup (gemm_tc.cu); null if unavailable.
+typedef CUresult (*TensorMapEncodeFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
+                                      const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                      CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+TensorMapEncodeFn tensor_map_encoder();
 
 // ---- prefill GEMM on tcgen05 (gemm_tc.cu) ----
 struct GemmTcArgs {

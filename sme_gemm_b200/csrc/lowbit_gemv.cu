@@ -92,8 +92,12 @@ __global__ void __launch_bounds__(128) act_quant_kernel(ActQuantArgs p) {
     __syncthreads();
     if (tid == 0) {
         const bool real = d0 < (size_t)p.k;
-        p.sa[(size_t)row * p.nbq + b] = real ? __fdiv_rn(amax, 127.0f) : 0.0f;
-        if (p.qsum) p.qsum[(size_t)row * p.nbq + b] = s_sum[0] + s_sum[1] + s_sum[2] + s_sum[3];
+        const float sa = real ? __fdiv_rn(amax, 127.0f) : 0.0f;
+        const int qsum = s_sum[0] + s_sum[1] + s_sum[2] + s_sum[3];
+        p.sa[(size_t)row * p.nbq + b] = sa;
+        if (p.qsum) p.qsum[(size_t)row * p.nbq + b] = qsum;
+        if (p.sa_t) p.sa_t[(size_t)b * p.mpad + row] = sa;
+        if (p.qsum_t) p.qsum_t[(size_t)b * p.mpad + row] = qsum;
     }
 }
 
@@ -826,6 +830,7 @@ extern "C" int smeg_matmul_lowbit_static_dev(const smeg_lowbit* w, const uint16_
     if (rc) return rc;
 
     ActQuantArgs aq;
+    memset(&aq, 0, sizeof(aq));
     aq.a = a;
     aq.q = reinterpret_cast<int8_t*>(st->base);
     aq.sa = reinterpret_cast<float*>(st->base + kStaticQBytes);
