@@ -54,11 +54,11 @@ int g_direct_rows = []() {
     return v < 0 ? 0 : (v > 4 ? 4 : v);
 }();
 
-// 2-bit / 1-bit calls above the direct kernels' rows run their block sums on tcgen05 kind::i8; SMEG_LOWBIT_TC=0
-// keeps them on the warp-level kernel (tuning knob).
+// Rows from which 2-bit / 1-bit calls form their block sums on the tensor cores (lowbit_tc.cu); below it, and above
+// the direct kernels' rows, the warp-level kernel runs.  SMEG_LOWBIT_TC_MIN_ROWS is a tuning knob (0 = never).
 int g_lowbit_tc = []() {
-    const char* e = getenv("SMEG_LOWBIT_TC");
-    return (e && e[0] == '0') ? 0 : 1;
+    const char* e = getenv("SMEG_LOWBIT_TC_MIN_ROWS");
+    return e ? atoi(e) : 17;
 }();
 
 }  // namespace
@@ -673,22 +673,23 @@ static int lowbit_dev(const smeg_lowbit* w, const uint16_t* a, uint16_t* c, size
     } else {
         // quantise first, into stream-ordered scratch; above the direct kernels' rows the block sums run on the
         // tensor cores (lowbit_tc.cu), which wants the per-block scales and sums block-major as well
-        const bool tc = (int)m > g_direct_rows && g_lowbit_tc && lowbit_tc_supported(w->bits, (int)m, (int)k, w->d.log2_block);
+        const bool tc = (int)m > g_direct_rows && g_lowbit_tc > 0 && (int)m >= g_lowbit_tc && lowbit_tc_supported(w->bits, (int)m, (int)k, w->d.log2_block);
         const size_t mpad = (m + 63) / 64 * 64;
         const size_t q_bytes = (m * kq + 255) / 256 * 256, sa_bytes = (m * nb * 4 + 255) / 256 * 256;
-        const size_t t_bytes = tc ? (mpad * nb * 4 + 255) / 256 * 256 : 0;
-        if (cudaMallocAsync(&ws, q_bytes + 2 * sa_bytes + 2 * t_bytes + 256, stream) != cudaSuccess) {
+        const size_t t_bytes = tc ? (mpad * nb * 4 + 255) / 256 * 256 : 0, qh_bytes = tc ? (m * kq * 2 + 255) / 256 * 256 : 0;
+        if (cudaMallocAsync(&ws, q_bytes + 2 * sa_bytes + 2 * t_bytes + qh_bytes + 256, stream) != cudaSuccess) {
             if (ext) cudaFreeAsync(ext, stream);
             return -2;
         }
         ActQuantArgs aq;
         memset(&aq, 0, sizeof(aq));
         aq.a = a; aq.q = (int8_t*)ws; aq.sa = (float*)(ws + q_bytes);
-        aq.qsum = w->bits == 1 ? (int32_t*)(ws + q_bytes + sa_bytes) : nullptr;
+        aq.qsum = (w->bits == 1 || tc) ? (int32_t*)(ws + q_bytes + sa_bytes) : nullptr;
         aq.m = (int)m; aq.k = (int)k; aq.kq = (int)kq; aq.nbq = (int)nb; aq.log2_block = w->d.log2_block;
         if (tc) {
             aq.sa_t = (float*)(ws + q_bytes + 2 * sa_bytes);
             aq.qsum_t = (int32_t*)(ws + q_bytes + 2 * sa_bytes + t_bytes);
+            aq.qh = (uint16_t*)(ws + q_bytes + 2 * sa_bytes + 2 * t_bytes);
             aq.mpad = (int)mpad;
         }
         e = act_quant_launch(aq, stream);
@@ -697,11 +698,11 @@ static int lowbit_dev(const smeg_lowbit* w, const uint16_t* a, uint16_t* c, size
             if (tc) {
                 LowbitTcArgs t;
                 memset(&t, 0, sizeof(t));
-                t.codes = w->codes; t.scales = w->scales; t.q = aq.q; t.sa_t = aq.sa_t; t.qsum_t = aq.qsum_t; t.mpad = (int)mpad;
+                t.codes = w->codes; t.scales = w->scales; t.qh = aq.qh; t.sa_t = aq.sa_t; t.qsum_t = aq.qsum_t; t.mpad = (int)mpad;
                 t.c = c; t.sums_out = sums_out;
                 t.m = (int)m; t.n = (int)n; t.k = (int)k; t.kq = (int)kq;
                 t.n16 = (int)w->d.n16; t.ku = (int)w->d.ku; t.nb = (int)nb; t.nb_real = (int)w->d.nb_real;
-                t.log2_block = w->d.log2_block; t.bits = w->bits; t.lut = w->lut; t.status = ds->status; t.ep = g.ep;
+                t.log2_block = w->d.log2_block; t.bits = w->bits; t.lut = w->lut ^ 0x80808080u; t.status = ds->status; t.ep = g.ep;
                 e = lowbit_tc_launch(t, stream);
             } else if ((int)m <= g_direct_rows && lowbit_direct_supported(g, false)) e = lowbit_direct_launch(g, w->bits, ds->sm_count, stream);
             else e = lowbit_gemv_launch(g, w->bits, ds->sm_count, stream);

@@ -207,7 +207,7 @@ __global__ void __launch_bounds__(kDThreads, M <= 2 ? 3 : 2) q4_direct_kernel(co
 // ---------------------------------------------------------------------------------------------
 // 2-bit / 1-bit weights x int8 activations, M rows (1..4).
 // Shared memory: ring [8 warps][PF][32 lanes] of 16 B codes | Qs [M][kq + 16] int8 | SAs [M][nb] f32 |
-//                QSs [M][nb] i32 | AMX [M][nb] i32 | sums [nb][CPC][M][16] i32.
+//                QSs [M][nb] i32 | AMX [M][nb] i32 | sums [2][nb][M][16] i32 | staged scale rows.
 // ---------------------------------------------------------------------------------------------
 constexpr int kLbPF = 8;                                           // units in flight per warp
 constexpr size_t kLbRingBytes = (size_t)kDWarps * kLbPF * 512;
@@ -234,7 +234,7 @@ __global__ void __launch_bounds__(kDThreads, 3) lowbit_direct_kernel(const __gri
     int* AMX = QSs + (size_t)M * nb;
     int* sums = AMX + (size_t)M * nb;
     // [ncg][nb][16] when p.dsc; 16-byte aligned for the asynchronous copies
-    uint16_t* SCs = reinterpret_cast<uint16_t*>((reinterpret_cast<uintptr_t>(sums + (size_t)nb * CPC * M * 16) + 15) & ~(uintptr_t)15);
+    uint16_t* SCs = reinterpret_cast<uint16_t*>((reinterpret_cast<uintptr_t>(sums + (size_t)2 * nb * M * 16) + 15) & ~(uintptr_t)15);
     const int cg_first = (int)blockIdx.x * p.dq + min((int)blockIdx.x, p.dr);
     const int ncg = p.dq + ((int)blockIdx.x < p.dr ? 1 : 0);
     const int upw = p.dupw;
@@ -264,7 +264,7 @@ __global__ void __launch_bounds__(kDThreads, 3) lowbit_direct_kernel(const __gri
         cp_async_commit();
     }
     pdl_launch_dependents();
-    for (int idx = tid; idx < nb * CPC * M * 16; idx += kDThreads) sums[idx] = 0;
+    for (int idx = tid; idx < 2 * nb * M * 16; idx += kDThreads) sums[idx] = 0;
     for (int idx = tid; idx < M * nb; idx += kDThreads) { AMX[idx] = 0; QSs[idx] = 0; SAs[idx] = 0.0f; }
     pdl_wait();
 
@@ -371,7 +371,8 @@ __global__ void __launch_bounds__(kDThreads, 3) lowbit_direct_kernel(const __gri
     int acc[M][2];
 #pragma unroll
     for (int r = 0; r < M; ++r) acc[r][0] = acc[r][1] = 0;
-    int cc = 0, cu = u_begin;                                      // compute cursor
+    int cu = u_begin;                                              // compute cursor
+    int* sb = sums;                                                // the column group's block sums
     // flush: the lanes of a column holding the same block add into one cell
     auto flush = [&](int bl) {
 #pragma unroll
@@ -383,74 +384,79 @@ __global__ void __launch_bounds__(kDThreads, 3) lowbit_direct_kernel(const __gri
                 if (block >= 32) {
                     v += __shfl_xor_sync(0xffffffffu, v, 1);
                     v += __shfl_xor_sync(0xffffffffu, v, 2);
-                    if (t == 0 && v != 0) atomicAdd(&sums[(((size_t)bl * CPC + cc) * M + r) * 16 + g + 8 * j], v);
+                    if (t == 0 && v != 0) atomicAdd(&sb[((size_t)bl * M + r) * 16 + g + 8 * j], v);
                 } else if (v != 0) {
-                    atomicAdd(&sums[(((size_t)bl * CPC + cc) * M + r) * 16 + g + 8 * j], v);
+                    atomicAdd(&sb[((size_t)bl * M + r) * 16 + g + 8 * j], v);
                 }
             }
     };
-    int slot = 0;
-    for (int j = 0; j < total; ++j) {
-        cp_async_wait<PF - 1>();                                   // this lane's copy of unit j has landed
-        const uint4 wv = ring_w[slot * 32];
-        const uint32_t words[4] = {wv.x, wv.y, wv.z, wv.w};
+    // One column group at a time: its block sums meet in one of two buffers; when every warp has added its share the
+    // cells' owners fold them (and clear the buffer) while the other warps go on with the next column group.
+    int slot = 0, j = 0;
+    for (int c = 0; c < ncg; ++c) {
+        sb = sums + (size_t)(c & 1) * nb * M * 16;
+        for (cu = u_begin; cu < u_end; ++cu, ++j) {
+            cp_async_wait<PF - 1>();                               // this lane's copy of unit j has landed
+            const uint4 wv = ring_w[slot * 32];
+            const uint32_t words[4] = {wv.x, wv.y, wv.z, wv.w};
 #pragma unroll
-        for (int s = 0; s < STEPS; ++s) {
-            const int d = cu * UD + 32 * s + 8 * t;                // this lane's 8 depths
-            const uint32_t w = words[BITS == 2 ? s : (s >> 1)];
-            uint32_t af[4];
-            if (BITS == 2) {
-                const uint32_t e = w & 0x33333333u, o = (w >> 2) & 0x33333333u;
-                af[0] = prmt_lut(p.lut, e);
-                af[1] = prmt_lut(p.lut, o);
-                af[2] = prmt_lut(p.lut, e >> 16);
-                af[3] = prmt_lut(p.lut, o >> 16);
-            } else {
-                const int sh = 4 * (s & 1);
-                af[0] = (w >> (sh + 0)) & 0x01010101u;
-                af[1] = (w >> (sh + 1)) & 0x01010101u;
-                af[2] = (w >> (sh + 2)) & 0x01010101u;
-                af[3] = (w >> (sh + 3)) & 0x01010101u;
-            }
+            for (int s = 0; s < STEPS; ++s) {
+                const int d = cu * UD + 32 * s + 8 * t;            // this lane's 8 depths
+                const uint32_t w = words[BITS == 2 ? s : (s >> 1)];
+                uint32_t af[4];
+                if (BITS == 2) {
+                    const uint32_t e = w & 0x33333333u, o = (w >> 2) & 0x33333333u;
+                    af[0] = prmt_lut(p.lut, e);
+                    af[1] = prmt_lut(p.lut, o);
+                    af[2] = prmt_lut(p.lut, e >> 16);
+                    af[3] = prmt_lut(p.lut, o >> 16);
+                } else {
+                    const int sh = 4 * (s & 1);
+                    af[0] = (w >> (sh + 0)) & 0x01010101u;
+                    af[1] = (w >> (sh + 1)) & 0x01010101u;
+                    af[2] = (w >> (sh + 2)) & 0x01010101u;
+                    af[3] = (w >> (sh + 3)) & 0x01010101u;
+                }
 #pragma unroll
-            for (int r = 0; r < M; ++r) {
-                const uint2 aq = *reinterpret_cast<const uint2*>(Qs + (size_t)r * q_stride + d);
-                acc[r][0] = __dp4a((int)af[0], (int)aq.x, acc[r][0]);
-                acc[r][0] = __dp4a((int)af[2], (int)aq.y, acc[r][0]);
-                acc[r][1] = __dp4a((int)af[1], (int)aq.x, acc[r][1]);
-                acc[r][1] = __dp4a((int)af[3], (int)aq.y, acc[r][1]);
+                for (int r = 0; r < M; ++r) {
+                    const uint2 aq = *reinterpret_cast<const uint2*>(Qs + (size_t)r * q_stride + d);
+                    acc[r][0] = __dp4a((int)af[0], (int)aq.x, acc[r][0]);
+                    acc[r][0] = __dp4a((int)af[2], (int)aq.y, acc[r][0]);
+                    acc[r][1] = __dp4a((int)af[1], (int)aq.x, acc[r][1]);
+                    acc[r][1] = __dp4a((int)af[3], (int)aq.y, acc[r][1]);
+                }
+                // end of a K-block for this lane's depths (blocks of 16: lanes t < 2 and t >= 2 differ),
+                // or of this warp's share of the column group
+                if (!BIGBLK && (((d + 32) >> p.log2_block) != (d >> p.log2_block) || (s == STEPS - 1 && cu == u_end - 1))) flush(d >> p.log2_block);
             }
-            // end of a K-block for this lane's depths (blocks of 16: lanes t < 2 and t >= 2 differ),
-            // or of this warp's share of the column group
-            if (!BIGBLK && (((d + 32) >> p.log2_block) != (d >> p.log2_block) || (s == STEPS - 1 && cu == u_end - 1))) flush(d >> p.log2_block);
+            // blocks of a whole unit or more: one test per unit
+            if (BIGBLK && ((((cu + 1) * UD) & (block - 1)) == 0 || cu == u_end - 1)) flush((cu * UD) >> p.log2_block);
+            if (j + PF < total) issue(slot);
+            cp_async_commit();
+            slot = slot + 1 == PF ? 0 : slot + 1;
         }
-        // blocks of a whole unit or more: one test per unit
-        if (BIGBLK && ((((cu + 1) * UD) & (block - 1)) == 0 || cu == u_end - 1)) flush((cu * UD) >> p.log2_block);
-        if (j + PF < total) issue(slot);
-        cp_async_commit();
-        slot = slot + 1 == PF ? 0 : slot + 1;
-        if (++cu == u_end) { cu = u_begin; ++cc; }
+        if (c == 0) cp_async_wait<0>();                            // the staged scale rows (first group of copies) as well
+        __syncthreads();
+        // ---- ordered fold of the column group's cells, epilogue, store ----
+        if (tid < M * 16) {
+            const int col16 = tid & 15, r = tid >> 4;
+            const int col = (cg_first + c) * 16 + col16;
+            const uint16_t* sc = (p.dsc ? SCs + (size_t)c * nb * 16 : p.scales + ((size_t)(cg_first + c) * nb) * 16) + scale_slot(col16);
+            int* cell = sb + (size_t)r * 16 + col16;
+            float tot = 0.0f;
+#pragma unroll 4
+            for (int bl = 0; bl < p.nb_real; ++bl) {
+                int sum = cell[(size_t)bl * M * 16];
+                cell[(size_t)bl * M * 16] = 0;
+                if (BITS == 1) sum = 2 * sum - QSs[r * nb + bl];
+                if (p.sums_out && col < p.n) p.sums_out[((size_t)r * p.n + col) * p.nb_real + bl] = sum;
+                const float scale = __half2float(__ushort_as_half(sc[(size_t)bl * 16]));
+                tot = fmaf((float)sum, __fmul_rn(scale, SAs[r * nb + bl]), tot);
+            }
+            if (col < p.n) p.c[(size_t)r * p.n + col] = ep_store_value<0>(p.ep, tot, (size_t)r, (size_t)col);
+        }
     }
     cp_async_wait<0>();
-    __syncthreads();
-
-    // ---- ordered fold of every output cell's blocks, epilogue, store ----
-    for (int o = tid; o < ncg * M * 16; o += kDThreads) {
-        const int col16 = o & 15, r = (o >> 4) % M, c = o / (16 * M);
-        const int col = (cg_first + c) * 16 + col16;
-        if (col >= p.n) continue;
-        const uint16_t* sc = (p.dsc ? SCs + (size_t)c * nb * 16 : p.scales + ((size_t)(cg_first + c) * nb) * 16) + scale_slot(col16);
-        float tot = 0.0f;
-#pragma unroll 4
-        for (int bl = 0; bl < p.nb_real; ++bl) {
-            int s = sums[(((size_t)bl * CPC + c) * M + r) * 16 + col16];
-            if (BITS == 1) s = 2 * s - QSs[r * nb + bl];
-            if (p.sums_out) p.sums_out[((size_t)r * p.n + col) * p.nb_real + bl] = s;
-            const float scale = __half2float(__ushort_as_half(sc[(size_t)bl * 16]));
-            tot = fmaf((float)s, __fmul_rn(scale, SAs[r * nb + bl]), tot);
-        }
-        p.c[(size_t)r * p.n + col] = ep_store_value<0>(p.ep, tot, (size_t)r, (size_t)col);
-    }
 }
 
 template <typename K>
@@ -506,7 +512,7 @@ cudaError_t q4_direct_launch(Q4GemvArgs a, int sm_count, cudaStream_t stream) {
 // ---- 2-bit / 1-bit ----
 static bool lowbit_scales_staged(const LowbitGemvArgs& a, int cpc) { return (size_t)cpc * a.nb * 32 <= 16 * 1024; }
 static size_t lowbit_direct_smem(const LowbitGemvArgs& a, int cpc) {
-    return kLbRingBytes + (size_t)a.m * (a.kq + 16) + (size_t)3 * a.m * a.nb * 4 + (size_t)a.nb * cpc * a.m * 16 * 4 +
+    return kLbRingBytes + (size_t)a.m * (a.kq + 16) + (size_t)3 * a.m * a.nb * 4 + (size_t)2 * a.nb * a.m * 16 * 4 +
            (lowbit_scales_staged(a, cpc) ? (size_t)cpc * a.nb * 32 + 16 : 0);
 }
 

@@ -69,6 +69,7 @@ struct ActQuantArgs {
     float* sa;            // m x nbq per-block activation scales (amax / 127), padded blocks 0
     int32_t* qsum;        // m x nbq per-block sums of q (1-bit path only; may be null)
     int m, k, kq, nbq, log2_block;
+    uint16_t* qh;         // optional: the codes as f16 integers, m x kq, for the tensor-core kernel
     float* sa_t;          // optional: the same scales as nbq x mpad (block-major), for the tensor-core kernel
     int32_t* qsum_t;      // optional: the same sums as nbq x mpad
     int mpad;
@@ -108,7 +109,7 @@ cudaError_t lowbit_direct_launch(LowbitGemvArgs a, int bits, int sm_count, cudaS
 struct LowbitTcArgs {
     const unsigned char* codes;   // packed units [n16][ku][512 B]
     const uint16_t* scales;       // f16 bits [n16][nb][16]
-    const int8_t* q;              // m x kq int8 activation codes (act_quant_kernel)
+    const uint16_t* qh;           // m x kq activation codes as f16 integers (act_quant_kernel)
     const float* sa_t;            // nb x mpad activation scales, block-major
     const int32_t* qsum_t;        // nb x mpad per-block sums of q (read for 1-bit weights only)
     int mpad;                     // m rounded up to a multiple of 64
@@ -117,7 +118,7 @@ struct LowbitTcArgs {
     int m, n, k, kq;
     int n16, ku, nb, nb_real;
     int log2_block, bits;
-    uint32_t lut;                 // 2-bit codebook, byte c = value of code c
+    uint32_t lut;                 // 2-bit codebook, byte c = value of code c + 128
     unsigned* status;
     EpParams ep;
 };

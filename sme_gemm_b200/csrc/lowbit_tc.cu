@@ -1,6 +1,6 @@
 // 2-bit / 1-bit weights x int8-quantised activations on the 5th-generation tensor cores
-// (tcgen05.mma.kind::i8, int32 accumulators in tensor memory): matmul_q2 / matmul_q1 above a
-// handful of rows, up to prefill-sized batches.
+// (tcgen05.mma, accumulators in tensor memory): matmul_q2 / matmul_q1 above a handful of rows, up to
+// prefill-sized batches.
 //
 // Replaces the reference's SME kernel for these batch sizes (q2_core / run_q2_gemv / Q2_FOLD,
 // csrc/gemm_q2.cc:180-204,300-404, which walks the rows in groups of five) and reproduces the bits
@@ -8,27 +8,35 @@
 // is an exact int32, and an output cell folds its blocks in K order with
 // total = fmaf((float)sum, scale * sa, total).
 //
+// The block sums are integer dot products, formed EXACTLY on the f16 tensor-core path: the int8
+// activation codes travel as f16 integers (act_quant_kernel writes them so), a weight travels as
+// the f16 whose bit pattern is a small unsigned integer u (u * 2^-24: the sign bit itself for
+// 1-bit weights, codebook value + 128 for 2-bit ones), products of such numbers are exact, and an
+// f32 accumulator holds their sum exactly while it stays below 2^24 units -- which a run of at
+// most 256 depths guarantees (255 * 128 * 256 < 2^24).  A K-block longer than that is accumulated
+// in runs of 256 depths whose integer sums are added in the fold.  (tcgen05.mma.kind::i8 gives the
+// same integers, and an earlier form of this kernel used it, but the int8 tensor path of this
+// part sustains only ~135 TOP/s against ~1500 TFLOP/s for f16.)
+//
 // One CTA owns 128 weight columns (the MMA's M dimension) x a tile of up to 64 activation rows (the
-// MMA's N dimension) over the whole depth, walked in 128-deep stages.  Roles (640 threads):
-//   warp 16 (rows)      one TMA tile load per stage of the int8 activation codes that
-//                       act_quant_kernel left in global memory (tensor map, 128-byte swizzle, rows
-//                       past m read as zero).
+// MMA's N dimension) over the whole depth, walked in 64-deep stages.  Roles (640 threads):
+//   warp 16 (rows)      one TMA tile load per stage of the activation codes (tensor map, 128-byte
+//                       swizzle, rows past m read as zero).
 //   warp 18 (weights)   the packed units of the CTA's 8 column groups, 512 depths per bulk copy.
-//   warps 0-7 (expand)  one column group each: 2-bit codes through a byte-permute lookup of the
-//                       codebook, sign bits as {0, 1} bytes (the sum is corrected to
-//                       2 S - sum(q) at the fold), written as the K-major, 128-byte-swizzled
-//                       int8 operand.
-//   warp 17 (MMA)       one elected thread issues the stage's four K = 32 instructions.  A
-//                       K-block's steps accumulate into one of a ring of accumulators in tensor
-//                       memory (512 columns / row tile); the block's last step commits it to
-//                       the fold warps.
+//   warps 0-7 (expand)  four pairs taking the stages in turn, a warp four column groups of its
+//                       stage: 2-bit codes through a byte-permute lookup of the offset codebook,
+//                       sign bits as they are, widened to 16 bits and written as the K-major,
+//                       128-byte-swizzled operand.
+//   warp 17 (MMA)       one elected thread issues the stage's four K = 16 instructions.  A run's
+//                       steps accumulate into one of a ring of accumulators in tensor memory
+//                       (512 columns / row tile); the run's last step commits it to the fold warps.
 //   warp 19 (scales)    per K-block the operands of the fold -- the rows' activation scales and code
 //                       sums, the column groups' scale rows -- into a small ring, so that no fold
 //                       warp ever waits for a global load.
-//   warps 8-15 (fold)   thread = weight column: read a finished block sum per row
-//                       (tcgen05.ld), release the accumulator, fold it into the running f32 total with
-//                       the block's scale; after the last block the epilogue graph runs on the
-//                       f16-rounded product and C is stored.
+//   warps 8-15 (fold)   thread = weight column: read a finished run per row (tcgen05.ld), release
+//                       the accumulator, and at the end of a K-block fold the block's integer into
+//                       the running f32 total with the block's scale; after the last block the
+//                       epilogue graph runs on the f16-rounded product and C is stored.
 // Every wait is bounded; a timed-out wait raises the status word and the kernel drains and exits.
 #include "epilogue.cuh"
 #include "kernels.h"
@@ -39,44 +47,35 @@ namespace smeg {
 namespace {
 
 constexpr int kLtThreads = 32 * 20;
-constexpr int kLtStage = 128;                    // depths per stage (one 128-byte swizzle row of int8)
+constexpr int kLtStage = 64;                     // depths per stage (one 128-byte swizzle row of f16)
 constexpr int kLtATile = 128 * 128;              // expanded weights of a stage: 16 KB
-constexpr int kLtNA = 4, kLtNB = 4, kLtNK = 4;   // ring depths: operand, rows, packed
-constexpr int kLtSlotDepth = 512;                // depths of one packed-ring slot (four stages)
+constexpr int kLtNA = 6, kLtNB = 6, kLtNK = 3;   // ring depths: operand, rows, packed
+constexpr int kLtSlotStages = 8;                 // stages of one packed-ring slot (512 depths)
 constexpr int kLtNF = 8;                         // ring depth of the fold operands (K-blocks)
+constexpr int kLtRun = 256;                      // most depths summed in one accumulator
 
-__device__ __forceinline__ uint32_t prmt_cb(uint32_t lut, uint32_t sel) {
+__device__ __forceinline__ uint32_t prmt2(uint32_t a, uint32_t b, uint32_t sel) {
     uint32_t d;
-    asm("prmt.b32 %0, %1, %2, %3;" : "=r"(d) : "r"(lut), "r"(0u), "r"(sel));
+    asm("prmt.b32 %0, %1, %2, %3;" : "=r"(d) : "r"(a), "r"(b), "r"(sel));
     return d;
 }
-__device__ __forceinline__ void umma_i8(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc, uint32_t accumulate) {
-    asm volatile(
-        "{\n\t.reg .pred p;\n\t"
-        "setp.ne.b32 p, %4, 0;\n\t"
-        "tcgen05.mma.cta_group::1.kind::i8 [%0], %1, %2, %3, {%5, %6, %7, %8}, p;\n\t}"
-        ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate), "r"(0u), "r"(0u), "r"(0u), "r"(0u)
-        : "memory");
-}
-// Instruction descriptor, kind::i8: D = s32 (bits 4..5 = 2), A/B signed 8-bit (bits 7..9 / 10..12 = 1),
-// both K-major, N >> 3 in bits 17..22, M >> 4 in bits 24..28.
-__device__ __forceinline__ uint32_t umma_idesc_i8(int m, int n) {
-    return (2u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(n >> 3) << 17) | ((uint32_t)(m >> 4) << 24);
-}
+// Four bytes -> four 16-bit values with zero high bytes (f16 bit patterns u * 2^-24).
+__device__ __forceinline__ uint2 widen4(uint32_t v) { return make_uint2(prmt2(v, 0u, 0x4140u), prmt2(v, 0u, 0x4342u)); }
 __device__ __forceinline__ void tmem_ld8(uint32_t taddr, uint32_t (&r)[8]) {
     asm volatile("tcgen05.ld.sync.aligned.32x32b.x8.b32 {%0,%1,%2,%3,%4,%5,%6,%7}, [%8];"
                  : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7])
                  : "r"(taddr));
 }
 
-// TPW = rows one fold warp takes (8, 16 or 32), DW = fold warps per lane quarter (1 or 2): the row
+// TPW = rows one fold warp takes (16 or 32), DW = fold warps per lane quarter (1 or 2): the row
 // tile of a CTA is TPW * DW rows.
 template <int BITS, int TPW, int DW>
 __global__ void __launch_bounds__(kLtThreads, 1) lowbit_tc_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant__ LowbitTcArgs p) {
     constexpr int NT = TPW * DW;                               // rows per CTA tile
     constexpr int ACC_STRIDE = NT < 32 ? 32 : NT;              // tensor-memory columns between accumulators
     constexpr int NACC = 512 / ACC_STRIDE;
-    constexpr int UPS = BITS == 2 ? 4 : 2;                     // packed units per slot and column group
+    constexpr int UPS = BITS == 2 ? 4 : 2;                     // packed units per slot and column group (512 depths)
+    constexpr int SPU = BITS == 2 ? 2 : 4;                     // stages per unit
     constexpr int KSLOT = 8 * UPS * kUnitBytes;                // bytes of a packed slot
     constexpr int BTILE = NT * 128;
     extern __shared__ unsigned char smem_dyn[];
@@ -88,12 +87,12 @@ __global__ void __launch_bounds__(kLtThreads, 1) lowbit_tc_kernel(const __grid_c
     constexpr int BSLOT = (BTILE + 1023) / 1024 * 1024;
     unsigned char* ring_k = ring_b + (size_t)kLtNB * BSLOT;                    // [NK][KSLOT]
     uint64_t* bars = reinterpret_cast<uint64_t*>(ring_k + (size_t)kLtNK * KSLOT);
-    uint64_t* a_full = bars;                      // [NA] operand written (256 arrivals)
+    uint64_t* a_full = bars;                      // [NA] operand written (the stage's two expand warps)
     uint64_t* a_empty = a_full + kLtNA;           // [NA] the stage's MMAs retired
     uint64_t* b_full = a_empty + kLtNA;           // [NB] row tile landed
     uint64_t* b_empty = b_full + kLtNB;           // [NB] the stage's MMAs retired
     uint64_t* k_full = b_empty + kLtNB;           // [NK] packed units landed
-    uint64_t* k_empty = k_full + kLtNK;           // [NK] the 8 expand warps are past the slot
+    uint64_t* k_empty = k_full + kLtNK;           // [NK] every stage of the slot has been expanded
     uint64_t* acc_full = k_empty + kLtNK;         // [NACC] a K-block's sums are complete
     uint64_t* acc_empty = acc_full + NACC;        // [NACC] ... and read by every fold warp
     uint64_t* f_full = acc_empty + NACC;          // [NF] fold operands of a K-block landed
@@ -107,15 +106,17 @@ __global__ void __launch_bounds__(kLtThreads, 1) lowbit_tc_kernel(const __grid_c
     const int col0 = blockIdx.x * 128, cg0 = blockIdx.x * 8;
     const int tok0 = blockIdx.y * NT;
     const int block = 1 << p.log2_block;
+    const int log2_run = min(p.log2_block, 8);                 // an accumulator sums a run of min(block, 256) depths
+    const int run = 1 << log2_run;
     // depths that belong to a real K-block and are staged (>= k: what lies past k multiplies zero activations)
     const int k_end = (int)min((long long)p.nb_real << p.log2_block, (long long)p.kq);
     const int stages = (k_end + kLtStage - 1) / kLtStage;
-    const int slots = (stages + 3) / 4;
+    const int slots = (stages + kLtSlotStages - 1) / kLtSlotStages;
 
     if (tid == 0) {
-        for (int s = 0; s < kLtNA; ++s) { mbar_init(&a_full[s], 256); mbar_init(&a_empty[s], 1); }
+        for (int s = 0; s < kLtNA; ++s) { mbar_init(&a_full[s], 2); mbar_init(&a_empty[s], 1); }
         for (int s = 0; s < kLtNB; ++s) { mbar_init(&b_full[s], 1); mbar_init(&b_empty[s], 1); }
-        for (int s = 0; s < kLtNK; ++s) { mbar_init(&k_full[s], 1); mbar_init(&k_empty[s], 8); }
+        for (int s = 0; s < kLtNK; ++s) { mbar_init(&k_full[s], 1); mbar_init(&k_empty[s], 2 * kLtSlotStages); }
         for (int s = 0; s < NACC; ++s) { mbar_init(&acc_full[s], 1); mbar_init(&acc_empty[s], 4 * DW); }
         for (int s = 0; s < kLtNF; ++s) { mbar_init(&f_full[s], 1); mbar_init(&f_empty[s], 4 * DW); }
         *abort_flag = 0;
@@ -138,7 +139,7 @@ __global__ void __launch_bounds__(kLtThreads, 1) lowbit_tc_kernel(const __grid_c
                 const int slot = i % kLtNB;
                 if (i >= kLtNB && !mbar_wait_poll(&b_empty[slot], ((i / kLtNB) - 1) & 1, abort_flag, p.status, STATUS_TMEM_TIMEOUT)) break;
                 mbar_expect_tx(&b_full[slot], (unsigned)BTILE);
-                tma_load_2d(ring_b + (size_t)slot * BSLOT, &tmap_q, i * kLtStage, tok0, &b_full[slot]);
+                tma_load_2d(ring_b + (size_t)slot * BSLOT, &tmap_q, i * kLtStage, tok0, &b_full[slot]);   // x in f16 elements
             }
         }
     } else if (warp == 18) {
@@ -163,10 +164,10 @@ __global__ void __launch_bounds__(kLtThreads, 1) lowbit_tc_kernel(const __grid_c
             const int fs = blk % kLtNF;
             if (blk >= kLtNF && !__all_sync(0xffffffffu, mbar_wait_poll(&f_empty[fs], ((blk / kLtNF) - 1) & 1, abort_flag, p.status, STATUS_TMEM_TIMEOUT))) break;
             unsigned char* dst = ring_f + (size_t)fs * FSLOT;
-            if (lane == 0) mbar_expect_tx(&f_full[fs], (unsigned)(NT * 4 * (BITS == 1 ? 2 : 1) + 8 * 32));
+            if (lane == 0) mbar_expect_tx(&f_full[fs], (unsigned)(NT * 8 + 8 * 32));
             __syncwarp();
             if (lane == 0) bulk_g2s(dst, p.sa_t + (size_t)blk * p.mpad + tok0, NT * 4, &f_full[fs]);
-            else if (lane == 1 && BITS == 1) bulk_g2s(dst + NT * 4, p.qsum_t + (size_t)blk * p.mpad + tok0, NT * 4, &f_full[fs]);
+            else if (lane == 1) bulk_g2s(dst + NT * 4, p.qsum_t + (size_t)blk * p.mpad + tok0, NT * 4, &f_full[fs]);
             else if (lane >= 2 && lane < 10) {
                 const size_t cgi = (size_t)min(cg0 + lane - 2, p.n16 - 1);
                 bulk_g2s(dst + NT * 8 + (lane - 2) * 32, p.scales + (cgi * p.nb + (size_t)blk) * 16, 32, &f_full[fs]);
@@ -175,7 +176,7 @@ __global__ void __launch_bounds__(kLtThreads, 1) lowbit_tc_kernel(const __grid_c
         }
     } else if (warp == 17) {
         // ===================== MMA issuer =====================
-        const uint32_t idesc = umma_idesc_i8(128, NT);
+        const uint32_t idesc = umma_idesc(0, 128, NT);
         for (int i = 0; i < stages; ++i) {
             const int as = i % kLtNA, bs = i % kLtNB;
             if (!__all_sync(0xffffffffu, mbar_wait_poll(&b_full[bs], (i / kLtNB) & 1, abort_flag, p.status, STATUS_TMEM_TIMEOUT))) break;
@@ -183,79 +184,88 @@ __global__ void __launch_bounds__(kLtThreads, 1) lowbit_tc_kernel(const __grid_c
             tc_fence_after();
             const uint64_t a_desc0 = umma_desc_sw128(smem_u32(ring_a + (size_t)as * kLtATile));
             const uint64_t b_desc0 = umma_desc_sw128(smem_u32(ring_b + (size_t)bs * BSLOT));
+            // the runs that begin in this stage take the next accumulators of the ring once the fold warps have read
+            // their last use: wait for those first, then issue the whole stage from one thread
             bool ok = true;
 #pragma unroll
-            for (int ks = 0; ks < kLtStage / 32; ++ks) {
-                const int depth = i * kLtStage + 32 * ks;
-                if (depth >= k_end) break;                                 // padding past the last real K-block
-                const int blk = depth >> p.log2_block, buf = blk % NACC;
-                const bool first = (depth & (block - 1)) == 0;
-                const bool last = ((depth + 32) & (block - 1)) == 0 || depth + 32 >= k_end;
-                // a new K-block takes the next accumulator of the ring once the fold warps have read its last use
-                if (first && blk >= NACC)
-                    ok = __all_sync(0xffffffffu, mbar_wait_poll(&acc_empty[buf], ((blk / NACC) - 1) & 1, abort_flag, p.status, STATUS_TMEM_TIMEOUT));
-                if (!ok) break;
-                tc_fence_after();
-                if (elect_one()) {
-                    umma_i8(tmem_base + (uint32_t)(buf * ACC_STRIDE), a_desc0 + 2 * ks, b_desc0 + 2 * ks, idesc, first ? 0u : 1u);
-                    if (last) umma_commit(&acc_full[buf]);
-                }
-                __syncwarp();
+            for (int ks = 0; ks < kLtStage / 16; ++ks) {
+                const int depth = i * kLtStage + 16 * ks;
+                const int ri = depth >> log2_run;
+                if (depth < k_end && (depth & (run - 1)) == 0 && ri >= NACC && ok)
+                    ok = __all_sync(0xffffffffu, mbar_wait_poll(&acc_empty[ri % NACC], ((ri / NACC) - 1) & 1, abort_flag, p.status, STATUS_TMEM_TIMEOUT));
             }
             if (!ok) break;
+            tc_fence_after();
             if (elect_one()) {
+#pragma unroll
+                for (int ks = 0; ks < kLtStage / 16; ++ks) {
+                    const int depth = i * kLtStage + 16 * ks;
+                    if (depth >= k_end) break;                             // padding past the last real K-block
+                    const int buf = (depth >> log2_run) % NACC;             // the accumulator of the depth's run
+                    const bool first = (depth & (run - 1)) == 0;
+                    const bool last = ((depth + 16) & (run - 1)) == 0 || depth + 16 >= k_end;
+                    umma_f16(tmem_base + (uint32_t)(buf * ACC_STRIDE), a_desc0 + 2 * ks, b_desc0 + 2 * ks, idesc, first ? 0u : 1u);
+                    if (last) umma_commit(&acc_full[buf]);
+                }
                 umma_commit(&a_empty[as]);
                 umma_commit(&b_empty[bs]);
             }
             __syncwarp();
         }
     } else if (warp < 8) {
-        // ===================== expand warps: warp = column group of the CTA =====================
+        // ===================== expand warps: four pairs of warps take the stages in turn =====================
+        // A warp's trip through one stage (waits, loads, expansion, stores, fence, arrival) is a chain of
+        // latencies several hundred cycles long however little it computes, so a stage is not spread over
+        // all eight warps: pair (stage % 4) expands it, each warp four column groups with independent
+        // instruction chains, and four stages are in flight at once.
         const int g = lane >> 2, t = lane & 3;
-        const int row_lo = 16 * warp + g, row_hi = row_lo + 8;
-        // 8 bytes (depths 8 t .. 8 t + 7 of a 32-deep step) land in chunk 2 * step + (t >> 1), half (t & 1)
-        const uint32_t off_lo = (uint32_t)((row_lo >> 3) * 1024 + (row_lo & 7) * 128 + 8 * (t & 1));
-        const uint32_t off_hi = (uint32_t)((row_hi >> 3) * 1024 + (row_hi & 7) * 128 + 8 * (t & 1));
-        const uint32_t sw_lo = (uint32_t)(row_lo & 7), sw_hi = (uint32_t)(row_hi & 7);
-        for (int i = 0; i < stages; ++i) {
-            const int gq = i >> 2, si = i & 3, ks_slot = gq % kLtNK, as = i % kLtNA;
-            const bool last_of_slot = si == 3 || i == stages - 1;
+        const int pair = warp >> 1, half = warp & 1;
+        for (int i = pair; i < stages; i += 4) {
+            const int gq = i / kLtSlotStages, si = i % kLtSlotStages, ks_slot = gq % kLtNK, as = i % kLtNA;
             if (i >= kLtNA && !__all_sync(0xffffffffu, mbar_wait_poll(&a_empty[as], ((i / kLtNA) - 1) & 1, abort_flag, p.status, STATUS_TMEM_TIMEOUT))) break;
             if (!__all_sync(0xffffffffu, mbar_wait_poll(&k_full[ks_slot], (gq / kLtNK) & 1, abort_flag, p.status, STATUS_TMEM_TIMEOUT))) break;
-            const unsigned char* pk = ring_k + (size_t)ks_slot * KSLOT + (size_t)warp * UPS * kUnitBytes;
             unsigned char* at = ring_a + (size_t)as * kLtATile;
-            uint32_t words[4];
-            if (BITS == 2) {
-                const uint4 wv = *reinterpret_cast<const uint4*>(pk + si * kUnitBytes + lane * 16);
-                words[0] = wv.x; words[1] = wv.y; words[2] = wv.z; words[3] = wv.w;
-            } else {
-                const uint2 wv = *reinterpret_cast<const uint2*>(pk + (si >> 1) * kUnitBytes + lane * 16 + 8 * (si & 1));
-                words[0] = wv.x; words[1] = wv.y; words[2] = 0; words[3] = 0;
-            }
+            const int h = si % SPU;                                            // 64-deep part of the unit
+            const unsigned char* pk = ring_k + (size_t)ks_slot * KSLOT + (si / SPU) * kUnitBytes + lane * 16;
+            uint4 wv[4];
 #pragma unroll
-            for (int s = 0; s < 4; ++s) {
-                // step s of the stage: 8 depths of columns g (lo) and g + 8 (hi)
-                uint2 lo, hi;
-                if (BITS == 2) {
-                    const uint32_t w = words[s];
-                    const uint32_t e = w & 0x33333333u, o = (w >> 2) & 0x33333333u;
-                    lo = make_uint2(prmt_cb(p.lut, e), prmt_cb(p.lut, e >> 16));
-                    hi = make_uint2(prmt_cb(p.lut, o), prmt_cb(p.lut, o >> 16));
-                } else {
-                    const uint32_t w = words[s >> 1];
-                    const int sh = 4 * (s & 1);
-                    lo = make_uint2((w >> (sh + 0)) & 0x01010101u, (w >> (sh + 2)) & 0x01010101u);
-                    hi = make_uint2((w >> (sh + 1)) & 0x01010101u, (w >> (sh + 3)) & 0x01010101u);
+            for (int cc = 0; cc < 4; ++cc) wv[cc] = *reinterpret_cast<const uint4*>(pk + (size_t)(4 * half + cc) * UPS * kUnitBytes);
+#pragma unroll
+            for (int cc = 0; cc < 4; ++cc) {
+                const int row_lo = 16 * (4 * half + cc) + g, row_hi = row_lo + 8;
+                // 8 depths (16 bytes) of a 32-deep step land in chunk 4 * step + t of the row
+                const uint32_t off_lo = (uint32_t)((row_lo >> 3) * 1024 + (row_lo & 7) * 128);
+                const uint32_t off_hi = (uint32_t)((row_hi >> 3) * 1024 + (row_hi & 7) * 128);
+                const uint32_t sw_lo = (uint32_t)(row_lo & 7), sw_hi = (uint32_t)(row_hi & 7);
+                // 2-bit: words 2 h, 2 h + 1 (32 depths each); 1-bit: word h (its two 4-bit halves are the two steps)
+                const uint32_t w0 = BITS == 2 ? (h ? wv[cc].z : wv[cc].x) : (h == 0 ? wv[cc].x : (h == 1 ? wv[cc].y : (h == 2 ? wv[cc].z : wv[cc].w)));
+                const uint32_t w1 = h ? wv[cc].w : wv[cc].y;
+#pragma unroll
+                for (int s = 0; s < 2; ++s) {
+                    // 32-deep step s of the stage: depths 8 t .. 8 t + 7 of columns g (lo) and g + 8 (hi)
+                    uint32_t lo03, lo47, hi03, hi47;                           // four bytes each: u of depths +0..3 / +4..7
+                    if (BITS == 2) {
+                        const uint32_t w = s ? w1 : w0;
+                        const uint32_t e = w & 0x33333333u, o = (w >> 2) & 0x33333333u;
+                        lo03 = prmt2(p.lut, 0u, e); lo47 = prmt2(p.lut, 0u, e >> 16);
+                        hi03 = prmt2(p.lut, 0u, o); hi47 = prmt2(p.lut, 0u, o >> 16);
+                    } else {
+                        const uint32_t w = w0;
+                        const int sh = 4 * s;
+                        lo03 = (w >> (sh + 0)) & 0x01010101u; lo47 = (w >> (sh + 2)) & 0x01010101u;
+                        hi03 = (w >> (sh + 1)) & 0x01010101u; hi47 = (w >> (sh + 3)) & 0x01010101u;
+                    }
+                    const uint2 l0 = widen4(lo03), l1 = widen4(lo47), h0 = widen4(hi03), h1 = widen4(hi47);
+                    const uint32_t chunk = (uint32_t)(4 * s + t);
+                    *reinterpret_cast<uint4*>(at + off_lo + ((chunk ^ sw_lo) << 4)) = make_uint4(l0.x, l0.y, l1.x, l1.y);
+                    *reinterpret_cast<uint4*>(at + off_hi + ((chunk ^ sw_hi) << 4)) = make_uint4(h0.x, h0.y, h1.x, h1.y);
                 }
-                const uint32_t chunk = (uint32_t)(2 * s + (t >> 1));
-                *reinterpret_cast<uint2*>(at + off_lo + ((chunk ^ sw_lo) << 4)) = lo;
-                *reinterpret_cast<uint2*>(at + off_hi + ((chunk ^ sw_hi) << 4)) = hi;
             }
             fence_proxy_async();
-            mbar_arrive(&a_full[as]);
-            if (last_of_slot) {
-                __syncwarp();
-                if (lane == 0) mbar_arrive(&k_empty[ks_slot]);
+            __syncwarp();
+            if (lane == 0) {
+                mbar_arrive(&a_full[as]);
+                mbar_arrive(&k_empty[ks_slot]);        // one arrival per warp and stage: a full slot collects 16
             }
         }
     } else if (warp < 16) {
@@ -271,41 +281,54 @@ __global__ void __launch_bounds__(kLtThreads, 1) lowbit_tc_kernel(const __grid_c
 #pragma unroll
             for (int j = 0; j < TPW; ++j) tot[j] = 0.0f;
             bool ok = true;
-            for (int blk = 0; blk < p.nb_real; ++blk) {
-                const int buf = blk % NACC, fs = blk % kLtNF;
-                ok = mbar_wait_poll(&f_full[fs], (blk / kLtNF) & 1, abort_flag, p.status, STATUS_TMEM_TIMEOUT) &&
-                     mbar_wait_poll(&acc_full[buf], (blk / NACC) & 1, abort_flag, p.status, STATUS_TMEM_TIMEOUT);
+            const int rpb = block >> log2_run;                              // runs per K-block
+            int ri = 0;                                                     // run counter
+            for (int blk = 0; blk < p.nb_real && ok; ++blk) {
+                const int fs = blk % kLtNF;
+                int sblk[TPW];                                              // the block's integer sums
+#pragma unroll
+                for (int j = 0; j < TPW; ++j) sblk[j] = 0;
+                // runs of this block that hold staged depths
+                const int runs = min(rpb, (k_end - (blk << p.log2_block) + run - 1) >> log2_run);
+                for (int rr = 0; rr < runs; ++rr, ++ri) {
+                    const int buf = ri % NACC;
+                    ok = mbar_wait_poll(&acc_full[buf], (ri / NACC) & 1, abort_flag, p.status, STATUS_TMEM_TIMEOUT);
+                    if (!__all_sync(0xffffffffu, ok)) { ok = false; break; }
+                    tc_fence_after();
+#pragma unroll
+                    for (int j0 = 0; j0 < TPW; j0 += 8) {
+                        uint32_t r[8];
+                        tmem_ld8(lane_base + (uint32_t)(buf * ACC_STRIDE + j0), r);
+                        tmem_ld_wait();
+                        // the accumulator holds (sum of u * q) * 2^-24 exactly
+#pragma unroll
+                        for (int j = 0; j < 8; ++j) sblk[j0 + j] += __float2int_rn(__uint_as_float(r[j]) * 16777216.0f);
+                    }
+                    // the accumulator is in registers: hand it back to the MMA warp
+                    tc_fence_before();
+                    __syncwarp();
+                    if (lane == 0) mbar_arrive(&acc_empty[buf]);
+                }
+                if (!ok) break;
+                ok = mbar_wait_poll(&f_full[fs], (blk / kLtNF) & 1, abort_flag, p.status, STATUS_TMEM_TIMEOUT);
                 if (!__all_sync(0xffffffffu, ok)) { ok = false; break; }
-                tc_fence_after();
                 const unsigned char* fo = ring_f + (size_t)fs * FSLOT;
                 const float scale = __half2float(__ushort_as_half(*reinterpret_cast<const uint16_t*>(fo + sc_off)));
                 const float* sa = reinterpret_cast<const float*>(fo) + part * TPW;
                 const int* qs = reinterpret_cast<const int*>(fo + NT * 4) + part * TPW;
 #pragma unroll
-                for (int j0 = 0; j0 < TPW; j0 += 8) {
-                    uint32_t r[8];
-                    tmem_ld8(lane_base + (uint32_t)(buf * ACC_STRIDE + j0), r);
-                    tmem_ld_wait();
-                    if (j0 + 8 >= TPW) {
-                        // the accumulator is in registers: hand it back to the MMA warp
-                        tc_fence_before();
-                        __syncwarp();
-                        if (lane == 0) mbar_arrive(&acc_empty[buf]);
-                    }
-                    const float4 s0 = *reinterpret_cast<const float4*>(sa + j0), s1 = *reinterpret_cast<const float4*>(sa + j0 + 4);
-                    const float sv[8] = {s0.x, s0.y, s0.z, s0.w, s1.x, s1.y, s1.z, s1.w};
-                    int qv[8] = {0, 0, 0, 0, 0, 0, 0, 0};
-                    if (BITS == 1) {
-                        const int4 q0 = *reinterpret_cast<const int4*>(qs + j0), q1 = *reinterpret_cast<const int4*>(qs + j0 + 4);
-                        qv[0] = q0.x; qv[1] = q0.y; qv[2] = q0.z; qv[3] = q0.w; qv[4] = q1.x; qv[5] = q1.y; qv[6] = q1.z; qv[7] = q1.w;
-                    }
+                for (int j0 = 0; j0 < TPW; j0 += 4) {
+                    const float4 s0 = *reinterpret_cast<const float4*>(sa + j0);
+                    const int4 q0 = *reinterpret_cast<const int4*>(qs + j0);
+                    const float sv[4] = {s0.x, s0.y, s0.z, s0.w};
+                    const int qv[4] = {q0.x, q0.y, q0.z, q0.w};
 #pragma unroll
-                    for (int j = 0; j < 8; ++j) {
-                        int s = (int)r[j];
-                        if (BITS == 1) s = 2 * s - qv[j];
+                    for (int j = 0; j < 4; ++j) {
+                        // 1-bit: u is the sign bit, value = 2 u - 1; 2-bit: u = value + 128
+                        const int sum = BITS == 1 ? 2 * sblk[j0 + j] - qv[j] : sblk[j0 + j] - 128 * qv[j];
                         if (p.sums_out && col < p.n && row0 + j0 + j < p.m)
-                            p.sums_out[((size_t)(row0 + j0 + j) * p.n + col) * p.nb_real + blk] = s;
-                        tot[j0 + j] = fmaf((float)s, __fmul_rn(scale, sv[j]), tot[j0 + j]);
+                            p.sums_out[((size_t)(row0 + j0 + j) * p.n + col) * p.nb_real + blk] = sum;
+                        tot[j0 + j] = fmaf((float)sum, __fmul_rn(scale, sv[j]), tot[j0 + j]);
                     }
                 }
                 __syncwarp();
@@ -347,20 +370,21 @@ cudaError_t launch_lt(const CUtensorMap& tm, const LowbitTcArgs& a, dim3 grid, s
 
 bool lowbit_tc_supported(int bits, int m, int k, int log2_block) {
     if (bits != 1 && bits != 2) return false;
-    if (m < 1 || k < 1 || log2_block < 5) return false;           // an MMA step is 32 deep: K-blocks of 32 and up
+    if (m < 1 || k < 1 || log2_block < 4) return false;           // an MMA step is 16 deep: K-blocks of 16 and up
     return tensor_map_encoder() != nullptr;
 }
 
-int lowbit_tc_row_tile(int m) { return m <= 8 ? 8 : (m <= 16 ? 16 : (m <= 32 ? 32 : 64)); }
+// an MMA of 128 weight columns takes 16 rows or more
+int lowbit_tc_row_tile(int m) { return m <= 16 ? 16 : (m <= 32 ? 32 : 64); }
 
 cudaError_t lowbit_tc_launch(LowbitTcArgs a, cudaStream_t stream) {
     const int nt = lowbit_tc_row_tile(a.m);
     CUtensorMap tm;
     const cuuint64_t gdim[2] = {(cuuint64_t)a.kq, (cuuint64_t)a.m};
-    const cuuint64_t gstride[1] = {(cuuint64_t)a.kq};
+    const cuuint64_t gstride[1] = {(cuuint64_t)a.kq * 2};
     const cuuint32_t box[2] = {(cuuint32_t)kLtStage, (cuuint32_t)nt};
     const cuuint32_t estr[2] = {1, 1};
-    CUresult r = tensor_map_encoder()(&tm, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, (void*)a.q, gdim, gstride, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+    CUresult r = tensor_map_encoder()(&tm, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, (void*)a.qh, gdim, gstride, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
                                       CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
     if (r != CUDA_SUCCESS) return cudaErrorInvalidValue;
     const int ups = a.bits == 2 ? 4 : 2;
@@ -370,7 +394,6 @@ cudaError_t lowbit_tc_launch(LowbitTcArgs a, cudaStream_t stream) {
     const dim3 grid((a.n + 127) / 128, (a.m + nt - 1) / nt);
 #define SMEG_LT(B)                                                                     \
     if (a.bits == B) {                                                                 \
-        if (nt == 8) return launch_lt<B, 8, 1>(tm, a, grid, smem, stream);             \
         if (nt == 16) return launch_lt<B, 16, 1>(tm, a, grid, smem, stream);           \
         if (nt == 32) return launch_lt<B, 16, 2>(tm, a, grid, smem, stream);           \
         return launch_lt<B, 32, 2>(tm, a, grid, smem, stream);                         \
