@@ -213,6 +213,15 @@ int smeg_act_f16_dev(uint16_t *dst, const uint16_t *src, size_t len, uint32_t ac
 int smeg_f32_to_f16_dev(uint16_t *dst, const float *src, size_t len, void *stream);
 int smeg_f16_to_f32_dev(float *dst, const uint16_t *src, size_t len, void *stream);
 
+/* Norm::forward on f32 rows into f16 (y16) and / or f32 (y32) rows: layer_norm (rms == 0) or rms_norm
+ * (src/nn.rs:73-161, norm_row :126-153; replaces neon_norm_row_f16 / _f32, csrc/sme_gemm_api.h:221-224).
+ * weight: dim f32; bias: dim f32 or NULL.  The step before the MLP in Block::accumulate (src/block.rs:96-105). */
+int smeg_norm_rows_dev(uint16_t *y16, float *y32, const float *x, const float *weight, const float *bias,
+                       size_t rows, size_t dim, float eps, int rms, void *stream);
+/* rms_scales (src/nn.rs:234-248): out[i] = f16(1 / sqrt(mean(x_i^2) + eps)) per k-wide f16 row -- the leading
+ * MulRow operand of a Linear whose RMS-norm weight was folded into it (src/linear.rs:305-308, 452-457). */
+int smeg_rms_scales_dev(uint16_t *out, const uint16_t *x, size_t rows, size_t k, float eps, void *stream);
+
 /* ---- compute, host pointers, handle based ------------------------------------ */
 
 int smeg_matmul_q4_f16(const smeg_q4 *w, const uint16_t *a, uint16_t *c, size_t m, const ep_desc16 *ep);
@@ -303,6 +312,9 @@ int gemm_sme_f16f16_q2(size_t m, size_t n, size_t k, uint16_t *dst, const uint16
 /* csrc/sme_gemm_api.h:216-220 (host pointers) */
 void neon_glu_f16(uint16_t *out, const uint16_t *in, size_t m, size_t n, uint32_t act);
 void neon_add_f16_to_f32(float *dst, const uint16_t *src, size_t n);
+void neon_act_f16(uint16_t *dst, const uint16_t *src, size_t n, uint32_t act);
+void neon_f32_to_f16(uint16_t *dst, const float *src, size_t n);
+void neon_f16_to_f32(float *dst, const uint16_t *src, size_t n);
 /* Drops the device copy cached for a packed array (call from the weights' Drop). */
 void smeg_forget(const void *packed);
 

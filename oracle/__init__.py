@@ -261,6 +261,29 @@ def add_f16(src, dst) -> None:
     lib().orc_add_f16(_p(src), _p(dst), C.c_size_t(src.size))
 
 
+def norm_rows(x, weight, bias, eps: float, rms: bool):
+    """layer_norm / rms_norm (src/nn.rs:73-161) over every row: (f16 bits, f32) outputs."""
+    x = np.ascontiguousarray(x, np.float32)
+    weight = np.ascontiguousarray(weight, np.float32)
+    dim = weight.size
+    rows = x.size // dim
+    b = None if bias is None else np.ascontiguousarray(bias, np.float32)
+    y16 = np.zeros((rows, dim), np.uint16)
+    y32 = np.zeros((rows, dim), np.float32)
+    lib().orc_norm_rows(_p(x), _p(weight), _p(b) if b is not None else None, C.c_float(eps), C.c_int(1 if rms else 0),
+                        C.c_size_t(rows), C.c_size_t(dim), _p(y16), _p(y32))
+    return y16, y32
+
+
+def rms_scales(x, k: int, eps: float) -> np.ndarray:
+    """rms_scales (src/nn.rs:234-248): f16 bits of 1 / sqrt(mean(x_i^2) + eps) per k-wide row of f16 x."""
+    x = _u16(x)
+    rows = x.size // k
+    out = np.zeros(rows, np.uint16)
+    lib().orc_rms_scales(_p(x), C.c_size_t(rows), C.c_size_t(k), C.c_float(eps), _p(out))
+    return out
+
+
 def interleave(g, u, n, k) -> np.ndarray:
     """g, u: k x n row-major (InOut) arrays of one dtype -> k x 2n."""
     g, u = np.ascontiguousarray(g), np.ascontiguousarray(u)

@@ -651,6 +651,66 @@ void orc_add_f16(const uint16_t *src, float *dst, size_t len) {
     for (size_t i = 0; i < len; i++) dst[i] += orc_f16_to_f32(src[i]);
 }
 
+/* lane_sum, src/nn.rs:20-32: eight running sums over whole groups of eight, their sum
+ * (in index order) plus the tail's sum.  sq: sum of (x - mean)^2, else of x. */
+static float orc_lane_sum(const float *x, size_t n, float mean, int sq) {
+    float acc[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+    size_t whole = n / 8 * 8;
+    for (size_t i = 0; i < whole; i += 8)
+        for (int l = 0; l < 8; l++) {
+            float v = x[i + l];
+            acc[l] += sq ? (v - mean) * (v - mean) : v;
+        }
+    float tail = 0.0f;
+    for (size_t i = whole; i < n; i++) {
+        float v = x[i];
+        tail += sq ? (v - mean) * (v - mean) : v;
+    }
+    float sum = 0.0f;
+    for (int l = 0; l < 8; l++) sum += acc[l];
+    return sum + tail;
+}
+
+/* layer_norm / rms_norm rows, portable arm of norm_row (src/nn.rs:126-153), f32 in, rounded to
+ * f16 (y16) and / or kept as f32 (y32): (v - mean) * r * w + b with r = 1 / sqrt(ss / dim + eps). */
+void orc_norm_rows(const float *x, const float *weight, const float *bias, float eps, int rms, size_t rows,
+                   size_t dim, uint16_t *y16, float *y32) {
+    for (size_t i = 0; i < rows; i++) {
+        const float *xr = x + i * dim;
+        float fdim = (float)dim;
+        float mean = rms ? 0.0f : orc_lane_sum(xr, dim, 0.0f, 0) / fdim;
+        float r = 1.0f / sqrtf(orc_lane_sum(xr, dim, mean, 1) / fdim + eps);
+        for (size_t j = 0; j < dim; j++) {
+            float o = (xr[j] - mean) * r * weight[j] + (bias ? bias[j] : 0.0f);
+            if (y16) y16[i * dim + j] = orc_f32_to_f16(o);
+            if (y32) y32[i * dim + j] = o;
+        }
+    }
+}
+
+/* rms_scales, src/nn.rs:234-248: out[i] = f16(1 / sqrt(mean(x_i^2) + eps)) per k-wide f16 row. */
+void orc_rms_scales(const uint16_t *x, size_t rows, size_t k, float eps, uint16_t *out) {
+    for (size_t i = 0; i < rows; i++) {
+        const uint16_t *xr = x + i * k;
+        float acc[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+        size_t whole = k / 8 * 8;
+        for (size_t d = 0; d < whole; d += 8)
+            for (int l = 0; l < 8; l++) {
+                float v = orc_f16_to_f32(xr[d + l]);
+                acc[l] += v * v;
+            }
+        float tail = 0.0f;
+        for (size_t d = whole; d < k; d++) {
+            float v = orc_f16_to_f32(xr[d]);
+            tail += v * v;
+        }
+        float sum = 0.0f;
+        for (int l = 0; l < 8; l++) sum += acc[l];
+        float ms = (sum + tail) / (float)k;
+        out[i] = orc_f32_to_f16(1.0f / sqrtf(ms + eps));
+    }
+}
+
 /* interleave(), src/linear.rs:603-617: [gate | up] as k x 2n row-major,
  * 32 gate columns then 32 up columns per chunk.  g, u: k x n row-major
  * (InOut).  Generic over element size `es` bytes. */

@@ -88,6 +88,8 @@ SIGNATURES = {
     "smeg_act_f16_dev": (_i, [_vp, _vp, _sz, _u32, _vp]),
     "smeg_f32_to_f16_dev": (_i, [_vp, _vp, _sz, _vp]),
     "smeg_f16_to_f32_dev": (_i, [_vp, _vp, _sz, _vp]),
+    "smeg_norm_rows_dev": (_i, [_vp, _vp, _vp, _vp, _vp, _sz, _sz, C.c_float, _i, _vp]),
+    "smeg_rms_scales_dev": (_i, [_vp, _vp, _sz, _sz, C.c_float, _vp]),
     "smeg_matmul_q4_f16": (_i, [_vp, _vp, _vp, _sz, _epp]),
     "smeg_matmul_q4_bf16": (_i, [_vp, _vp, _vp, _sz, _epp]),
     "smeg_matmul_lowbit": (_i, [_vp, _vp, _vp, _sz, _epp]),
@@ -113,6 +115,9 @@ SIGNATURES = {
     "gemm_sme_f16f16_q2": (_i, [_sz, _sz, _sz, _vp, _vp, _vp, _vp, _vp, _sz, _epp]),
     "neon_glu_f16": (None, [_vp, _vp, _sz, _sz, _u32]),
     "neon_add_f16_to_f32": (None, [_vp, _vp, _sz]),
+    "neon_act_f16": (None, [_vp, _vp, _sz, _u32]),
+    "neon_f32_to_f16": (None, [_vp, _vp, _sz]),
+    "neon_f16_to_f32": (None, [_vp, _vp, _sz]),
     "smeg_forget": (None, [_vp]),
 }
 

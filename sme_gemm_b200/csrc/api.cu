@@ -466,6 +466,7 @@ int smeg_q1_from_band(const uint8_t* signs, const uint16_t* scales, size_t n, si
 void smeg_lowbit_destroy(smeg_lowbit* w) {
     if (!w) return;
     smeg_q4_destroy(w->twin.load());
+    smeg_dense_destroy(w->twin_dense.load());
     if (w->codes) cudaFree(w->codes);
     if (w->scales) cudaFree(w->scales);
     delete w;
@@ -764,8 +765,46 @@ static int lowbit_twin(const smeg_lowbit* w, const smeg_q4** out) {
     return 0;
 }
 
+static bool lowbit_needs_dense_twin(const smeg_lowbit* w) {
+    if (w->bits != 2) return false;
+    for (int i = 0; i < 4; ++i)
+        if (w->codebook[i] < -8 || w->codebook[i] > 7) return true;
+    return false;
+}
+
+// The dense f16 twin (see transcode.cu), built once under the handle's lock like the 4-bit one.
+static int lowbit_twin_dense(const smeg_lowbit* w, const smeg_dense** out) {
+    smeg_dense* t = w->twin_dense.load(std::memory_order_acquire);
+    if (t) { *out = t; return 0; }
+    std::lock_guard<std::mutex> lock(w->twin_lock);
+    t = w->twin_dense.load(std::memory_order_acquire);
+    if (t) { *out = t; return 0; }
+    if (!dev_state()) return -5;
+    smeg_dense* h = new smeg_dense();
+    h->n = w->d.n; h->k = w->d.k; h->kd = (w->d.k + 7) / 8 * 8; h->bf16 = 0;
+    const size_t elems = h->n * h->kd;
+    if (cudaMalloc(&h->w, (elems ? elems : 8) * 2) != cudaSuccess) { smeg_dense_destroy(h); return -2; }
+    LowbitToQ4Args a;
+    memset(&a, 0, sizeof(a));
+    a.src = w->codes; a.src_scales = w->scales; a.n = w->d.n; a.k = w->d.k;
+    a.ku_src = w->d.ku; a.n16_src = w->d.n16; a.nb_src = w->d.nb; a.bits = w->bits; a.lut = w->lut;
+    cudaStream_t s = nullptr;
+    if (cudaStreamCreateWithFlags(&s, cudaStreamNonBlocking) != cudaSuccess) { smeg_dense_destroy(h); return -2; }
+    cudaError_t e = lowbit_to_dense_launch(a, h->w, h->kd, w->d.log2_block, s);
+    if (e == cudaSuccess) e = cudaStreamSynchronize(s);
+    cudaStreamDestroy(s);
+    if (e != cudaSuccess) { smeg_dense_destroy(h); return -6; }
+    w->twin_dense.store(h, std::memory_order_release);
+    *out = h;
+    return 0;
+}
+
 int smeg_lowbit_prepare_f16(const smeg_lowbit* w) {
     if (!w) return -4;
+    if (lowbit_needs_dense_twin(w)) {
+        const smeg_dense* d = nullptr;
+        return lowbit_twin_dense(w, &d);
+    }
     const smeg_q4* t = nullptr;
     return lowbit_twin(w, &t);
 }
@@ -774,6 +813,12 @@ int smeg_matmul_lowbit_f16_dev(const smeg_lowbit* w, const uint16_t* a, uint16_t
                                void* stream) {
     if (!w) return -4;
     if (m == 0 || w->d.n == 0) return 0;
+    if (lowbit_needs_dense_twin(w)) {
+        const smeg_dense* d = nullptr;
+        const int rc = lowbit_twin_dense(w, &d);
+        if (rc) return rc;
+        return smeg_gemm_dense_dev(d, a, c, m, 0x3c00 /* beta = 1 */, 0, ep, stream);
+    }
     const smeg_q4* t = nullptr;
     const int rc = lowbit_twin(w, &t);
     if (rc) return rc;
@@ -811,21 +856,34 @@ int smeg_gemm_dense_dev(const smeg_dense* w, const uint16_t* a, uint16_t* c, siz
     const size_t n = w->n, k = w->k;
     if (m == 0 || n == 0) return 0;
     if (!c || (k && !a) || m > 0x7fffffffu || n > 0x7fffffffu || k > 0x7fffffffu) return -4;
-    // the token tile travels by TMA: rows of 16-byte multiples at a 16-byte aligned base
-    if (k == 0 || k % 8 != 0 || ((uintptr_t)a & 15) != 0) return -3;
     DeviceState* ds = dev_state();
     if (!ds) return -5;
-    if (!gemm_tc_supported(16, (int)m, (int)k, 5, a)) return -3;
+    if (k == 0) {
+        // an empty depth: C = ep(T(0)) (the reference's k == 0 product is all zeros)
+        return -3;
+    }
+    // the token tile travels by TMA: rows of 16-byte multiples at a 16-byte aligned base.  Any other A is
+    // staged through a zero-padded copy [m][kd] (the weights are already padded to kd along K)
+    uint16_t* a_pad = nullptr;
+    if (k % 8 != 0 || ((uintptr_t)a & 15) != 0) {
+        if (cudaMallocAsync(&a_pad, m * w->kd * 2, stream) != cudaSuccess) return -2;
+        cudaError_t ce = cudaMemsetAsync(a_pad, 0, m * w->kd * 2, stream);
+        if (ce == cudaSuccess) ce = cudaMemcpy2DAsync(a_pad, w->kd * 2, a, k * 2, k * 2, m, cudaMemcpyDeviceToDevice, stream);
+        if (ce != cudaSuccess) { cudaFreeAsync(a_pad, stream); return -6; }
+    }
+    const uint16_t* a_run = a_pad ? a_pad : a;
+    const size_t k_run = a_pad ? w->kd : k;
+    if (!gemm_tc_supported(16, (int)m, (int)k_run, 5, a_run)) { if (a_pad) cudaFreeAsync(a_pad, stream); return -3; }
     GemmTcArgs t;
     memset(&t, 0, sizeof(t));
     EpNodeDev* ext = nullptr;
     int rc = make_ep(ep, n, &t.ep, stream, &ext);
-    if (rc) { if (ext) cudaFreeAsync(ext, stream); return rc; }
-    t.wdense = w->w; t.kd = (int)w->kd; t.a = a; t.c = c;
+    if (rc) { if (ext) cudaFreeAsync(ext, stream); if (a_pad) cudaFreeAsync(a_pad, stream); return rc; }
+    t.wdense = w->w; t.kd = (int)w->kd; t.a = a_run; t.c = c;
     t.beta = w->bf16 ? __uint_as_float_host((uint32_t)beta_bits << 16) : h2f(beta_bits);
     t.col_major = col_major ? 1 : 0;
-    t.m = (int)m; t.n = (int)n; t.k = (int)k;
-    t.n16 = (int)((n + 15) / 16); t.ku = (int)((k + 63) / 64); t.nb = 0; t.log2_block = 5;
+    t.m = (int)m; t.n = (int)n; t.k = (int)k_run;
+    t.n16 = (int)((n + 15) / 16); t.ku = (int)((k_run + 63) / 64); t.nb = 0; t.log2_block = 5;
     t.status = ds->status;
     dim3 grid;
     size_t smem = 0, ws_floats = 0, ncounters = 0;
@@ -833,12 +891,14 @@ int smeg_gemm_dense_dev(const smeg_dense* w, const uint16_t* a, uint16_t* c, siz
     TcScratch sc;
     if (ws_floats && tc_scratch(stream, ws_floats, ncounters, &sc)) {
         if (ext) cudaFreeAsync(ext, stream);
+        if (a_pad) cudaFreeAsync(a_pad, stream);
         return -2;
     }
     t.ws = sc.ws;
     t.counters = sc.counters;
     cudaError_t e = gemm_tc_launch(t, w->bf16, grid, smem, stream);
     if (ext) cudaFreeAsync(ext, stream);
+    if (a_pad) cudaFreeAsync(a_pad, stream);
     return e == cudaSuccess ? 0 : -6;
 }
 
@@ -854,6 +914,19 @@ int smeg_act_f16_dev(uint16_t* dst, const uint16_t* src, size_t len, uint32_t ac
 }
 int smeg_f32_to_f16_dev(uint16_t* dst, const float* src, size_t len, void* stream) {
     return f32_to_f16_launch(dst, src, len, (cudaStream_t)stream) == cudaSuccess ? 0 : -6;
+}
+int smeg_norm_rows_dev(uint16_t* y16, float* y32, const float* x, const float* weight, const float* bias, size_t rows, size_t dim,
+                       float eps, int rms, void* stream) {
+    if (rows == 0 || dim == 0) return 0;
+    if ((!y16 && !y32) || !x || !weight || rows > 0x7fffffffu) return -4;
+    if (!dev_state()) return -5;
+    return norm_rows_launch(y16, y32, x, weight, bias, rows, dim, eps, rms ? 1 : 0, (cudaStream_t)stream) == cudaSuccess ? 0 : -6;
+}
+int smeg_rms_scales_dev(uint16_t* out, const uint16_t* x, size_t rows, size_t k, float eps, void* stream) {
+    if (rows == 0) return 0;
+    if (!out || !x || k == 0 || rows > 0x7fffffffu) return -4;
+    if (!dev_state()) return -5;
+    return rms_scales_launch(out, x, rows, k, eps, (cudaStream_t)stream) == cudaSuccess ? 0 : -6;
 }
 int smeg_f16_to_f32_dev(float* dst, const uint16_t* src, size_t len, void* stream) {
     return f16_to_f32_launch(dst, src, len, (cudaStream_t)stream) == cudaSuccess ? 0 : -6;
@@ -1157,6 +1230,30 @@ void neon_glu_f16(uint16_t* out, const uint16_t* in, size_t m, size_t n, uint32_
     if (cudaMemcpy(di.p, in, m * 2 * n * 2, cudaMemcpyHostToDevice) != cudaSuccess) return;
     if (glu_launch((uint16_t*)dout.p, (const uint16_t*)di.p, m, n, act, 0) != cudaSuccess) return;
     cudaMemcpy(out, dout.p, m * n * 2, cudaMemcpyDeviceToHost);
+}
+void neon_act_f16(uint16_t* dst, const uint16_t* src, size_t n, uint32_t act) {
+    if (n == 0 || !dev_state()) return;
+    DevBuf dd, dsrc;
+    if (dd.alloc(n * 2) || dsrc.alloc(n * 2)) return;
+    if (cudaMemcpy(dsrc.p, src, n * 2, cudaMemcpyHostToDevice) != cudaSuccess) return;
+    if (act_f16_launch((uint16_t*)dd.p, (const uint16_t*)dsrc.p, n, act, 0) != cudaSuccess) return;
+    cudaMemcpy(dst, dd.p, n * 2, cudaMemcpyDeviceToHost);
+}
+void neon_f32_to_f16(uint16_t* dst, const float* src, size_t n) {
+    if (n == 0 || !dev_state()) return;
+    DevBuf dd, dsrc;
+    if (dd.alloc(n * 2) || dsrc.alloc(n * 4)) return;
+    if (cudaMemcpy(dsrc.p, src, n * 4, cudaMemcpyHostToDevice) != cudaSuccess) return;
+    if (f32_to_f16_launch((uint16_t*)dd.p, (const float*)dsrc.p, n, 0) != cudaSuccess) return;
+    cudaMemcpy(dst, dd.p, n * 2, cudaMemcpyDeviceToHost);
+}
+void neon_f16_to_f32(float* dst, const uint16_t* src, size_t n) {
+    if (n == 0 || !dev_state()) return;
+    DevBuf dd, dsrc;
+    if (dd.alloc(n * 4) || dsrc.alloc(n * 2)) return;
+    if (cudaMemcpy(dsrc.p, src, n * 2, cudaMemcpyHostToDevice) != cudaSuccess) return;
+    if (f16_to_f32_launch((float*)dd.p, (const uint16_t*)dsrc.p, n, 0) != cudaSuccess) return;
+    cudaMemcpy(dst, dd.p, n * 4, cudaMemcpyDeviceToHost);
 }
 void neon_add_f16_to_f32(float* dst, const uint16_t* src, size_t n) {
     if (n == 0 || !dev_state()) return;

@@ -40,6 +40,18 @@ namespace smeg {
 
 namespace {
 
+// Position in a ring of n slots, advanced once per use: slot index, parity of the current round, first round or not.
+// (The ring depths are run-time values: computing slot and round from the stage number costs an integer division each,
+// and the role loops are latency chains of one warp -- every instruction in them is on the critical path.)
+struct RingPos {
+    int slot = 0;
+    unsigned phase = 0;
+    bool wrapped = false;
+    __device__ __forceinline__ void next(int n) {
+        if (++slot == n) { slot = 0; phase ^= 1u; wrapped = true; }
+    }
+};
+
 constexpr int kDeqWarps = 16;                    // dequant warps (the first 8 also drain tensor memory)
 constexpr int kTcThreads = 32 * (kDeqWarps + 3);   // + token producer, MMA issuer, packed-weight producer
 constexpr int kStageK = 64;                       // depths per stage (one 128-byte swizzle row)
@@ -195,9 +207,10 @@ __global__ void __launch_bounds__(kTcThreads, 1) gemm_tc_kernel(const __grid_con
     if (warp == kDeqWarps) {
         // ===================== token producer =====================
         if (lane == 0) {
-            for (int i = 0; i < num_stages; ++i) {
-                const int slot = i % NT;
-                if (i >= NT && !mbar_wait(&t_empty[slot], ((i / NT) - 1) & 1, abort_flag, p.status, STATUS_TMEM_TIMEOUT)) break;
+            RingPos tp;
+            for (int i = 0; i < num_stages; ++i, tp.next(NT)) {
+                const int slot = tp.slot;
+                if (tp.wrapped && !mbar_wait(&t_empty[slot], tp.phase ^ 1u, abort_flag, p.status, STATUS_TMEM_TIMEOUT)) break;
                 unsigned char* sb = ring_t + (size_t)slot * t_stride;
                 const int u0 = (st_begin + i) * US;
                 const int units = min(US, p.ku - u0);
@@ -218,9 +231,10 @@ __global__ void __launch_bounds__(kTcThreads, 1) gemm_tc_kernel(const __grid_con
             // dense 16-bit weights need no expansion: their K-major tiles go straight into the operand ring
             if (lane == 0) {
                 tma_prefetch_desc(&maps.w);
-                for (int i = 0; i < num_stages; ++i) {
-                    const int os = i % O;
-                    if (i >= O && !mbar_wait(&o_empty[os], ((i / O) - 1) & 1, abort_flag, p.status, STATUS_TMEM_TIMEOUT)) break;
+                RingPos op;
+                for (int i = 0; i < num_stages; ++i, op.next(O)) {
+                    const int os = op.slot;
+                    if (op.wrapped && !mbar_wait(&o_empty[os], op.phase ^ 1u, abort_flag, p.status, STATUS_TMEM_TIMEOUT)) break;
                     unsigned char* ob = ring_o + (size_t)os * o_stride;
                     const int u0 = (st_begin + i) * US;
                     const int units = min(US, p.ku - u0);
@@ -231,9 +245,10 @@ __global__ void __launch_bounds__(kTcThreads, 1) gemm_tc_kernel(const __grid_con
                 }
             }
         } else
-        for (int gq = 0; gq < num_groups; ++gq) {
-            const int slot = gq % NK;
-            if (gq >= NK && !__all_sync(0xffffffffu, mbar_wait(&k_empty[slot], ((gq / NK) - 1) & 1, abort_flag, p.status, STATUS_TMEM_TIMEOUT))) break;
+        RingPos kp;
+        for (int gq = 0; gq < num_groups; ++gq, kp.next(NK)) {
+            const int slot = kp.slot;
+            if (kp.wrapped && !__all_sync(0xffffffffu, mbar_wait(&k_empty[slot], kp.phase ^ 1u, abort_flag, p.status, STATUS_TMEM_TIMEOUT))) break;
             unsigned char* sb = ring_k + (size_t)slot * k_stride;
             const int u0 = (st_begin + gq * PU) * US;                   // first 64-deep unit of the slot
             const int units = min(PU * US, min(st_end * US, p.ku) - u0);
@@ -258,10 +273,11 @@ __global__ void __launch_bounds__(kTcThreads, 1) gemm_tc_kernel(const __grid_con
         // the whole warp walks the stages (converged); one elected lane issues
         const uint32_t idesc = umma_idesc(BF16, 128, p.ntok_box);
         const uint32_t tok_half = (uint32_t)(tok_bytes / 2);
-        for (int i = 0; i < num_stages; ++i) {
-            const int ts = i % NT, os = i % O;
-            if (!__all_sync(0xffffffffu, mbar_wait(&t_full[ts], (i / NT) & 1, abort_flag, p.status, STATUS_TMEM_TIMEOUT))) break;
-            if (!__all_sync(0xffffffffu, mbar_wait(&o_full[os], (i / O) & 1, abort_flag, p.status, STATUS_TMEM_TIMEOUT))) break;
+        RingPos tq, oq;
+        for (int i = 0; i < num_stages; ++i, tq.next(NT), oq.next(O)) {
+            const int ts = tq.slot, os = oq.slot;
+            if (!__all_sync(0xffffffffu, mbar_wait(&t_full[ts], tq.phase, abort_flag, p.status, STATUS_TMEM_TIMEOUT))) break;
+            if (!__all_sync(0xffffffffu, mbar_wait(&o_full[os], oq.phase, abort_flag, p.status, STATUS_TMEM_TIMEOUT))) break;
             tc_fence_after();
             const uint32_t tok_addr = smem_u32(ring_t + (size_t)ts * t_stride);
             const uint32_t w_addr = smem_u32(ring_o + (size_t)os * o_stride);
@@ -291,10 +307,12 @@ __global__ void __launch_bounds__(kTcThreads, 1) gemm_tc_kernel(const __grid_con
     } else {
         // ===================== dequant warps (0..15), then epilogue =====================
         const int g = lane >> 2, t = lane & 3;
-        const int wig = warp % deq_wpg;                        // warp within its group
-        for (int i = 0; i < (dense ? 0 : num_stages); ++i) {
-            const int gq = i / PU, ks = gq % NK;
-            const bool last_of_slot = (i % PU == PU - 1) || (i == num_stages - 1);
+        const int wig = deq_groups == 2 ? (warp & 7) : warp;   // warp within its group
+        RingPos dk, dq;                                        // packed ring (advanced once per PU stages), operand ring
+        int iu = 0;                                            // stage within its packed slot
+        for (int i = 0; i < (dense ? 0 : num_stages); ++i, dq.next(O), (++iu == PU ? (iu = 0, dk.next(NK)) : (void)0)) {
+            const int ks = dk.slot;
+            const bool last_of_slot = (iu == PU - 1) || (i == num_stages - 1);
             if (deq_groups == 2 && (i & 1) != (warp >> 3)) {
                 // not this group's stage; a warp that walks past the end of a packed slot still releases it
                 if (last_of_slot) {
@@ -303,13 +321,13 @@ __global__ void __launch_bounds__(kTcThreads, 1) gemm_tc_kernel(const __grid_con
                 }
                 continue;
             }
-            const int os = i % O;
-            if (i >= O && !__all_sync(0xffffffffu, mbar_wait(&o_empty[os], ((i / O) - 1) & 1, abort_flag, p.status, STATUS_TMEM_TIMEOUT))) break;
-            if (!__all_sync(0xffffffffu, mbar_wait(&k_full[ks], (gq / NK) & 1, abort_flag, p.status, STATUS_TMEM_TIMEOUT))) break;
-            const int uq = (i % PU) * US;                           // first unit of the stage within the packed slot
+            const int os = dq.slot;
+            if (dq.wrapped && !__all_sync(0xffffffffu, mbar_wait(&o_empty[os], dq.phase ^ 1u, abort_flag, p.status, STATUS_TMEM_TIMEOUT))) break;
+            if (!__all_sync(0xffffffffu, mbar_wait(&k_full[ks], dk.phase, abort_flag, p.status, STATUS_TMEM_TIMEOUT))) break;
+            const int uq = iu * US;                                 // first unit of the stage within the packed slot
             const int u0 = (st_begin + i) * US;                     // first unit of the stage
             const int units = min(US, p.ku - u0);
-            const int blk0 = ((st_begin + gq * PU) * US * kStageK) >> p.log2_block;   // first scale row of the slot
+            const int blk0 = ((st_begin + i - iu) * US * kStageK) >> p.log2_block;    // first scale row of the slot
             const unsigned char* pk = ring_k + (size_t)ks * k_stride;
             const uint16_t* scs = reinterpret_cast<const uint16_t*>(pk + (size_t)8 * NW * k_code);
             unsigned char* ob = ring_o + (size_t)os * o_stride;

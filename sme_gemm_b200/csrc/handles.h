@@ -14,6 +14,7 @@ struct smeg_q4 {
     uint16_t* scales = nullptr;       // device: f16 scale rows
     size_t code_bytes = 0, scale_elems = 0;
 };
+struct smeg_dense;
 struct smeg_lowbit {
     smeg::PackedDims d;
     int bits = 0;                     // 2 or 1
@@ -25,6 +26,8 @@ struct smeg_lowbit {
     // 4-bit twin for the f16 tensor-core path, built on the first such call (transcode.cu)
     mutable std::mutex twin_lock;
     mutable std::atomic<smeg_q4*> twin{nullptr};
+    // dense f16 twin instead, for a 2-bit codebook with a value outside [-8, 7]
+    mutable std::atomic<smeg_dense*> twin_dense{nullptr};
 };
 // Dense 16-bit weights for the Gemm builder: W[n][kd], K-major, kd = k padded to a multiple of 8.
 struct smeg_dense {

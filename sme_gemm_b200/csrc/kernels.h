@@ -177,6 +177,8 @@ struct LowbitToQ4Args {
     uint32_t lut;                   // 2-bit codebook, byte c = value of code c
 };
 cudaError_t lowbit_to_q4_launch(const LowbitToQ4Args& a, cudaStream_t s);
+// Dense K-major f16 weights W[n][kd] of a 2-bit / 1-bit set (for codebooks the 4-bit plane cannot hold).
+cudaError_t lowbit_to_dense_launch(const LowbitToQ4Args& a, uint16_t* dst, size_t kd, int log2_block, cudaStream_t s);
 
 // ---- element-wise model ops (elementwise.cu) ----
 cudaError_t glu_launch(uint16_t* out, const uint16_t* both, size_t m, size_t n, uint32_t act, cudaStream_t s);
@@ -184,6 +186,9 @@ cudaError_t add_f16_to_f32_launch(float* dst, const uint16_t* src, size_t n, cud
 cudaError_t act_f16_launch(uint16_t* dst, const uint16_t* src, size_t n, uint32_t act, cudaStream_t s);
 cudaError_t f32_to_f16_launch(uint16_t* dst, const float* src, size_t n, cudaStream_t s);
 cudaError_t f16_to_f32_launch(float* dst, const uint16_t* src, size_t n, cudaStream_t s);
+cudaError_t norm_rows_launch(uint16_t* y16, float* y32, const float* x, const float* weight, const float* bias, size_t rows, size_t dim,
+                             float eps, int rms, cudaStream_t s);
+cudaError_t rms_scales_launch(uint16_t* out, const uint16_t* x, size_t rows, size_t k, float eps, cudaStream_t s);
 cudaError_t round_add_f32_launch(float* y, const float* partial_sum, size_t n, cudaStream_t s);
 
 // ---- tensor-parallel sum + f16 rounding + residual add over peer memory (tp_reduce.cu) ----

@@ -63,7 +63,41 @@ __global__ void lowbit_scales_to_q4_kernel(LowbitToQ4Args p) {
     p.dst_scales[idx] = v;
 }
 
+// A 2-bit codebook with a value outside [-8, 7] has no 4-bit twin: its weights are written out as the dense
+// K-major f16 matrix W[n][kd] the tensor-core GEMM takes directly, each f16(scale * value) -- the eager
+// dequant of the reference's fallback arm (prepack_f16(Codes::dequant()), src/kernels/lowbit/matmul.rs:347-349).
+// One thread per weight.
+__global__ void lowbit_to_dense_kernel(LowbitToQ4Args p, uint16_t* dst, size_t kd, int log2_block) {
+    const size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (idx >= p.n * kd) return;
+    const size_t j = idx / kd, d = idx % kd;
+    uint16_t out = 0;
+    if (d < p.k) {
+        size_t wb;
+        int f;
+        int value;
+        if (p.bits == 2) {
+            q2_locate(d, j, p.ku_src, &wb, &f);
+            const uint32_t w = *reinterpret_cast<const uint32_t*>(p.src + wb);
+            value = (int)(int8_t)((p.lut >> (8 * ((w >> (2 * f)) & 3u))) & 0xffu);
+        } else {
+            q1_locate(d, j, p.ku_src, &wb, &f);
+            const uint32_t w = *reinterpret_cast<const uint32_t*>(p.src + wb);
+            value = ((w >> f) & 1u) ? 1 : -1;
+        }
+        const float s = __half2float(__ushort_as_half(p.src_scales[((j / 16) * p.nb_src + (d >> log2_block)) * 16 + scale_slot((int)(j % 16))]));
+        out = __half_as_ushort(__float2half_rn(__fmul_rn(s, (float)value)));   // the f32 product is exact: one rounding
+    }
+    dst[idx] = out;
+}
+
 }  // namespace
+
+cudaError_t lowbit_to_dense_launch(const LowbitToQ4Args& a, uint16_t* dst, size_t kd, int log2_block, cudaStream_t s) {
+    const size_t total = a.n * kd;
+    if (total) lowbit_to_dense_kernel<<<(unsigned)((total + 255) / 256), 256, 0, s>>>(a, dst, kd, log2_block);
+    return cudaGetLastError();
+}
 
 cudaError_t lowbit_to_q4_launch(const LowbitToQ4Args& a, cudaStream_t s) {
     if (a.dst_words) lowbit_to_q4_kernel<<<(unsigned)((a.dst_words + 255) / 256), 256, 0, s>>>(a);

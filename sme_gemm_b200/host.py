@@ -724,29 +724,115 @@ def interleave_gate_up(g, u, layout: WeightLayout, n: int, k: int) -> np.ndarray
 
 
 class Linear:
-    """A Q4 projection with an optional bias applied as a leading AddCol
-    (Linear, src/linear.rs:133-155,440-463; Q4 arm only)."""
+    """A projection on Q4, 2-bit, 1-bit or dense f16 weights with an optional bias (a leading AddCol) and an optional
+    folded RMS norm of its input (a leading MulRow of rms_scales) -- Linear, src/linear.rs:133-155, 440-463; kernel
+    routing by rows as run_ep, src/linear.rs:535-552.
 
-    def __init__(self, q4: Q4Weights, bias=None):
-        self.q4, self.bias = q4, bias
+    The reference switches Q4 from its GEMV to the f16 panel at PANEL_ROWS = 8 rows and opted-in low-bit weights to
+    the f16 MOPA path at LOWBIT_MOPA_ROWS = 64 (measured on M5).  Here the Q4 switch between the decode kernels and
+    the tensor-core GEMM sits inside the library (17 rows on B200); the low-bit opt-in keeps the reference's constant."""
+
+    PANEL_ROWS = 8
+    LOWBIT_MOPA_ROWS = 64
+
+    def __init__(self, q4: "Q4Weights | None" = None, bias=None, *, q2: "Q2Weights | None" = None,
+                 q1: "Q1Weights | None" = None, f16: "Packed | None" = None):
+        given = [w for w in (q4, q2, q1, f16) if w is not None]
+        assert len(given) == 1, "a Linear holds exactly one weight set"
+        self.q4, self.q2, self.q1, self.f16, self.bias = q4, q2, q1, f16, bias
+        self.mopa = False
+        self.rms_eps = None
 
     @staticmethod
     def quantize(w, layout: WeightLayout, n: int, k: int, p: Q4Params | None = None, bias=None) -> "Linear":
         return Linear(Q4Weights.quantize(w, layout, n, k, p), bias)
 
+    @staticmethod
+    def from_q4(q4: Q4Weights, bias=None) -> "Linear":
+        return Linear(q4, bias)
+
+    @staticmethod
+    def from_q2(q2: Q2Weights, bias=None) -> "Linear":
+        """Linear::from_q2, src/linear.rs:214."""
+        return Linear(None, bias, q2=q2)
+
+    @staticmethod
+    def from_q1(q1: Q1Weights, bias=None) -> "Linear":
+        """Linear::from_q1, src/linear.rs:234."""
+        return Linear(None, bias, q1=q1)
+
+    @staticmethod
+    def from_f16(packed: "Packed", bias=None) -> "Linear":
+        assert packed.dtype == "f16"
+        return Linear(None, bias, f16=packed)
+
+    def lowbit_mopa(self, on: bool = True) -> "Linear":
+        """Opt 2-bit / 1-bit weights into the f16 tensor-core path from LOWBIT_MOPA_ROWS rows (Linear::lowbit_mopa)."""
+        self.mopa = bool(on)
+        return self
+
+    def rms_norm_input(self, eps: float) -> "Linear":
+        """The layer computes rms_norm(x) @ W for weights whose rows were scaled by the norm's gamma beforehand
+        (WeightLayout::scale_inputs): the per-row 1 / rms rides as a leading MulRow (src/linear.rs:305-308, 452-457)."""
+        self.rms_eps = float(eps)
+        return self
+
+    def _w(self):
+        return self.q4 or self.q2 or self.q1 or self.f16
+
     def n(self) -> int:
-        return self.q4.n()
+        w = self._w()
+        return w.n if isinstance(w, Packed) else w.n()
 
     def k(self) -> int:
-        return self.q4.k()
+        w = self._w()
+        return w.k if isinstance(w, Packed) else w.k()
+
+    def _lead(self, x, m: int):
+        """with_lead, src/linear.rs:440-463: the RMS row scale of x, then the bias."""
+        if self.rms_eps is None and self.bias is None:
+            return None
+        lead = Epilogue()
+        if self.rms_eps is not None:
+            k = self.k()
+            assert _numel(x) == m * k, "x is m*k"
+            if _is_torch(x):
+                r = torch.empty(m, dtype=torch.float16, device=x.device)
+                check("smeg_rms_scales_dev", lib().smeg_rms_scales_dev(_ptr(r), _ptr(x), m, k, self.rms_eps, _stream()))
+            else:
+                xd = torch.from_numpy(np.ascontiguousarray(_np_bits(x, "x")).view(np.float16)).cuda()
+                rd = torch.empty(m, dtype=torch.float16, device="cuda")
+                check("smeg_rms_scales_dev", lib().smeg_rms_scales_dev(_ptr(rd), _ptr(xd), m, k, self.rms_eps, _stream()))
+                r = rd.cpu().numpy()
+            lead = lead.mul_row(r)
+        if self.bias is not None:
+            lead = lead.add_col(self.bias)
+        return lead
 
     def forward_ep(self, x, y, m: int, ep: Epilogue | None = None) -> None:
-        if self.bias is not None:
-            ep = (ep or Epilogue()).with_leading(Epilogue().add_col(self.bias))
-        _run_q4(x, self.q4, y, m, ep, False)
+        lead = self._lead(x, m)
+        if lead is not None:
+            ep = (ep or Epilogue()).with_leading(lead)
+        if self.q4 is not None:
+            _run_q4(x, self.q4, y, m, ep, False)
+        elif self.f16 is not None:
+            g = Gemm(x, self.f16, m)
+            if ep is not None:
+                g._ep = ep
+            g.run(y)
+        else:
+            w = self.q2 if self.q2 is not None else self.q1
+            _run_lowbit(x, w, y, m, ep, mopa=self.mopa and m >= Linear.LOWBIT_MOPA_ROWS)
 
     def forward(self, x, y, m: int) -> None:
         self.forward_ep(x, y, m, None)
+
+    def accumulate(self, x, y, m: int) -> None:
+        """y (f32) += f32(forward(x)) -- Linear::accumulate, src/linear.rs:425-432.  Device tensors."""
+        assert _is_torch(x) and _numel(y) == m * self.n(), "y is m*n"
+        out = torch.empty((m, self.n()), dtype=torch.float16, device=x.device)
+        self.forward(x, out, m)
+        check("smeg_add_f16_to_f32_dev", lib().smeg_add_f16_to_f32_dev(_ptr(y), _ptr(out), m * self.n(), _stream()))
 
 
 class GatedLinear:
@@ -760,6 +846,11 @@ class GatedLinear:
     def quantize(w_gate, w_up, layout: WeightLayout, n: int, k: int, gate: Gate, p: Q4Params | None = None):
         w = interleave_gate_up(np.asarray(w_gate, np.float32), np.asarray(w_up, np.float32), layout, n, k)
         return GatedLinear(Linear.quantize(w, WeightLayout.InOut, 2 * n, k, p), gate)
+
+    @staticmethod
+    def from_q1(gate: Q1Weights, up: Q1Weights, act: Gate) -> "GatedLinear":
+        """GatedLinear::from_q1, src/linear.rs:686: 1-bit gate and up projections as one interleaved layer."""
+        return GatedLinear(Linear.from_q1(Q1Weights.interleave(gate, up)), act)
 
     def n(self) -> int:
         return self.inner.n() // 2
@@ -781,21 +872,32 @@ class GatedLinear:
 
 
 class Mlp:
-    """y += down(act(x @ W_gate) * (x @ W_up)) (Mlp::gated / accumulate,
-    src/mlp.rs:80-146)."""
+    """y += down(act(up(x))) (Mlp::new) or y += down(act(x @ W_gate) * (x @ W_up)) (Mlp::gated); accumulate,
+    src/mlp.rs:67-146.  The gated Q4 form without biases or folded norms runs as one library call (fused kernels
+    above 64 rows); every other form runs its layers one after the other exactly as the reference's three-call path."""
 
-    def __init__(self, up: GatedLinear, down: Linear):
+    def __init__(self, up, down: Linear, act: "Gate | None" = None):
+        gated = isinstance(up, GatedLinear)
         assert down.k() == up.n(), "down takes up's outputs"
-        assert up.inner.bias is None and down.bias is None
-        self.up, self.down = up, down
-        h = C.c_void_p()
-        check("smeg_mlp_create", lib().smeg_mlp_create(up.inner.q4._h, down.q4._h, int(up.gate), C.byref(h)))
-        self._h = h
+        assert gated or act is not None, "a plain MLP names its activation"
+        self.up, self.down, self.act = up, down, act
+        self._h = None
+        inner = up.inner if gated else None
+        if (gated and inner.q4 is not None and down.q4 is not None and inner.bias is None and down.bias is None
+                and inner.rms_eps is None and down.rms_eps is None):
+            h = C.c_void_p()
+            check("smeg_mlp_create", lib().smeg_mlp_create(inner.q4._h, down.q4._h, int(up.gate), C.byref(h)))
+            self._h = h
 
     def __del__(self):
         h, self._h = getattr(self, "_h", None), None
         if h:
             lib().smeg_mlp_destroy(h)
+
+    @staticmethod
+    def new(up: Linear, act: Gate, down: Linear) -> "Mlp":
+        """Mlp::new, src/mlp.rs:67: the plain MLP of GPT-2, y += down(act(up(x)))."""
+        return Mlp(up, down, act)
 
     @staticmethod
     def gated(up: GatedLinear, down: Linear) -> "Mlp":
@@ -813,16 +915,28 @@ class Mlp:
     def accumulate(self, x, y, m: int) -> None:
         assert _numel(x) == m * self.k(), "x is m*k"
         assert _numel(y) == m * self.n(), "y is m*n"
-        if _is_torch(x):
-            assert x.dtype == torch.float16 and y.dtype == torch.float32 and x.is_contiguous() and y.is_contiguous()
-            check("smeg_mlp_accumulate_dev", lib().smeg_mlp_accumulate_dev(self._h, _ptr(x), _ptr(y), m, _stream()))
+        if self._h is not None:
+            if _is_torch(x):
+                assert x.dtype == torch.float16 and y.dtype == torch.float32 and x.is_contiguous() and y.is_contiguous()
+                check("smeg_mlp_accumulate_dev", lib().smeg_mlp_accumulate_dev(self._h, _ptr(x), _ptr(y), m, _stream()))
+            else:
+                xb = _np_bits(x, "x")
+                assert y.dtype == np.float32 and y.flags.c_contiguous
+                check("smeg_mlp_accumulate", lib().smeg_mlp_accumulate(self._h, _ptr(xb), _ptr(y), m))
+            return
+        # the three-call path of src/mlp.rs:133-146 on device tensors
+        assert _is_torch(x) and x.dtype == torch.float16 and y.dtype == torch.float32
+        hid = torch.empty((m, self.hidden()), dtype=torch.float16, device=x.device)
+        if isinstance(self.up, GatedLinear):
+            self.up.forward(x, hid, m)
         else:
-            xb = _np_bits(x, "x")
-            assert y.dtype == np.float32 and y.flags.c_contiguous
-            check("smeg_mlp_accumulate", lib().smeg_mlp_accumulate(self._h, _ptr(xb), _ptr(y), m))
+            ep = Epilogue().gelu() if self.act == Gate.Gelu else Epilogue().silu()
+            self.up.forward_ep(x, hid, m, ep)
+        self.down.accumulate(hid, y, m)
 
     def partial(self, x, partial, m: int) -> None:
         """This rank's f32 partial sums of the down projection (tensor parallel)."""
+        assert self._h is not None, "the tensor-parallel halves exist for the gated Q4 block"
         assert _is_torch(x) and partial.dtype == torch.float32 and partial.numel() == m * self.n()
         check("smeg_mlp_partial_dev", lib().smeg_mlp_partial_dev(self._h, _ptr(x), _ptr(partial), m, _stream()))
 
@@ -830,6 +944,61 @@ class Mlp:
     def finish(y, total) -> None:
         """y += f32(f16(total)): the f16 store of the down projection, then the residual add."""
         check("smeg_mlp_finish_dev", lib().smeg_mlp_finish_dev(_ptr(y), _ptr(total), y.numel(), _stream()))
+
+
+class Norm:
+    """A norm layer with its parameters: layer_norm (Norm::layer) or rms_norm (Norm::rms), src/nn.rs:163-230.
+    forward takes f32 rows on the device and writes f16 (or f32) rows."""
+
+    def __init__(self, weight, bias, eps: float, rms: bool):
+        w = np.ascontiguousarray(weight, np.float32)
+        assert w.size > 0, "a norm needs at least one feature"
+        if bias is not None:
+            assert np.asarray(bias).size == w.size, "bias holds weight.len() values"
+        self.weight = torch.from_numpy(w).cuda()
+        self.bias = None if bias is None else torch.from_numpy(np.ascontiguousarray(bias, np.float32)).cuda()
+        self.eps, self.is_rms = float(eps), bool(rms)
+
+    @staticmethod
+    def layer(weight, bias, eps: float) -> "Norm":
+        return Norm(weight, bias, eps, False)
+
+    @staticmethod
+    def rms(weight, eps: float) -> "Norm":
+        return Norm(weight, None, eps, True)
+
+    def width(self) -> int:
+        return self.weight.numel()
+
+    def forward(self, x, y) -> None:
+        dim = self.width()
+        assert _is_torch(x) and x.dtype == torch.float32 and x.numel() % dim == 0, "x holds whole rows of weight.len()"
+        assert y.numel() == x.numel(), "y is the same shape as x"
+        y16 = _ptr(y) if y.dtype == torch.float16 else None
+        y32 = _ptr(y) if y.dtype == torch.float32 else None
+        assert y16 or y32
+        check("smeg_norm_rows_dev", lib().smeg_norm_rows_dev(y16, y32, _ptr(x), _ptr(self.weight), _ptr(self.bias), x.numel() // dim,
+                                                             dim, self.eps, int(self.is_rms), _stream()))
+
+
+class Block:
+    """The MLP half of a pre-norm transformer layer: x += mlp(norm2(x)) (Block::accumulate, src/block.rs:96-105, its
+    last two lines).  The attention half (norm1, SelfAttention, the KV cache) is not part of this library: a caller
+    runs it and then this."""
+
+    def __init__(self, norm2: Norm, mlp: Mlp):
+        d = norm2.width()
+        assert mlp.k() == d and mlp.n() == d, "the norms, attention and MLP share the residual's width"
+        self.norm2, self.mlp = norm2, mlp
+
+    def width(self) -> int:
+        return self.norm2.width()
+
+    def accumulate(self, x, rows: int) -> None:
+        assert _is_torch(x) and x.dtype == torch.float32 and x.numel() == rows * self.width(), "x is rows * width"
+        h = torch.empty((rows, self.width()), dtype=torch.float16, device=x.device)
+        self.norm2.forward(x, h)
+        self.mlp.accumulate(h, x, rows)
 
 
 def last_status() -> int:

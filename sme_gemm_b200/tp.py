@@ -54,7 +54,7 @@ class PeerReduce:
         # two buffers, taken in turn from step to step (the one-shot form of the kernel needs that); each holds
         # the f32 partial sums followed by the f16 results the owners of the other slices write back
         self._len = m * d
-        self._stride = self._len + self._len // 2             # floats per buffer (len % 4 == 0)
+        self._stride = (self._len + self._len // 2 + 3) // 4 * 4   # floats per buffer, a whole number of 16-byte vectors
         self._both = symm.empty((2, self._stride), dtype=torch.float32, device=dev)
         self.flags = symm.empty((FLAG_WORDS,), dtype=torch.int32, device=dev)
         self.flags.zero_()

@@ -75,7 +75,18 @@ def test_host_pointer_entry_and_unsupported_depth():
     sg.Gemm.new(a.view(np.float16).reshape(m, k), w, m).relu().run(c)
     want = orc.apply_ep(orc.gemm16(a, b, m, n, k), m, n, orc.Nodes([(8, 1, 0.0, None, 0)]))
     assert max_rel(c.astype(np.float32), orc.f16_bits_to_f32(want).reshape(m, n)) <= 1e-2
-    # a depth that is not a multiple of 8 cannot travel by TMA: reported, never computed elsewhere
-    w2 = sg.prepack_f16(b[: 60 * n], n, 60)
-    with pytest.raises(sg.SmegError):
-        sg.Gemm.new(torch.zeros((m, 60), dtype=torch.float16, device="cuda"), w2, m).run(torch.zeros((m, n), dtype=torch.float16, device="cuda"))
+
+
+@pytest.mark.parametrize("m,n,k", [(5, 48, 60), (3, 130, 37), (70, 200, 513)])
+def test_ragged_depth_runs_through_a_padded_copy(m, n, k):
+    """Gemm::run takes any k (src/exec/builder.rs:803-813): a depth that is not a multiple of 8, or an A that is not
+    16-byte aligned, is staged through a zero-padded copy on the device."""
+    a, b, _ = _case(m, n, k, False, 9)
+    w = sg.prepack_f16(b, n, k)
+    ad = torch.from_numpy(a.view(np.float16).reshape(m, k).copy()).cuda()
+    c = torch.zeros((m, n), dtype=torch.float16, device="cuda")
+    sg.Gemm.new(ad, w, m).relu().run(c)
+    torch.cuda.synchronize()
+    want = orc.apply_ep(orc.gemm16(a, b, m, n, k), m, n, orc.Nodes([(8, 1, 0.0, None, 0)]))
+    assert max_rel(c.float().cpu().numpy(), orc.f16_bits_to_f32(want).reshape(m, n)) <= 1e-2
+    assert sg.last_status() == 0

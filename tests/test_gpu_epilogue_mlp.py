@@ -253,3 +253,83 @@ def test_concurrent_host_threads_share_weights_bit_identically():
     [t.join() for t in th]
     assert not errs and len(results) == 16
     assert all(np.array_equal(r.view(np.uint16), base.view(np.uint16)) for r in results)
+
+
+def test_converts_and_activation_passes_device_and_host_entries():
+    """neon_f32_to_f16 / neon_f16_to_f32 / neon_act_f16 (csrc/sme_gemm_api.h:216-220; convert::to_f16,
+    src/convert.rs:12-35): the device entries and the host-pointer drop-ins against the oracle's conversions and
+    its scalar activation (the epilogue's ACT node on an identity product)."""
+    import ctypes as C
+    L = sg.lib()
+    rng = np.random.default_rng(41)
+    n = 5003
+    x = (rng.standard_normal(n) * 3.0).astype(np.float32)
+    x[:4] = [0.0, -0.0, 65520.0, 1e-8]
+    want16 = orc.f32_to_f16_bits(x)
+    # device entries
+    xd = torch.from_numpy(x).cuda()
+    h = torch.zeros(n, dtype=torch.float16, device="cuda")
+    s = torch.cuda.current_stream().cuda_stream
+    assert L.smeg_f32_to_f16_dev(h.data_ptr(), xd.data_ptr(), n, s) == 0
+    assert np.array_equal(bits_of(h), want16)
+    back = torch.zeros(n, dtype=torch.float32, device="cuda")
+    assert L.smeg_f16_to_f32_dev(back.data_ptr(), h.data_ptr(), n, s) == 0
+    assert np.array_equal(back.cpu().numpy().view(np.uint32), orc.f16_bits_to_f32(want16).view(np.uint32))
+    # host drop-ins
+    out16 = np.zeros(n, np.uint16)
+    L.neon_f32_to_f16(out16.ctypes.data, x.ctypes.data, n)
+    assert np.array_equal(out16, want16)
+    out32 = np.zeros(n, np.float32)
+    L.neon_f16_to_f32(out32.ctypes.data, want16.ctypes.data, n)
+    assert np.array_equal(out32.view(np.uint32), orc.f16_bits_to_f32(want16).view(np.uint32))
+    for kind in (1, 2, 3, 4, 5):
+        small = orc.f32_to_f16_bits((rng.standard_normal(n) * 2.0).astype(np.float32))
+        want = orc.apply_ep(small.reshape(1, n), 1, n, orc.Nodes([(8, kind, 0.0, None, 0)])).reshape(-1)
+        got_h = np.zeros(n, np.uint16)
+        L.neon_act_f16(got_h.ctypes.data, small.ctypes.data, n, kind)
+        got_d = torch.zeros(n, dtype=torch.float16, device="cuda")
+        assert L.smeg_act_f16_dev(got_d.data_ptr(), f16_bits_dev(small).data_ptr(), n, kind, s) == 0
+        assert np.array_equal(bits_of(got_d), got_h)
+        g32, w32 = orc.f16_bits_to_f32(got_h), orc.f16_bits_to_f32(want)
+        err = np.abs(g32 - w32) - (np.abs(w32) * 2.0 ** -9 + 1e-6)
+        assert (err <= 0).all(), (kind, float(err.max()), g32[err > 0][:4], w32[err > 0][:4])
+
+
+def test_concurrent_host_threads_on_shapes_that_grow_the_scratch():
+    """Host threads calling shapes with different scratch needs on one stream (the streaming decode kernel's shares and
+    counters, the depth-split GEMM's partial tiles): a block that is outgrown stays valid for the launch that read its
+    address, and every result equals the quiet run's bits (tests/concurrency.rs:130-180)."""
+    import threading
+    rng = np.random.default_rng(77)
+    cases = []
+    for (m, n, k) in ((1, 4096, 2048), (5, 9216, 4096), (40, 256, 8192), (1, 12288, 4096), (33, 512, 4096)):
+        q, s = q4_logical(rng, n, k, 32, from_f32=False)
+        w = sg.Q4Weights.new(q, s, n, k)
+        a = f16_bits_dev(orc.f32_to_f16_bits(rng.standard_normal((m, k)).astype(np.float32)))
+        c = torch.zeros((m, n), dtype=torch.float16, device="cuda")
+        sg.matmul_q4(a, w, c, m)
+        torch.cuda.synchronize()
+        cases.append((m, w, a, bits_of(c).copy()))
+    errors = []
+
+    def worker(order):
+        try:
+            torch.cuda.set_device(0)
+            for rep in range(3):
+                for ci in order:
+                    m, w, a, want = cases[ci]
+                    c = torch.zeros((m, w.n()), dtype=torch.float16, device="cuda")
+                    sg.matmul_q4(a, w, c, m)
+                    torch.cuda.synchronize()
+                    if not np.array_equal(bits_of(c), want):
+                        errors.append((ci, rep))
+        except Exception as e:      # pragma: no cover
+            errors.append(repr(e))
+
+    threads = [threading.Thread(target=worker, args=(o,)) for o in ([0, 1, 2, 3, 4], [4, 3, 2, 1, 0], [2, 0, 4, 1, 3], [1, 3, 0, 2, 4])]
+    for t in threads:
+        t.start()
+    for t in threads:
+        t.join()
+    assert not errors, errors[:5]
+    assert sg.last_status() == 0

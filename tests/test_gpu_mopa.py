@@ -59,14 +59,10 @@ def test_mopa_matches_eager_dequant(si):
             ep = None if ei == 0 else sg.Epilogue("f16").add_col(bias).silu()
             nodes = None if ei == 0 else orc.Nodes([(4, 0, 0.0, bias_f.view(np.uint16), 0), (8, 3, 0.0, None, 0)])
             what = f"{m}x{n}x{k} block {block} ep {ei}"
-            if max(book) <= 7 and min(book) >= -8:
-                want = _want(a_bits, 2, codes, 1, scales, book, n, k, block, m, nodes)
-                _check((sg.matmul_q2_mopa, sg.matmul_q2_mopa_ep), q2, a_bits, m, n, k, ep, want, f"q2 {book} {what}")
-            else:
-                # a codebook value outside the 4-bit range has no twin on the f16 path
-                c = torch.zeros((m, n), dtype=torch.float16, device="cuda")
-                with pytest.raises(sg.SmegError):
-                    sg.matmul_q2_mopa(f16_bits_dev(a_bits).reshape(m, k), q2, c, m)
+            # values inside [-8, 7] run on the 4-bit twin, any other codebook (the reference's own third test
+            # codebook among them) on a dense f16 twin
+            want = _want(a_bits, 2, codes, 1, scales, book, n, k, block, m, nodes)
+            _check((sg.matmul_q2_mopa, sg.matmul_q2_mopa_ep), q2, a_bits, m, n, k, ep, want, f"q2 {book} {what}")
             want = _want(a_bits, 1, signs, 0, scales, None, n, k, block, m, nodes)
             _check((sg.matmul_q1_mopa, sg.matmul_q1_mopa_ep), q1, a_bits, m, n, k, ep, want, f"q1 {what}")
 
@@ -90,3 +86,25 @@ def test_mopa_twin_is_bit_identical_to_dequant():
     got[got == 0x8000] = 0
     want[want == 0x8000] = 0
     assert np.array_equal(got, want)
+
+
+def test_wide_codebook_twin_is_bit_identical_to_dequant():
+    """A codebook with values outside [-8, 7]: the dense f16 twin holds exactly Codes::dequant's weights
+    (one-hot activations: each output is a single weight), for a depth that is not a multiple of 8 as well."""
+    for (n, k, block) in ((48, 64, 16), (33, 52, 32)):
+        rng = np.random.default_rng(6)
+        codes = rng.integers(0, 256, (k * n + 3) // 4).astype(np.uint8)
+        nbk = -(-k // block)
+        scales = orc.f32_to_f16_bits(rng.uniform(-0.2, 0.2, n * nbk).astype(np.float32))
+        book = [-128, 127, 3, -7]
+        w = sg.Q2Weights.new(codes, scales, n, k, sg.Q2Params(block).with_codebook(book))
+        eye = torch.eye(k, dtype=torch.float16, device="cuda")
+        c = torch.zeros((k, n), dtype=torch.float16, device="cuda")
+        sg.matmul_q2_mopa(eye, w, c, k)
+        torch.cuda.synchronize()
+        assert sg.last_status() == 0
+        want = orc.lowbit_dequant(2, codes, 1, scales, book, n, k, block).reshape(k, n).copy()
+        got = bits_of(c).reshape(k, n).copy()
+        got[got == 0x8000] = 0
+        want[want == 0x8000] = 0
+        assert np.array_equal(got, want)

@@ -63,6 +63,66 @@ def test_peer_reduce_finish_equals_gathered_sum_bit_for_bit(tmp_path):
     assert "PEER_REDUCE_OK" in out.stdout, out.stdout[-2000:] + out.stderr[-2000:]
 
 
+WORKER_MLP = r'''
+import os, sys
+import numpy as np
+import torch, torch.distributed as dist
+sys.path.insert(0, os.getcwd())
+import sme_gemm_b200 as sg
+from sme_gemm_b200.tp import PeerReduce, TpMlp
+rank, world = int(os.environ["RANK"]), int(os.environ["WORLD_SIZE"])
+torch.cuda.set_device(rank)
+dist.init_process_group("nccl", device_id=torch.device("cuda", rank))
+d, f = 512, 2048
+rng = np.random.default_rng(9)
+wg = (rng.standard_normal((f, d)) * 0.05).astype(np.float32)
+wu = (rng.standard_normal((f, d)) * 0.05).astype(np.float32)
+wd = (rng.standard_normal((d, f)) * 0.05).astype(np.float32)
+whole = sg.Mlp.gated(sg.GatedLinear.quantize(wg, wu, sg.WeightLayout.OutIn, f, d, sg.Gate.Silu),
+                     sg.Linear.quantize(wd, sg.WeightLayout.OutIn, d, f))
+ok = True
+for m in (1, 3, 200):
+    tp = TpMlp.quantize(wg, wu, wd, rank, world)
+    tp.peer = PeerReduce(m, d)
+    x = torch.from_numpy(rng.standard_normal((m, d)).astype(np.float16)).cuda()
+    y0 = torch.from_numpy(rng.standard_normal((m, d)).astype(np.float32)).cuda()
+    for step in range(3):
+        y = y0.clone()
+        tp.accumulate(x, y, m)
+        want = y0.clone()
+        whole.accumulate(x, want, m)          # the unsharded block on this GPU
+        torch.cuda.synchronize()
+        rel = float(((y - want).abs() / (1 + want.abs())).max().item())
+        # every rank holds the same bits
+        bits = y.view(torch.int32).to(torch.int64).sum().reshape(1)
+        lo, hi = bits.clone(), bits.clone()
+        dist.all_reduce(lo, op=dist.ReduceOp.MIN); dist.all_reduce(hi, op=dist.ReduceOp.MAX)
+        if sg.last_status() != 0 or rel > 1e-2 or int(lo.item()) != int(hi.item()):
+            ok = False
+            print(f"rank {rank}: m={m} step {step}: max_rel {rel}, identical {int(lo.item()) == int(hi.item())}", flush=True)
+    dist.barrier()
+flag = torch.tensor([1 if ok else 0], device="cuda")
+dist.all_reduce(flag, op=dist.ReduceOp.MIN)
+if rank == 0:
+    print("TP_MLP_OK" if int(flag.item()) == 1 else "TP_MLP_FAILED", flush=True)
+dist.destroy_process_group()
+'''
+
+
+@pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs two GPUs on one box")
+def test_sharded_mlp_with_peer_reduce_matches_the_unsharded_block(tmp_path):
+    """The whole tensor-parallel block -- sharded GEMMs, sum over peer memory, rounding, residual add -- against the
+    one-GPU block (tolerance of an f32 sum taken in another order) and bit for bit across ranks."""
+    world = min(torch.cuda.device_count(), 8)
+    script = tmp_path / "worker_mlp.py"
+    script.write_text(WORKER_MLP)
+    env = dict(os.environ, NCCL_NVLS_ENABLE="0")
+    out = subprocess.run([sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={world}",
+                          "--master-addr", "127.0.0.1", "--master-port", "29741", str(script)],
+                         capture_output=True, text=True, timeout=280, env=env, cwd=os.getcwd())
+    assert "TP_MLP_OK" in out.stdout, out.stdout[-2000:] + out.stderr[-2000:]
+
+
 def _call(y, bufs, flags, rank, world, seq, oneshot):
     import ctypes as C
     from sme_gemm_b200._lib import check, lib
