@@ -23,12 +23,7 @@ __global__ void glu_kernel(uint16_t* __restrict__ out, const uint16_t* __restric
     const uint16_t* br = both + i * 2 * n;
     const float g = __half2float(__ushort_as_half(br[2 * c0 + j]));
     const float u = __half2float(__ushort_as_half(br[2 * c0 + w + j]));
-    float a;
-    if (act == 3) a = __fdiv_rn(g, __fadd_rn(1.0f, expf(-g)));
-    else {
-        const float g3 = __fmul_rn(__fmul_rn(__fmul_rn(0.044715f, g), g), g);
-        a = __fmul_rn(__fmul_rn(0.5f, g), __fadd_rn(1.0f, tanhf(__fmul_rn(0.7978846f, __fadd_rn(g, g3)))));
-    }
+    const float a = glu_gate(act, g);
     out[idx] = __half_as_ushort(__float2half_rn(__fmul_rn(a, u)));
 }
 

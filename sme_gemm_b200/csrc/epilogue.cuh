@@ -252,6 +252,17 @@ __device__ __forceinline__ void fast_ep_apply16(const FastEp& f, const uint32_t 
     for (int j = 0; j < 16; ++j) out[j] = f32_to_t<BF16>(x[j]);
 }
 
+// The gate activation of the gated MLP product (act 3 = SiLU, else the tanh form of GELU), the same expression at every
+// site that forms act(gate) * up so that the fused drain, the depth-split reduce and the element-wise pass agree bit
+// for bit.  Both are x * sigmoid(y) -- 0.5 x (1 + tanh z) = x / (1 + exp(-2 z)) -- on the hardware's approximate
+// exp2 and reciprocal: relative error of a few 2^-22, far below the f16 / bf16 rounding of the store that follows, and a
+// dozen instructions less per element than the exact division and expf (the drain of a 256 x 256 tile is bound by them).
+__device__ __forceinline__ float glu_gate(uint32_t act, float g) {
+    float y = g;
+    if (act != 3u) y = __fmul_rn(1.5957691f, __fadd_rn(g, __fmul_rn(__fmul_rn(__fmul_rn(0.044715f, g), g), g)));
+    return __fdividef(g, __fadd_rn(1.0f, __expf(-y)));
+}
+
 template <int BF16>
 __device__ __forceinline__ uint16_t fast_ep_store(const FastEp& f, float acc) {
     float x = t_to_f32<BF16>(f32_to_t<BF16>(acc));

@@ -129,19 +129,199 @@ __device__ __forceinline__ void dequant_unit_q4(unsigned char* tile, int cu, con
 
 // The kernel's tensor maps: the token matrix, and for dense weights the weight matrix as well.
 template <int DENSE> struct TcMaps { CUtensorMap tok; CUtensorMap w; };
-template <> struct TcMaps<0> { CUtensorMap tok; };
+template <> struct TcMaps<0> { CUtensorMap tok; CUtensorMap codes; CUtensorMap scales; };
 
-template <int BF16, int US, int DENSE>
-__global__ void __launch_bounds__(kTcThreads, 1) gemm_tc_kernel(const __grid_constant__ TcMaps<DENSE> maps, GemmTcArgs p) {
+// The hot forms of the drain -- the gated product of a gate/up pair, the residual add of the down projection, the f32
+// partial tile of a depth slice, the plain rounded store -- out of line and on scalar arguments: sixteen accumulators
+// per tcgen05.ld, one thread per weight column (TMEM lane), lanes of a warp on consecutive columns of C.
+template <int BF16>
+__device__ __noinline__ void drain_glu(uint32_t lane_base, int ntok, int j_begin, int j_end, uint16_t* c, int m, int hn, int hcol, int tok0,
+                                       uint32_t act) {
+    // accumulator set 0 = gate, set 1 = up of hidden unit hcol (glu, src/linear.rs:804-835)
+    for (int j0 = j_begin; j0 < j_end; j0 += 16) {
+        uint32_t rg[16], ru[16];
+        tmem_ld16(lane_base + (uint32_t)j0, rg);
+        tmem_ld16(lane_base + (uint32_t)(ntok + j0), ru);
+        tmem_ld_wait();
+        if (hcol >= hn) continue;
+        uint16_t* dst = c + (size_t)(tok0 + j0) * hn + hcol;
+        const int left = m - tok0 - j0;
+#pragma unroll
+        for (int j = 0; j < 16; ++j) {
+            const float gv = t_to_f32<BF16>(f32_to_t<BF16>(__uint_as_float(rg[j])));
+            const float uv = t_to_f32<BF16>(f32_to_t<BF16>(__uint_as_float(ru[j])));
+            const uint16_t v = f32_to_t<BF16>(__fmul_rn(glu_gate(act, gv), uv));
+            if (j < left) dst[(size_t)j * hn] = v;
+        }
+    }
+}
+
+template <int BF16>
+__device__ __noinline__ void drain_residual(uint32_t lane_base, int j_begin, int j_end, float* y, int m, int n, int col, int tok0) {
+    for (int j0 = j_begin; j0 < j_end; j0 += 16) {
+        uint32_t r[16];
+        tmem_ld16(lane_base + (uint32_t)j0, r);
+        tmem_ld_wait();
+        if (col >= n) continue;
+        float* dst = y + (size_t)(tok0 + j0) * n + col;
+        const int left = m - tok0 - j0;
+        float yv[16];
+#pragma unroll
+        for (int j = 0; j < 16; ++j) yv[j] = j < left ? dst[(size_t)j * n] : 0.0f;
+#pragma unroll
+        for (int j = 0; j < 16; ++j)
+            if (j < left) dst[(size_t)j * n] = __fadd_rn(yv[j], t_to_f32<BF16>(f32_to_t<BF16>(__uint_as_float(r[j]))));
+    }
+}
+
+__device__ __noinline__ void drain_partial(uint32_t lane_base, int j_begin, int j_end, float* dst, int stride) {
+    // partial tile of this depth slice: ws[tile][slice][token][column]
+    for (int j0 = j_begin; j0 < j_end; j0 += 16) {
+        uint32_t r[16];
+        tmem_ld16(lane_base + (uint32_t)j0, r);
+        tmem_ld_wait();
+#pragma unroll
+        for (int j = 0; j < 16; ++j) dst[(size_t)(j0 + j) * stride] = __uint_as_float(r[j]);
+    }
+}
+
+template <int BF16>
+__device__ __noinline__ void drain_store(uint32_t lane_base, int j_begin, int j_end, uint16_t* c, int m, int n, int col, int tok0) {
+    for (int j0 = j_begin; j0 < j_end; j0 += 16) {
+        uint32_t r[16];
+        tmem_ld16(lane_base + (uint32_t)j0, r);
+        tmem_ld_wait();
+        if (col >= n) continue;
+        uint16_t* dst = c + (size_t)(tok0 + j0) * n + col;
+        const int left = m - tok0 - j0;
+#pragma unroll
+        for (int j = 0; j < 16; ++j)
+            if (j < left) dst[(size_t)j * n] = f32_to_t<BF16>(__uint_as_float(r[j]));
+    }
+}
+
+// The drain of a CTA's accumulators, out of line: its sixteen-wide register groups would otherwise set the register
+// budget of the role loops above (which then spill inside their per-stage latency chains).
+template <int BF16, int DENSE>
+__device__ __noinline__ void drain_tile(const GemmTcArgs& p, uint32_t tmem_base, int warp, int lane, int num_stages, uint64_t* acc_full,
+                                        volatile int* abort_flag, const EpNodeDev* ep_nodes, int col0, int tok0) {
+    const int NW = p.nw;
+    // ---- drain: thread = weight column (TMEM lane), registers = tokens.  A warp reaches the
+    // lane quarter warp % 4; the token columns are split over 4 (or 2) warps per quarter ----
+    const int ntok = p.ntok_pad;                           // a multiple of 32
+    const int parts = (ntok % 64 == 0) ? 4 : 2;            // every part is whole groups of 16 tokens
+    if (warp < 4 * parts) {
+    if (num_stages > 0) mbar_wait(acc_full, 0, abort_flag, p.status, STATUS_TMEM_TIMEOUT);
+    tc_fence_after();
+    const int q = warp & 3, part = warp >> 2;              // lane quarter, token part
+    const uint32_t lane_base = tmem_base + ((uint32_t)(32 * q) << 16);
+    const EpNodeDev* nodes = p.ep.n_nodes <= kMaxInlineNodes ? ep_nodes : p.ep.ext;
+    const int j_begin = part * (ntok / parts), j_end = j_begin + ntok / parts;
+    const int splits = (int)gridDim.z;
+    const int tile_id = blockIdx.y * gridDim.x + blockIdx.x;
+    float* ws_tile = p.ws + ((size_t)tile_id * splits) * (size_t)(NW * 128) * ntok;
+
+    if (p.glu && splits == 1) {
+        // accumulator set 0 = gate, set 1 = up of hidden unit hcol (glu, src/linear.rs:804-835)
+        const int hn = p.n >> 1, hcol = blockIdx.x * 128 + 32 * q + lane;
+        for (int j0 = j_begin; j0 < j_end; j0 += 16) {
+            uint32_t rg[16], ru[16];
+            tmem_ld16(lane_base + (uint32_t)j0, rg);
+            tmem_ld16(lane_base + (uint32_t)(ntok + j0), ru);
+            tmem_ld_wait();
+            if (hcol < hn) {
+#pragma unroll
+                for (int j = 0; j < 16; ++j) {
+                    const float gv = t_to_f32<BF16>(f32_to_t<BF16>(__uint_as_float(rg[j])));
+                    const float uv = t_to_f32<BF16>(f32_to_t<BF16>(__uint_as_float(ru[j])));
+                    const float a = glu_gate((uint32_t)p.glu, gv);
+                    if (tok0 + j0 + j < p.m) p.c[(size_t)(tok0 + j0 + j) * hn + hcol] = f32_to_t<BF16>(__fmul_rn(a, uv));
+                }
+            }
+        }
+    } else
+    for (int w = 0; w < NW; ++w) {
+        const int col = col0 + 128 * w + 32 * q + lane;
+        FastEp fe;
+        if (p.ep_fast) fast_ep_build<BF16>(nodes, p.ep.n_nodes, col, col < p.n, fe);
+        for (int j0 = j_begin; j0 < j_end; j0 += 16) {
+            uint32_t r[16];
+            if (num_stages > 0) {
+                tmem_ld16(lane_base + (uint32_t)(w * ntok + j0), r);
+                tmem_ld_wait();
+            } else {
+#pragma unroll
+                for (int j = 0; j < 16; ++j) r[j] = 0u;
+            }
+            if (splits == 1) {
+                if (DENSE && p.beta != 1.0f) {
+#pragma unroll
+                    for (int j = 0; j < 16; ++j) r[j] = __float_as_uint(__fmul_rn(p.beta, __uint_as_float(r[j])));
+                }
+                if (col < p.n) {
+                    if (p.c32) {
+#pragma unroll
+                        for (int j = 0; j < 16; ++j)
+                            if (tok0 + j0 + j < p.m) p.c32[(size_t)(tok0 + j0 + j) * p.n + col] = __uint_as_float(r[j]);
+                    } else if (p.yacc) {
+                        float yv[16];
+#pragma unroll
+                        for (int j = 0; j < 16; ++j) yv[j] = (tok0 + j0 + j < p.m) ? p.yacc[(size_t)(tok0 + j0 + j) * p.n + col] : 0.0f;
+#pragma unroll
+                        for (int j = 0; j < 16; ++j)
+                            if (tok0 + j0 + j < p.m)
+                                p.yacc[(size_t)(tok0 + j0 + j) * p.n + col] = __fadd_rn(yv[j], t_to_f32<BF16>(f32_to_t<BF16>(__uint_as_float(r[j]))));
+                    } else {
+                        uint16_t v[16];
+                        if (p.ep_fast) fast_ep_apply16<BF16>(fe, r, v);
+                        else if (p.ep.n_nodes == 0) {
+#pragma unroll
+                            for (int j = 0; j < 16; ++j) v[j] = f32_to_t<BF16>(__uint_as_float(r[j]));
+                        } else {
+#pragma unroll
+                            for (int j = 0; j < 16; ++j)
+                                v[j] = (tok0 + j0 + j < p.m) ? ep_store_nodes<BF16>(nodes, p.ep.n_nodes, __uint_as_float(r[j]), (size_t)(tok0 + j0 + j), (size_t)col) : (uint16_t)0;
+                        }
+#pragma unroll
+                        for (int j = 0; j < 16; ++j)
+                            if (tok0 + j0 + j < p.m) {
+                                if (!DENSE || !p.col_major) p.c[(size_t)(tok0 + j0 + j) * p.n + col] = v[j];
+                                else p.c[(size_t)col * p.m + (tok0 + j0 + j)] = v[j];
+                            }
+                    }
+                }
+            } else {
+                // partial tile of this depth slice: ws[tile][slice][token][column]
+                float* dst = ws_tile + ((size_t)blockIdx.z * ntok) * (NW * 128) + (128 * w + 32 * q + lane);
+#pragma unroll
+                for (int j = 0; j < 16; ++j) dst[(size_t)(j0 + j) * (NW * 128)] = __uint_as_float(r[j]);
+            }
+        }
+    }
+    tc_fence_before();
+
+    }   // drain warps
+}
+
+template <int BF16, int US, int DENSE, int CG>
+__global__ void __launch_bounds__(kTcThreads, 1) gemm_tc_kernel(const __grid_constant__ TcMaps<DENSE> maps, const __grid_constant__ GemmTcArgs p) {
     const CUtensorMap& tmap_tok = maps.tok;
     extern __shared__ unsigned char smem_dyn[];
     // the swizzled operands need 1024-byte aligned tiles: align the window by hand
     unsigned char* smem_raw = smem_dyn + ((1024u - (smem_u32(smem_dyn) & 1023u)) & 1023u);
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int NT = p.nt, NK = p.nk, O = p.no, NW = p.nw, PU = p.pu;
-    const int tok_bytes = p.ntok_pad * 128;                    // token operand per 64-deep unit (a stage is US units)
+    // CG == 2: the CTA is one of a pair (cluster of two along x).  Each CTA expands its own columns and loads half of
+    // the token rows; the even CTA issues MMAs of 256 weight columns that read both CTAs' shared memory and write both
+    // CTAs' tensor memory, so a CTA moves half the token bytes per flop.
+    const uint32_t pair_rank = CG == 2 ? cluster_ctarank() : 0u;
+    const bool leader = pair_rank == 0u;
+    const int tok_bytes = p.ntok_pad * 128 / CG;               // this CTA's token operand per 64-deep unit (a stage is US units)
     const int rpg = p.rpg;                                     // scale rows (blocks) staged per packed slot
-    const int k_code = PU * US * kUnitBytes;                   // packed slot: [8 NW groups][PU * US units] then [8 NW groups][rpg rows]
+    // packed slot: boxes of [8 NW groups][up to 4 units] (one tiled copy each) covering PU * US units, then [8 NW groups][rpg rows]
+    const int k_code = PU * US * kUnitBytes;                   // code bytes per column group and slot
+    const int kbox_shift = PU * US >= 4 ? 2 : (PU * US == 2 ? 1 : 0);   // log2(units per code box)
+    const int kbox_bytes = 8 * NW * (kUnitBytes << kbox_shift);        // one code box
     const int k_stride = ((8 * NW * (k_code + rpg * 32) + 1023) / 1024) * 1024;
     const int o_stride = NW * US * kWTile;                     // ring O slot: NW x US operand tiles
     const int t_stride = US * tok_bytes;                       // ring T slot: US token tiles
@@ -186,7 +366,7 @@ __global__ void __launch_bounds__(kTcThreads, 1) gemm_tc_kernel(const __grid_con
             mbar_init(&k_empty[s], kDeqWarps);
         }
         for (int s = 0; s < O; ++s) {
-            mbar_init(&o_full[s], dense ? 1 : 32 * deq_wpg);
+            mbar_init(&o_full[s], dense ? 1 : CG * deq_wpg);
             mbar_init(&o_empty[s], 1);
         }
         mbar_init(acc_full, 1);
@@ -195,14 +375,23 @@ __global__ void __launch_bounds__(kTcThreads, 1) gemm_tc_kernel(const __grid_con
     }
     if (tid < p.ep.n_nodes && p.ep.n_nodes <= kMaxInlineNodes) ep_nodes[tid] = p.ep.nodes[tid];
     if (warp == kDeqWarps + 1) {
-        tmem_alloc(tmem_slot, p.tmem_cols);
-        tmem_relinquish();
+        if (CG == 2) {
+            tmem_alloc2(tmem_slot, p.tmem_cols);
+            tmem_relinquish2();
+        } else {
+            tmem_alloc(tmem_slot, p.tmem_cols);
+            tmem_relinquish();
+        }
     }
     if (warp == kDeqWarps && lane == 0) tma_prefetch_desc(&tmap_tok);
     tc_fence_before();
-    __syncthreads();
+    if (CG == 2) cluster_sync_all();                            // the peer's barriers are initialised before anything signals them
+    else __syncthreads();
     tc_fence_after();
     const uint32_t tmem_base = *tmem_slot;
+    // the even CTA's "landed" barriers, which both CTAs signal
+    const uint32_t t_full_lead = CG == 2 ? mapa_shared(smem_u32(t_full), 0u) : smem_u32(t_full);
+    const uint32_t o_full_lead = CG == 2 ? mapa_shared(smem_u32(o_full), 0u) : smem_u32(o_full);
 
     if (warp == kDeqWarps) {
         // ===================== token producer =====================
@@ -214,11 +403,24 @@ __global__ void __launch_bounds__(kTcThreads, 1) gemm_tc_kernel(const __grid_con
                 unsigned char* sb = ring_t + (size_t)slot * t_stride;
                 const int u0 = (st_begin + i) * US;
                 const int units = min(US, p.ku - u0);
+                if (CG == 2) {
+                    // the even CTA expects both halves; each CTA loads its half of every MMA's token rows
+                    if (leader) mbar_expect_tx(&t_full[slot], (unsigned)(2 * units * tok_bytes));
+                    const int half = p.ntok_box / 2;
+                    for (int uu = 0; uu < units; ++uu) {
+                        const int d0 = (u0 + uu) * kStageK;
+                        tma_load_2d_pair(sb + uu * tok_bytes, &tmap_tok, d0, tok0 + (int)pair_rank * half, t_full_lead + 8u * slot);
+                        if (p.nmma == 2)
+                            tma_load_2d_pair(sb + uu * tok_bytes + tok_bytes / 2, &tmap_tok, d0, tok0 + p.ntok_box + (int)pair_rank * half,
+                                             t_full_lead + 8u * slot);
+                    }
+                } else {
                 mbar_expect_tx(&t_full[slot], (unsigned)(units * tok_bytes));
                 for (int uu = 0; uu < units; ++uu) {
                     const int d0 = (u0 + uu) * kStageK;
                     tma_load_2d(sb + uu * tok_bytes, &tmap_tok, d0, tok0, &t_full[slot]);
                     if (p.nmma == 2) tma_load_2d(sb + uu * tok_bytes + tok_bytes / 2, &tmap_tok, d0, tok0 + p.ntok_box, &t_full[slot]);
+                }
                 }
             }
         }
@@ -238,43 +440,45 @@ __global__ void __launch_bounds__(kTcThreads, 1) gemm_tc_kernel(const __grid_con
                     unsigned char* ob = ring_o + (size_t)os * o_stride;
                     const int u0 = (st_begin + i) * US;
                     const int units = min(US, p.ku - u0);
+                    if (CG == 2) {
+                        if (leader) mbar_expect_tx(&o_full[os], (unsigned)(2 * NW * units * kWTile));
+                        for (int w = 0; w < NW; ++w)
+                            for (int uu = 0; uu < units; ++uu)
+                                tma_load_2d_pair(ob + (w * US + uu) * kWTile, &maps.w, (u0 + uu) * kStageK, col0 + 128 * w, o_full_lead + 8u * os);
+                    } else {
                     mbar_expect_tx(&o_full[os], (unsigned)(NW * units * kWTile));
                     for (int w = 0; w < NW; ++w)
                         for (int uu = 0; uu < units; ++uu)
                             tma_load_2d(ob + (w * US + uu) * kWTile, &maps.w, (u0 + uu) * kStageK, col0 + 128 * w, &o_full[os]);
+                    }
                 }
             }
-        } else
-        RingPos kp;
-        for (int gq = 0; gq < num_groups; ++gq, kp.next(NK)) {
-            const int slot = kp.slot;
-            if (kp.wrapped && !__all_sync(0xffffffffu, mbar_wait(&k_empty[slot], kp.phase ^ 1u, abort_flag, p.status, STATUS_TMEM_TIMEOUT))) break;
-            unsigned char* sb = ring_k + (size_t)slot * k_stride;
-            const int u0 = (st_begin + gq * PU) * US;                   // first 64-deep unit of the slot
-            const int units = min(PU * US, min(st_end * US, p.ku) - u0);
-            const int d0 = u0 * kStageK;
-            const int blk0 = d0 >> p.log2_block;
-            const int blk1 = min(p.nb, ((d0 + units * kStageK - 1) >> p.log2_block) + 1);
-            const int rows = blk1 - blk0;
-            if (lane == 0) mbar_expect_tx(&k_full[slot], (unsigned)(8 * NW) * (unsigned)(units * kUnitBytes + rows * 32));
-            __syncwarp();
-            const int c = lane & 15;
-            if (c < 8 * NW) {
-                const size_t cgi = (size_t)min(sg0 * 8 + c, p.n16 - 1);   // a tail group re-reads the last one
-                if (lane < 16)
-                    bulk_g2s(sb + (size_t)c * k_code, p.codes + q4_unit_offset(cgi, (size_t)u0, p.ku), units * kUnitBytes, &k_full[slot]);
-                else
-                    bulk_g2s(sb + (size_t)8 * NW * k_code + (size_t)c * rpg * 32, p.scales + q4_scale_row(cgi, blk0, p.nb), rows * 32, &k_full[slot]);
+        } else {
+        if (lane == 0) {
+            tma_prefetch_desc(&maps.codes);
+            tma_prefetch_desc(&maps.scales);
+            RingPos kp;
+            for (int gq = 0; gq < num_groups; ++gq, kp.next(NK)) {
+                const int slot = kp.slot;
+                if (kp.wrapped && !mbar_wait(&k_empty[slot], kp.phase ^ 1u, abort_flag, p.status, STATUS_TMEM_TIMEOUT)) break;
+                unsigned char* sb = ring_k + (size_t)slot * k_stride;
+                const int u0 = (st_begin + gq * PU) * US;               // first 64-deep unit of the slot
+                const int blk0 = (u0 * kStageK) >> p.log2_block;
+                // whole boxes always: what lies past the last unit, block or column group arrives as zeros and is never used
+                mbar_expect_tx(&k_full[slot], (unsigned)(8 * NW) * (unsigned)(k_code + rpg * 32));
+                for (int x = 0; x < PU * US; x += 4)
+                    tma_load_2d(sb + (size_t)(x >> 2) * kbox_bytes, &maps.codes, (u0 + x) * (kUnitBytes / 8), sg0 * 8, &k_full[slot]);
+                tma_load_2d(sb + (size_t)8 * NW * k_code, &maps.scales, blk0 * 4, sg0 * 8, &k_full[slot]);
             }
-            __syncwarp();
+        }
         }
     } else if (warp == kDeqWarps + 1) {
         // ===================== MMA issuer =====================
         // the whole warp walks the stages (converged); one elected lane issues
-        const uint32_t idesc = umma_idesc(BF16, 128, p.ntok_box);
+        const uint32_t idesc = umma_idesc(BF16, 128 * CG, p.ntok_box);
         const uint32_t tok_half = (uint32_t)(tok_bytes / 2);
         RingPos tq, oq;
-        for (int i = 0; i < num_stages; ++i, tq.next(NT), oq.next(O)) {
+        for (int i = 0; i < (leader ? num_stages : 0); ++i, tq.next(NT), oq.next(O)) {
             const int ts = tq.slot, os = oq.slot;
             if (!__all_sync(0xffffffffu, mbar_wait(&t_full[ts], tq.phase, abort_flag, p.status, STATUS_TMEM_TIMEOUT))) break;
             if (!__all_sync(0xffffffffu, mbar_wait(&o_full[os], oq.phase, abort_flag, p.status, STATUS_TMEM_TIMEOUT))) break;
@@ -293,16 +497,25 @@ __global__ void __launch_bounds__(kTcThreads, 1) gemm_tc_kernel(const __grid_con
                             const uint32_t d_tmem = tmem_base + (uint32_t)((w * p.nmma + h) * p.ntok_box);
 #pragma unroll
                             for (int ks = 0; ks < kStageK / 16; ++ks)
-                                umma_f16(d_tmem, a_desc0 + 2 * ks, b_desc0 + 2 * ks, idesc, (i > 0 || uu > 0 || ks > 0) ? 1u : 0u);
+                                if (CG == 2) umma_f16_2(d_tmem, a_desc0 + 2 * ks, b_desc0 + 2 * ks, idesc, (i > 0 || uu > 0 || ks > 0) ? 1u : 0u);
+                                else umma_f16(d_tmem, a_desc0 + 2 * ks, b_desc0 + 2 * ks, idesc, (i > 0 || uu > 0 || ks > 0) ? 1u : 0u);
                         }
                     }
                 }
-                umma_commit(&o_empty[os]);
-                umma_commit(&t_empty[ts]);
+                if (CG == 2) {
+                    umma_commit2(&o_empty[os]);
+                    umma_commit2(&t_empty[ts]);
+                } else {
+                    umma_commit(&o_empty[os]);
+                    umma_commit(&t_empty[ts]);
+                }
             }
             __syncwarp();
         }
-        if (elect_one()) umma_commit(acc_full);
+        if (leader && elect_one()) {
+            if (CG == 2) umma_commit2(acc_full);
+            else umma_commit(acc_full);
+        }
         __syncwarp();
     } else {
         // ===================== dequant warps (0..15), then epilogue =====================
@@ -337,7 +550,7 @@ __global__ void __launch_bounds__(kTcThreads, 1) gemm_tc_kernel(const __grid_con
                 const int ra = ((du + 8 * t) >> p.log2_block) - blk0, rb = ((du + 32 + 8 * t) >> p.log2_block) - blk0;
                 for (int c = wig; c < 8 * NW; c += deq_wpg) {
                     const int cgl = c & 7, w = c >> 3;
-                    const uint4 wv = *reinterpret_cast<const uint4*>(pk + (size_t)c * k_code + uq * kUnitBytes + lane * 16);
+                    const uint4 wv = *reinterpret_cast<const uint4*>(pk + (size_t)(uq >> kbox_shift) * kbox_bytes + (((size_t)c << kbox_shift) + (uq & ((1 << kbox_shift) - 1))) * kUnitBytes + lane * 16);
                     // gate/up matrix: gate column groups go to operand tile 0 and the matching up groups to tile 1,
                     // so that a thread of the drain holds both values of one hidden unit
                     int tw = w, rg = cgl;
@@ -354,7 +567,8 @@ __global__ void __launch_bounds__(kTcThreads, 1) gemm_tc_kernel(const __grid_con
                 if (uu >= units) continue;
                 const int du = (u0 + uu) * kStageK;                 // depth of the unit
                 const int ra = ((du + 8 * t) >> p.log2_block) - blk0, rb = ((du + 32 + 8 * t) >> p.log2_block) - blk0;
-                const uint4 wv = *reinterpret_cast<const uint4*>(pk + (size_t)c * k_code + (uq + uu) * kUnitBytes + lane * 16);
+                const int un = uq + uu;
+                const uint4 wv = *reinterpret_cast<const uint4*>(pk + (size_t)(un >> kbox_shift) * kbox_bytes + (((size_t)c << kbox_shift) + (un & ((1 << kbox_shift) - 1))) * kUnitBytes + lane * 16);
                 // gate/up matrix: gate column groups go to operand tile 0 and the matching up groups to tile 1,
                 // so that a thread of the drain holds both values of one hidden unit
                 int tw = w, rg = cgl;
@@ -366,118 +580,57 @@ __global__ void __launch_bounds__(kTcThreads, 1) gemm_tc_kernel(const __grid_con
             }
             }
             fence_proxy_async();
-            mbar_arrive(&o_full[os]);
+            __syncwarp();
+            if (lane == 0) {
+                if (CG == 2) mbar_arrive_cluster(o_full_lead + 8u * os);
+                else mbar_arrive(&o_full[os]);
+            }
             if (last_of_slot) {
                 __syncwarp();
                 if (lane == 0) mbar_arrive(&k_empty[ks]);
             }
         }
 
-        // ---- drain: thread = weight column (TMEM lane), registers = tokens.  A warp reaches the
-        // lane quarter warp % 4; the token columns are split over 4 (or 2) warps per quarter ----
-        const int ntok = p.ntok_pad;                           // a multiple of 32
-        const int parts = (ntok % 64 == 0) ? 4 : 2;            // every part is whole groups of 16 tokens
-        if (warp < 4 * parts) {
-        if (num_stages > 0) mbar_wait(acc_full, 0, abort_flag, p.status, STATUS_TMEM_TIMEOUT);
-        tc_fence_after();
-        const int q = warp & 3, part = warp >> 2;              // lane quarter, token part
-        const uint32_t lane_base = tmem_base + ((uint32_t)(32 * q) << 16);
-        const EpNodeDev* nodes = p.ep.n_nodes <= kMaxInlineNodes ? ep_nodes : p.ep.ext;
-        const int j_begin = part * (ntok / parts), j_end = j_begin + ntok / parts;
+        // ---- drain: thread = weight column (TMEM lane), registers = tokens.  A warp reaches the lane quarter warp % 4;
+        // the token columns are split over 4 (or 2) warps per quarter ----
+        const int ntok = p.ntok_pad;                               // a multiple of 32
+        const int parts = (ntok % 64 == 0) ? 4 : 2;                // every part is whole groups of 16 tokens
         const int splits = (int)gridDim.z;
-        const int tile_id = blockIdx.y * gridDim.x + blockIdx.x;
-        float* ws_tile = p.ws + ((size_t)tile_id * splits) * (size_t)(NW * 128) * ntok;
-
-        if (p.glu && splits == 1) {
-            // accumulator set 0 = gate, set 1 = up of hidden unit hcol (glu, src/linear.rs:804-835)
-            const int hn = p.n >> 1, hcol = blockIdx.x * 128 + 32 * q + lane;
-            for (int j0 = j_begin; j0 < j_end; j0 += 16) {
-                uint32_t rg[16], ru[16];
-                tmem_ld16(lane_base + (uint32_t)j0, rg);
-                tmem_ld16(lane_base + (uint32_t)(ntok + j0), ru);
-                tmem_ld_wait();
-                if (hcol < hn) {
-#pragma unroll
-                    for (int j = 0; j < 16; ++j) {
-                        const float gv = t_to_f32<BF16>(f32_to_t<BF16>(__uint_as_float(rg[j])));
-                        const float uv = t_to_f32<BF16>(f32_to_t<BF16>(__uint_as_float(ru[j])));
-                        float a;
-                        if (p.glu == 3) a = __fdiv_rn(gv, __fadd_rn(1.0f, expf(-gv)));
-                        else {
-                            const float g3 = __fmul_rn(__fmul_rn(__fmul_rn(0.044715f, gv), gv), gv);
-                            a = __fmul_rn(__fmul_rn(0.5f, gv), __fadd_rn(1.0f, tanhf(__fmul_rn(0.7978846f, __fadd_rn(gv, g3)))));
-                        }
-                        if (tok0 + j0 + j < p.m) p.c[(size_t)(tok0 + j0 + j) * hn + hcol] = f32_to_t<BF16>(__fmul_rn(a, uv));
-                    }
-                }
-            }
-        } else
-        for (int w = 0; w < NW; ++w) {
-            const int col = col0 + 128 * w + 32 * q + lane;
-            FastEp fe;
-            if (p.ep_fast) fast_ep_build<BF16>(nodes, p.ep.n_nodes, col, col < p.n, fe);
-            for (int j0 = j_begin; j0 < j_end; j0 += 16) {
-                uint32_t r[16];
-                if (num_stages > 0) {
-                    tmem_ld16(lane_base + (uint32_t)(w * ntok + j0), r);
-                    tmem_ld_wait();
+        const bool plain = !p.c32 && !p.yacc && !p.glu && p.ep.n_nodes == 0 && !(DENSE && (p.col_major || p.beta != 1.0f));
+        if (num_stages > 0 && (splits > 1 || p.glu || p.yacc || plain)) {
+            if (warp < 4 * parts) {
+                mbar_wait(acc_full, 0, abort_flag, p.status, STATUS_TMEM_TIMEOUT);
+                tc_fence_after();
+                const int q = warp & 3, part = warp >> 2;              // lane quarter, token part
+                const uint32_t lane_base = tmem_base + ((uint32_t)(32 * q) << 16);
+                const int j_begin = part * (ntok / parts), j_end = j_begin + ntok / parts;
+                if (splits > 1) {
+                    const int tile_id = blockIdx.y * gridDim.x + blockIdx.x;
+                    float* ws_tile = p.ws + ((size_t)tile_id * splits + blockIdx.z) * (size_t)(NW * 128) * ntok;
+                    for (int w = 0; w < NW; ++w)
+                        drain_partial(lane_base + (uint32_t)(w * ntok), j_begin, j_end, ws_tile + (128 * w + 32 * q + lane), NW * 128);
+                } else if (p.glu) {
+                    drain_glu<BF16>(lane_base, ntok, j_begin, j_end, p.c, p.m, p.n >> 1, blockIdx.x * 128 + 32 * q + lane, tok0, (uint32_t)p.glu);
+                } else if (p.yacc) {
+                    for (int w = 0; w < NW; ++w)
+                        drain_residual<BF16>(lane_base + (uint32_t)(w * ntok), j_begin, j_end, p.yacc, p.m, p.n, col0 + 128 * w + 32 * q + lane, tok0);
                 } else {
-#pragma unroll
-                    for (int j = 0; j < 16; ++j) r[j] = 0u;
+                    for (int w = 0; w < NW; ++w)
+                        drain_store<BF16>(lane_base + (uint32_t)(w * ntok), j_begin, j_end, p.c, p.m, p.n, col0 + 128 * w + 32 * q + lane, tok0);
                 }
-                if (splits == 1) {
-                    if (DENSE && p.beta != 1.0f) {
-#pragma unroll
-                        for (int j = 0; j < 16; ++j) r[j] = __float_as_uint(__fmul_rn(p.beta, __uint_as_float(r[j])));
-                    }
-                    if (col < p.n) {
-                        if (p.c32) {
-#pragma unroll
-                            for (int j = 0; j < 16; ++j)
-                                if (tok0 + j0 + j < p.m) p.c32[(size_t)(tok0 + j0 + j) * p.n + col] = __uint_as_float(r[j]);
-                        } else if (p.yacc) {
-                            float yv[16];
-#pragma unroll
-                            for (int j = 0; j < 16; ++j) yv[j] = (tok0 + j0 + j < p.m) ? p.yacc[(size_t)(tok0 + j0 + j) * p.n + col] : 0.0f;
-#pragma unroll
-                            for (int j = 0; j < 16; ++j)
-                                if (tok0 + j0 + j < p.m)
-                                    p.yacc[(size_t)(tok0 + j0 + j) * p.n + col] = __fadd_rn(yv[j], t_to_f32<BF16>(f32_to_t<BF16>(__uint_as_float(r[j]))));
-                        } else {
-                            uint16_t v[16];
-                            if (p.ep_fast) fast_ep_apply16<BF16>(fe, r, v);
-                            else if (p.ep.n_nodes == 0) {
-#pragma unroll
-                                for (int j = 0; j < 16; ++j) v[j] = f32_to_t<BF16>(__uint_as_float(r[j]));
-                            } else {
-#pragma unroll
-                                for (int j = 0; j < 16; ++j)
-                                    v[j] = (tok0 + j0 + j < p.m) ? ep_store_nodes<BF16>(nodes, p.ep.n_nodes, __uint_as_float(r[j]), (size_t)(tok0 + j0 + j), (size_t)col) : (uint16_t)0;
-                            }
-#pragma unroll
-                            for (int j = 0; j < 16; ++j)
-                                if (tok0 + j0 + j < p.m) {
-                                    if (!DENSE || !p.col_major) p.c[(size_t)(tok0 + j0 + j) * p.n + col] = v[j];
-                                    else p.c[(size_t)col * p.m + (tok0 + j0 + j)] = v[j];
-                                }
-                        }
-                    }
-                } else {
-                    // partial tile of this depth slice: ws[tile][slice][token][column]
-                    float* dst = ws_tile + ((size_t)blockIdx.z * ntok) * (NW * 128) + (128 * w + 32 * q + lane);
-#pragma unroll
-                    for (int j = 0; j < 16; ++j) dst[(size_t)(j0 + j) * (NW * 128)] = __uint_as_float(r[j]);
-                }
+                tc_fence_before();
             }
+        } else {
+            drain_tile<BF16, DENSE>(p, tmem_base, warp, lane, num_stages, acc_full, abort_flag, ep_nodes, col0, tok0);
         }
-        tc_fence_before();
-
-        }   // drain warps
     }
-    __syncthreads();
+    // (every thread reaches this point, also after a timed-out wait: nothing above returns)
+    if (CG == 2) cluster_sync_all();                            // neither CTA frees tensor memory or leaves while the other may still use its memory
+    else __syncthreads();
     if (warp == kDeqWarps + 1) {
         tc_fence_after();
-        tmem_dealloc(tmem_base, p.tmem_cols);
+        if (CG == 2) tmem_dealloc2(tmem_base, p.tmem_cols);
+        else tmem_dealloc(tmem_base, p.tmem_cols);
     }
 }
 
@@ -513,12 +666,7 @@ __global__ void __launch_bounds__(256) splitk_reduce_kernel(const __grid_constan
         for (int jj = 0; jj < 8; ++jj) {
             const int tok = tok0 + j0 + jj;
             const float gv = t_to_f32<BF16>(f32_to_t<BF16>(ag[jj])), uv = t_to_f32<BF16>(f32_to_t<BF16>(au[jj]));
-            float a;
-            if (p.glu == 3) a = __fdiv_rn(gv, __fadd_rn(1.0f, expf(-gv)));
-            else {
-                const float g3 = __fmul_rn(__fmul_rn(__fmul_rn(0.044715f, gv), gv), gv);
-                a = __fmul_rn(__fmul_rn(0.5f, gv), __fadd_rn(1.0f, tanhf(__fmul_rn(0.7978846f, __fadd_rn(gv, g3)))));
-            }
+            const float a = glu_gate((uint32_t)p.glu, gv);
             if (tok < p.m) p.c[(size_t)tok * hn + hcol] = f32_to_t<BF16>(__fmul_rn(a, uv));
         }
         return;
@@ -555,9 +703,9 @@ __global__ void __launch_bounds__(256) splitk_reduce_kernel(const __grid_constan
     }
 }
 
-template <int BF16, int US, int DENSE>
-cudaError_t launch_tc(const CUtensorMap& tm, const CUtensorMap& tw, const GemmTcArgs& a, dim3 grid, size_t smem, cudaStream_t stream) {
-    auto kern = gemm_tc_kernel<BF16, US, DENSE>;
+template <int BF16, int US, int DENSE, int CG>
+cudaError_t launch_tc(const CUtensorMap& tm, const CUtensorMap& tw, const CUtensorMap& ts, const GemmTcArgs& a, dim3 grid, size_t smem, cudaStream_t stream) {
+    auto kern = gemm_tc_kernel<BF16, US, DENSE, CG>;
     static int attr_dev = -1;
     int dev = 0;
     cudaGetDevice(&dev);
@@ -569,6 +717,25 @@ cudaError_t launch_tc(const CUtensorMap& tm, const CUtensorMap& tw, const GemmTc
     TcMaps<DENSE> maps;
     maps.tok = tm;
     if constexpr (DENSE) maps.w = tw;
+    else {
+        maps.codes = tw;
+        maps.scales = ts;
+    }
+    if (CG == 2) {
+        cudaLaunchConfig_t cfg = {};
+        cfg.gridDim = grid;
+        cfg.blockDim = dim3(kTcThreads);
+        cfg.dynamicSmemBytes = smem;
+        cfg.stream = stream;
+        cudaLaunchAttribute attr;
+        attr.id = cudaLaunchAttributeClusterDimension;
+        attr.val.clusterDim.x = 2;
+        attr.val.clusterDim.y = 1;
+        attr.val.clusterDim.z = 1;
+        cfg.attrs = &attr;
+        cfg.numAttrs = 1;
+        return cudaLaunchKernelEx(&cfg, kern, maps, a);
+    }
     kern<<<grid, kTcThreads, smem, stream>>>(maps, a);
     return cudaGetLastError();
 }
@@ -629,6 +796,9 @@ void gemm_tc_plan(GemmTcArgs& a, int sm_count, dim3* grid, size_t* smem, size_t*
     // wastes little of its last wave; larger ones only when the column tiles alone cannot fill the
     // machine (each slice costs a workspace round trip of the whole partial tile)
     a.us = (pad <= 64 && !a.wdense) ? 2 : 1;                        // small token tiles: two 64-deep units per stage halve the per-stage hand-offs
+    // CTA pairs from 128 tokens up: a CTA then loads half the token rows per flop and the MMAs read half as much shared memory
+    static const int env_cg = []() { const char* e = getenv("SMEG_TC_CG"); return e ? atoi(e) : 0; }();
+    a.cg = (a.us == 1 && pad >= 128 && col_tiles >= 2 && env_cg != 1) ? 2 : 1;
     const int stages_all = (a.ku + a.us - 1) / a.us;
     int splits = 1;
     {
@@ -649,7 +819,7 @@ void gemm_tc_plan(GemmTcArgs& a, int sm_count, dim3* grid, size_t* smem, size_t*
     }
     // shared memory: operand ring (NW x 16 KB per slot), token ring (pad x 128 B per slot) and the packed-weight
     // ring, whose slots cover PU stages each so that one bulk copy moves a column group's units of PU stages
-    const int tok_bytes = a.us * pad * 128, o_stride = a.nw * a.us * kWTile;
+    const int tok_bytes = a.us * pad * 128 / a.cg, o_stride = a.nw * a.us * kWTile;
     const int budget = 214 * 1024;
     static const int env_no = []() { const char* e = getenv("SMEG_TC_NO"); return e ? atoi(e) : 0; }();
     static const int env_pu = []() { const char* e = getenv("SMEG_TC_PU"); return e ? atoi(e) : 0; }();
@@ -659,16 +829,17 @@ void gemm_tc_plan(GemmTcArgs& a, int sm_count, dim3* grid, size_t* smem, size_t*
         if (env_pu && pu != env_pu) continue;
         const int sdepth = pu * a.us * kStageK;                       // depths covered by a packed slot
         const int rpg = block <= kStageK ? sdepth / block : sdepth / block + 1;
+        if (rpg > 64) continue;                                       // the scale rows of a slot travel as one box of at most 256 eight-byte elements
         const int k_stride = ((8 * a.nw * (pu * a.us * kUnitBytes + rpg * 32) + 1023) / 1024) * 1024;
-        for (int no = 3; no >= 2; --no) {
-            if (env_no >= 2 && env_no <= 3 && no != env_no) continue;
+        for (int no = 4; no >= 2; --no) {
+            if (env_no >= 2 && env_no <= 4 && no != env_no) continue;
             for (int nk = 4; nk >= 2; --nk) {
                 const int left = budget - 2048 - no * o_stride - (a.wdense ? 0 : nk * k_stride);
                 if (left < 2 * tok_bytes) continue;
                 int nt = left / tok_bytes;
                 if (nt > 8) nt = 8;
                 // prefer: at least three token slots, then few copies per stage (large PU), then depth
-                const int score = (nt >= 3 ? 1000 : 0) + (pu > per_cta_stages ? 0 : pu * 50) + (no == 3 ? 20 : 0) + nk * 5 + nt;
+                const int score = (nt >= 3 ? 1000 : 0) + (pu > per_cta_stages ? 0 : pu * 50) + (no >= 3 ? 20 : 0) + nk * 5 + nt;
                 if (score > best_score) {
                     best_score = score;
                     a.pu = pu; a.rpg = rpg; a.no = no; a.nk = nk; a.nt = nt;
@@ -680,16 +851,17 @@ void gemm_tc_plan(GemmTcArgs& a, int sm_count, dim3* grid, size_t* smem, size_t*
     *smem = 1024 + (size_t)a.no * o_stride + (size_t)a.nt * tok_bytes + (a.wdense ? 0 : (size_t)a.nk * k_stride) +
             (size_t)(2 * a.nt + 2 * a.nk + 2 * a.no + 4) * 8 + kMaxInlineNodes * sizeof(EpNodeDev) + 64;
     a.defer = splits >= 2 ? 1 : 0;
-    *grid = dim3(col_tiles, tiles, splits);
-    *ws_floats = splits > 1 ? (size_t)col_tiles * tiles * splits * (a.nw * 128) * pad : 0;
-    *n_counters = splits > 1 ? (size_t)col_tiles * tiles : 0;
+    const int grid_x = a.cg == 2 ? (col_tiles + 1) / 2 * 2 : col_tiles;     // whole pairs: a CTA past the last column computes nothing it stores
+    *grid = dim3(grid_x, tiles, splits);
+    *ws_floats = splits > 1 ? (size_t)grid_x * tiles * splits * (a.nw * 128) * pad : 0;
+    *n_counters = splits > 1 ? (size_t)grid_x * tiles : 0;
 }
 
 cudaError_t gemm_tc_launch(GemmTcArgs a, int bf16, dim3 grid, size_t smem, cudaStream_t stream) {
     CUtensorMap tm;
     const cuuint64_t gdim[2] = {(cuuint64_t)a.k, (cuuint64_t)a.m};
     const cuuint64_t gstride[1] = {(cuuint64_t)a.k * 2};
-    const cuuint32_t box[2] = {(cuuint32_t)kStageK, (cuuint32_t)a.ntok_box};
+    const cuuint32_t box[2] = {(cuuint32_t)kStageK, (cuuint32_t)(a.ntok_box / (a.cg == 2 ? 2 : 1))};
     const cuuint32_t estr[2] = {1, 1};
     CUresult r = tensor_map_encoder()(&tm, bf16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, (void*)a.a, gdim,
                              gstride, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
@@ -706,11 +878,31 @@ cudaError_t gemm_tc_launch(GemmTcArgs a, int bf16, dim3 grid, size_t smem, cudaS
                         CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
         if (r != CUDA_SUCCESS) return cudaErrorInvalidValue;
     }
+    CUtensorMap ts = tm;                                         // scale rows of packed weights
+    if (!a.wdense) {
+        // packed codes: one row per column group, ku units of 512 bytes, as 8-byte elements; a box = the CTA's column groups x up to 4 units
+        const int box_units = a.pu * a.us >= 4 ? 4 : a.pu * a.us;
+        const cuuint64_t cdim[2] = {(cuuint64_t)a.ku * (kUnitBytes / 8), (cuuint64_t)a.n16};
+        const cuuint64_t cstride[1] = {(cuuint64_t)a.ku * kUnitBytes};
+        const cuuint32_t cbox[2] = {(cuuint32_t)(box_units * (kUnitBytes / 8)), (cuuint32_t)(8 * a.nw)};
+        r = tensor_map_encoder()(&tw, CU_TENSOR_MAP_DATA_TYPE_UINT64, 2, (void*)a.codes, cdim, cstride, cbox, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                                 CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+        if (r != CUDA_SUCCESS) return cudaErrorInvalidValue;
+        // scale rows: per column group nb rows of 32 bytes
+        const cuuint64_t sdim[2] = {(cuuint64_t)a.nb * 4, (cuuint64_t)a.n16};
+        const cuuint64_t sstride[1] = {(cuuint64_t)a.nb * 32};
+        const cuuint32_t sbox[2] = {(cuuint32_t)(a.rpg * 4), (cuuint32_t)(8 * a.nw)};
+        r = tensor_map_encoder()(&ts, CU_TENSOR_MAP_DATA_TYPE_UINT64, 2, (void*)a.scales, sdim, sstride, sbox, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                                 CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+        if (r != CUDA_SUCCESS) return cudaErrorInvalidValue;
+    }
     if (a.beta == 0.0f && !a.wdense) a.beta = 1.0f;
     cudaError_t e;
-    if (a.wdense) e = bf16 ? launch_tc<1, 1, 1>(tm, tw, a, grid, smem, stream) : launch_tc<0, 1, 1>(tm, tw, a, grid, smem, stream);
-    else if (a.us == 2) e = bf16 ? launch_tc<1, 2, 0>(tm, tw, a, grid, smem, stream) : launch_tc<0, 2, 0>(tm, tw, a, grid, smem, stream);
-    else e = bf16 ? launch_tc<1, 1, 0>(tm, tw, a, grid, smem, stream) : launch_tc<0, 1, 0>(tm, tw, a, grid, smem, stream);
+    if (a.cg == 2 && a.wdense) e = bf16 ? launch_tc<1, 1, 1, 2>(tm, tw, ts, a, grid, smem, stream) : launch_tc<0, 1, 1, 2>(tm, tw, ts, a, grid, smem, stream);
+    else if (a.cg == 2) e = bf16 ? launch_tc<1, 1, 0, 2>(tm, tw, ts, a, grid, smem, stream) : launch_tc<0, 1, 0, 2>(tm, tw, ts, a, grid, smem, stream);
+    else if (a.wdense) e = bf16 ? launch_tc<1, 1, 1, 1>(tm, tw, ts, a, grid, smem, stream) : launch_tc<0, 1, 1, 1>(tm, tw, ts, a, grid, smem, stream);
+    else if (a.us == 2) e = bf16 ? launch_tc<1, 2, 0, 1>(tm, tw, ts, a, grid, smem, stream) : launch_tc<0, 2, 0, 1>(tm, tw, ts, a, grid, smem, stream);
+    else e = bf16 ? launch_tc<1, 1, 0, 1>(tm, tw, ts, a, grid, smem, stream) : launch_tc<0, 1, 0, 1>(tm, tw, ts, a, grid, smem, stream);
     if (e != cudaSuccess || !a.defer || grid.z < 2) return e;
     const dim3 rgrid(grid.x * grid.y, a.ntok_pad / 8);
     if (bf16) splitk_reduce_kernel<1><<<rgrid, 256, 0, stream>>>(a, (int)grid.z, (int)grid.x);

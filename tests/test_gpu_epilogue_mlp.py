@@ -128,9 +128,11 @@ def test_glu_and_residual_add_match_the_scalar_statements():
         torch.cuda.synchronize()
         want = orc.f16_bits_to_f32(orc.glu(both, m, n, act))
         got = y.float().cpu().numpy()
-        # device expf / tanhf against glibc's: at most the last f16 place
-        assert (np.abs(got - want) <= np.abs(want) * 2.0 ** -10 + 1e-7).all()
-        assert (got == want).mean() > 0.99
+        # the device's approximate exp2 / reciprocal against glibc's expf / tanhf and an exact division: at most the last f16 place
+        # (0.5 g (1 + tanh z) cancels for very negative g: there the f32 statement itself is only good to about |g u| 2^-22,
+        # and the inputs here stay below 16)
+        assert (np.abs(got - want) <= np.abs(want) * 2.0 ** -10 + 2.0 ** -16).all()
+        assert (got == want).mean() > 0.97
     dst = torch.from_numpy(rng.standard_normal(m * n).astype(np.float32)).cuda()
     want = dst.cpu().numpy().copy()
     src = orc.f32_to_f16_bits(rng.standard_normal(m * n).astype(np.float32))
