@@ -134,6 +134,22 @@ __device__ __forceinline__ uint16_t f32_to_t(float x) {
     return __half_as_ushort(__float2half_rn(x));
 }
 
+// Two f32 values rounded to T and back (one packed conversion each way), and two f32 values rounded to a pair of T bits.
+template <int BF16>
+__device__ __forceinline__ float2 round2_t(float a, float b) {
+    if (BF16) return __bfloat1622float2(__floats2bfloat162_rn(a, b));
+    return __half22float2(__floats2half2_rn(a, b));
+}
+template <int BF16>
+__device__ __forceinline__ uint32_t pack2_t(float a, float b) {
+    if (BF16) {
+        const __nv_bfloat162 v = __floats2bfloat162_rn(a, b);
+        return *reinterpret_cast<const uint32_t*>(&v);
+    }
+    const __half2 v = __floats2half2_rn(a, b);
+    return *reinterpret_cast<const uint32_t*>(&v);
+}
+
 __device__ __forceinline__ uint32_t lop3_and_or(uint32_t a, uint32_t mask, uint32_t orv) {
     uint32_t r;
     asm("lop3.b32 %0, %1, %2, %3, 0xea;" : "=r"(r) : "r"(a), "r"(mask), "r"(orv));  // (a & mask) | orv

@@ -146,12 +146,14 @@ __device__ __noinline__ void drain_glu(uint32_t lane_base, int ntok, int j_begin
         if (hcol >= hn) continue;
         uint16_t* dst = c + (size_t)(tok0 + j0) * hn + hcol;
         const int left = m - tok0 - j0;
+        // two tokens at a time: the roundings are packed conversions (the scalar ones share a quarter-rate pipe with exp2 / rcp)
 #pragma unroll
-        for (int j = 0; j < 16; ++j) {
-            const float gv = t_to_f32<BF16>(f32_to_t<BF16>(__uint_as_float(rg[j])));
-            const float uv = t_to_f32<BF16>(f32_to_t<BF16>(__uint_as_float(ru[j])));
-            const uint16_t v = f32_to_t<BF16>(__fmul_rn(glu_gate(act, gv), uv));
-            if (j < left) dst[(size_t)j * hn] = v;
+        for (int j = 0; j < 16; j += 2) {
+            const float2 gv = round2_t<BF16>(__uint_as_float(rg[j]), __uint_as_float(rg[j + 1]));
+            const float2 uv = round2_t<BF16>(__uint_as_float(ru[j]), __uint_as_float(ru[j + 1]));
+            const uint32_t v = pack2_t<BF16>(__fmul_rn(glu_gate(act, gv.x), uv.x), __fmul_rn(glu_gate(act, gv.y), uv.y));
+            if (j < left) dst[(size_t)j * hn] = (uint16_t)(v & 0xffffu);
+            if (j + 1 < left) dst[(size_t)(j + 1) * hn] = (uint16_t)(v >> 16);
         }
     }
 }
@@ -169,8 +171,11 @@ __device__ __noinline__ void drain_residual(uint32_t lane_base, int j_begin, int
 #pragma unroll
         for (int j = 0; j < 16; ++j) yv[j] = j < left ? dst[(size_t)j * n] : 0.0f;
 #pragma unroll
-        for (int j = 0; j < 16; ++j)
-            if (j < left) dst[(size_t)j * n] = __fadd_rn(yv[j], t_to_f32<BF16>(f32_to_t<BF16>(__uint_as_float(r[j]))));
+        for (int j = 0; j < 16; j += 2) {
+            const float2 v = round2_t<BF16>(__uint_as_float(r[j]), __uint_as_float(r[j + 1]));
+            if (j < left) dst[(size_t)j * n] = __fadd_rn(yv[j], v.x);
+            if (j + 1 < left) dst[(size_t)(j + 1) * n] = __fadd_rn(yv[j + 1], v.y);
+        }
     }
 }
 
@@ -195,8 +200,11 @@ __device__ __noinline__ void drain_store(uint32_t lane_base, int j_begin, int j_
         uint16_t* dst = c + (size_t)(tok0 + j0) * n + col;
         const int left = m - tok0 - j0;
 #pragma unroll
-        for (int j = 0; j < 16; ++j)
-            if (j < left) dst[(size_t)j * n] = f32_to_t<BF16>(__uint_as_float(r[j]));
+        for (int j = 0; j < 16; j += 2) {
+            const uint32_t v = pack2_t<BF16>(__uint_as_float(r[j]), __uint_as_float(r[j + 1]));
+            if (j < left) dst[(size_t)j * n] = (uint16_t)(v & 0xffffu);
+            if (j + 1 < left) dst[(size_t)(j + 1) * n] = (uint16_t)(v >> 16);
+        }
     }
 }
 
