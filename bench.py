@@ -709,7 +709,7 @@ def main():
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--tokens", dest="m", type=int, default=256, help="tokens per step (BASELINE.json: 1 or 256)")
-    ap.add_argument("--ref-rows", type=int, default=4, help="rows of the batch the CPU arm computes per step")
+    ap.add_argument("--ref-rows", type=int, default=32, help="rows of the batch the CPU arm computes per step")
     ap.add_argument("--no-kernels", action="store_true", help="skip the single-kernel configs")
     ap.add_argument("--no-m1", action="store_true", help="skip the one-token leg")
     ap.add_argument("--collective", default="peer", choices=["peer", "nccl"],

@@ -197,7 +197,11 @@ template <int BF16>
 __device__ __forceinline__ void fast_ep_apply16(const FastEp& f, const uint32_t (&acc)[16], uint16_t (&out)[16]) {
     float x[16];
 #pragma unroll
-    for (int j = 0; j < 16; ++j) x[j] = t_to_f32<BF16>(f32_to_t<BF16>(__uint_as_float(acc[j])));
+    for (int j = 0; j < 16; j += 2) {
+        const float2 v = round2_t<BF16>(__uint_as_float(acc[j]), __uint_as_float(acc[j + 1]));
+        x[j] = v.x;
+        x[j + 1] = v.y;
+    }
 #pragma unroll
     for (int q = 0; q < 4; ++q) {
         const int cls = f.cls[q];
@@ -249,7 +253,11 @@ __device__ __forceinline__ void fast_ep_apply16(const FastEp& f, const uint32_t 
         }
     }
 #pragma unroll
-    for (int j = 0; j < 16; ++j) out[j] = f32_to_t<BF16>(x[j]);
+    for (int j = 0; j < 16; j += 2) {
+        const uint32_t v = pack2_t<BF16>(x[j], x[j + 1]);
+        out[j] = (uint16_t)(v & 0xffffu);
+        out[j + 1] = (uint16_t)(v >> 16);
+    }
 }
 
 // The gate activation of the gated MLP product (act 3 = SiLU, else the tanh form of GELU), the same expression at every

@@ -208,6 +208,24 @@ __device__ __noinline__ void drain_store(uint32_t lane_base, int j_begin, int j_
     }
 }
 
+// The epilogue graphs that fit a FastEp (up to four slots of a scalar or per-column operand or an activation), row-major C.
+template <int BF16>
+__device__ __noinline__ void drain_fast_ep(uint32_t lane_base, int j_begin, int j_end, uint16_t* c, int m, int n, int col, int tok0, FastEp fe) {
+    for (int j0 = j_begin; j0 < j_end; j0 += 16) {
+        uint32_t r[16];
+        tmem_ld16(lane_base + (uint32_t)j0, r);
+        tmem_ld_wait();
+        if (col >= n) continue;
+        uint16_t v[16];
+        fast_ep_apply16<BF16>(fe, r, v);
+        uint16_t* dst = c + (size_t)(tok0 + j0) * n + col;
+        const int left = m - tok0 - j0;
+#pragma unroll
+        for (int j = 0; j < 16; ++j)
+            if (j < left) dst[(size_t)j * n] = v[j];
+    }
+}
+
 // The drain of a CTA's accumulators, out of line: its sixteen-wide register groups would otherwise set the register
 // budget of the role loops above (which then spill inside their per-stage latency chains).
 template <int BF16, int DENSE>
@@ -604,8 +622,9 @@ __global__ void __launch_bounds__(kTcThreads, 1) gemm_tc_kernel(const __grid_con
         const int ntok = p.ntok_pad;                               // a multiple of 32
         const int parts = (ntok % 64 == 0) ? 4 : 2;                // every part is whole groups of 16 tokens
         const int splits = (int)gridDim.z;
-        const bool plain = !p.c32 && !p.yacc && !p.glu && p.ep.n_nodes == 0 && !(DENSE && (p.col_major || p.beta != 1.0f));
-        if (num_stages > 0 && (splits > 1 || p.glu || p.yacc || plain)) {
+        const bool rowmajor_c = !p.c32 && !p.yacc && !p.glu && !(DENSE && (p.col_major || p.beta != 1.0f));
+        const bool plain = rowmajor_c && p.ep.n_nodes == 0, fast = rowmajor_c && p.ep.n_nodes > 0 && p.ep_fast;
+        if (num_stages > 0 && (splits > 1 || p.glu || p.yacc || plain || fast)) {
             if (warp < 4 * parts) {
                 mbar_wait(acc_full, 0, abort_flag, p.status, STATUS_TMEM_TIMEOUT);
                 tc_fence_after();
@@ -622,6 +641,14 @@ __global__ void __launch_bounds__(kTcThreads, 1) gemm_tc_kernel(const __grid_con
                 } else if (p.yacc) {
                     for (int w = 0; w < NW; ++w)
                         drain_residual<BF16>(lane_base + (uint32_t)(w * ntok), j_begin, j_end, p.yacc, p.m, p.n, col0 + 128 * w + 32 * q + lane, tok0);
+                } else if (fast) {
+                    const EpNodeDev* nodes = p.ep.n_nodes <= kMaxInlineNodes ? ep_nodes : p.ep.ext;
+                    for (int w = 0; w < NW; ++w) {
+                        const int col = col0 + 128 * w + 32 * q + lane;
+                        FastEp fe;
+                        fast_ep_build<BF16>(nodes, p.ep.n_nodes, col, col < p.n, fe);
+                        drain_fast_ep<BF16>(lane_base + (uint32_t)(w * ntok), j_begin, j_end, p.c, p.m, p.n, col, tok0, fe);
+                    }
                 } else {
                     for (int w = 0; w < NW; ++w)
                         drain_store<BF16>(lane_base + (uint32_t)(w * ntok), j_begin, j_end, p.c, p.m, p.n, col0 + 128 * w + 32 * q + lane, tok0);
@@ -806,7 +833,9 @@ void gemm_tc_plan(GemmTcArgs& a, int sm_count, dim3* grid, size_t* smem, size_t*
     a.us = (pad <= 64 && !a.wdense) ? 2 : 1;                        // small token tiles: two 64-deep units per stage halve the per-stage hand-offs
     // CTA pairs from 128 tokens up: a CTA then loads half the token rows per flop and the MMAs read half as much shared memory
     static const int env_cg = []() { const char* e = getenv("SMEG_TC_CG"); return e ? atoi(e) : 0; }();
-    a.cg = (a.us == 1 && pad >= 128 && col_tiles >= 2 && env_cg != 1) ? 2 : 1;
+    // (measured at 256 tokens: pairs gain a few percent on the 128-column tiles of the plain and down projections and
+    // lose as much on the 256-column tiles of the fused gate/up form; SMEG_TC_CG = 1 / 2 forces either)
+    a.cg = (a.us == 1 && pad >= 128 && col_tiles >= 2 && env_cg != 1 && (env_cg == 2 || !a.glu)) ? 2 : 1;
     const int stages_all = (a.ku + a.us - 1) / a.us;
     int splits = 1;
     {
