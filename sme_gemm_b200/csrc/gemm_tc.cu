@@ -127,6 +127,44 @@ __device__ __forceinline__ void dequant_unit_q4(unsigned char* tile, int cu, con
     *reinterpret_cast<uint4*>(tile + swz_off(row_hi, cb)) = (g & 1) ? v_hi_a : v_hi_b;
 }
 
+__device__ __forceinline__ uint4 lds128(uint32_t a) {
+    uint4 v;
+    asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "r"(a));
+    return v;
+}
+__device__ __forceinline__ uint32_t lds32(uint32_t a) {
+    uint32_t v;
+    asm volatile("ld.shared.u32 %0, [%1];" : "=r"(v) : "r"(a));
+    return v;
+}
+__device__ __forceinline__ void sts128(uint32_t a, uint4 v) {
+    asm volatile("st.shared.v4.u32 [%0], {%1,%2,%3,%4};" ::"r"(a), "r"(v.x), "r"(v.y), "r"(v.z), "r"(v.w) : "memory");
+}
+
+// The same expansion on addresses the caller keeps per lane (the role loop's per-stage work is then the waits, three
+// loads, the arithmetic and four stores).  `row` = shared address of the 128-byte row of column g in the operand tile
+// (column g + 8 lies 1024 bytes on), `off_first` / `off_second` = swizzled chunk offsets.  Lanes of odd g take the two
+// halves of the unit in the other order (the caller swaps the words and scale words), so that the eight lanes of a
+// quarter warp hit distinct banks in every store.
+template <int BF16>
+__device__ __forceinline__ void dequant_unit_q4_at(uint32_t row, uint32_t off_first, uint32_t off_second, const uint4 wv, uint32_t s_first,
+                                                   uint32_t s_second) {
+    __half2 w0[4], w1[4], w2[4], w3[4];
+    q4_word_codes(wv.x, w0);
+    q4_word_codes(wv.y, w1);
+    q4_word_codes(wv.z, w2);
+    q4_word_codes(wv.w, w3);
+    const __half2 lo_a[4] = {w0[0], w0[2], w1[0], w1[2]};
+    const __half2 lo_b[4] = {w2[0], w2[2], w3[0], w3[2]};
+    const __half2 hi_a[4] = {w0[1], w0[3], w1[1], w1[3]};
+    const __half2 hi_b[4] = {w2[1], w2[3], w3[1], w3[3]};
+    const __half2 sa = *reinterpret_cast<const __half2*>(&s_first), sb = *reinterpret_cast<const __half2*>(&s_second);
+    sts128(row + off_first, scale_chunk<BF16>(lo_a, __low2half(sa)));
+    sts128(row + off_second, scale_chunk<BF16>(lo_b, __low2half(sb)));
+    sts128(row + 1024u + off_first, scale_chunk<BF16>(hi_a, __high2half(sa)));
+    sts128(row + 1024u + off_second, scale_chunk<BF16>(hi_b, __high2half(sb)));
+}
+
 // The kernel's tensor maps: the token matrix, and for dense weights the weight matrix as well.
 template <int DENSE> struct TcMaps { CUtensorMap tok; CUtensorMap w; };
 template <> struct TcMaps<0> { CUtensorMap tok; CUtensorMap codes; CUtensorMap scales; };
@@ -500,7 +538,8 @@ __global__ void __launch_bounds__(kTcThreads, 1) gemm_tc_kernel(const __grid_con
         }
     } else if (warp == kDeqWarps + 1) {
         // ===================== MMA issuer =====================
-        // the whole warp walks the stages (converged); one elected lane issues
+        // The whole warp walks the stages, converged, and one elected lane issues: the descriptors and barrier addresses
+        // are then warp-uniform values.  (A loop run by one lane alone measured 10-25 % slower.)
         const uint32_t idesc = umma_idesc(BF16, 128 * CG, p.ntok_box);
         const uint32_t tok_half = (uint32_t)(tok_bytes / 2);
         RingPos tq, oq;
@@ -549,6 +588,54 @@ __global__ void __launch_bounds__(kTcThreads, 1) gemm_tc_kernel(const __grid_con
         const int wig = deq_groups == 2 ? (warp & 7) : warp;   // warp within its group
         RingPos dk, dq;                                        // packed ring (advanced once per PU stages), operand ring
         int iu = 0;                                            // stage within its packed slot
+        if (US == 1 && !dense) {
+            // One unit per warp and stage (8 NW column groups = the warps of a group): everything that does not change
+            // from stage to stage is formed here, once.
+            const int c = wig;                                  // this warp's column group within the CTA
+            // gate/up matrix: gate column groups go to operand tile 0 and the matching up groups to tile 1, so that a
+            // thread of the drain holds both values of one hidden unit (chunks of [2 gate | 2 up] groups)
+            const int tw = p.glu ? (c >> 1) & 1 : c >> 3, rg = p.glu ? ((c >> 2) << 1) | (c & 1) : c & 7;
+            const bool odd = (g & 1) != 0;
+            const uint32_t off_first = (uint32_t)(((odd ? 4 + t : t) ^ g) << 4), off_second = (uint32_t)(((odd ? t : 4 + t) ^ g) << 4);
+            const uint32_t row_off = (uint32_t)(tw * kWTile + rg * 2048 + g * 128);
+            const uint32_t code_off = (uint32_t)(((c << kbox_shift) * kUnitBytes) + lane * 16);
+            const uint32_t sc_off = (uint32_t)(8 * NW * k_code + c * rpg * 32 + 4 * g);
+            const uint32_t ring_k_a = smem_u32(ring_k), ring_o_a = smem_u32(ring_o);
+            const int L = p.log2_block, box_mask = (1 << kbox_shift) - 1;
+            int du = st_begin * kStageK, blk0 = du >> L;       // depth of the stage, first scale row of its packed slot
+            for (int i = 0; i < num_stages; ++i, du += kStageK, dq.next(O)) {
+                const int ks = dk.slot;
+                const bool last_of_slot = (iu == PU - 1) || (i == num_stages - 1);
+                if (iu == 0) blk0 = du >> L;
+                if (deq_groups == 1 || (i & 1) == (warp >> 3)) {
+                    const int os = dq.slot;
+                    if (dq.wrapped && !__all_sync(0xffffffffu, mbar_wait(&o_empty[os], dq.phase ^ 1u, abort_flag, p.status, STATUS_TMEM_TIMEOUT))) break;
+                    if (!__all_sync(0xffffffffu, mbar_wait(&k_full[ks], dk.phase, abort_flag, p.status, STATUS_TMEM_TIMEOUT))) break;
+                    const uint32_t pk = ring_k_a + (uint32_t)(ks * k_stride);
+                    uint4 wv = lds128(pk + code_off + (uint32_t)((iu >> kbox_shift) * kbox_bytes + (iu & box_mask) * kUnitBytes));
+                    const int ra = ((du + 8 * t) >> L) - blk0, rb = ((du + 32 + 8 * t) >> L) - blk0;
+                    uint32_t sa = lds32(pk + sc_off + (uint32_t)(ra * 32)), sb = lds32(pk + sc_off + (uint32_t)(rb * 32));
+                    if (odd) {
+                        uint32_t x = wv.x; wv.x = wv.z; wv.z = x;
+                        x = wv.y; wv.y = wv.w; wv.w = x;
+                        x = sa; sa = sb; sb = x;
+                    }
+                    dequant_unit_q4_at<BF16>(ring_o_a + (uint32_t)(os * o_stride) + row_off, off_first, off_second, wv, sa, sb);
+                    fence_proxy_async();
+                    __syncwarp();
+                    if (lane == 0) {
+                        if (CG == 2) mbar_arrive_cluster(o_full_lead + 8u * os);
+                        else mbar_arrive(&o_full[os]);
+                    }
+                }
+                // a warp that walks past the end of a packed slot releases it, whether it expanded this stage or not
+                if (last_of_slot) {
+                    __syncwarp();
+                    if (lane == 0) mbar_arrive(&k_empty[ks]);
+                }
+                if (++iu == PU) { iu = 0; dk.next(NK); }
+            }
+        } else
         for (int i = 0; i < (dense ? 0 : num_stages); ++i, dq.next(O), (++iu == PU ? (iu = 0, dk.next(NK)) : (void)0)) {
             const int ks = dk.slot;
             const bool last_of_slot = (iu == PU - 1) || (i == num_stages - 1);
@@ -833,9 +920,9 @@ void gemm_tc_plan(GemmTcArgs& a, int sm_count, dim3* grid, size_t* smem, size_t*
     a.us = (pad <= 64 && !a.wdense) ? 2 : 1;                        // small token tiles: two 64-deep units per stage halve the per-stage hand-offs
     // CTA pairs from 128 tokens up: a CTA then loads half the token rows per flop and the MMAs read half as much shared memory
     static const int env_cg = []() { const char* e = getenv("SMEG_TC_CG"); return e ? atoi(e) : 0; }();
-    // (measured at 256 tokens: pairs gain a few percent on the 128-column tiles of the plain and down projections and
-    // lose as much on the 256-column tiles of the fused gate/up form; SMEG_TC_CG = 1 / 2 forces either)
-    a.cg = (a.us == 1 && pad >= 128 && col_tiles >= 2 && env_cg != 1 && (env_cg == 2 || !a.glu)) ? 2 : 1;
+    // (measured at 256 and 512 tokens: 10-20 % faster than single CTAs, whose token tiles leave room for two operand
+    // slots only; SMEG_TC_CG = 1 / 2 forces either)
+    a.cg = (a.us == 1 && pad >= 128 && col_tiles >= 2 && env_cg != 1) ? 2 : 1;
     const int stages_all = (a.ku + a.us - 1) / a.us;
     int splits = 1;
     {
@@ -875,8 +962,10 @@ void gemm_tc_plan(GemmTcArgs& a, int sm_count, dim3* grid, size_t* smem, size_t*
                 if (left < 2 * tok_bytes) continue;
                 int nt = left / tok_bytes;
                 if (nt > 8) nt = 8;
-                // prefer: at least three token slots, then few copies per stage (large PU), then depth
-                const int score = (nt >= 3 ? 1000 : 0) + (pu > per_cta_stages ? 0 : pu * 50) + (no >= 3 ? 20 : 0) + nk * 5 + nt;
+                // prefer: at least three token slots, then three operand slots (with two, a stage's expansion cannot start
+                // before the MMAs two stages back have retired: measured 15 % slower at 512 tokens), then few copies per
+                // stage (large PU), then depth
+                const int score = (nt >= 3 ? 1000 : 0) + (no >= 3 ? 400 : 0) + (pu > per_cta_stages ? 0 : pu * 50) + nk * 5 + nt;
                 if (score > best_score) {
                     best_score = score;
                     a.pu = pu; a.rpg = rpg; a.no = no; a.nk = nk; a.nt = nt;
