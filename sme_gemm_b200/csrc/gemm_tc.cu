@@ -166,21 +166,33 @@ __device__ __forceinline__ void dequant_unit_q4_at(uint32_t row, uint32_t off_fi
 }
 
 // The kernel's tensor maps: the token matrix, and for dense weights the weight matrix as well.
-template <int DENSE> struct TcMaps { CUtensorMap tok; CUtensorMap w; };
-template <> struct TcMaps<0> { CUtensorMap tok; CUtensorMap codes; CUtensorMap scales; };
+template <int DENSE> struct TcMaps { CUtensorMap tok; CUtensorMap c; CUtensorMap w; };
+template <> struct TcMaps<0> { CUtensorMap tok; CUtensorMap c; CUtensorMap codes; CUtensorMap scales; };
 
 // The hot forms of the drain -- the gated product of a gate/up pair, the residual add of the down projection, the f32
 // partial tile of a depth slice, the plain rounded store -- out of line and on scalar arguments: sixteen accumulators
 // per tcgen05.ld, one thread per weight column (TMEM lane), lanes of a warp on consecutive columns of C.
 template <int BF16>
 __device__ __noinline__ void drain_glu(uint32_t lane_base, int ntok, int j_begin, int j_end, uint16_t* c, int m, int hn, int hcol, int tok0,
-                                       uint32_t act) {
+                                       uint32_t act, uint32_t stage) {
     // accumulator set 0 = gate, set 1 = up of hidden unit hcol (glu, src/linear.rs:804-835)
     for (int j0 = j_begin; j0 < j_end; j0 += 16) {
         uint32_t rg[16], ru[16];
         tmem_ld16(lane_base + (uint32_t)j0, rg);
         tmem_ld16(lane_base + (uint32_t)(ntok + j0), ru);
         tmem_ld_wait();
+        if (stage) {
+            // into the staging tile [token][128 columns]: the bulk store clips what lies outside C
+#pragma unroll
+            for (int j = 0; j < 16; j += 2) {
+                const float2 gv = round2_t<BF16>(__uint_as_float(rg[j]), __uint_as_float(rg[j + 1]));
+                const float2 uv = round2_t<BF16>(__uint_as_float(ru[j]), __uint_as_float(ru[j + 1]));
+                const uint32_t v = pack2_t<BF16>(__fmul_rn(glu_gate(act, gv.x), uv.x), __fmul_rn(glu_gate(act, gv.y), uv.y));
+                sts16(stage + (uint32_t)((j0 + j) * 256), (uint16_t)(v & 0xffffu));
+                sts16(stage + (uint32_t)((j0 + j + 1) * 256), (uint16_t)(v >> 16));
+            }
+            continue;
+        }
         if (hcol >= hn) continue;
         uint16_t* dst = c + (size_t)(tok0 + j0) * hn + hcol;
         const int left = m - tok0 - j0;
@@ -229,11 +241,20 @@ __device__ __noinline__ void drain_partial(uint32_t lane_base, int j_begin, int 
 }
 
 template <int BF16>
-__device__ __noinline__ void drain_store(uint32_t lane_base, int j_begin, int j_end, uint16_t* c, int m, int n, int col, int tok0) {
+__device__ __noinline__ void drain_store(uint32_t lane_base, int j_begin, int j_end, uint16_t* c, int m, int n, int col, int tok0, uint32_t stage) {
     for (int j0 = j_begin; j0 < j_end; j0 += 16) {
         uint32_t r[16];
         tmem_ld16(lane_base + (uint32_t)j0, r);
         tmem_ld_wait();
+        if (stage) {
+#pragma unroll
+            for (int j = 0; j < 16; j += 2) {
+                const uint32_t v = pack2_t<BF16>(__uint_as_float(r[j]), __uint_as_float(r[j + 1]));
+                sts16(stage + (uint32_t)((j0 + j) * 256), (uint16_t)(v & 0xffffu));
+                sts16(stage + (uint32_t)((j0 + j + 1) * 256), (uint16_t)(v >> 16));
+            }
+            continue;
+        }
         if (col >= n) continue;
         uint16_t* dst = c + (size_t)(tok0 + j0) * n + col;
         const int left = m - tok0 - j0;
@@ -248,14 +269,20 @@ __device__ __noinline__ void drain_store(uint32_t lane_base, int j_begin, int j_
 
 // The epilogue graphs that fit a FastEp (up to four slots of a scalar or per-column operand or an activation), row-major C.
 template <int BF16>
-__device__ __noinline__ void drain_fast_ep(uint32_t lane_base, int j_begin, int j_end, uint16_t* c, int m, int n, int col, int tok0, FastEp fe) {
+__device__ __noinline__ void drain_fast_ep(uint32_t lane_base, int j_begin, int j_end, uint16_t* c, int m, int n, int col, int tok0, FastEp fe,
+                                           uint32_t stage) {
     for (int j0 = j_begin; j0 < j_end; j0 += 16) {
         uint32_t r[16];
         tmem_ld16(lane_base + (uint32_t)j0, r);
         tmem_ld_wait();
-        if (col >= n) continue;
+        if (col >= n && !stage) continue;
         uint16_t v[16];
         fast_ep_apply16<BF16>(fe, r, v);
+        if (stage) {
+#pragma unroll
+            for (int j = 0; j < 16; ++j) sts16(stage + (uint32_t)((j0 + j) * 256), v[j]);
+            continue;
+        }
         uint16_t* dst = c + (size_t)(tok0 + j0) * n + col;
         const int left = m - tok0 - j0;
 #pragma unroll
@@ -718,13 +745,18 @@ __global__ void __launch_bounds__(kTcThreads, 1) gemm_tc_kernel(const __grid_con
                 const int q = warp & 3, part = warp >> 2;              // lane quarter, token part
                 const uint32_t lane_base = tmem_base + ((uint32_t)(32 * q) << 16);
                 const int j_begin = part * (ntok / parts), j_end = j_begin + ntok / parts;
+                // C leaves through shared memory: the rings are idle once the accumulators are complete (every load has
+                // landed, every MMA has retired), a thread stores its column of a [token][128 columns] tile there, and one
+                // thread sends the tiles off as tiled bulk stores, which clip at the edges of C
+                const bool staged = p.c_tma && splits == 1 && (p.glu || plain || fast);
+                const uint32_t stage_lane = smem_u32(ring_o) + (uint32_t)((32 * q + lane) * 2);
                 if (splits > 1) {
                     const int tile_id = blockIdx.y * gridDim.x + blockIdx.x;
                     float* ws_tile = p.ws + ((size_t)tile_id * splits + blockIdx.z) * (size_t)(NW * 128) * ntok;
                     for (int w = 0; w < NW; ++w)
                         drain_partial(lane_base + (uint32_t)(w * ntok), j_begin, j_end, ws_tile + (128 * w + 32 * q + lane), NW * 128);
                 } else if (p.glu) {
-                    drain_glu<BF16>(lane_base, ntok, j_begin, j_end, p.c, p.m, p.n >> 1, blockIdx.x * 128 + 32 * q + lane, tok0, (uint32_t)p.glu);
+                    drain_glu<BF16>(lane_base, ntok, j_begin, j_end, p.c, p.m, p.n >> 1, blockIdx.x * 128 + 32 * q + lane, tok0, (uint32_t)p.glu, staged ? stage_lane : 0u);
                 } else if (p.yacc) {
                     for (int w = 0; w < NW; ++w)
                         drain_residual<BF16>(lane_base + (uint32_t)(w * ntok), j_begin, j_end, p.yacc, p.m, p.n, col0 + 128 * w + 32 * q + lane, tok0);
@@ -734,13 +766,29 @@ __global__ void __launch_bounds__(kTcThreads, 1) gemm_tc_kernel(const __grid_con
                         const int col = col0 + 128 * w + 32 * q + lane;
                         FastEp fe;
                         fast_ep_build<BF16>(nodes, p.ep.n_nodes, col, col < p.n, fe);
-                        drain_fast_ep<BF16>(lane_base + (uint32_t)(w * ntok), j_begin, j_end, p.c, p.m, p.n, col, tok0, fe);
+                        drain_fast_ep<BF16>(lane_base + (uint32_t)(w * ntok), j_begin, j_end, p.c, p.m, p.n, col, tok0, fe, staged ? stage_lane + (uint32_t)(w * ntok * 256) : 0u);
                     }
                 } else {
                     for (int w = 0; w < NW; ++w)
-                        drain_store<BF16>(lane_base + (uint32_t)(w * ntok), j_begin, j_end, p.c, p.m, p.n, col0 + 128 * w + 32 * q + lane, tok0);
+                        drain_store<BF16>(lane_base + (uint32_t)(w * ntok), j_begin, j_end, p.c, p.m, p.n, col0 + 128 * w + 32 * q + lane, tok0, staged ? stage_lane + (uint32_t)(w * ntok * 256) : 0u);
                 }
                 tc_fence_before();
+                if (staged) {
+                    fence_proxy_async();
+                    named_barrier_sync(1, 128 * parts);
+                    if (warp == 0 && lane == 0) {
+                        const int tiles_out = p.glu ? 1 : NW;
+                        const int x0 = p.glu ? (int)blockIdx.x * 128 : col0;
+                        const int rows = ntok > 256 ? ntok / 2 : ntok;          // a box holds at most 256 rows
+                        const int ncols = p.glu ? p.n >> 1 : p.n;
+                        for (int w = 0; w < tiles_out; ++w)
+                            for (int r0 = 0; r0 < ntok; r0 += rows)
+                                if (x0 + 128 * w < ncols && tok0 + r0 < p.m)
+                                    tma_store_2d(&maps.c, smem_u32(ring_o) + (uint32_t)((w * ntok + r0) * 256), x0 + 128 * w, tok0 + r0);
+                        bulk_commit_group();
+                        bulk_wait_read_all();
+                    }
+                }
             }
         } else {
             drain_tile<BF16, DENSE>(p, tmem_base, warp, lane, num_stages, acc_full, abort_flag, ep_nodes, col0, tok0);
@@ -826,7 +874,7 @@ __global__ void __launch_bounds__(256) splitk_reduce_kernel(const __grid_constan
 }
 
 template <int BF16, int US, int DENSE, int CG>
-cudaError_t launch_tc(const CUtensorMap& tm, const CUtensorMap& tw, const CUtensorMap& ts, const GemmTcArgs& a, dim3 grid, size_t smem, cudaStream_t stream) {
+cudaError_t launch_tc(const CUtensorMap& tm, const CUtensorMap& tc, const CUtensorMap& tw, const CUtensorMap& ts, const GemmTcArgs& a, dim3 grid, size_t smem, cudaStream_t stream) {
     auto kern = gemm_tc_kernel<BF16, US, DENSE, CG>;
     static int attr_dev = -1;
     int dev = 0;
@@ -838,6 +886,7 @@ cudaError_t launch_tc(const CUtensorMap& tm, const CUtensorMap& tw, const CUtens
     }
     TcMaps<DENSE> maps;
     maps.tok = tm;
+    maps.c = tc;
     if constexpr (DENSE) maps.w = tw;
     else {
         maps.codes = tw;
@@ -1023,12 +1072,34 @@ cudaError_t gemm_tc_launch(GemmTcArgs a, int bf16, dim3 grid, size_t smem, cudaS
         if (r != CUDA_SUCCESS) return cudaErrorInvalidValue;
     }
     if (a.beta == 0.0f && !a.wdense) a.beta = 1.0f;
+    // C as a tensor for the bulk stores of the drain: row-major 16-bit rows that start on 16-byte boundaries, and room for a
+    // CTA's whole tile in the operand and token rings
+    CUtensorMap tc = tm;
+    a.c_tma = 0;
+    {
+        const size_t ncols = a.glu ? (size_t)a.n / 2 : (size_t)a.n;
+        const int rows = a.ntok_pad > 256 ? a.ntok_pad / 2 : a.ntok_pad;
+        const size_t tile_bytes = (size_t)(a.glu ? 1 : a.nw) * a.ntok_pad * 256;
+        const size_t ring_bytes = (size_t)a.no * a.nw * a.us * kWTile + (size_t)a.nt * a.us * a.ntok_pad * 128 / a.cg;
+        static const int env_ctma = []() { const char* e = getenv("SMEG_TC_CTMA"); return e ? atoi(e) : 1; }();
+        if (env_ctma && a.c && !a.c32 && !a.yacc && !(a.wdense && a.col_major) && grid.z == 1 && ncols % 8 == 0 && ((uintptr_t)a.c & 15) == 0 &&
+            tile_bytes <= ring_bytes) {
+            const cuuint64_t cdim[2] = {(cuuint64_t)ncols, (cuuint64_t)a.m};
+            const cuuint64_t cstride[1] = {(cuuint64_t)ncols * 2};
+            const cuuint32_t cbox[2] = {128, (cuuint32_t)rows};
+            r = tensor_map_encoder()(&tc, bf16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, (void*)a.c, cdim, cstride,
+                                     cbox, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
+                                     CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+            if (r != CUDA_SUCCESS) return cudaErrorInvalidValue;
+            a.c_tma = 1;
+        }
+    }
     cudaError_t e;
-    if (a.cg == 2 && a.wdense) e = bf16 ? launch_tc<1, 1, 1, 2>(tm, tw, ts, a, grid, smem, stream) : launch_tc<0, 1, 1, 2>(tm, tw, ts, a, grid, smem, stream);
-    else if (a.cg == 2) e = bf16 ? launch_tc<1, 1, 0, 2>(tm, tw, ts, a, grid, smem, stream) : launch_tc<0, 1, 0, 2>(tm, tw, ts, a, grid, smem, stream);
-    else if (a.wdense) e = bf16 ? launch_tc<1, 1, 1, 1>(tm, tw, ts, a, grid, smem, stream) : launch_tc<0, 1, 1, 1>(tm, tw, ts, a, grid, smem, stream);
-    else if (a.us == 2) e = bf16 ? launch_tc<1, 2, 0, 1>(tm, tw, ts, a, grid, smem, stream) : launch_tc<0, 2, 0, 1>(tm, tw, ts, a, grid, smem, stream);
-    else e = bf16 ? launch_tc<1, 1, 0, 1>(tm, tw, ts, a, grid, smem, stream) : launch_tc<0, 1, 0, 1>(tm, tw, ts, a, grid, smem, stream);
+    if (a.cg == 2 && a.wdense) e = bf16 ? launch_tc<1, 1, 1, 2>(tm, tc, tw, ts, a, grid, smem, stream) : launch_tc<0, 1, 1, 2>(tm, tc, tw, ts, a, grid, smem, stream);
+    else if (a.cg == 2) e = bf16 ? launch_tc<1, 1, 0, 2>(tm, tc, tw, ts, a, grid, smem, stream) : launch_tc<0, 1, 0, 2>(tm, tc, tw, ts, a, grid, smem, stream);
+    else if (a.wdense) e = bf16 ? launch_tc<1, 1, 1, 1>(tm, tc, tw, ts, a, grid, smem, stream) : launch_tc<0, 1, 1, 1>(tm, tc, tw, ts, a, grid, smem, stream);
+    else if (a.us == 2) e = bf16 ? launch_tc<1, 2, 0, 1>(tm, tc, tw, ts, a, grid, smem, stream) : launch_tc<0, 2, 0, 1>(tm, tc, tw, ts, a, grid, smem, stream);
+    else e = bf16 ? launch_tc<1, 1, 0, 1>(tm, tc, tw, ts, a, grid, smem, stream) : launch_tc<0, 1, 0, 1>(tm, tc, tw, ts, a, grid, smem, stream);
     if (e != cudaSuccess || !a.defer || grid.z < 2) return e;
     const dim3 rgrid(grid.x * grid.y, a.ntok_pad / 8);
     if (bf16) splitk_reduce_kernel<1><<<rgrid, 256, 0, stream>>>(a, (int)grid.z, (int)grid.x);

@@ -151,6 +151,7 @@ struct GemmTcArgs {
     int ep_fast;                  // the graph runs as a per-thread FastEp (see epilogue.cuh)
     int nt, nk, no, nw;           // ring depths (tokens / packed / operand), accumulator sets per CTA
     int us;                       // 64-deep units per stage (2 for small token tiles)
+    int c_tma;                    // launcher-filled: C leaves through shared memory and tiled bulk stores (16-byte aligned rows of C)
     int cg;                       // CTAs per MMA: 2 = pairs of CTAs (a cluster of two along x) run MMAs of 256 weight columns
     int pu;                       // stages covered by one packed-ring slot
     int rpg;                      // scale rows staged per packed-ring slot
