@@ -675,9 +675,18 @@ static int lowbit_dev(const smeg_lowbit* w, const uint16_t* a, uint16_t* c, size
         // quantise first, into stream-ordered scratch; above the direct kernels' rows the block sums run on the
         // tensor cores (lowbit_tc.cu), which wants the per-block scales and sums block-major as well
         const bool tc = (int)m > g_direct_rows && g_lowbit_tc > 0 && (int)m >= g_lowbit_tc && lowbit_tc_supported(w->bits, (int)m, (int)k, w->d.log2_block);
+        // between the two, warp-level tensor-core instructions (lowbit_mma.cu); SMEG_LOWBIT_MMA=0 leaves those row counts
+        // to the staged dp4a kernel
+        static const int use_mma = []() { const char* e = getenv("SMEG_LOWBIT_MMA"); return e ? atoi(e) : 1; }();
+        bool mma = false;
+        if (!tc && use_mma && (int)m > g_direct_rows && m <= 16) {
+            LowbitGemvArgs probe = g;
+            probe.qh = (const uint16_t*)1; probe.sa = (const float*)1; probe.qsum = (const int32_t*)1;   // set below
+            mma = lowbit_mma_supported(probe, ds->sm_count);
+        }
         const size_t mpad = (m + 63) / 64 * 64;
         const size_t q_bytes = (m * kq + 255) / 256 * 256, sa_bytes = (m * nb * 4 + 255) / 256 * 256;
-        const size_t t_bytes = tc ? (mpad * nb * 4 + 255) / 256 * 256 : 0, qh_bytes = tc ? (m * kq * 2 + 255) / 256 * 256 : 0;
+        const size_t t_bytes = tc ? (mpad * nb * 4 + 255) / 256 * 256 : 0, qh_bytes = (tc || mma) ? ((m + 7) / 8 * 8 * kq * 2 + 255) / 256 * 256 : 0;
         if (cudaMallocAsync(&ws, q_bytes + 2 * sa_bytes + 2 * t_bytes + qh_bytes + 256, stream) != cudaSuccess) {
             if (ext) cudaFreeAsync(ext, stream);
             return -2;
@@ -685,7 +694,7 @@ static int lowbit_dev(const smeg_lowbit* w, const uint16_t* a, uint16_t* c, size
         ActQuantArgs aq;
         memset(&aq, 0, sizeof(aq));
         aq.a = a; aq.q = (int8_t*)ws; aq.sa = (float*)(ws + q_bytes);
-        aq.qsum = (w->bits == 1 || tc) ? (int32_t*)(ws + q_bytes + sa_bytes) : nullptr;
+        aq.qsum = (w->bits == 1 || tc || mma) ? (int32_t*)(ws + q_bytes + sa_bytes) : nullptr;
         aq.m = (int)m; aq.k = (int)k; aq.kq = (int)kq; aq.nbq = (int)nb; aq.log2_block = w->d.log2_block;
         if (tc) {
             aq.sa_t = (float*)(ws + q_bytes + 2 * sa_bytes);
@@ -693,8 +702,14 @@ static int lowbit_dev(const smeg_lowbit* w, const uint16_t* a, uint16_t* c, size
             aq.qh = (uint16_t*)(ws + q_bytes + 2 * sa_bytes + 2 * t_bytes);
             aq.mpad = (int)mpad;
         }
+        if (mma) {
+            aq.qh = (uint16_t*)(ws + q_bytes + 2 * sa_bytes + 2 * t_bytes);
+            aq.qh_perm = w->bits == 1 ? 1 : 0;
+            // the rows up to the next multiple of eight are zero rows (the kernel's B fragments read whole tiles of eight)
+            if (m % 8 != 0) cudaMemsetAsync(aq.qh + m * kq, 0, (8 - m % 8) * kq * 2, stream);
+        }
         e = act_quant_launch(aq, stream);
-        g.q = aq.q; g.sa = aq.sa; g.qsum = aq.qsum;
+        g.q = aq.q; g.sa = aq.sa; g.qsum = aq.qsum; g.qh = aq.qh;
         if (e == cudaSuccess) {
             if (tc) {
                 LowbitTcArgs t;
@@ -705,7 +720,8 @@ static int lowbit_dev(const smeg_lowbit* w, const uint16_t* a, uint16_t* c, size
                 t.n16 = (int)w->d.n16; t.ku = (int)w->d.ku; t.nb = (int)nb; t.nb_real = (int)w->d.nb_real;
                 t.log2_block = w->d.log2_block; t.bits = w->bits; t.lut = w->lut ^ 0x80808080u; t.status = ds->status; t.ep = g.ep;
                 e = lowbit_tc_launch(t, stream);
-            } else if ((int)m <= g_direct_rows && lowbit_direct_supported(g, false)) e = lowbit_direct_launch(g, w->bits, ds->sm_count, stream);
+            } else if (mma) e = lowbit_mma_launch(g, w->bits, ds->sm_count, stream);
+            else if ((int)m <= g_direct_rows && lowbit_direct_supported(g, false)) e = lowbit_direct_launch(g, w->bits, ds->sm_count, stream);
             else e = lowbit_gemv_launch(g, w->bits, ds->sm_count, stream);
         }
         if (e == cudaSuccess && q_out)

@@ -69,7 +69,8 @@ struct ActQuantArgs {
     float* sa;            // m x nbq per-block activation scales (amax / 127), padded blocks 0
     int32_t* qsum;        // m x nbq per-block sums of q (1-bit path only; may be null)
     int m, k, kq, nbq, log2_block;
-    uint16_t* qh;         // optional: the codes as f16 integers, m x kq, for the tensor-core kernel
+    uint16_t* qh;         // optional: the codes as f16 integers, m x kq, for the tensor-core kernels
+    int qh_perm;          // qh holds every run of 8 depths in the order 0 2 1 3 4 6 5 7 (B fragments of the 1-bit mma kernel)
     float* sa_t;          // optional: the same scales as nbq x mpad (block-major), for the tensor-core kernel
     int32_t* qsum_t;      // optional: the same sums as nbq x mpad
     int mpad;
@@ -83,7 +84,8 @@ struct LowbitGemvArgs {
     int a_vec_ok;                 // rows of a are 16-byte aligned
     const int8_t* q;              // m x kq
     const float* sa;              // m x nb
-    const int32_t* qsum;          // m x nb (1-bit)
+    const int32_t* qsum;          // m x nb (1-bit; the mma kernel reads it for 2-bit weights too)
+    const uint16_t* qh;           // mma kernel: the codes as f16, (m rounded up to 8) x kq with zero rows past m, runs of 8 depths in fragment order
     uint16_t* c;                  // m x n f16 bits
     int32_t* sums_out;            // optional debug: m x n x nb_real exact block sums
     int8_t* q_out;                // optional debug (with a): m x k int8 codes
@@ -104,6 +106,10 @@ bool lowbit_gemv_fuses_quant(LowbitGemvArgs a, int bits, int sm_count);
 // itself (a.a set, at most two rows); otherwise a.q / a.sa / a.qsum come from act_quant_kernel.
 bool lowbit_direct_supported(const LowbitGemvArgs& a, bool fused);
 cudaError_t lowbit_direct_launch(LowbitGemvArgs a, int bits, int sm_count, cudaStream_t stream);
+// Up to sixteen rows on warp-level tensor-core instructions, exact block sums (lowbit_mma.cu); a.q / a.sa / a.qsum from
+// act_quant_kernel (a.qsum for 2-bit weights as well).
+bool lowbit_mma_supported(const LowbitGemvArgs& a, int sm_count);
+cudaError_t lowbit_mma_launch(LowbitGemvArgs a, int bits, int sm_count, cudaStream_t stream);
 
 // ---- 2-bit / 1-bit x int8 activations on tcgen05 kind::i8 (lowbit_tc.cu) ----
 struct LowbitTcArgs {

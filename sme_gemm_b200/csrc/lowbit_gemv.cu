@@ -84,7 +84,7 @@ __global__ void __launch_bounds__(128) act_quant_kernel(ActQuantArgs p) {
             else v = (int)fminf(fmaxf(r, -128.0f), 127.0f);
         }
         qr[d] = (int8_t)v;
-        if (p.qh) p.qh[(size_t)row * p.kq + d] = __half_as_ushort(__int2half_rn(v));
+        if (p.qh) p.qh[(size_t)row * p.kq + (p.qh_perm ? ((d & ~(size_t)3) | ((d & 1) << 1) | ((d >> 1) & 1)) : d)] = __half_as_ushort(__int2half_rn(v));
         local += v;
     }
 #pragma unroll
