@@ -269,11 +269,24 @@ def kernel_cases(torch, sg, orc):
         return ((lambda i: sg.matmul_q4_bf16_ep(ab, ws[i], cb, 512, ep4)), len(ws),
                 {"config": "q4_prefill_gemm_bf16_512x4096x14336_addcol_silu_clamp", "flops": 2.0 * 512 * k * n})
 
-    return {"q4_gemv": q4_gemv, "q2_gemv": q2_gemv, "q1_gemv": q1_gemv, "q4_prefill": q4_prefill}
+    def q1_prefill():
+        # the int8-activation path at prompt size: 1-bit weights, 512 rows (exact int32 block sums on the f16 tensor-core
+        # path, ordered f32 fold); operations = 2 m n k, against the measured f16/bf16 tensor peak
+        n = 14336
+        signs = rng.integers(0, 256, k * n // 8).astype(np.uint8)
+        sc = rng.uniform(0.005, 0.03, n * (k // 128)).astype(np.float16).view(np.uint16)
+        ws = [sg.Q1Weights.new(signs, sc, sg.WeightLayout.OutIn, n, k, 128) for _ in range(4)]
+        a = torch.randn(512, k, device="cuda", dtype=torch.float16)
+        c = torch.zeros(512, n, device="cuda", dtype=torch.float16)
+        return ((lambda i: sg.matmul_q1(a, ws[i], c, 512)), len(ws),
+                {"config": "q1_int8act_prefill_512x4096x14336", "flops": 2.0 * 512 * k * n,
+                 "note": "activation int8 quantisation pass included; 4 weight sets of 7.3 MB rotate (tokens and output exceed the L2 share)"})
+
+    return {"q4_gemv": q4_gemv, "q2_gemv": q2_gemv, "q1_gemv": q1_gemv, "q4_prefill": q4_prefill, "q1_prefill": q1_prefill}
 
 
 def kernel_configs(torch, sg, orc, peaks):
-    """The four single-kernel configs on one GPU, timed by CUDA-graph replay."""
+    """The single-kernel configs on one GPU, timed by CUDA-graph replay."""
     out = []
     for name, build in kernel_cases(torch, sg, orc).items():
         fn, nsets, d = build()
@@ -286,7 +299,7 @@ def kernel_configs(torch, sg, orc, peaks):
             tf = d["flops"] / us / 1e6
             out.append({"config": d["config"], "us": us, "value": tf, "unit": "TFLOP/s",
                         "frac_of_measured_bf16_burst": tf / peaks["bf16_tflops"], "frac_of_nominal_2250": tf / 2250.0,
-                        "algorithmic_flops": d["flops"]})
+                        "algorithmic_flops": d["flops"], **({"note": d["note"]} if "note" in d else {})})
         del fn
     return out
 
@@ -715,7 +728,7 @@ def main():
     ap.add_argument("--collective", default="peer", choices=["peer", "nccl"],
                     help="N > 1: fused sum + finish over peer memory (this library's kernel) or NCCL all-reduce + finishing pass")
     ap.add_argument("--profile-case", default=None,
-                    choices=["q4_gemv", "q2_gemv", "q1_gemv", "q4_prefill", "mlp_gate_up", "mlp_down"],
+                    choices=["q4_gemv", "q2_gemv", "q1_gemv", "q4_prefill", "q1_prefill", "mlp_gate_up", "mlp_down"],
                     help="run six plain launches of one kernel and exit (for profiler captures)")
     args = ap.parse_args()
     if args.profile_case:

@@ -232,7 +232,7 @@ struct HostEp {
     std::vector<EpNode> nodes;
     ep_desc16 desc{0, nullptr};
     void* dbuf = nullptr;
-    ~HostEp() { if (dbuf) cudaFree(dbuf); }
+    ~HostEp() { if (dbuf) cudaFreeAsync(dbuf, 0); }
     int build(const ep_desc16* ep, size_t m, size_t n) {
         if (!ep || ep->n_nodes == 0 || !ep->nodes) return 0;
         nodes.assign(ep->nodes, ep->nodes + ep->n_nodes);
@@ -254,7 +254,7 @@ struct HostEp {
             total += (l * 2 + 15) / 16 * 16;
         }
         if (total) {
-            if (cudaMalloc(&dbuf, total) != cudaSuccess) return -2;
+            if (cudaMallocAsync(&dbuf, total, 0) != cudaSuccess) return -2;   // (cached by the pool: no synchronising allocation per call)
             for (size_t i = 0; i < nodes.size(); ++i)
                 if (len[i]) {
                     if (cudaMemcpy((char*)dbuf + off[i], nodes[i].ptr, len[i] * 2, cudaMemcpyHostToDevice) != cudaSuccess) return -2;
@@ -953,15 +953,18 @@ int smeg_f16_to_f32_dev(float* dst, const uint16_t* src, size_t len, void* strea
 // ---------------------------------------------------------------------------
 }  // extern "C"
 namespace {
+// Device staging of a host-pointer call: stream-ordered allocations on the default stream, which the device's pool keeps
+// cached between calls (its release threshold is raised when the device is first used), so that a call neither
+// synchronises the device for an allocation nor returns memory to the driver.
 struct DevBuf {
     void* p = nullptr;
-    ~DevBuf() { if (p) cudaFree(p); }
-    int alloc(size_t bytes) { return cudaMalloc(&p, bytes ? bytes : 16) == cudaSuccess ? 0 : -2; }
+    ~DevBuf() { if (p) cudaFreeAsync(p, 0); }
+    int alloc(size_t bytes) { return cudaMallocAsync(&p, bytes ? bytes : 16, 0) == cudaSuccess ? 0 : -2; }
 };
 
 // status word check after a synchronous call
 int finish_sync(DeviceState* ds) {
-    if (cudaDeviceSynchronize() != cudaSuccess) return -6;
+    if (cudaStreamSynchronize(0) != cudaSuccess) return -6;
     unsigned v = 0;
     if (cudaMemcpy(&v, ds->status, sizeof(v), cudaMemcpyDeviceToHost) != cudaSuccess) return -6;
     if (v) {
