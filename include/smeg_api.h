@@ -97,8 +97,11 @@ typedef struct smeg_dense smeg_dense;    /* Packed<f16> / Packed<bf16>, src/elem
 /* Q4Weights::with_params (src/kernels/q4/weights.rs:63-123).  quants: ceil(k*n/2)
  * bytes, weight idx = d*n + j in nibble idx%2 (low first), signed 4-bit codes;
  * scales (and mins, NULL for Q4_0): n*ceil(k/block) f16 bits at [j*nbk + blk].
- * block: power of two.  Returns -1 for a bad block size (csrc/gemm_f16f16_q4.h:474),
- * -3 for the affine form (mins != NULL), which this build does not run yet. */
+ * block: power of two.  Returns -1 for a bad block size (csrc/gemm_f16f16_q4.h:474).
+ * The affine form (Q4_1, mins != NULL: weight = scale * code + min) is kept as given and runs through dense twins
+ * of the reference's expanded weights -- round_T(f64(scale) * code + f64(min)), src/kernels/q4/weights.rs:250-256 --
+ * one per operand type, built on the first call of that type (2 bytes per weight of device memory each).  The
+ * fused forms of the MLP block (smeg_mlp_create) take Q4_0 handles only and return -3 for an affine one. */
 int smeg_q4_create(const uint8_t *quants, const uint16_t *scales, const uint16_t *mins, size_t n,
                    size_t k, size_t block, smeg_q4 **out);
 /* Q4Weights::quantize (src/kernels/q4/quantize.rs:29-81). */
@@ -186,7 +189,8 @@ int smeg_matmul_lowbit_dev(const smeg_lowbit *w, const uint16_t *a, uint16_t *c,
  * weights f16(scale * value) as Codes::dequant (:178-197) rounds them, f32 accumulation on
  * the tensor cores.  The first such call on a handle builds a 4-bit twin of the weights on
  * the device (synchronously; smeg_lowbit_prepare_f16 does it ahead of time, e.g. before a
- * stream capture).  A 2-bit codebook with a value outside [-8, 7] has no twin: rc = -3. */
+ * stream capture).  A 2-bit codebook with a value outside [-8, 7] does not fit 4-bit codes: its twin is a dense f16
+ * matrix of the same rounded weights (2 bytes per weight). */
 int smeg_lowbit_prepare_f16(const smeg_lowbit *w);
 int smeg_matmul_lowbit_f16_dev(const smeg_lowbit *w, const uint16_t *a, uint16_t *c, size_t m,
                                const ep_desc16 *ep, void *stream);
@@ -240,7 +244,8 @@ size_t smeg_dense_k(const smeg_dense *w);
 /* Gemm::run (src/exec/builder.rs:803-813 -> packed_ep_impl, src/exec/macros.rs:98-200):
  * C = ep( T(beta * (A @ B)) ), C row-major m x n or, with col_major, c[i + j * m].  Replaces
  * gemm_sme_f16f16_run_packed / gemm_sme_b16b16_run_packed (csrc/sme_gemm_api.h) for this use.
- * k must be a multiple of 8 and a 16-byte aligned (rc = -3 otherwise). */
+ * Any k: a depth that is not a multiple of 8, or an A whose rows do not start on 16-byte boundaries, is staged through a
+ * zero-padded copy of A in stream-ordered scratch (k == 0 is refused: rc = -3). */
 int smeg_gemm_dense_dev(const smeg_dense *w, const uint16_t *a, uint16_t *c, size_t m, uint16_t beta_bits,
                         int col_major, const ep_desc16 *ep, void *stream);
 int smeg_gemm_dense(const smeg_dense *w, const uint16_t *a, uint16_t *c, size_t m, uint16_t beta_bits,

@@ -8,6 +8,7 @@
 #include <string.h>
 
 #include <chrono>
+#include <cmath>
 #include <map>
 #include <utility>
 #include <mutex>
@@ -300,6 +301,20 @@ unsigned smeg_last_status(void) {
 void smeg_trace(int on) { g_trace = on ? 1 : 0; }
 
 // ---- Q4 handles ----
+// An affine handle keeps the logical arrays; its dense twins are built by q4_affine_twin on first use.
+static int q4_finish_affine(std::vector<uint8_t>& quants, std::vector<uint16_t>& scales, std::vector<uint16_t>& mins, size_t n, size_t k,
+                            size_t block, smeg_q4** out) {
+    if (!dev_state()) return -5;
+    smeg_q4* h = new smeg_q4();
+    h->d = make_dims(n, k, block, kQ4UnitDepth);
+    h->affine = true;
+    h->h_quants.swap(quants);
+    h->h_scales.swap(scales);
+    h->h_mins.swap(mins);
+    *out = h;
+    return 0;
+}
+
 static int q4_finish(const std::vector<uint8_t>& quants, const std::vector<uint16_t>& scales, size_t n, size_t k,
                      size_t block, smeg_q4** out) {
     if (!dev_state()) return -5;
@@ -323,11 +338,14 @@ int smeg_q4_create(const uint8_t* quants, const uint16_t* scales, const uint16_t
     if (!out) return -4;
     *out = nullptr;
     if (!is_pow2(block)) return -1;
-    if (mins) return -3;
     if (mul_overflows(n, k) || ((n != 0 && k != 0) && (!quants || !scales))) return -4;
     const size_t nbk = div_up(k, block);
     std::vector<uint8_t> q(quants, quants + (n * k + 1) / 2);
     std::vector<uint16_t> s(scales, scales + n * nbk);
+    if (mins) {
+        std::vector<uint16_t> mn(mins, mins + n * nbk);
+        return q4_finish_affine(q, s, mn, n, k, block, out);
+    }
     return q4_finish(q, s, n, k, block, out);
 }
 
@@ -335,11 +353,11 @@ int smeg_q4_quantize(const float* w, int layout, size_t n, size_t k, size_t bloc
     if (!out) return -4;
     *out = nullptr;
     if (!is_pow2(block)) return -1;
-    if (affine) return -3;
     if (mul_overflows(n, k) || ((n != 0 && k != 0) && !w)) return -4;
     std::vector<uint8_t> q;
     std::vector<uint16_t> s, mn;
-    q4_quantize_host(w, layout, n, k, block, 0, q, s, mn);
+    q4_quantize_host(w, layout, n, k, block, affine ? 1 : 0, q, s, mn);
+    if (affine) return q4_finish_affine(q, s, mn, n, k, block, out);
     return q4_finish(q, s, n, k, block, out);
 }
 
@@ -348,16 +366,18 @@ int smeg_q4_from_band(const uint8_t* nibbles, const uint16_t* scales, const uint
     if (!out) return -4;
     *out = nullptr;
     if (!is_pow2(block)) return -1;
-    if (mins) return -3;
     if (mul_overflows(n, k) || ((n != 0 && k != 0) && (!nibbles || !scales))) return -4;
     std::vector<uint8_t> q;
     std::vector<uint16_t> s, mn;
-    q4_from_band(nibbles, scales, nullptr, n, k, block, q, s, mn);
+    q4_from_band(nibbles, scales, mins, n, k, block, q, s, mn);
+    if (mins) return q4_finish_affine(q, s, mn, n, k, block, out);
     return q4_finish(q, s, n, k, block, out);
 }
 
 void smeg_q4_destroy(smeg_q4* w) {
     if (!w) return;
+    if (smeg_dense* t = w->twin_f16.load()) smeg_dense_destroy(t);
+    if (smeg_dense* t = w->twin_bf16.load()) smeg_dense_destroy(t);
     if (w->codes) cudaFree(w->codes);
     if (w->scales) cudaFree(w->scales);
     delete w;
@@ -365,10 +385,18 @@ void smeg_q4_destroy(smeg_q4* w) {
 size_t smeg_q4_n(const smeg_q4* w) { return w->d.n; }
 size_t smeg_q4_k(const smeg_q4* w) { return w->d.k; }
 size_t smeg_q4_block(const smeg_q4* w) { return w->d.block; }
-size_t smeg_q4_device_bytes(const smeg_q4* w) { return w->code_bytes + w->scale_elems * 2; }
+size_t smeg_q4_device_bytes(const smeg_q4* w) {
+    if (w->affine) return ((w->twin_f16.load() ? 1 : 0) + (w->twin_bf16.load() ? 1 : 0)) * w->d.n * ((w->d.k + 7) / 8 * 8) * 2;
+    return w->code_bytes + w->scale_elems * 2;
+}
 
 int smeg_q4_unpack(const smeg_q4* w, uint8_t* quants, uint16_t* scales) {
     if (!w || !quants || !scales) return -4;
+    if (w->affine) {
+        memcpy(quants, w->h_quants.data(), w->h_quants.size());
+        memcpy(scales, w->h_scales.data(), w->h_scales.size() * 2);
+        return 0;
+    }
     std::vector<uint8_t> codes(w->code_bytes);
     std::vector<uint16_t> sc(w->scale_elems);
     if (w->code_bytes && cudaMemcpy(codes.data(), w->codes, w->code_bytes, cudaMemcpyDeviceToHost) != cudaSuccess) return -2;
@@ -568,6 +596,66 @@ static bool q4_uses_tc(const smeg_q4* w, const uint16_t* a, size_t m) {
     return (int)m > g_tc_min_rows && gemm_tc_supported(4, (int)m, (int)w->d.k, w->d.log2_block, a);
 }
 
+static float half_bits_to_float(uint16_t h) {
+    const uint32_t sign = (uint32_t)(h & 0x8000u) << 16, ex = (h >> 10) & 0x1fu, man = h & 0x3ffu;
+    float f;
+    if (ex == 0) {
+        f = std::ldexp((float)man, -24);
+        return sign ? -f : f;
+    }
+    const uint32_t bits = ex == 31 ? (sign | 0x7f800000u | (man << 13)) : (sign | ((ex + 112u) << 23) | (man << 13));
+    memcpy(&f, &bits, 4);
+    return f;
+}
+// f64 -> f16 bits, round to nearest even, one rounding (the values here are far from overflow; handled all the same).
+static uint16_t f64_to_f16_bits(double v) {
+    if (v != v) return 0x7e00;
+    const uint16_t sign = std::signbit(v) ? 0x8000 : 0;
+    const double a = std::fabs(v);
+    if (a >= 65520.0) return sign | 0x7c00;
+    if (a < 6.103515625e-05) return sign | (uint16_t)std::nearbyint(a * 16777216.0);   // subnormal: quantum 2^-24
+    int e;
+    (void)std::frexp(a, &e);
+    int m10 = (int)std::nearbyint((std::ldexp(a, 1 - e) - 1.0) * 1024.0), ex = e - 1 + 15;
+    if (m10 == 1024) { m10 = 0; ++ex; }
+    if (ex >= 31) return sign | 0x7c00;
+    return sign | (uint16_t)(ex << 10) | (uint16_t)m10;
+}
+static uint16_t f32_to_bf16_bits(float f) {
+    uint32_t x;
+    memcpy(&x, &f, 4);
+    if ((x & 0x7fffffffu) > 0x7f800000u) return (uint16_t)((x >> 16) | 0x40);
+    return (uint16_t)((x + 0x7fffu + ((x >> 16) & 1u)) >> 16);
+}
+
+// The dense twin of an affine handle for one operand type: W[n][kd] = round_T(f64(scale) * code + f64(min)), T = f16
+// straight from f64, bf16 through f32 (dequant_rows, src/kernels/q4/weights.rs:232-259).
+static int q4_affine_twin(const smeg_q4* w, int bf16, const smeg_dense** out) {
+    std::atomic<smeg_dense*>& slot = bf16 ? w->twin_bf16 : w->twin_f16;
+    smeg_dense* t = slot.load(std::memory_order_acquire);
+    if (t) { *out = t; return 0; }
+    std::lock_guard<std::mutex> lock(w->twin_lock);
+    t = slot.load(std::memory_order_acquire);
+    if (t) { *out = t; return 0; }
+    const size_t n = w->d.n, k = w->d.k, block = w->d.block, nbk = div_up(k, block), kd = (k + 7) / 8 * 8;
+    std::vector<uint16_t> dense(n * kd, 0);
+    for (size_t d = 0; d < k; ++d)
+        for (size_t j = 0; j < n; ++j) {
+            const size_t idx = d * n + j;
+            const int nib = (idx % 2 == 0) ? (w->h_quants[idx / 2] & 0x0f) : (w->h_quants[idx / 2] >> 4);
+            const int code = nib < 8 ? nib : nib - 16;
+            const size_t si = j * nbk + d / block;
+            const double v = (double)half_bits_to_float(w->h_scales[si]) * (double)code + (double)half_bits_to_float(w->h_mins[si]);
+            dense[j * kd + d] = bf16 ? f32_to_bf16_bits((float)v) : f64_to_f16_bits(v);
+        }
+    smeg_dense* h = new smeg_dense();
+    h->n = n; h->k = k; h->kd = kd; h->bf16 = bf16 ? 1 : 0;
+    if (upload(dense, &h->w)) { smeg_dense_destroy(h); return -2; }
+    slot.store(h, std::memory_order_release);
+    *out = h;
+    return 0;
+}
+
 // glu / yacc: the fused forms of the MLP block (tensor-core GEMM only, see GemmTcArgs).
 static int q4_dev(const smeg_q4* w, const uint16_t* a, uint16_t* c, size_t m, const ep_desc16* ep, int bf16,
                   cudaStream_t stream, float* c32 = nullptr, int glu = 0, float* yacc = nullptr) {
@@ -575,6 +663,13 @@ static int q4_dev(const smeg_q4* w, const uint16_t* a, uint16_t* c, size_t m, co
     const size_t n = w->d.n, k = w->d.k;
     if (m == 0 || n == 0) return 0;
     if ((!c && !c32 && !yacc) || (k && !a) || m > 0x7fffffffu || n > 0x7fffffffu || k > 0x7fffffffu) return -4;
+    if (w->affine) {
+        if (c32 || glu || yacc) return -3;                       // the fused forms of the MLP block take Q4_0 weights
+        const smeg_dense* t = nullptr;
+        const int rc = q4_affine_twin(w, bf16, &t);
+        if (rc) return rc;
+        return smeg_gemm_dense_dev(t, a, c, m, bf16 ? 0x3f80 : 0x3c00 /* beta = 1 */, 0, ep, stream);
+    }
     if ((glu || yacc) && !q4_uses_tc(w, a, m)) return -4;
     DeviceState* ds = dev_state();
     if (!ds) return -5;
@@ -1042,6 +1137,7 @@ int smeg_mlp_create(const smeg_q4* gate_up, const smeg_q4* down, uint32_t gate_a
     *out = nullptr;
     if (gate_act != SMEG_ACT_SILU && gate_act != SMEG_ACT_GELU) return -4;
     if (gate_up->d.n % 2 != 0 || down->d.k != gate_up->d.n / 2) return -4;   // "down takes up's outputs"
+    if (gate_up->affine || down->affine) return -3;                          // the block's fused forms take Q4_0 weights
     smeg_mlp* h = new smeg_mlp{gate_up, down, gate_act};
     *out = h;
     return 0;

@@ -5,16 +5,26 @@
 
 #include <atomic>
 #include <mutex>
+#include <vector>
 
 #include "pack.h"
 
+struct smeg_dense;
 struct smeg_q4 {
     smeg::PackedDims d;
     unsigned char* codes = nullptr;   // device: packed units
     uint16_t* scales = nullptr;       // device: f16 scale rows
     size_t code_bytes = 0, scale_elems = 0;
+    // Affine form (Q4_1: weight = scale * code + min).  The reference's prefill path expands it once to the 16-bit
+    // operand type -- round_T(f64(scale) * code + f64(min)), src/kernels/q4/weights.rs:250-256 -- and multiplies dense;
+    // this build keeps the logical arrays and runs such weights through dense twins of exactly those values, one per
+    // operand type, built on the first call of that type.
+    bool affine = false;
+    std::vector<uint8_t> h_quants;
+    std::vector<uint16_t> h_scales, h_mins;
+    mutable std::mutex twin_lock;
+    mutable std::atomic<smeg_dense*> twin_f16{nullptr}, twin_bf16{nullptr};
 };
-struct smeg_dense;
 struct smeg_lowbit {
     smeg::PackedDims d;
     int bits = 0;                     // 2 or 1

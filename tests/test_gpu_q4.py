@@ -249,3 +249,52 @@ def test_length_contracts_raise_like_the_reference_panics():
                         sg.Epilogue().add_col(torch.zeros(15, dtype=torch.float16, device="cuda")))
     # m == 0: nothing touched
     sg.matmul_q4(torch.zeros(0, dtype=torch.float16, device="cuda"), w, torch.zeros(0, dtype=torch.float16, device="cuda"), 0)
+
+
+# ---- Q4_1: the affine form (weight = scale * code + min) ----
+
+@pytest.mark.parametrize("bf16", [False, True])
+@pytest.mark.parametrize("m,n,k,block", [(1, 33, 256, 32), (3, 129, 1027, 32), (7, 200, 513, 64), (64, 300, 1024, 32), (130, 257, 2050, 128)])
+def test_affine_weights_match_the_scalar_statement(m, n, k, block, bf16):
+    """tests/correctness/q4.rs:272-328 on the GPU: quantised with per-block minima, the product runs on the weights
+    round_T(f64(scale) * code + f64(min)) (dequant_rows, src/kernels/q4/weights.rs:250-256) with f32 accumulation."""
+    rng = np.random.default_rng(900 + m + n + k)
+    w32 = (rng.standard_normal((n, k)) * 0.05 + 0.02).astype(np.float32)
+    q, s, mins = orc.q4_quantize(w32, 0, n, k, block, True)
+    w = sg.Q4Weights.with_params(q, s, mins, n, k, sg.Q4Params(block).affine())
+    a32 = rng.standard_normal((m, k)).astype(np.float32)
+    a_bits = orc.f32_to_bf16_bits(a32) if bf16 else orc.f32_to_f16_bits(a32)
+    bias = (rng.standard_normal(n) * 0.1).astype(np.float32)
+    b_bits = orc.f32_to_bf16_bits(bias) if bf16 else orc.f32_to_f16_bits(bias)
+    b_dev = bf16_bits_dev(b_bits) if bf16 else f16_bits_dev(b_bits)
+    ep = sg.Epilogue("bf16" if bf16 else "f16").add_col(b_dev).relu()
+    want = orc.matmul_q4(a_bits, q, s, mins, n, k, block, m, orc.Nodes([(4, 0, 0.0, b_bits, 0), (8, 1, 0.0, None, 0)]), bf16)
+    a_dev = bf16_bits_dev(a_bits) if bf16 else f16_bits_dev(a_bits)
+    c = torch.full((m, n), 9.0, dtype=a_dev.dtype, device="cuda")
+    (sg.matmul_q4_bf16_ep if bf16 else sg.matmul_q4_ep)(a_dev, w, c, m, ep)
+    torch.cuda.synchronize()
+    assert sg.last_status() == 0
+    g32, w32o = orc.t_bits_to_f32(bits_of(c), bf16), orc.t_bits_to_f32(want, bf16)
+    assert max_rel(g32, w32o) <= (2e-2 if bf16 else TOL)
+
+
+def test_affine_with_zero_minima_equals_the_scale_form_and_the_library_quantiser_agrees():
+    """Scale == Affine(zero mins) (tests/correctness/q4.rs:300-328), and Q4Weights.quantize with the affine parameter
+    produces the oracle's codes, scales and minima."""
+    rng = np.random.default_rng(77)
+    m, n, k, block = 5, 96, 512, 32
+    q, s = q4_logical(rng, n, k, block)
+    a = f16_bits_dev(orc.f32_to_f16_bits(rng.standard_normal((m, k)).astype(np.float32)))
+    scale_form = sg.Q4Weights.with_params(q, s, None, n, k, sg.Q4Params(block))
+    affine = sg.Q4Weights.with_params(q, s, np.zeros(n * (k // block), np.uint16), n, k, sg.Q4Params(block).affine())
+    c0 = torch.zeros((m, n), dtype=torch.float16, device="cuda")
+    c1 = torch.zeros_like(c0)
+    sg.matmul_q4(a, scale_form, c0, m)
+    sg.matmul_q4(a, affine, c1, m)
+    assert max_rel(c1.float().cpu().numpy(), c0.float().cpu().numpy()) <= 3e-3      # f16 block sums against f32 accumulation
+    w32 = (rng.standard_normal((n, k)) * 0.05 + 0.01).astype(np.float32)
+    wq = sg.Q4Weights.quantize(w32, sg.WeightLayout.OutIn, n, k, sg.Q4Params(block).affine())
+    qo, so, mo = orc.q4_quantize(w32, 0, n, k, block, True)
+    want = orc.matmul_q4(bits_of(a), qo, so, mo, n, k, block, m)
+    sg.matmul_q4(a, wq, c1, m)
+    assert max_rel(c1.float().cpu().numpy(), orc.f16_bits_to_f32(want).reshape(m, n)) <= TOL
