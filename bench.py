@@ -357,7 +357,7 @@ def run_ours(args):
     m = args.m
 
     # ---- weights: this rank's shard, quantised once, uploaded as several distinct copies ----
-    from sme_gemm_b200.tp import shard_bounds
+    from sme_gemm_b200.tp import TpMlp, shard_bounds
     wg, wu, wd = mlp_weights_f32(5)
     lo, hi = shard_bounds(INTER, rank, world)
     fl = hi - lo
@@ -403,8 +403,7 @@ def run_ours(args):
             mlp.accumulate(xb, yb, m)
         else:
             if peer is not None:
-                mlp.partial(xb, peer.partial, m)
-                peer.finish(yb)
+                TpMlp(mlp, world, None, peer).accumulate(xb, yb, m)   # pushes the partial rows to their owners when it can
             else:
                 mlp.partial(xb, partial, m)
                 dist.all_reduce(partial)
@@ -418,6 +417,9 @@ def run_ours(args):
     def timed(fn, steps, tail=None):
         sync()
         e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        # device time of the steps: a short spin kernel ahead of the first event gives the host a head start, so that the
+        # interval between the events is the steps' own device time and not the host's launch pace
+        torch.cuda._sleep(2_000_000)
         e0.record()
         for i in range(steps):
             fn(i)
@@ -544,7 +546,7 @@ def run_ours(args):
         if peer is not None:
             # the exchange alone: sum + rounding + residual add over peer memory, partial buffers as they stand
             def only_finish(i):
-                peer.finish(y)
+                peer.finish(y, pushed=peer.push)
             for i in range(5):
                 only_finish(i)
             exchange_us = timed(only_finish, 20) * 1e3 / 20

@@ -285,6 +285,18 @@ int smeg_mlp_finish_dev(float *y, const float *sum, size_t len, void *stream);
 int smeg_mlp_reduce_finish_dev(float *y, const uint64_t *buf_ptrs, const uint64_t *flag_ptrs, int rank, int world,
                                size_t len, uint32_t seq, int oneshot, void *stream);
 
+/* The same exchange with the partial sums PUSHED: smeg_mlp_partial_push_dev runs the rank's two GEMMs and its down
+ * projection's last stage stores every f32 result row straight into the receive area of the rank that owns it (plain
+ * stores to peer-mapped memory; row i belongs to rank i / rows, rows = ceil(m / world)), so that the owner later sums
+ * from its own memory.  A buffer is then world slots of rows * d floats (slot s = rank s's partial of this rank's rows)
+ * followed by m * d f16 results: (world * rows * d) * 4 + m * d * 2 bytes.  smeg_mlp_reduce_finish_pushed_dev is the
+ * matching finish (same flag protocol and guarantees as above; no one-shot form).  rc -3: the step is too small for
+ * this form (m <= 64) -- use smeg_mlp_partial_dev + smeg_mlp_reduce_finish_dev. */
+int smeg_mlp_partial_push_dev(smeg_mlp *mlp, const uint16_t *x, const uint64_t *buf_ptrs, int rank, int world, size_t m,
+                              void *stream);
+int smeg_mlp_reduce_finish_pushed_dev(float *y, const uint64_t *buf_ptrs, const uint64_t *flag_ptrs, int rank, int world,
+                                      size_t m, size_t d, uint32_t seq, void *stream);
+
 /* ---- drop-in entry points: the reference's own signatures --------------------- */
 /* These take what src/kernels/{q4,lowbit}/matmul.rs pass today: host pointers and
  * the reference's band-major packed arrays.  The first call on a weight set

@@ -107,6 +107,8 @@ SIGNATURES = {
     "smeg_mlp_partial_dev": (_i, [_vp, _vp, _vp, _sz, _vp]),
     "smeg_mlp_finish_dev": (_i, [_vp, _vp, _sz, _vp]),
     "smeg_mlp_reduce_finish_dev": (_i, [_vp, C.POINTER(C.c_uint64), C.POINTER(C.c_uint64), _i, _i, _sz, _u32, _i, _vp]),
+    "smeg_mlp_partial_push_dev": (_i, [_vp, _vp, C.POINTER(C.c_uint64), _i, _i, _sz, _vp]),
+    "smeg_mlp_reduce_finish_pushed_dev": (_i, [_vp, C.POINTER(C.c_uint64), C.POINTER(C.c_uint64), _i, _i, _sz, _sz, _u32, _vp]),
     "gemm_sme_f16f16_q4": (_i, [_sz, _sz, _sz, _vp, _vp, _vp, _vp, _vp, _sz, _epp]),
     "gemm_sme_b16b16_q4": (_i, [_sz, _sz, _sz, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _sz, _epp]),
     "gemm_sme_f16_q1": (_i, [_sz, _sz, _sz, _vp, _vp, _vp, _vp, _sz, _epp]),

@@ -657,8 +657,9 @@ static int q4_affine_twin(const smeg_q4* w, int bf16, const smeg_dense** out) {
 }
 
 // glu / yacc: the fused forms of the MLP block (tensor-core GEMM only, see GemmTcArgs).
+struct TpPush { float* bufs[8]; int world, rank, rows; };
 static int q4_dev(const smeg_q4* w, const uint16_t* a, uint16_t* c, size_t m, const ep_desc16* ep, int bf16,
-                  cudaStream_t stream, float* c32 = nullptr, int glu = 0, float* yacc = nullptr) {
+                  cudaStream_t stream, float* c32 = nullptr, int glu = 0, float* yacc = nullptr, const TpPush* push = nullptr) {
     if (!w) return -4;
     const size_t n = w->d.n, k = w->d.k;
     if (m == 0 || n == 0) return 0;
@@ -671,6 +672,7 @@ static int q4_dev(const smeg_q4* w, const uint16_t* a, uint16_t* c, size_t m, co
         return smeg_gemm_dense_dev(t, a, c, m, bf16 ? 0x3f80 : 0x3c00 /* beta = 1 */, 0, ep, stream);
     }
     if ((glu || yacc) && !q4_uses_tc(w, a, m)) return -4;
+    if (push && (!c32 || !q4_uses_tc(w, a, m))) return -3;
     DeviceState* ds = dev_state();
     if (!ds) return -5;
     Q4GemvArgs g;
@@ -693,6 +695,10 @@ static int q4_dev(const smeg_q4* w, const uint16_t* a, uint16_t* c, size_t m, co
         t.n16 = (int)w->d.n16; t.ku = (int)w->d.ku; t.nb = (int)w->d.nb; t.log2_block = w->d.log2_block;
         t.status = ds->status;
         t.ep = g.ep;
+        if (push) {
+            for (int s = 0; s < push->world; ++s) t.push[s] = push->bufs[s];
+            t.push_world = push->world; t.push_rank = push->rank; t.push_rows = push->rows;
+        }
         dim3 grid;
         size_t smem = 0, ws_floats = 0, ncounters = 0;
         gemm_tc_plan(t, ds->sm_count, &grid, &smem, &ws_floats, &ncounters);
@@ -1146,7 +1152,7 @@ void smeg_mlp_destroy(smeg_mlp* mlp) { delete mlp; }
 
 // both = x @ gate_up (f16), hid = glu(both), then the down projection either
 // rounded to f16 and added into y (partial == nullptr) or left as f32 partial sums.
-static int mlp_run(smeg_mlp* mlp, const uint16_t* x, float* y, float* partial, size_t m, cudaStream_t stream) {
+static int mlp_run(smeg_mlp* mlp, const uint16_t* x, float* y, float* partial, size_t m, cudaStream_t stream, const TpPush* push = nullptr) {
     if (!mlp) return -4;
     if (m == 0) return 0;
     const size_t h = mlp->down->d.k, d_out = mlp->down->d.n;
@@ -1156,6 +1162,7 @@ static int mlp_run(smeg_mlp* mlp, const uint16_t* x, float* y, float* partial, s
     const size_t out_bytes = (m * d_out * 2 + 255) / 256 * 256;
     // prefill-sized batches: the gated product is formed in the gate/up GEMM's drain and the residual add in the
     // down GEMM's, with the arithmetic of the separate passes (two launches instead of four)
+    if (push && !(m > 64)) return -3;
     const bool fuse = m > 64 && h % 32 == 0 && mlp->gate_up->d.n == 2 * h && q4_uses_tc(mlp->gate_up, x, m) &&
                       mlp->down->d.k % 8 == 0 && (int)m > g_tc_min_rows && mlp->down->d.log2_block >= 3;
     if (cudaMallocAsync(&ws, (fuse ? 0 : both_bytes) + hid_bytes + out_bytes, stream) != cudaSuccess) return -2;
@@ -1165,14 +1172,14 @@ static int mlp_run(smeg_mlp* mlp, const uint16_t* x, float* y, float* partial, s
     int rc;
     if (fuse) {
         rc = q4_dev(mlp->gate_up, x, hid, m, nullptr, 0, stream, nullptr, (int)mlp->act);
-        if (!rc) rc = partial ? q4_dev(mlp->down, hid, nullptr, m, nullptr, 0, stream, partial)
+        if (!rc) rc = partial ? q4_dev(mlp->down, hid, nullptr, m, nullptr, 0, stream, partial, 0, nullptr, push)
                               : q4_dev(mlp->down, hid, nullptr, m, nullptr, 0, stream, nullptr, 0, y);
     } else {
         rc = q4_dev(mlp->gate_up, x, both, m, nullptr, 0, stream);
         if (!rc) rc = glu_launch(hid, both, m, h, mlp->act, stream) == cudaSuccess ? 0 : -6;
         if (!rc) {
             if (partial) {
-                rc = q4_dev(mlp->down, hid, nullptr, m, nullptr, 0, stream, partial);
+                rc = push ? -3 : q4_dev(mlp->down, hid, nullptr, m, nullptr, 0, stream, partial);
             } else {
                 rc = q4_dev(mlp->down, hid, out, m, nullptr, 0, stream);
                 if (!rc) rc = add_f16_to_f32_launch(y, out, m * d_out, stream) == cudaSuccess ? 0 : -6;
@@ -1188,6 +1195,17 @@ int smeg_mlp_accumulate_dev(smeg_mlp* mlp, const uint16_t* x, float* y, size_t m
 }
 int smeg_mlp_partial_dev(smeg_mlp* mlp, const uint16_t* x, float* partial, size_t m, void* stream) {
     return mlp_run(mlp, x, nullptr, partial, m, (cudaStream_t)stream);
+}
+int smeg_mlp_partial_push_dev(smeg_mlp* mlp, const uint16_t* x, const uint64_t* buf_ptrs, int rank, int world, size_t m, void* stream) {
+    if (!mlp || !buf_ptrs || world < 2 || world > 8 || rank < 0 || rank >= world) return -4;
+    TpPush push;
+    memset(&push, 0, sizeof(push));
+    for (int s = 0; s < world; ++s) {
+        if (!buf_ptrs[s] || (buf_ptrs[s] & 15) != 0) return -4;
+        push.bufs[s] = reinterpret_cast<float*>(buf_ptrs[s]);
+    }
+    push.world = world; push.rank = rank; push.rows = (int)((m + world - 1) / world);
+    return mlp_run(mlp, x, nullptr, push.bufs[rank], m, (cudaStream_t)stream, &push);
 }
 int smeg_mlp_finish_dev(float* y, const float* sum, size_t len, void* stream) {
     return round_add_f32_launch(y, sum, len, (cudaStream_t)stream) == cudaSuccess ? 0 : -6;
@@ -1208,6 +1226,26 @@ int smeg_mlp_reduce_finish_dev(float* y, const uint64_t* buf_ptrs, const uint64_
     }
     a.y = y; a.rank = rank; a.world = world; a.len = len; a.seq = seq; a.status = ds->status;
     a.oneshot = oneshot ? 1 : 0;
+    a.res_off = len;
+    return tp_reduce_finish_launch(a, ds->sm_count, (cudaStream_t)stream) == cudaSuccess ? 0 : -6;
+}
+int smeg_mlp_reduce_finish_pushed_dev(float* y, const uint64_t* buf_ptrs, const uint64_t* flag_ptrs, int rank, int world,
+                                      size_t m, size_t d, uint32_t seq, void* stream) {
+    if (m == 0 || d == 0) return 0;
+    if (!y || !buf_ptrs || !flag_ptrs || world < 2 || rank < 0 || rank >= world) return -4;
+    if (world > 8 || d % 4 != 0 || ((uintptr_t)y & 15) != 0) return -3;
+    DeviceState* ds = dev_state();
+    if (!ds) return -5;
+    TpReduceArgs a;
+    memset(&a, 0, sizeof(a));
+    for (int s = 0; s < world; ++s) {
+        if (!buf_ptrs[s] || !flag_ptrs[s] || (buf_ptrs[s] & 15) != 0 || (flag_ptrs[s] & 3) != 0) return -4;
+        a.bufs[s] = reinterpret_cast<float*>(buf_ptrs[s]);
+        a.flags[s] = reinterpret_cast<uint32_t*>(flag_ptrs[s]);
+    }
+    const size_t rows = (m + world - 1) / world;
+    a.y = y; a.rank = rank; a.world = world; a.len = m * d; a.seq = seq; a.status = ds->status;
+    a.pushed = 1; a.slice = rows * d; a.res_off = (size_t)world * rows * d;
     return tp_reduce_finish_launch(a, ds->sm_count, (cudaStream_t)stream) == cudaSuccess ? 0 : -6;
 }
 int smeg_mlp_accumulate(smeg_mlp* mlp, const uint16_t* x, float* y, size_t m) {

@@ -866,7 +866,14 @@ __global__ void __launch_bounds__(256) splitk_reduce_kernel(const __grid_constan
         if (tok >= p.m) continue;
         if (p.beta != 1.0f) acc[jj] = __fmul_rn(p.beta, acc[jj]);
         const size_t ci = p.col_major ? (size_t)col * p.m + tok : (size_t)tok * p.n + col;
-        if (p.c32) p.c32[(size_t)tok * p.n + col] = acc[jj];
+        if (p.c32) {
+            if (p.push_world) {
+                const int owner = tok / p.push_rows;
+                p.push[owner][((size_t)p.push_rank * p.push_rows + (size_t)(tok - owner * p.push_rows)) * p.n + col] = acc[jj];
+            } else {
+                p.c32[(size_t)tok * p.n + col] = acc[jj];
+            }
+        }
         else if (p.yacc) p.yacc[(size_t)tok * p.n + col] = __fadd_rn(yv[jj], t_to_f32<BF16>(f32_to_t<BF16>(acc[jj])));
         else if (p.ep_fast) p.c[ci] = fast_ep_store<BF16>(fe, acc[jj]);
         else p.c[ci] = ep_store_nodes<BF16>(nodes, p.ep.n_nodes, acc[jj], (size_t)tok, (size_t)col);
@@ -990,6 +997,7 @@ void gemm_tc_plan(GemmTcArgs& a, int sm_count, dim3* grid, size_t* smem, size_t*
             while (base * splits * 2 <= sm_count && stages_all / (splits * 2) >= 7 && splits < 8) splits *= 2;
         }
     }
+    if (a.push_world && splits < 2 && stages_all >= 2) splits = 2;     // the pushing store lives in the depth-split reduce stage
     // shared memory: operand ring (NW x 16 KB per slot), token ring (pad x 128 B per slot) and the packed-weight
     // ring, whose slots cover PU stages each so that one bulk copy moves a column group's units of PU stages
     const int tok_bytes = a.us * pad * 128 / a.cg, o_stride = a.nw * a.us * kWTile;

@@ -157,6 +157,11 @@ struct GemmTcArgs {
     int ep_fast;                  // the graph runs as a per-thread FastEp (see epilogue.cuh)
     int nt, nk, no, nw;           // ring depths (tokens / packed / operand), accumulator sets per CTA
     int us;                       // 64-deep units per stage (2 for small token tiles)
+    // Tensor-parallel push (with c32 set): the f32 result rows go straight into their owner rank's receive area instead of
+    // c32 -- row i belongs to rank i / push_rows and lands in slot push_rank of that rank's area, push[owner] +
+    // (push_rank * push_rows + i % push_rows) * n -- by plain stores to peer-mapped memory from splitk_reduce_kernel.
+    float* push[8];
+    int push_world, push_rank, push_rows;
     int c_tma;                    // launcher-filled: C leaves through shared memory and tiled bulk stores (16-byte aligned rows of C)
     int cg;                       // CTAs per MMA: 2 = pairs of CTAs (a cluster of two along x) run MMAs of 256 weight columns
     int pu;                       // stages covered by one packed-ring slot
@@ -211,6 +216,9 @@ struct TpReduceArgs {
     size_t len;            // multiple of 4
     uint32_t seq;          // call number, the same on every rank, growing by one per call from 1
     int oneshot;           // every rank sums everything itself (short vectors; the caller double-buffers bufs)
+    int pushed;            // the partials of this rank's slice are already here: bufs[rank] holds world slots of slice floats (rank order)
+    size_t slice;          // pushed: floats per slot (rows per rank x row length)
+    size_t res_off;        // offset (floats) of the f16 result area in a buffer: len, or world * slice when pushed
     unsigned* status;
 };
 cudaError_t tp_reduce_finish_launch(const TpReduceArgs& a, int sm_count, cudaStream_t stream);

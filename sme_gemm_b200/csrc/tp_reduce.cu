@@ -67,9 +67,11 @@ __device__ __forceinline__ bool wait_flag(const uint32_t* flag, uint32_t seq) {
 // Sum over ranks in rank order of vector v; every load is issued before the first add.
 __device__ __forceinline__ float4 sum_ranks(const TpReduceArgs& p, size_t v) {
     float4 x[8];
+    // pushed: the ranks' partials of this slice lie in this rank's own buffer, slot s = rank s (plain local loads)
+    const float* mine = p.bufs[p.rank] + (4 * v - (size_t)p.rank * p.slice);
 #pragma unroll
     for (int s = 0; s < 8; ++s)
-        if (s < p.world) x[s] = ld_sys_f4(p.bufs[s] + 4 * v);
+        if (s < p.world) x[s] = p.pushed ? *reinterpret_cast<const float4*>(mine + (size_t)s * p.slice) : ld_sys_f4(p.bufs[s] + 4 * v);
     float4 acc = x[0];
 #pragma unroll
     for (int s = 1; s < 8; ++s)
@@ -118,7 +120,7 @@ __global__ void __launch_bounds__(256) tp_reduce_finish_kernel(const __grid_cons
     }
 
     // ---- 1: part b of my slice ----
-    const size_t per = (nvec + W - 1) / W;                         // vectors per slice
+    const size_t per = p.pushed ? p.slice / 4 : (nvec + W - 1) / W;    // vectors per slice
     const size_t cper = (per + G - 1) / G;                         // vectors per CTA and slice
     {
         const size_t v0 = per * r + cper * b, v1 = min(min(nvec, per * (r + 1)), v0 + cper);
@@ -137,7 +139,7 @@ __global__ void __launch_bounds__(256) tp_reduce_finish_kernel(const __grid_cons
                 const __half2 lo = __floats2half2_rn(acc[u].x, acc[u].y), hi = __floats2half2_rn(acc[u].z, acc[u].w);
                 const uint2 h = make_uint2(*reinterpret_cast<const uint32_t*>(&lo), *reinterpret_cast<const uint32_t*>(&hi));
                 for (int s = 0; s < W; ++s)
-                    if (s != r) st_sys_u2(reinterpret_cast<unsigned char*>(p.bufs[s] + p.len) + 8 * v, h);
+                    if (s != r) st_sys_u2(reinterpret_cast<unsigned char*>(p.bufs[s] + p.res_off) + 8 * v, h);
                 const float2 f0 = __half22float2(lo), f1 = __half22float2(hi);
                 add_into(p.y, v, make_float4(f0.x, f0.y, f1.x, f1.y));
             }
@@ -155,7 +157,7 @@ __global__ void __launch_bounds__(256) tp_reduce_finish_kernel(const __grid_cons
         if (tid == 0 && p.status) atomicOr(p.status, STATUS_PEER_TIMEOUT);
         return;
     }
-    const unsigned char* mine = reinterpret_cast<const unsigned char*>(p.bufs[r] + p.len);
+    const unsigned char* mine = reinterpret_cast<const unsigned char*>(p.bufs[r] + p.res_off);
     for (int s = 0; s < W; ++s) {
         if (s == r) continue;
         const size_t v0 = per * s + cper * b, v1 = min(min(nvec, per * (s + 1)), v0 + cper);
@@ -175,7 +177,7 @@ cudaError_t tp_reduce_finish_launch(const TpReduceArgs& a, int sm_count, cudaStr
     // the same grid on every rank (it depends on the length and the world size only): one vector per
     // thread of an owner's slice where the slice is that long, at most kTpMaxGrid CTAs
     const size_t nvec = a.len / 4;
-    size_t ctas = ((a.oneshot ? nvec : (nvec + a.world - 1) / a.world) + 255) / 256;
+    size_t ctas = ((a.oneshot ? nvec : (a.pushed ? a.slice / 4 : (nvec + a.world - 1) / a.world)) + 255) / 256;
     if (ctas < 1) ctas = 1;
     if (ctas > (size_t)kTpMaxGrid) ctas = (size_t)kTpMaxGrid;
     tp_reduce_finish_kernel<<<(unsigned)ctas, 256, 0, stream>>>(a);

@@ -11,6 +11,8 @@ and the residual add follow on every rank.
 """
 from __future__ import annotations
 
+import os
+
 import numpy as np
 
 from .host import Gate, GatedLinear, Linear, Mlp, Q4Params, WeightLayout
@@ -54,7 +56,11 @@ class PeerReduce:
         # two buffers, taken in turn from step to step (the one-shot form of the kernel needs that); each holds
         # the f32 partial sums followed by the f16 results the owners of the other slices write back
         self._len = m * d
-        self._stride = (self._len + self._len // 2 + 3) // 4 * 4   # floats per buffer, a whole number of 16-byte vectors
+        # the pushed form keeps `world` slots of ceil(m / world) rows (one per sending rank) ahead of the f16 results
+        self._rows = -(-m // self.world)
+        self._recv = self.world * self._rows * d
+        self._stride = (max(self._len, self._recv) + self._len // 2 + 3) // 4 * 4   # floats per buffer, whole 16-byte vectors
+        self.push = m > 64 and self.world > 1 and os.environ.get("SMEG_TP_PUSH", "1") != "0"
         self._both = symm.empty((2, self._stride), dtype=torch.float32, device=dev)
         self.flags = symm.empty((FLAG_WORDS,), dtype=torch.int32, device=dev)
         self.flags.zero_()
@@ -77,13 +83,24 @@ class PeerReduce:
         """The buffer this rank's partial product of the coming step goes into."""
         return self._both[(self.seq + 1) & 1][: self._len].view(self._m, self._d)
 
-    def finish(self, y) -> None:
-        """y += f32(f16(sum over ranks of their `partial`)), on every rank."""
+    def next_bufs(self):
+        """Every rank's buffer of the coming step, as the C ABI takes them."""
+        off = ((self.seq + 1) & 1) * self._stride * 4
+        return (self._C.c_uint64 * self.world)(*[b + off for b in self._base])
+
+    def finish(self, y, pushed: bool = False) -> None:
+        """y += f32(f16(sum over ranks of their `partial`)), on every rank.  pushed: the partials were stored into their
+        owners' receive areas by smeg_mlp_partial_push_dev."""
         from ._lib import check, lib
         from .host import _ptr, _stream
         self.seq += 1
         off = (self.seq & 1) * self._stride * 4
         bufs = (self._C.c_uint64 * self.world)(*[b + off for b in self._base])
+        if pushed:
+            check("smeg_mlp_reduce_finish_pushed_dev",
+                  lib().smeg_mlp_reduce_finish_pushed_dev(_ptr(y), bufs, self._flags, self.rank, self.world, self._m, self._d,
+                                                          self.seq & 0xffffffff, _stream()))
+            return
         check("smeg_mlp_reduce_finish_dev",
               lib().smeg_mlp_reduce_finish_dev(_ptr(y), bufs, self._flags, self.rank, self.world, y.numel(),
                                                self.seq & 0xffffffff, self.oneshot, _stream()))
@@ -116,6 +133,16 @@ class TpMlp:
             self.mlp.accumulate(x, y, m)
             return
         if self.peer is not None:
+            if self.peer.push and m == self.peer._m:
+                # the down projection's last stage stores each result row into its owner rank's receive area
+                from ._lib import check, lib
+                from .host import _ptr, _stream
+                rc = lib().smeg_mlp_partial_push_dev(self.mlp._h, _ptr(x), self.peer.next_bufs(), self.peer.rank, self.world, m, _stream())
+                if rc == 0:
+                    self.peer.finish(y, pushed=True)
+                    return
+                if rc != -3:
+                    check("smeg_mlp_partial_push_dev", rc)
             self.mlp.partial(x, self.peer.partial, m)
             self.peer.finish(y)
             return

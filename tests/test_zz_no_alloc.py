@@ -74,3 +74,44 @@ def test_sizes_beyond_the_fixed_scratch_are_rejected_and_leave_the_output_alone(
     assert L.smeg_matmul_lowbit_static_dev(wbig._h, a2.data_ptr(), c2.data_ptr(), 1, None, 0) == -4
     torch.cuda.synchronize()
     assert bool((c2 == 7.0).all())
+
+
+def test_static_calls_allocate_nothing():
+    """What the entry point exists for: after one warm call, calls of every supported shape (1, 3 and 8 rows, with and
+    without an epilogue) leave the device's free memory, the driver's default pool and torch's allocator unchanged.
+    (The allocating entry takes its scratch from the stream-ordered pool; the static one must not touch it.)"""
+    n, k, block = 520, 1536, 128
+    rng = np.random.default_rng(5)
+    w = sg.Q1Weights.new(rng.integers(0, 256, k * n // 8).astype(np.uint8),
+                         rng.uniform(0.01, 0.05, n * (k // block)).astype(np.float16), sg.WeightLayout.OutIn, n, k, block)
+    bias = torch.from_numpy((rng.standard_normal(n) * 0.1).astype(np.float16)).cuda()
+    nodes = (EpNode * 2)(EpNode(4, 0, 0.0, bias.data_ptr(), 0), EpNode(8, 1, 0.0, None, 0))
+    desc = EpDesc16(2, nodes)
+    L = sg.lib()
+    stream = torch.cuda.current_stream().cuda_stream
+    a = torch.from_numpy(rng.standard_normal((8, k)).astype(np.float16)).cuda()
+    c = torch.zeros((8, n), dtype=torch.float16, device="cuda")
+    assert L.smeg_matmul_lowbit_static_dev(w._h, a.data_ptr(), c.data_ptr(), 8, None, stream) == 0      # warm
+    torch.cuda.synchronize()
+
+    from cuda.bindings import runtime as rt          # cuda-python: the default pool's own counters
+    err, pool = rt.cudaDeviceGetDefaultMemPool(torch.cuda.current_device())
+    assert int(err) == 0
+
+    def pool_counters():
+        out = []
+        for attr in (rt.cudaMemPoolAttr.cudaMemPoolAttrReservedMemCurrent, rt.cudaMemPoolAttr.cudaMemPoolAttrUsedMemCurrent,
+                     rt.cudaMemPoolAttr.cudaMemPoolAttrReservedMemHigh, rt.cudaMemPoolAttr.cudaMemPoolAttrUsedMemHigh):
+            e, v = rt.cudaMemPoolGetAttribute(pool, attr)
+            assert int(e) == 0
+            out.append(int(v))
+        return out
+
+    before = (torch.cuda.mem_get_info()[0], pool_counters(), torch.cuda.memory_reserved(), torch.cuda.memory_allocated())
+    for m, ep in ((1, None), (3, C.byref(desc)), (8, None), (8, C.byref(desc)), (1, C.byref(desc))):
+        assert L.smeg_matmul_lowbit_static_dev(w._h, a.data_ptr(), c.data_ptr(), m, ep, stream) == 0
+    torch.cuda.synchronize()
+    after = (torch.cuda.mem_get_info()[0], pool_counters(), torch.cuda.memory_reserved(), torch.cuda.memory_allocated())
+    assert after == before
+    # the entry's own status word is part of what last_status reports
+    assert sg.last_status() == 0
