@@ -21,7 +21,9 @@ the host cores with the same metric, on a bounded row sample of the same batch.
 HBM.  `e2e` is the same step through the same public call with host buffers: every
 step copies its tokens from pinned host memory and its result back to pinned host
 memory inside the timed region, the copies running on their own streams with two
-buffers each way so that they overlap the neighbouring steps' compute.  `roofline`
+buffers each way so that they overlap the neighbouring steps' compute (at N > 1 every rank
+copies the tokens in and returns its 1 / N of the rows of the replicated result, so the N
+ranks together return all of it; the byte counts in the line are the totals).  `roofline`
 is the gate/up projection's GEMM timed alone against the measured tensor peak.
 
 The extra "kernels" list reports the single-kernel configs of BASELINE.json
@@ -476,6 +478,8 @@ def run_ours(args):
     for e in ev_done + ev_out:
         e.record(cur)
 
+    row_lo, row_hi = rank * m // world, (rank + 1) * m // world
+
     def e2e_step(i):
         b = i & 1
         s_in.wait_event(ev_done[b])                 # the step two back has finished reading xs[b]
@@ -486,11 +490,11 @@ def run_ours(args):
         cur.wait_event(ev_out[b])                   # ys[b]'s previous read-back is complete before it changes
         step(i, xs[b], ys[b])
         ev_done[b].record(cur)
-        if rank == 0:
-            s_out.wait_event(ev_done[b])
-            with torch.cuda.stream(s_out):
-                yh[b].copy_(ys[b], non_blocking=True)
-                ev_out[b].record(s_out)
+        # y is replicated: every rank returns its 1 / N of the rows to its pinned host buffer, together they return all of it
+        s_out.wait_event(ev_done[b])
+        with torch.cuda.stream(s_out):
+            yh[b][row_lo:row_hi].copy_(ys[b][row_lo:row_hi], non_blocking=True)
+            ev_out[b].record(s_out)
 
     def e2e_tail():
         cur.wait_stream(s_out)                      # the last result has reached the host inside the timed region
