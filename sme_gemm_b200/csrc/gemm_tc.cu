@@ -733,6 +733,9 @@ __global__ void __launch_bounds__(kTcThreads, 1) gemm_tc_kernel(const __grid_con
 
         // ---- drain: thread = weight column (TMEM lane), registers = tokens.  A warp reaches the lane quarter warp % 4;
         // the token columns are split over 4 (or 2) warps per quarter ----
+        // the kernel behind in the stream (the depth-split reduce, the tensor-parallel finish) may be scheduled from here
+        // on: it waits (griddepcontrol.wait) for this grid to complete before it touches anything
+        pdl_launch_dependents();
         const int ntok = p.ntok_pad;                               // a multiple of 32
         const int parts = (ntok % 64 == 0) ? 4 : 2;                // every part is whole groups of 16 tokens
         const int splits = (int)gridDim.z;
@@ -809,6 +812,8 @@ __global__ void __launch_bounds__(kTcThreads, 1) gemm_tc_kernel(const __grid_con
 // a thread owns one column (for a gate/up matrix: one hidden unit, i.e. a gate and an up column).
 template <int BF16>
 __global__ void __launch_bounds__(256) splitk_reduce_kernel(const __grid_constant__ GemmTcArgs p, int splits, int col_tiles) {
+    pdl_launch_dependents();
+    pdl_wait();                                                    // launched while the GEMM ahead of it drains
     const int NW = p.nw, ntok = p.ntok_pad;
     const int tile_id = blockIdx.x, bx = tile_id % col_tiles, by = tile_id / col_tiles;
     const int tok0 = by * p.ntok_tile, j0 = blockIdx.y * 8;
@@ -1110,9 +1115,8 @@ cudaError_t gemm_tc_launch(GemmTcArgs a, int bf16, dim3 grid, size_t smem, cudaS
     else e = bf16 ? launch_tc<1, 1, 0, 1>(tm, tc, tw, ts, a, grid, smem, stream) : launch_tc<0, 1, 0, 1>(tm, tc, tw, ts, a, grid, smem, stream);
     if (e != cudaSuccess || !a.defer || grid.z < 2) return e;
     const dim3 rgrid(grid.x * grid.y, a.ntok_pad / 8);
-    if (bf16) splitk_reduce_kernel<1><<<rgrid, 256, 0, stream>>>(a, (int)grid.z, (int)grid.x);
-    else splitk_reduce_kernel<0><<<rgrid, 256, 0, stream>>>(a, (int)grid.z, (int)grid.x);
-    return cudaGetLastError();
+    if (bf16) return launch_pdl(splitk_reduce_kernel<1>, rgrid, dim3(256), 0, stream, a, (int)grid.z, (int)grid.x);
+    return launch_pdl(splitk_reduce_kernel<0>, rgrid, dim3(256), 0, stream, a, (int)grid.z, (int)grid.x);
 }
 
 }  // namespace smeg

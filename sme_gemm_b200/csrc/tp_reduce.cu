@@ -180,6 +180,10 @@ cudaError_t tp_reduce_finish_launch(const TpReduceArgs& a, int sm_count, cudaStr
     size_t ctas = ((a.oneshot ? nvec : (a.pushed ? a.slice / 4 : (nvec + a.world - 1) / a.world)) + 255) / 256;
     if (ctas < 1) ctas = 1;
     if (ctas > (size_t)kTpMaxGrid) ctas = (size_t)kTpMaxGrid;
+    // A plain launch, on purpose: the kernel ahead of it in the stream may have pushed this rank's partial rows into
+    // peer memory, and only the end of that grid guarantees those stores are performed at the peers before the "ready"
+    // flag below can be seen there.  (Launched as a programmatic dependent, griddepcontrol.wait made them visible to this
+    // grid but not to the peers: the cross-rank check of the bench caught wrong sums.)
     tp_reduce_finish_kernel<<<(unsigned)ctas, 256, 0, stream>>>(a);
     return cudaGetLastError();
 }
