@@ -289,8 +289,10 @@ int smeg_mlp_reduce_finish_dev(float *y, const uint64_t *buf_ptrs, const uint64_
  * projection's last stage stores every f32 result row straight into the receive area of the rank that owns it (plain
  * stores to peer-mapped memory; row i belongs to rank i / rows, rows = ceil(m / world)), so that the owner later sums
  * from its own memory.  A buffer is then world slots of rows * d floats (slot s = rank s's partial of this rank's rows)
- * followed by m * d f16 results: (world * rows * d) * 4 + m * d * 2 bytes.  smeg_mlp_reduce_finish_pushed_dev is the
- * matching finish (same flag protocol and guarantees as above; no one-shot form).  rc -3: the step is too small for
+ * followed by m * d result words of 4 bytes: (world * rows * d + m * d) * 4 bytes.  smeg_mlp_reduce_finish_pushed_dev is
+ * the matching finish: one "ready" flag round as above, then every owner sums its rows from its own memory and sends the
+ * f16 results to the peers as 8-byte words that carry the call's sequence number beside two values, which the receivers
+ * poll -- no fence and no second flag round; same guarantees as above (bounded waits, rc -7), no one-shot form.  rc -3: the step is too small for
  * this form (m <= 64) -- use smeg_mlp_partial_dev + smeg_mlp_reduce_finish_dev. */
 int smeg_mlp_partial_push_dev(smeg_mlp *mlp, const uint16_t *x, const uint64_t *buf_ptrs, int rank, int world, size_t m,
                               void *stream);

@@ -52,15 +52,29 @@ __device__ __forceinline__ uint2 ld_sys_u2(const void* p) {
 __device__ __forceinline__ void st_sys_u2(void* p, uint2 v) {
     asm volatile("st.relaxed.sys.global.v2.u32 [%0], {%1,%2};" ::"l"(p), "r"(v.x), "r"(v.y) : "memory");
 }
+__device__ __forceinline__ void st_sys_u4(void* p, uint4 v) {
+    asm volatile("st.relaxed.sys.global.v4.u32 [%0], {%1,%2,%3,%4};" ::"l"(p), "r"(v.x), "r"(v.y), "r"(v.z), "r"(v.w) : "memory");
+}
+__device__ __forceinline__ uint4 ld_sys_u4(const void* p) {
+    uint4 v;
+    asm volatile("ld.relaxed.sys.global.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(p) : "memory");
+    return v;
+}
 __device__ __forceinline__ float round_f16(float x) { return __half2float(__float2half_rn(x)); }
 
-// Waits until *flag >= seq (sequence numbers compared as a signed difference).  One second at most.
+__device__ __forceinline__ uint32_t ld_relaxed_sys(const uint32_t* p) {
+    uint32_t v;
+    asm volatile("ld.relaxed.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+    return v;
+}
+// Waits until *flag >= seq (sequence numbers compared as a signed difference).  One second at most.  The flag lives
+// in this rank's own memory; it is polled with relaxed loads (the timer is read every 32 polls) and acquired once.
 __device__ __forceinline__ bool wait_flag(const uint32_t* flag, uint32_t seq) {
+    if ((int)(ld_acquire_sys(flag) - seq) >= 0) return true;
     const unsigned long long t0 = global_ns();
-    for (;;) {
-        if ((int)(ld_acquire_sys(flag) - seq) >= 0) return true;
-        if (global_ns() - t0 > 1000000000ull) return false;
-        __nanosleep(100);
+    for (unsigned spins = 0;; ++spins) {
+        if ((int)(ld_relaxed_sys(flag) - seq) >= 0) return (int)(ld_acquire_sys(flag) - seq) >= 0;
+        if ((spins & 31u) == 31u && global_ns() - t0 > 1000000000ull) return false;
     }
 }
 
@@ -138,17 +152,53 @@ __global__ void __launch_bounds__(256) tp_reduce_finish_kernel(const __grid_cons
                 if (v >= v1) continue;
                 const __half2 lo = __floats2half2_rn(acc[u].x, acc[u].y), hi = __floats2half2_rn(acc[u].z, acc[u].w);
                 const uint2 h = make_uint2(*reinterpret_cast<const uint32_t*>(&lo), *reinterpret_cast<const uint32_t*>(&hi));
-                for (int s = 0; s < W; ++s)
-                    if (s != r) st_sys_u2(reinterpret_cast<unsigned char*>(p.bufs[s] + p.res_off) + 8 * v, h);
+                if (p.pushed) {
+                    // results travel with their own arrival mark: two 8-byte words (2 f16, sequence number) per vector,
+                    // each written whole, so the receiver needs no fence and no flag round -- it polls the words
+                    const uint4 ll = make_uint4(h.x, p.seq, h.y, p.seq);
+                    for (int s = 0; s < W; ++s)
+                        if (s != r) st_sys_u4(reinterpret_cast<unsigned char*>(p.bufs[s] + p.res_off) + 16 * v, ll);
+                } else {
+                    for (int s = 0; s < W; ++s)
+                        if (s != r) st_sys_u2(reinterpret_cast<unsigned char*>(p.bufs[s] + p.res_off) + 8 * v, h);
+                }
                 const float2 f0 = __half22float2(lo), f1 = __half22float2(hi);
                 add_into(p.y, v, make_float4(f0.x, f0.y, f1.x, f1.y));
             }
         }
     }
+    if (p.pushed) {
+        // ---- 2'/3': the other owners' results arrive marked; a word is taken when both of its marks carry this call's
+        // sequence number (an owner writes them only after it has summed, i.e. after it has read this rank's partial) ----
+        const unsigned char* mine_ll = reinterpret_cast<const unsigned char*>(p.bufs[r] + p.res_off);
+        const unsigned long long t0 = global_ns();
+        bool ok = true;
+        for (int s = 0; s < W && ok; ++s) {
+            if (s == r) continue;
+            const size_t v0 = per * s + cper * b, v1 = min(min(nvec, per * (s + 1)), v0 + cper);
+            for (size_t v = v0 + tid; v < v1 && ok; v += blockDim.x) {
+                uint4 w = ld_sys_u4(mine_ll + 16 * v);
+                for (unsigned spins = 0; w.y != p.seq || w.w != p.seq; ++spins) {
+                    if ((spins & 63u) == 63u && global_ns() - t0 > 1000000000ull) { ok = false; break; }
+                    w = ld_sys_u4(mine_ll + 16 * v);
+                }
+                if (!ok) break;
+                const float2 f0 = __half22float2(*reinterpret_cast<const __half2*>(&w.x));
+                const float2 f1 = __half22float2(*reinterpret_cast<const __half2*>(&w.z));
+                add_into(p.y, v, make_float4(f0.x, f0.y, f1.x, f1.y));
+            }
+        }
+        if (!ok && p.status) atomicOr(p.status, STATUS_PEER_TIMEOUT);
+        return;
+    }
     // ---- 2: this CTA's part is written everywhere ----
-    __threadfence_system();
+    // (the barrier orders every thread's peer stores before the flag threads; their release at system scope is
+    // cumulative over what happened before it, so one fence per flag thread is enough)
     __syncthreads();
-    if (tid < W && tid != r) st_release_sys(p.flags[tid] + kTpReadyWords + r * kTpMaxGrid + b, p.seq);
+    if (tid < W && tid != r) {
+        __threadfence_system();
+        st_release_sys(p.flags[tid] + kTpReadyWords + r * kTpMaxGrid + b, p.seq);
+    }
 
     // ---- 3: the other owners' part b, from my own result area ----
     if (tid < W && tid != r && !wait_flag(p.flags[r] + kTpReadyWords + tid * kTpMaxGrid + b, p.seq)) s_fail = 1;

@@ -59,7 +59,8 @@ class PeerReduce:
         # the pushed form keeps `world` slots of ceil(m / world) rows (one per sending rank) ahead of the f16 results
         self._rows = -(-m // self.world)
         self._recv = self.world * self._rows * d
-        self._stride = (max(self._len, self._recv) + self._len // 2 + 3) // 4 * 4   # floats per buffer, whole 16-byte vectors
+        # (results: m * d f16 in the pulled form, m * d marked 4-byte words in the pushed form)
+        self._stride = (max(self._len, self._recv) + self._len + 3) // 4 * 4   # floats per buffer, whole 16-byte vectors
         self.push = m > 64 and self.world > 1 and os.environ.get("SMEG_TP_PUSH", "1") != "0"
         self._both = symm.empty((2, self._stride), dtype=torch.float32, device=dev)
         self.flags = symm.empty((FLAG_WORDS,), dtype=torch.int32, device=dev)
