@@ -397,6 +397,8 @@ def run_ours(args):
     x_host = x.cpu().pin_memory()
     y_host = torch.zeros(m, HIDDEN, dtype=torch.float32).pin_memory()
 
+    tps = [TpMlp(mm, world, None, peer) for mm in mlps] if (world > 1 and peer is not None) else None
+
     def step(i, xb=None, yb=None):
         mlp = mlps[i % nsets]
         xb = x if xb is None else xb
@@ -405,7 +407,7 @@ def run_ours(args):
             mlp.accumulate(xb, yb, m)
         else:
             if peer is not None:
-                TpMlp(mlp, world, None, peer).accumulate(xb, yb, m)   # pushes the partial rows to their owners when it can
+                tps[i % nsets].accumulate(xb, yb, m)   # pushes the partial rows to their owners when it can
             else:
                 mlp.partial(xb, partial, m)
                 dist.all_reduce(partial)
