@@ -253,6 +253,22 @@ int smeg_gemm_dense(const smeg_dense *w, const uint16_t *a, uint16_t *c, size_t 
 
 /* ---- MLP block ---------------------------------------------------------------- */
 
+/* The attention step of SelfAttention::accumulate (src/self_attention.rs:189-231) on the device.
+ * smeg_kv_append_dev -- KvCache::extend (src/kernels/kv_attention.rs:499-520): `rows` rows of row_len = kv_heads *
+ * head_dim f16 values each for keys and values, taken from rows of `src` (src_stride elements apart, the keys at
+ * element k_off and the values at v_off of a row: the [q | k | v] rows a fused projection produced), copied to cache
+ * rows pos .. pos + rows.
+ * smeg_attn_kv_causal_dev -- attention_kv_causal_f16 (src/kernels/kv_attention.rs:155-242; rows = 1, start = len - 1 is
+ * attention_kv_f16, :29-139): query row i attends to keys 0..=start+i of caches that already hold start + rows rows;
+ * q is f16 bits (q_f32 = 0) or f32 rows of heads * head_dim values q_stride elements apart, out f32 [rows][heads *
+ * head_dim].  Per head softmax(f16(q * scale) . k) @ v with f32 sums in key / depth order.  head_dim a multiple of 8 in
+ * 8..=256 and heads a positive multiple of kv_heads (-4 otherwise, where the reference panics); -3 beyond ~50 k keys. */
+int smeg_kv_append_dev(uint16_t *k_cache, uint16_t *v_cache, const uint16_t *src, size_t src_stride, size_t k_off,
+                       size_t v_off, size_t row_len, size_t pos, size_t rows, void *stream);
+int smeg_attn_kv_causal_dev(float *out, const void *q, int q_f32, size_t q_stride, const uint16_t *k, const uint16_t *v,
+                            size_t start, size_t rows, size_t heads, size_t kv_heads, size_t head_dim, float scale,
+                            void *stream);
+
 /* Mlp::gated (src/mlp.rs:80-92): gate_up is the 2*hidden-column interleaved
  * matrix GatedLinear::quantize builds (32 gate columns then 32 up columns,
  * src/linear.rs:603-656), down is hidden -> d.  The handles are borrowed and

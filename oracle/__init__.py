@@ -330,3 +330,14 @@ def q1_pack_band(signs, layout, scales, n, k, block):
     L.orc_q1_pack_band(_p(signs), C.c_int(layout), _p(_u16(scales)), C.c_size_t(n), C.c_size_t(k),
                        C.c_size_t(block), _p(packed), _p(sc))
     return packed, sc
+
+
+def attention_kv_causal(q, k, v, start: int, rows: int, heads: int, kv_heads: int, head_dim: int, scale: float) -> np.ndarray:
+    """attention_kv_causal_f16, portable arm (src/kernels/kv_attention.rs:155-331): q f32 [rows][heads][head_dim], k / v
+    f16 bits [start + rows][kv_heads * head_dim]; returns out f32 like q."""
+    q = np.ascontiguousarray(q, np.float32)
+    k, v = _u16(k), _u16(v)
+    out = np.zeros(rows * heads * head_dim, np.float32)
+    lib().orc_attention_kv_causal(_p(q), _p(k), _p(v), C.c_size_t(start), C.c_size_t(rows), C.c_size_t(heads),
+                                  C.c_size_t(kv_heads), C.c_size_t(head_dim), C.c_float(scale), _p(out))
+    return out.reshape(rows, heads * head_dim)

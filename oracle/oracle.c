@@ -819,3 +819,41 @@ void orc_q1_pack_band(const uint8_t *signs, int layout, const uint16_t *scales, 
         for (size_t blk = 0; blk < nbk; blk++) sc[lb_scale_index(spb, blk, j)] = scales[j * nbk + blk];
     }
 }
+
+/* attention_kv_causal_f16, portable arm (src/kernels/kv_attention.rs:155-242 with one_row :281-331): query row i of
+ * `rows` attends to keys 0..=start+i of an f16 cache whose rows hold kv_heads * head_dim values; per head
+ * softmax(f16(q * scale) . k) @ v with f32 sums in key / depth order, probabilities exp(s - max) in f32, the division
+ * by their sum last.  q and out are [rows][heads][head_dim] f32.  (attention_kv_f16, :29-139, is rows = 1 with
+ * start = len - 1.) */
+void orc_attention_kv_causal(const float *q, const uint16_t *k, const uint16_t *v, size_t start, size_t rows,
+                             size_t heads, size_t kv_heads, size_t head_dim, float scale, float *out) {
+    size_t ld = kv_heads * head_dim, qr = heads * head_dim, group = heads / kv_heads;
+    float *scores = (float *)malloc((start + rows) * sizeof(float));
+    float *qh = (float *)malloc(head_dim * sizeof(float));
+    for (size_t i = 0; i < rows; i++) {
+        size_t len = start + i + 1;
+        for (size_t h = 0; h < heads; h++) {
+            size_t off = (h / group) * head_dim;
+            for (size_t d = 0; d < head_dim; d++) qh[d] = orc_f16_to_f32(orc_f32_to_f16(q[i * qr + h * head_dim + d] * scale));
+            float mx = -INFINITY;
+            for (size_t t = 0; t < len; t++) {
+                float s = 0.0f;
+                for (size_t d = 0; d < head_dim; d++) s += qh[d] * orc_f16_to_f32(k[t * ld + off + d]);
+                scores[t] = s;
+                mx = s > mx ? s : mx;          /* f32::max */
+            }
+            float sum = 0.0f;
+            for (size_t t = 0; t < len; t++) {
+                scores[t] = expf(scores[t] - mx);
+                sum += scores[t];
+            }
+            float *oh = out + i * qr + h * head_dim;
+            for (size_t d = 0; d < head_dim; d++) oh[d] = 0.0f;
+            for (size_t t = 0; t < len; t++)
+                for (size_t d = 0; d < head_dim; d++) oh[d] += scores[t] * orc_f16_to_f32(v[t * ld + off + d]);
+            for (size_t d = 0; d < head_dim; d++) oh[d] /= sum;
+        }
+    }
+    free(scores);
+    free(qh);
+}

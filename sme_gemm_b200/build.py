@@ -15,7 +15,7 @@ HERE = os.path.dirname(os.path.abspath(__file__))
 CSRC = os.path.join(HERE, "csrc")
 OBJ = os.path.join(HERE, "build")
 LIB = os.path.join(HERE, "libsmeg_b200.so")
-SOURCES = ["api.cu", "q4_gemv.cu", "gemv_direct.cu", "lowbit_gemv.cu", "lowbit_tc.cu", "lowbit_mma.cu", "gemm_tc.cu", "elementwise.cu", "transcode.cu", "tp_reduce.cu", "pack.cc"]
+SOURCES = ["api.cu", "q4_gemv.cu", "gemv_direct.cu", "lowbit_gemv.cu", "lowbit_tc.cu", "lowbit_mma.cu", "gemm_tc.cu", "elementwise.cu", "attention.cu", "transcode.cu", "tp_reduce.cu", "pack.cc"]
 NVCC = os.environ.get("NVCC", "/usr/local/cuda/bin/nvcc")
 FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",
          "-Xcompiler", "-fPIC,-ffp-contract=off,-Wall", "--expt-relaxed-constexpr"]

@@ -1138,6 +1138,33 @@ int smeg_gemm_dense(const smeg_dense* w, const uint16_t* a, uint16_t* c, size_t 
 // ---------------------------------------------------------------------------
 // MLP block
 // ---------------------------------------------------------------------------
+// ---- attention against an f16 KV cache ----
+int smeg_kv_append_dev(uint16_t* k_cache, uint16_t* v_cache, const uint16_t* src, size_t src_stride, size_t k_off, size_t v_off,
+                       size_t row_len, size_t pos, size_t rows, void* stream) {
+    if (rows == 0 || row_len == 0) return 0;
+    if (!k_cache || !v_cache || !src || k_off + row_len > src_stride || v_off + row_len > src_stride) return -4;
+    if (!dev_state()) return -5;
+    return kv_append_launch(k_cache, v_cache, src, src_stride, k_off, v_off, row_len, pos, rows, (cudaStream_t)stream) == cudaSuccess ? 0 : -6;
+}
+int smeg_attn_kv_causal_dev(float* out, const void* q, int q_f32, size_t q_stride, const uint16_t* k, const uint16_t* v, size_t start,
+                            size_t rows, size_t heads, size_t kv_heads, size_t head_dim, float scale, void* stream) {
+    if (rows == 0) return 0;
+    // the reference's panics (src/kernels/kv_attention.rs:171-199) as rc -4
+    if (!out || !q || !k || !v) return -4;
+    if (head_dim % 8 != 0 || head_dim < 8 || head_dim > 256) return -4;
+    if (kv_heads == 0 || heads == 0 || heads % kv_heads != 0 || q_stride < heads * head_dim) return -4;
+    if (((uintptr_t)k & 15) != 0 || ((uintptr_t)v & 15) != 0) return -4;
+    if (start + rows > 0x7fffffffu || heads > 65535 || rows > 65535) return -3;
+    if (!dev_state()) return -5;
+    AttnArgs a;
+    memset(&a, 0, sizeof(a));
+    a.out = out; a.q = q; a.q_stride = q_stride; a.k = k; a.v = v;
+    a.start = (int)start; a.rows = (int)rows; a.heads = (int)heads; a.kv_heads = (int)kv_heads; a.head_dim = (int)head_dim;
+    a.scale = scale;
+    const cudaError_t e = attn_kv_causal_launch(a, q_f32, (cudaStream_t)stream);
+    return e == cudaSuccess ? 0 : (e == cudaErrorInvalidValue ? -3 : -6);
+}
+
 int smeg_mlp_create(const smeg_q4* gate_up, const smeg_q4* down, uint32_t gate_act, smeg_mlp** out) {
     if (!out || !gate_up || !down) return -4;
     *out = nullptr;

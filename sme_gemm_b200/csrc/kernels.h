@@ -208,6 +208,21 @@ cudaError_t round_add_f32_launch(float* y, const float* partial_sum, size_t n, c
 constexpr int kTpReadyWords = 8;                                   // "ready" from rank s at [s]
 constexpr int kTpMaxGrid = 160;                                    // most CTAs of the kernel
 constexpr int kTpFlagWords = kTpReadyWords + 8 * kTpMaxGrid;       // "done" from owner s, CTA b at [8 + s * kTpMaxGrid + b]
+// ---- causal attention against an f16 KV cache (attention.cu) ----
+struct AttnArgs {
+    float* out;            // [rows][heads][head_dim] f32
+    const void* q;         // rows of heads * head_dim queries, f16 bits or f32, q_stride elements apart
+    size_t q_stride;
+    const uint16_t* k;     // cache rows of kv_heads * head_dim f16 bits
+    const uint16_t* v;
+    int start, rows;       // query row i attends to keys 0..=start+i
+    int heads, kv_heads, head_dim;
+    float scale;
+};
+cudaError_t attn_kv_causal_launch(const AttnArgs& a, int q_f32, cudaStream_t stream);
+cudaError_t kv_append_launch(uint16_t* kc, uint16_t* vc, const uint16_t* src, size_t stride, size_t k_off, size_t v_off, size_t row_len,
+                             size_t pos, size_t rows, cudaStream_t stream);
+
 struct TpReduceArgs {
     float* bufs[8];        // every rank's buffer, peer-mapped into this process: len f32 partial sums, then len f16 results
     uint32_t* flags[8];    // every rank's flag array (kTpFlagWords words, zero before the first call)

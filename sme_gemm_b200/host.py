@@ -981,22 +981,182 @@ class Norm:
                                                              dim, self.eps, int(self.is_rms), _stream()))
 
 
-class Block:
-    """The MLP half of a pre-norm transformer layer: x += mlp(norm2(x)) (Block::accumulate, src/block.rs:96-105, its
-    last two lines).  The attention half (norm1, SelfAttention, the KV cache) is not part of this library: a caller
-    runs it and then this."""
+class KvCache:
+    """An f16 key/value cache for one attention layer, on the device, with the attention against it (KvCache,
+    src/kernels/kv_attention.rs:354-581): rows of kv_heads * head_dim values, one per position, appended in order;
+    queries have `heads` heads (a multiple of kv_heads: grouped-query attention); the score scale defaults to
+    1 / sqrt(head_dim)."""
 
-    def __init__(self, norm2: Norm, mlp: Mlp):
+    def __init__(self, heads: int, kv_heads: int, head_dim: int, capacity: int):
+        assert head_dim % 8 == 0 and 8 <= head_dim <= 256, "head_dim must be a multiple of 8 in 8..=256"
+        assert kv_heads > 0 and heads > 0 and heads % kv_heads == 0, "heads must be a positive multiple of kv_heads"
+        self._heads, self._kv_heads, self._head_dim, self._capacity = heads, kv_heads, head_dim, capacity
+        self._k = torch.zeros((max(capacity, 1), kv_heads * head_dim), dtype=torch.float16, device="cuda")
+        self._v = torch.zeros_like(self._k)
+        self._len = 0
+        self._scale = float(np.float32(1.0) / np.sqrt(np.float32(head_dim)))
+
+    def with_scale(self, scale: float) -> "KvCache":
+        self._scale = float(np.float32(scale))
+        return self
+
+    def len(self) -> int:
+        return self._len
+
+    def is_empty(self) -> bool:
+        return self._len == 0
+
+    def capacity(self) -> int:
+        return self._capacity
+
+    def row_len(self) -> int:
+        return self._kv_heads * self._head_dim
+
+    def query_len(self) -> int:
+        return self._heads * self._head_dim
+
+    def heads(self) -> int:
+        return self._heads
+
+    def kv_heads(self) -> int:
+        return self._kv_heads
+
+    def head_dim(self) -> int:
+        return self._head_dim
+
+    def scale(self) -> float:
+        return self._scale
+
+    def clear(self) -> None:
+        self._len = 0
+
+    def truncate(self, n: int) -> None:
+        self._len = min(self._len, n)
+
+    def keys(self):
+        return self._k[: self._len]
+
+    def values(self):
+        return self._v[: self._len]
+
+    def extend_from(self, src, stride: int, k_off: int, v_off: int, rows: int) -> None:
+        """Appends `rows` key and value rows taken from rows of the f16 device tensor `src` (stride elements apart,
+        keys at element k_off, values at v_off of a row): what a fused [q | k | v] projection produced."""
+        assert self._len + rows <= self._capacity, f"KvCache full: {self._len} + {rows} rows over capacity {self._capacity}"
+        check("smeg_kv_append_dev", lib().smeg_kv_append_dev(_ptr(self._k), _ptr(self._v), _ptr(src), stride, k_off, v_off,
+                                                            self.row_len(), self._len, rows, _stream()))
+        self._len += rows
+
+    def extend(self, k, v) -> None:
+        """KvCache::extend: whole rows of f16 keys and values (device tensors)."""
+        row = self.row_len()
+        assert _numel(k) == _numel(v) and _numel(k) % row == 0 and _numel(k) > 0, \
+            "k and v hold the same whole number of kv_heads * head_dim rows"
+        rows = _numel(k) // row
+        assert self._len + rows <= self._capacity, f"KvCache full: {self._len} + {rows} rows over capacity {self._capacity}"
+        self._k[self._len:self._len + rows].copy_(k.reshape(rows, row))
+        self._v[self._len:self._len + rows].copy_(v.reshape(rows, row))
+        self._len += rows
+
+    push = extend
+
+    def _attend(self, q, q_stride: int, rows: int, out) -> None:
+        q_f32 = 1 if q.dtype == torch.float32 else 0
+        check("smeg_attn_kv_causal_dev",
+              lib().smeg_attn_kv_causal_dev(_ptr(out), _ptr(q), q_f32, q_stride, _ptr(self._k), _ptr(self._v), self._len - rows, rows,
+                                            self._heads, self._kv_heads, self._head_dim, self._scale, _stream()))
+
+    def attend(self, q, out) -> None:
+        """One query row of heads * head_dim (f32 or f16) against every cached position; out f32."""
+        assert self._len > 0, "attention_kv_f16 needs at least one cached key"
+        assert _numel(q) == self.query_len() and _numel(out) == self.query_len(), "q is heads * head_dim"
+        self._attend(q, self.query_len(), 1, out)
+
+    def attend_causal(self, q, rows: int, out) -> None:
+        """`rows` query rows, row i attending to positions 0..=len - rows + i (the cache already holds the block)."""
+        assert rows <= self._len, f"attend_causal: {rows} rows but {self._len} cached"
+        assert _numel(q) == rows * self.query_len() and _numel(out) == rows * self.query_len(), "q is rows * heads * head_dim"
+        self._attend(q, self.query_len(), rows, out)
+
+
+class SelfAttention:
+    """A transformer self-attention block added into a residual stream (SelfAttention, src/self_attention.rs:66-231, its
+    separate-steps path): the fused qkv projection ([q | k | v] in head order), the new positions' keys and values
+    appended to a KvCache, causal attention over the cache, and the out projection: y += out(attention(q, K, V)).  No
+    rotary embedding, as there."""
+
+    def __init__(self, qkv: Linear, out: Linear, heads: int, kv_heads: int, head_dim: int):
+        assert kv_heads > 0 and heads > 0 and heads % kv_heads == 0, "heads must be a positive multiple of kv_heads"
+        assert qkv.n() == (heads + 2 * kv_heads) * head_dim, "qkv has (heads + 2 * kv_heads) * head_dim outputs"
+        assert out.k() == heads * head_dim, "out takes heads * head_dim inputs"
+        self.qkv, self.out, self._heads, self._kv_heads, self._head_dim = qkv, out, heads, kv_heads, head_dim
+
+    @staticmethod
+    def new(qkv: Linear, out: Linear, heads: int, kv_heads: int, head_dim: int) -> "SelfAttention":
+        return SelfAttention(qkv, out, heads, kv_heads, head_dim)
+
+    def width(self) -> int:
+        return self.qkv.k()
+
+    def out_width(self) -> int:
+        return self.out.n()
+
+    def cache(self, capacity: int) -> KvCache:
+        return KvCache(self._heads, self._kv_heads, self._head_dim, capacity)
+
+    def accumulate(self, x, cache: KvCache, y, m: int) -> None:
+        """y (m x out.n f32) += out(attention(qkv(x))) for m rows of f16 x at the cache's next positions, which this appends."""
+        d = self.width()
+        assert _is_torch(x) and x.dtype == torch.float16 and _numel(x) == m * d, "x is m * width"
+        assert _numel(y) == m * self.out.n(), "y is m * out.n()"
+        assert cache.heads() == self._heads and cache.kv_heads() == self._kv_heads and cache.head_dim() == self._head_dim, \
+            "the cache's heads match the block's"
+        assert cache.len() + m <= cache.capacity(), f"{m} rows do not fit in the cache"
+        q_len, kv_len = self._heads * self._head_dim, self._kv_heads * self._head_dim
+        w = q_len + 2 * kv_len
+        qkv = torch.empty((m, w), dtype=torch.float16, device=x.device)
+        self.qkv.forward(x, qkv, m)
+        cache.extend_from(qkv, w, q_len, q_len + kv_len, m)
+        att = torch.empty((m, q_len), dtype=torch.float32, device=x.device)
+        cache._attend(qkv, w, m, att)                       # the queries are the first q_len values of each projected row
+        att16 = torch.empty((m, q_len), dtype=torch.float16, device=x.device)
+        check("smeg_f32_to_f16_dev", lib().smeg_f32_to_f16_dev(_ptr(att16), _ptr(att), m * q_len, _stream()))
+        self.out.accumulate(att16, y, m)
+
+
+class Block:
+    """A pre-norm transformer layer over an f32 residual stream: x += attn(norm1(x)), then x += mlp(norm2(x))
+    (Block, src/block.rs:40-106).  Block(norm2, mlp) is the MLP half alone, for callers that run attention themselves."""
+
+    def __init__(self, *parts):
+        if len(parts) == 2:
+            norm1, attn, (norm2, mlp) = None, None, parts
+        else:
+            norm1, attn, norm2, mlp = parts
         d = norm2.width()
-        assert mlp.k() == d and mlp.n() == d, "the norms, attention and MLP share the residual's width"
-        self.norm2, self.mlp = norm2, mlp
+        assert mlp.k() == d and mlp.n() == d and (attn is None or (norm1.width() == d and attn.width() == d and attn.out_width() == d)), \
+            "the norms, attention and MLP share the residual's width"
+        self.norm1, self.attn, self.norm2, self.mlp = norm1, attn, norm2, mlp
+
+    @staticmethod
+    def new(norm1: Norm, attn: SelfAttention, norm2: Norm, mlp: Mlp) -> "Block":
+        return Block(norm1, attn, norm2, mlp)
 
     def width(self) -> int:
         return self.norm2.width()
 
-    def accumulate(self, x, rows: int) -> None:
+    def cache(self, capacity: int) -> KvCache:
+        return self.attn.cache(capacity)
+
+    def accumulate(self, x, *args) -> None:
+        """accumulate(x, cache, rows): both halves at the cache's next positions; accumulate(x, rows): the MLP half."""
+        cache, rows = (None, args[0]) if len(args) == 1 else args
         assert _is_torch(x) and x.dtype == torch.float32 and x.numel() == rows * self.width(), "x is rows * width"
         h = torch.empty((rows, self.width()), dtype=torch.float16, device=x.device)
+        if cache is not None:
+            assert self.attn is not None, "this block was built without its attention half"
+            self.norm1.forward(x, h)
+            self.attn.accumulate(h, cache, x, rows)
         self.norm2.forward(x, h)
         self.mlp.accumulate(h, x, rows)
 

@@ -398,3 +398,30 @@ def test_threads_do_not_change_results():
     orc.set_threads(1)
     assert np.array_equal(c1, c4)
     assert np.array_equal(c1, orc.gemm16(a, orc.q4_dequant(q, s, None, n, k), m, n, k))
+
+
+@pytest.mark.parametrize("heads,kv_heads,hd,start,rows", [(4, 4, 16, 0, 1), (6, 2, 32, 7, 5), (2, 1, 64, 30, 3)])
+def test_attention_oracle_against_an_f64_statement(heads, kv_heads, hd, start, rows):
+    """orc_attention_kv_causal (src/kernels/kv_attention.rs:155-331) against the same formula in f64: q * scale rounded
+    to f16 once, grouped-query head mapping, causal prefix, softmax, value average."""
+    rng = np.random.default_rng(heads + start)
+    n = start + rows
+    q = rng.standard_normal((rows, heads * hd)).astype(np.float32)
+    k = orc.f32_to_f16_bits(rng.standard_normal((n, kv_heads * hd)).astype(np.float32))
+    v = orc.f32_to_f16_bits(rng.standard_normal((n, kv_heads * hd)).astype(np.float32))
+    scale = 1.0 / np.sqrt(hd)
+    got = orc.attention_kv_causal(q, k, v, start, rows, heads, kv_heads, hd, scale).reshape(rows, heads, hd)
+    kf = orc.f16_bits_to_f32(k).reshape(n, kv_heads, hd).astype(np.float64)
+    vf = orc.f16_bits_to_f32(v).reshape(n, kv_heads, hd).astype(np.float64)
+    qh = orc.f16_bits_to_f32(orc.f32_to_f16_bits(q * np.float32(scale))).reshape(rows, heads, hd).astype(np.float64)
+    group = heads // kv_heads
+    for i in range(rows):
+        length = start + i + 1
+        for h in range(heads):
+            s = kf[:length, h // group] @ qh[i, h]
+            p = np.exp(s - s.max())
+            want = (p[:, None] * vf[:length, h // group]).sum(0) / p.sum()
+            assert np.max(np.abs(got[i, h] - want)) <= 2e-6 * (1.0 + np.max(np.abs(want)))
+    # one row with start = len - 1 is attention_kv_f16; a row of a block equals the one-row call over its prefix exactly
+    one = orc.attention_kv_causal(q[rows - 1:], k, v, n - 1, 1, heads, kv_heads, hd, scale)
+    assert np.array_equal(one.reshape(-1), got[rows - 1].reshape(-1))
