@@ -138,3 +138,69 @@ def test_block_equals_its_halves(rows):
     block.mlp.accumulate(h, xp, rows)
     assert torch.equal(x, xp)
     assert torch.isfinite(x).all() and sg.last_status() == 0
+
+
+def test_two_layer_model_from_a_checkpoint_file(tmp_path):
+    """A safetensors file -> Checkpoint -> Blocks (examples/shakespeare/model.rs:84-125 in small): a prompt through both
+    layers against the oracle's chain on the same quantised weights, then decode steps against re-running the longer prompt."""
+    from sme_gemm_b200.checkpoint import Checkpoint
+    from test_checkpoint import write_safetensors
+    rng = np.random.default_rng(42)
+    d, heads, hd, ff, layers = 64, 2, 32, 256, 2
+    tensors = {}
+    for i in range(layers):
+        p = f"transformer.h.{i}."
+        tensors[p + "ln_1.weight"] = ("F32", rng.uniform(0.5, 1.5, d).astype("<f4"))
+        tensors[p + "ln_2.weight"] = ("F32", rng.uniform(0.5, 1.5, d).astype("<f4"))
+        tensors[p + "attn.c_attn.weight"] = ("F32", (rng.standard_normal((3 * d, d)) * 0.1).astype("<f4"))
+        tensors[p + "attn.c_proj.weight"] = ("F32", (rng.standard_normal((d, d)) * 0.1).astype("<f4"))
+        tensors[p + "mlp.c_fc.weight"] = ("F32", (rng.standard_normal((ff, d)) * 0.1).astype("<f4"))
+        tensors[p + "mlp.c_proj.weight"] = ("F32", (rng.standard_normal((d, ff)) * 0.1).astype("<f4"))
+    path = tmp_path / "model.safetensors"
+    path.write_bytes(write_safetensors(tensors, {"format": "pt"}))
+    ck = Checkpoint.load(path)
+    blocks = []
+    for i in range(layers):
+        p = f"transformer.h.{i}."
+        blocks.append(sg.Block.new(ck.norm(p + "ln_1.weight"),
+                                   sg.SelfAttention.new(ck.linear(p + "attn.c_attn.weight"), ck.linear(p + "attn.c_proj.weight"), heads, heads, hd),
+                                   ck.norm(p + "ln_2.weight"),
+                                   sg.Mlp.new(ck.linear(p + "mlp.c_fc.weight"), sg.Gate.Gelu, ck.linear(p + "mlp.c_proj.weight"))))
+    rows, extra = 20, 3
+    x0 = rng.standard_normal((rows + extra, d)).astype(np.float32)
+
+    def run(n_prefill, n_decode):
+        caches = [b.cache(64) for b in blocks]
+        x = torch.from_numpy(x0[:n_prefill].copy()).cuda()
+        for b, c in zip(blocks, caches):
+            b.accumulate(x, c, n_prefill)
+        outs = [x]
+        for s in range(n_decode):
+            xs = torch.from_numpy(x0[n_prefill + s:n_prefill + s + 1].copy()).cuda()
+            for b, c in zip(blocks, caches):
+                b.accumulate(xs, c, 1)
+            outs.append(xs)
+        return torch.cat(outs).cpu().numpy()
+
+    got = run(rows, extra)
+    whole = run(rows + extra, 0)
+    assert max_rel(got, whole) <= 5e-3                                # prefill + decode steps == the longer prompt
+    # the oracle's chain for the prompt
+    x = x0[:rows].copy()
+    scale = float(np.float32(1.0) / np.sqrt(np.float32(hd)))
+    for i in range(layers):
+        p = f"transformer.h.{i}."
+        def lin(name, a_bits, m, nodes=None):
+            w, n, k = ck.matrix(p + name)
+            q, s, _ = orc.q4_quantize(w, 0, n, k)
+            return orc.matmul_q4(a_bits, q, s, None, n, k, 32, m, nodes)
+        h16, _ = orc.norm_rows(x, ck.get(p + "ln_1.weight"), None, 1e-5, False)
+        qkv = orc.f16_bits_to_f32(lin("attn.c_attn.weight", h16, rows)).reshape(rows, 3 * d)
+        att = orc.attention_kv_causal(qkv[:, :d], orc.f32_to_f16_bits(qkv[:, d:2 * d]), orc.f32_to_f16_bits(qkv[:, 2 * d:]), 0, rows,
+                                      heads, heads, hd, scale)
+        x = x + orc.f16_bits_to_f32(lin("attn.c_proj.weight", orc.f32_to_f16_bits(att), rows)).reshape(rows, d)
+        h16, _ = orc.norm_rows(x, ck.get(p + "ln_2.weight"), None, 1e-5, False)
+        hid = lin("mlp.c_fc.weight", h16, rows, orc.Nodes([(8, int(sg.Gate.Gelu), 0.0, None, 0)]))
+        x = x + orc.f16_bits_to_f32(lin("mlp.c_proj.weight", hid, rows)).reshape(rows, d)
+    assert max_rel(got[:rows], x) <= 2e-2
+    assert sg.last_status() == 0
