@@ -18,11 +18,17 @@
 //      and no CTA waits for another CTA of its own grid);
 //   3. CTA b waits for the "done" flags of part b from the other owners and adds their f16 results,
 //      now in its own memory, to its residual stream.
+// Pushed form (p.pushed): the ranks' partials of slice r were stored into rank r's own buffer by the kernel that produced
+// them (slot s = rank s, see GemmTcArgs::push), so step 1 sums from local memory; its f16 results travel as 8-byte words
+// {two values, the call's sequence number} -- each word written whole -- and steps 2 and 3 become: every CTA polls the
+// words of the other owners' part b in its own memory until they carry this call's number, and adds them.  No system
+// fence and no "done" flags; an owner writes its words only after it has summed, so "a rank's kernel ends only after
+// every owner has finished reading what that rank sent" still holds.
 // Flags carry the call's sequence number and only grow.  A rank's kernel ends only after every owner
 // has finished reading its buffer, so the next step may overwrite the buffer at once.  Short vectors
 // take a one-shot form instead (every rank adds all the partials itself after the "ready" flags).
 // Every wait is bounded: after a second it raises the status word and the CTA returns; when that
-// happens in round 0 the residual stream is untouched.
+// happens in the first flag round (0) the residual stream is untouched.
 #include "common.cuh"
 #include "kernels.h"
 
