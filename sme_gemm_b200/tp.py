@@ -78,6 +78,8 @@ class PeerReduce:
         # short vectors: every rank sums everything itself, one flag round instead of two
         self.oneshot = 1 if self._len * 4 <= 128 * 1024 else 0
         self.seq = 0
+        # the ranks' buffers of either parity, as the C ABI takes them (built once: a step is a few calls long)
+        self._bufs = [(C.c_uint64 * self.world)(*[b + par * self._stride * 4 for b in self._base]) for par in (0, 1)]
 
     @property
     def partial(self):
@@ -86,8 +88,7 @@ class PeerReduce:
 
     def next_bufs(self):
         """Every rank's buffer of the coming step, as the C ABI takes them."""
-        off = ((self.seq + 1) & 1) * self._stride * 4
-        return (self._C.c_uint64 * self.world)(*[b + off for b in self._base])
+        return self._bufs[(self.seq + 1) & 1]
 
     def finish(self, y, pushed: bool = False) -> None:
         """y += f32(f16(sum over ranks of their `partial`)), on every rank.  pushed: the partials were stored into their
@@ -95,8 +96,7 @@ class PeerReduce:
         from ._lib import check, lib
         from .host import _ptr, _stream
         self.seq += 1
-        off = (self.seq & 1) * self._stride * 4
-        bufs = (self._C.c_uint64 * self.world)(*[b + off for b in self._base])
+        bufs = self._bufs[self.seq & 1]
         if pushed:
             check("smeg_mlp_reduce_finish_pushed_dev",
                   lib().smeg_mlp_reduce_finish_pushed_dev(_ptr(y), bufs, self._flags, self.rank, self.world, self._m, self._d,
