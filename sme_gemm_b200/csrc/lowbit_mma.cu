@@ -32,7 +32,8 @@ namespace {
 constexpr int kMWarps = 4;
 constexpr int kMThreads = 32 * kMWarps;
 constexpr int kMPF = 8;                                            // units in flight per warp
-constexpr size_t kMRingBytes = (size_t)kMWarps * kMPF * 512;
+// ring slots per warp: no more than the units a warp walks per column group (a smaller CTA lets an SM hold one more)
+__host__ __device__ inline int ring_units(int upw) { return upw < kMPF ? (upw < 1 ? 1 : upw) : kMPF; }
 
 __device__ __forceinline__ void cpa16(void* smem_dst, const void* gsrc) {
     asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(smem_u32(smem_dst)), "l"(gsrc) : "memory");
@@ -63,8 +64,9 @@ __global__ void __launch_bounds__(kMThreads) lowbit_mma_kernel(const __grid_cons
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int g = lane >> 2, t = lane & 3;
     const int M = p.m, kq = p.kq, nb = p.nb, ku = p.ku;
-    uint4* ring_w = reinterpret_cast<uint4*>(smem_raw) + (size_t)warp * PF * 32 + lane;      // + slot * 32
-    uint16_t* SCs = reinterpret_cast<uint16_t*>(smem_raw + kMRingBytes);                      // [nb][16] this group's scale rows
+    const int pfu = ring_units(p.dupw);
+    uint4* ring_w = reinterpret_cast<uint4*>(smem_raw) + (size_t)warp * pfu * 32 + lane;     // + slot * 32
+    uint16_t* SCs = reinterpret_cast<uint16_t*>(smem_raw + (size_t)kMWarps * pfu * 512);      // [nb][16] this group's scale rows
     float* SAs = reinterpret_cast<float*>(SCs + (size_t)nb * 16);                             // [M][nb]
     int* QSs = reinterpret_cast<int*>(SAs + (size_t)M * nb);                                  // [M][nb]
     int* sums = QSs + (size_t)M * nb;                                                         // [nb][M][16]
@@ -207,7 +209,7 @@ __global__ void __launch_bounds__(kMThreads) lowbit_mma_kernel(const __grid_cons
 }
 
 size_t mma_smem(const LowbitGemvArgs& a) {
-    return kMRingBytes + (size_t)a.nb * 32 + (size_t)2 * a.m * a.nb * 4 + (size_t)a.nb * a.m * 16 * 4;
+    return (size_t)kMWarps * ring_units((a.ku + kMWarps - 1) / kMWarps) * 512 + (size_t)a.nb * 32 + (size_t)2 * a.m * a.nb * 4 + (size_t)a.nb * a.m * 16 * 4;
 }
 
 }  // namespace
