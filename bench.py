@@ -688,7 +688,7 @@ def run_ours(args):
     # fused into their stores), else GEMV, gate, GEMV, add; tensor-parallel steps add the finishing pass
     # (above 64 rows: gate/up GEMM, down GEMM and the down projection's depth-split reduce; a rank's shard adds the finish
     # kernel, and one more reduce launch where the planner also splits the gate/up shard's depth -- not counted here)
-    launches_per_step = (3 if m > 64 else 4) if world == 1 else (3 if m > 64 else 3) + 1
+    launches_per_step = (3 if m > 64 else (2 if m <= 4 else 4)) if world == 1 else (3 if m > 64 else (2 if m <= 4 else 3)) + 1
 
     line = {"metric": "q4_mlp_block_tokens_per_s", "value": value, "unit": "tokens/s", "n_gpus": args.gpus, "steps": args.steps,
             "warmup": args.warmup, "ms_per_step": ms / args.steps, "higher_is_better": True, "scaling": "strong",

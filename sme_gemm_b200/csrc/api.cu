@@ -656,7 +656,19 @@ static int q4_affine_twin(const smeg_q4* w, int bf16, const smeg_dense** out) {
     return 0;
 }
 
-// glu / yacc: the fused forms of the MLP block (tensor-core GEMM only, see GemmTcArgs).
+// Does a call of m rows run on the one-wave decode kernel (gemv_direct.cu)?  With glu: also that the matrix interleaves
+// whole 32-column gate / up chunks.
+static bool q4_takes_direct(const smeg_q4* w, const uint16_t* a, size_t m, int bf16, int glu) {
+    if (w->affine || q4_uses_tc(w, a, m) || g_direct_rows <= 0 || (int)m > g_direct_rows) return false;
+    if (glu && w->d.n % 64 != 0) return false;
+    Q4GemvArgs g;
+    memset(&g, 0, sizeof(g));
+    g.m = (int)m; g.n = (int)w->d.n; g.k = (int)w->d.k; g.k64 = (int)w->d.ku; g.log2_block = w->d.log2_block;
+    g.a_vec_ok = (w->d.k % 8 == 0) && ((uintptr_t)a % 16 == 0);
+    return q4_direct_supported(g, bf16);
+}
+
+// glu / yacc: the fused forms of the MLP block (the tensor-core GEMM, and the one-wave decode kernel at up to four rows).
 struct TpPush { float* bufs[8]; int world, rank, rows; };
 static int q4_dev(const smeg_q4* w, const uint16_t* a, uint16_t* c, size_t m, const ep_desc16* ep, int bf16,
                   cudaStream_t stream, float* c32 = nullptr, int glu = 0, float* yacc = nullptr, const TpPush* push = nullptr) {
@@ -671,7 +683,7 @@ static int q4_dev(const smeg_q4* w, const uint16_t* a, uint16_t* c, size_t m, co
         if (rc) return rc;
         return smeg_gemm_dense_dev(t, a, c, m, bf16 ? 0x3f80 : 0x3c00 /* beta = 1 */, 0, ep, stream);
     }
-    if ((glu || yacc) && !q4_uses_tc(w, a, m)) return -4;
+    if ((glu || yacc) && !q4_uses_tc(w, a, m) && !q4_takes_direct(w, a, m, bf16, glu)) return -4;
     if (push && (!c32 || !q4_uses_tc(w, a, m))) return -3;
     DeviceState* ds = dev_state();
     if (!ds) return -5;
@@ -711,6 +723,7 @@ static int q4_dev(const smeg_q4* w, const uint16_t* a, uint16_t* c, size_t m, co
         t.counters = sc.counters;
         e = gemm_tc_launch(t, bf16, grid, smem, stream);
     } else if (g_direct_rows > 0 && (int)m <= g_direct_rows && q4_direct_supported(g, bf16)) {
+        g.glu = glu; g.yacc = yacc;
         e = q4_direct_launch(g, ds->sm_count, stream);
     } else {
         size_t ws_floats = 0, ncounters = 0;
@@ -1200,6 +1213,12 @@ static int mlp_run(smeg_mlp* mlp, const uint16_t* x, float* y, float* partial, s
     if (fuse) {
         rc = q4_dev(mlp->gate_up, x, hid, m, nullptr, 0, stream, nullptr, (int)mlp->act);
         if (!rc) rc = partial ? q4_dev(mlp->down, hid, nullptr, m, nullptr, 0, stream, partial, 0, nullptr, push)
+                              : q4_dev(mlp->down, hid, nullptr, m, nullptr, 0, stream, nullptr, 0, y);
+    } else if (q4_takes_direct(mlp->gate_up, x, m, 0, (int)mlp->act) && q4_takes_direct(mlp->down, hid, m, 0, 0) && mlp->gate_up->d.n == 2 * h) {
+        // decode-sized steps on the one-wave kernels: the gated product is formed where the gate/up projection's sums
+        // meet and the residual add where the down projection's do (two launches instead of four, the same arithmetic)
+        rc = q4_dev(mlp->gate_up, x, hid, m, nullptr, 0, stream, nullptr, (int)mlp->act);
+        if (!rc) rc = partial ? q4_dev(mlp->down, hid, nullptr, m, nullptr, 0, stream, partial)
                               : q4_dev(mlp->down, hid, nullptr, m, nullptr, 0, stream, nullptr, 0, y);
     } else {
         rc = q4_dev(mlp->gate_up, x, both, m, nullptr, 0, stream);

@@ -86,16 +86,24 @@ __global__ void __launch_bounds__(kDThreads, M <= 2 ? 3 : 2) q4_direct_kernel(co
     float* red = reinterpret_cast<float*>(smem_raw + kQ4RingBytes + (size_t)M * a_stride * 2);
     const int CPC = p.cg;                                          // most column groups a CTA takes
     // this CTA's column groups: an equal share of all of them
-    const int cg_first = (int)blockIdx.x * p.dq + min((int)blockIdx.x, p.dr);
-    const int ncg = p.dq + ((int)blockIdx.x < p.dr ? 1 : 0);
+    // (gated form: the share is counted in pairs of a gate group 4q + e and its up group 4q + 2 + e, e = 0, 1 -- the
+    // matrix interleaves 32 gate and 32 up columns -- and the CTA walks gate, up, gate, up, ...)
+    const int first = (int)blockIdx.x * p.dq + min((int)blockIdx.x, p.dr);
+    const int share = p.dq + ((int)blockIdx.x < p.dr ? 1 : 0);
+    const int ncg = p.glu ? 2 * share : share;
+    auto group_of = [&](int c) -> int {
+        if (!p.glu) return first + c;
+        const int u = first + (c >> 1);
+        return 4 * (u >> 1) + (u & 1) + 2 * (c & 1);
+    };
     const int upw = p.dupw;                                        // units per warp: a contiguous run of the depth
     const int u_begin = min(warp * upw, p.k64), u_end = min(u_begin + upw, p.k64);
     const int total = ncg * (u_end - u_begin);                     // units this warp walks, column group by column group
 
     // load cursor: the unit's codes and the scale words of its two 32-deep halves (columns g, g + 8)
-    const unsigned char* lp = p.codes + q4_unit_offset((size_t)cg_first, (size_t)u_begin, p.k64) + lane * 16;
-    const uint16_t* ls = p.scales + q4_scale_row((size_t)cg_first, 0, p.nb) + 2 * g;
-    int lu = u_begin;
+    const unsigned char* lp = p.codes + q4_unit_offset((size_t)group_of(0), (size_t)u_begin, p.k64) + lane * 16;
+    const uint16_t* ls = p.scales + q4_scale_row((size_t)group_of(0), 0, p.nb) + 2 * g;
+    int lu = u_begin, lc = 0;
     auto issue = [&](int slot) {
         cp_async16(ring_w + slot * 32, lp);
         cp_async4(ring_s + slot * 64, ls + (size_t)((lu * 64) >> p.log2_block) * 16);
@@ -103,8 +111,9 @@ __global__ void __launch_bounds__(kDThreads, M <= 2 ? 3 : 2) q4_direct_kernel(co
         lp += kUnitBytes;
         if (++lu == u_end) {
             lu = u_begin;
-            lp += (size_t)(p.k64 - (u_end - u_begin)) * kUnitBytes;
-            ls += (size_t)p.nb * 16;
+            const int cgn = group_of(++lc);                        // (one past the last group is never loaded from)
+            lp = p.codes + q4_unit_offset((size_t)cgn, (size_t)u_begin, p.k64) + lane * 16;
+            ls = p.scales + q4_scale_row((size_t)cgn, 0, p.nb) + 2 * g;
         }
     };
 #pragma unroll
@@ -191,14 +200,33 @@ __global__ void __launch_bounds__(kDThreads, M <= 2 ? 3 : 2) q4_direct_kernel(co
     }
     __syncthreads();
     // ---- the warps' shares in warp order, epilogue, store ----
+    if (p.glu) {
+        // a hidden unit's gate and up sums lie in neighbouring local groups: out = f16(act(f16(gate)) * f16(up)), the
+        // arithmetic of the separate gate pass (glu, src/linear.rs:804-835) on the rounded projections
+        const int hn = p.n >> 1;
+        for (int o = tid; o < share * M * 16; o += kDThreads) {
+            const int col16 = o & 15, r = (o >> 4) % M, ul = o / (16 * M);
+            float ag = 0.0f, au = 0.0f;
+#pragma unroll
+            for (int w = 0; w < kDWarps; ++w) {
+                ag += red[(((size_t)w * CPC + 2 * ul) * M + r) * 16 + col16];
+                au += red[(((size_t)w * CPC + 2 * ul + 1) * M + r) * 16 + col16];
+            }
+            const float gv = __half2float(__float2half_rn(ag)), uv = __half2float(__float2half_rn(au));
+            const int hcol = (first + ul) * 16 + col16;
+            if (hcol < hn) p.c[(size_t)r * hn + hcol] = __half_as_ushort(__float2half_rn(__fmul_rn(glu_gate((uint32_t)p.glu, gv), uv)));
+        }
+        return;
+    }
     for (int o = tid; o < ncg * M * 16; o += kDThreads) {
         const int col16 = o & 15, r = (o >> 4) % M, c = o / (16 * M);
         float acc = 0.0f;
 #pragma unroll
         for (int w = 0; w < kDWarps; ++w) acc += red[(((size_t)w * CPC + c) * M + r) * 16 + col16];
-        const int col = (cg_first + c) * 16 + col16;
+        const int col = (first + c) * 16 + col16;
         if (col < p.n) {
             if (p.c32) p.c32[(size_t)r * p.n + col] = acc;
+            else if (p.yacc) p.yacc[(size_t)r * p.n + col] = __fadd_rn(p.yacc[(size_t)r * p.n + col], __half2float(__float2half_rn(acc)));
             else p.c[(size_t)r * p.n + col] = ep_store_value<0>(p.ep, acc, (size_t)r, (size_t)col);
         }
     }
@@ -491,8 +519,19 @@ cudaError_t q4_direct_launch(Q4GemvArgs a, int sm_count, cudaStream_t stream) {
     // three CTAs per SM when the matrix gives every SM that many, else two (and then never three on one SM
     // while another has one: the shared-memory request is padded past a third of an SM's)
     const int per_sm = (a.m <= 2 && n16 > 2 * sm_count) ? 3 : 2;
-    const int grid_x = direct_grid(n16, sm_count, 16, &a.cg, per_sm);
-    a.dq = n16 / grid_x; a.dr = n16 % grid_x; a.dupw = (a.k64 + kDWarps - 1) / kDWarps;
+    int grid_x;
+    if (a.glu) {
+        // shares are (gate group, up group) pairs: n16 / 2 of them, at most 8 (16 groups) per CTA
+        const int pairs = n16 / 2;
+        int cpp = 1;
+        grid_x = direct_grid(pairs, sm_count, 8, &cpp, per_sm);
+        a.cg = 2 * cpp;
+        a.dq = pairs / grid_x; a.dr = pairs % grid_x;
+    } else {
+        grid_x = direct_grid(n16, sm_count, 16, &a.cg, per_sm);
+        a.dq = n16 / grid_x; a.dr = n16 % grid_x;
+    }
+    a.dupw = (a.k64 + kDWarps - 1) / kDWarps;
     size_t smem = kQ4RingBytes + (size_t)a.m * ((size_t)a.k64 * 64 + 8) * 2 + (size_t)kDWarps * a.cg * a.m * 16 * sizeof(float);
     if (per_sm == 2 && smem < 80 * 1024) smem = 80 * 1024;
     const dim3 grid(grid_x);

@@ -16,6 +16,10 @@ struct Q4GemvArgs {
     const uint16_t* a;            // activations, row-major m x k (T bits)
     uint16_t* c;                  // output, row-major m x n (T bits)
     float* c32;                   // if set: raw f32 accumulators go here instead (no rounding, no epilogue)
+    // direct kernel only -- the fused forms of the MLP block at decode size:
+    int glu;                      // SMEG_ACT_SILU / _GELU: W is a gate/up matrix (32 gate columns, 32 up columns, ...) and c (m x n/2)
+                                  // receives f16(act(f16(gate)) * f16(up)); a CTA then owns (gate group, up group) pairs
+    float* yacc;                  // if set: y[m][n] += f32(f16(acc)) instead of storing c (the residual add)
     int m, n, k;
     int n16, k64, nb;             // column groups, 64-deep units, staged scale rows per group
     int log2_block;
