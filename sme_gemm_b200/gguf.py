@@ -6,6 +6,7 @@ Q1Weights) and adds the block formats whose arithmetic this library's weight kin
 
     Q1_0  (type 41)  128 weights: f16 scale, 16 bytes of sign bits            -> Q1Weights, block 128
     Q4_0  (type 2)    32 weights: f16 scale d, 16 bytes of nibbles q, d (q-8) -> Q4Weights, block 32
+    Q4_1  (type 3)    32 weights: f16 d, f16 m, 16 bytes of nibbles q, d q + m -> Q4Weights, block 32, affine form
     TQ2_0 (type 35)  256 weights: 64 bytes of 2-bit codes q, f16 d, d (q-1)   -> Q2Weights, block 256, codebook -1 0 1
     F32 / F16                                                                 -> numpy arrays
 
@@ -19,10 +20,10 @@ from dataclasses import dataclass
 
 import numpy as np
 
-F32, F16, Q4_0, TQ2_0, Q1_0 = 0, 1, 2, 35, 41
+F32, F16, Q4_0, Q4_1, TQ2_0, Q1_0 = 0, 1, 2, 3, 35, 41
 
 # (weights per block, bytes per block)
-_BLOCK = {F32: (1, 4), F16: (1, 2), Q4_0: (32, 18), TQ2_0: (256, 66), Q1_0: (128, 18)}
+_BLOCK = {F32: (1, 4), F16: (1, 2), Q4_0: (32, 18), Q4_1: (32, 20), TQ2_0: (256, 66), Q1_0: (128, 18)}
 
 
 @dataclass
@@ -222,6 +223,29 @@ def q4_0_arrays(g: Gguf, names):
     return quants, scales, n, k
 
 
+def q4_1_arrays(g: Gguf, names):
+    """Q4_1 tensors -> (quants, scales, mins, n, k) for Q4Weights.with_params(.., Q4Params(32).affine()).  The file's
+    weight is d * q + m with q in 0..15; the affine form of this library (src/kernels/q4/mod.rs:39-48) is
+    scale * code + min with code in -8..7, so scale = d, code = q - 8 and min = m + 8 d.  That offset is stored as f16:
+    where m + 8 d is not an f16 number it is rounded once (the f32 sum to f16, nearest even), and the block's weights
+    move by that rounding, at most half a unit in the last place of the offset."""
+    blocks, n, k = _rows(g, names, Q4_1, "Q4_1")
+    d = np.ascontiguousarray(blocks[:, :, 0:2]).view("<f2")
+    m = np.ascontiguousarray(blocks[:, :, 2:4]).view("<f2")
+    scales = d.view("<u2").reshape(-1).astype(np.uint16)
+    off = (m.astype(np.float32) + np.float32(8.0) * d.astype(np.float32)).astype(np.float32)
+    with np.errstate(over="ignore"):
+        mins = off.astype("<f2").view("<u2").reshape(-1).astype(np.uint16)
+    qs = blocks[:, :, 4:20]
+    nib = np.concatenate([qs & 0x0F, qs >> 4], axis=2).reshape(n, k)          # [j][d], q = code + 8
+    code = (nib ^ 8).astype(np.uint8)
+    flat = np.ascontiguousarray(code.T).reshape(-1)
+    if flat.size % 2:
+        flat = np.concatenate([flat, np.zeros(1, np.uint8)])
+    quants = (flat[0::2] | (flat[1::2] << 4)).astype(np.uint8)
+    return quants, scales, mins, n, k
+
+
 def tq2_0_arrays(g: Gguf, names):
     """TQ2_0 tensors -> (codes, scales, n, k) for Q2Weights.new(codes, scales, n, k, Q2Params(256) with codebook
     [-1, 0, 1, 0]).  A block is 64 bytes of codes then its f16 scale; weight 128 h + 32 l + i (h < 2, l < 4, i < 32) is
@@ -261,6 +285,12 @@ def dequant(g: Gguf, name: str) -> np.ndarray:
         qs = blocks[:, :, 2:18]
         nib = np.concatenate([qs & 0x0F, qs >> 4], axis=2).astype(np.float32)
         return ((nib - 8.0) * d).reshape(rows, k)
+    if t.ty == Q4_1:
+        d = np.ascontiguousarray(blocks[:, :, 0:2]).view("<f2").astype(np.float32)
+        m = np.ascontiguousarray(blocks[:, :, 2:4]).view("<f2").astype(np.float32)
+        qs = blocks[:, :, 4:20]
+        nib = np.concatenate([qs & 0x0F, qs >> 4], axis=2).astype(np.float32)
+        return (nib * d + m).reshape(rows, k)
     d = np.ascontiguousarray(blocks[:, :, 64:66]).view("<f2").astype(np.float32)
     qs = blocks[:, :, 0:64].reshape(rows, -1, 2, 1, 32)
     shifts = (2 * np.arange(4, dtype=np.uint8)).reshape(1, 1, 1, 4, 1)
@@ -280,6 +310,12 @@ def q4_0(g: Gguf, names):
     from .host import Q4Weights
     quants, scales, n, k = q4_0_arrays(g, names)
     return Q4Weights.new(quants, scales, n, k)
+
+
+def q4_1(g: Gguf, names):
+    from .host import Q4Params, Q4Weights
+    quants, scales, mins, n, k = q4_1_arrays(g, names)
+    return Q4Weights.with_params(quants, scales, mins, n, k, Q4Params(32).affine())
 
 
 def tq2_0(g: Gguf, names):

@@ -53,6 +53,18 @@ def q4_blocks(rng, n, k):
     return np.concatenate([sc.view(np.uint8).reshape(n, -1, 2), qs], axis=2).tobytes()
 
 
+def q4_1_blocks(rng, n, k, exact=False):
+    """exact: offsets m = -8 d + (a small multiple of d's unit), so that m + 8 d is an f16 number."""
+    sc = rng.uniform(0.01, 0.05, (n, k // 32)).astype("<f2")
+    if exact:
+        mn = (np.float32(-8.0) * sc.astype(np.float32)).astype("<f2")
+        sc = (mn.astype(np.float32) / np.float32(-8.0)).astype("<f2")          # d = -m / 8 exactly: m + 8 d = 0
+    else:
+        mn = rng.uniform(-0.4, 0.1, (n, k // 32)).astype("<f2")
+    qs = rng.integers(0, 256, (n, k // 32, 16)).astype(np.uint8)
+    return np.concatenate([sc.view(np.uint8).reshape(n, -1, 2), mn.view(np.uint8).reshape(n, -1, 2), qs], axis=2).tobytes()
+
+
 def tq2_blocks(rng, n, k):
     q = rng.integers(0, 3, (n, k // 256, 64, 4)).astype(np.uint8)          # codes 0..2 only
     qs = (q[..., 0] | (q[..., 1] << 2) | (q[..., 2] << 4) | (q[..., 3] << 6)).astype(np.uint8)
@@ -142,6 +154,27 @@ def test_q4_0_arrays_dequantise_to_the_formats_values():
     deq = orc.f16_bits_to_f32(orc.q4_dequant(quants, scales, None, n, k, 32)).reshape(k, n)      # [d][j], rounded to f16
     want = gguf.dequant(g, "w")                                                                   # [j][d], f32 product
     assert np.array_equal(deq.T, orc.f16_bits_to_f32(orc.f32_to_f16_bits(want)).reshape(n, k))
+
+
+def test_q4_1_arrays_are_the_affine_form():
+    """d q + m = d (q - 8) + (m + 8 d): codes and scales are the file's, the offset is rounded to f16 once."""
+    rng = np.random.default_rng(5)
+    n, k = 6, 128
+    for exact in (True, False):
+        g = gguf.Gguf(write_gguf([], [("w", [k, n], gguf.Q4_1, q4_1_blocks(rng, n, k, exact))]))
+        quants, scales, mins, nn, kk = gguf.q4_1_arrays(g, ["w"])
+        assert (nn, kk) == (n, k) and scales.size == mins.size == n * (k // 32)
+        deq = orc.f16_bits_to_f32(orc.q4_dequant(quants, scales, mins, n, k, 32)).reshape(k, n).T     # [j][d]
+        want = gguf.dequant(g, "w")
+        want16 = orc.f16_bits_to_f32(orc.f32_to_f16_bits(want)).reshape(n, k)
+        if exact:
+            assert np.array_equal(deq, want16)
+        else:
+            # the offset moved by at most half its last place (|m + 8 d| < 0.5: 2^-12), then one f16 rounding of a value < 1
+            assert np.max(np.abs(deq - want)) <= 2.0 ** -12 + 2.0 ** -11
+    g0 = gguf.Gguf(write_gguf([], [("x", [32, 1], gguf.Q4_0, q4_blocks(rng, 1, 32))]))
+    with pytest.raises(ValueError, match="x: expected a 2-D Q4_1 tensor"):
+        gguf.q4_1_arrays(g0, ["x"])
 
 
 def test_tq2_0_arrays_hold_the_formats_codes():

@@ -1,4 +1,4 @@
-"""GGUF files through to the kernels: Q1_0 (the Bonsai model's format, examples/bonsai/model.rs:134-160), Q4_0 and TQ2_0
+"""GGUF files through to the kernels: Q1_0 (the Bonsai model's format, examples/bonsai/model.rs:134-160), Q4_0, Q4_1 and TQ2_0
 tensors written to a file, loaded as weight sets and multiplied against the oracle on the arrays the loader made."""
 import numpy as np
 import pytest
@@ -8,7 +8,7 @@ import oracle as orc
 import sme_gemm_b200 as sg
 from gpu_util import bits_of, f16_bits_dev, max_rel
 from sme_gemm_b200 import gguf
-from test_gguf import q1_blocks, q4_blocks, tq2_blocks, write_gguf
+from test_gguf import q1_blocks, q4_1_blocks, q4_blocks, tq2_blocks, write_gguf
 
 pytestmark = pytest.mark.gpu
 
@@ -22,6 +22,7 @@ def test_gguf_weight_sets_multiply_like_their_arrays(tmp_path):
         [("blk.0.attn_q.weight", [k, 48], gguf.Q1_0, q1_blocks(rng, 48, k)[0]),
          ("blk.0.attn_k.weight", [k, 16], gguf.Q1_0, q1_blocks(rng, 16, k)[0]),
          ("blk.0.ffn_up.weight", [k, 72], gguf.Q4_0, q4_blocks(rng, 72, k)),
+         ("blk.0.ffn_gate.weight", [k, 56], gguf.Q4_1, q4_1_blocks(rng, 56, k)),
          ("blk.0.ffn_down.weight", [k, 40], gguf.TQ2_0, tq2_blocks(rng, 40, k))]))
     g = gguf.Gguf.load(path)
     assert g.int("synthetic.block_count") == 1 and g.str("general.architecture") == "synthetic"
@@ -51,4 +52,13 @@ def test_gguf_weight_sets_multiply_like_their_arrays(tmp_path):
         # and against the format's own dequantised weights in f64
         ref = a16.astype(np.float64) @ gguf.dequant(g, "blk.0.ffn_up.weight").astype(np.float64).T
         assert max_rel(c4.float().cpu().numpy(), ref.astype(np.float32)) <= 2e-2
+        # Q4_1: the affine form (offset m + 8 d rounded to f16 once)
+        w41 = gguf.q4_1(g, ["blk.0.ffn_gate.weight"])
+        quants1, scales1, mins1, n1, _ = gguf.q4_1_arrays(g, ["blk.0.ffn_gate.weight"])
+        c41 = torch.zeros((m, n1), dtype=torch.float16, device="cuda")
+        sg.matmul_q4(a, w41, c41, m)
+        want = orc.f16_bits_to_f32(orc.matmul_q4(orc.f32_to_f16_bits(a16.astype(np.float32)), quants1, scales1, mins1, n1, k, 32, m))
+        assert max_rel(c41.float().cpu().numpy(), want.reshape(m, n1)) <= 1e-2
+        ref = a16.astype(np.float64) @ gguf.dequant(g, "blk.0.ffn_gate.weight").astype(np.float64).T
+        assert max_rel(c41.float().cpu().numpy(), ref.astype(np.float32)) <= 2e-2
     assert sg.last_status() == 0
