@@ -284,6 +284,10 @@ int smeg_mlp_accumulate(smeg_mlp *mlp, const uint16_t *x, float *y, size_t m);
  * ranks' partials are summed, finish applies the f16 store rounding and the
  * residual add, y += f32(f16(sum)). */
 int smeg_mlp_partial_dev(smeg_mlp *mlp, const uint16_t *x, float *partial, size_t m, void *stream);
+/* The same for one projection whose input width is split over the ranks (the out projection of a self-attention
+ * block sharded by heads; no counterpart in the reference, which runs on one device): partial (m x n, f32) receives
+ * the un-rounded f32 sums A @ dequant(W) of this rank's rows of W.  Q4_0 weights, f16 activations (rc -3: affine). */
+int smeg_matmul_q4_partial_dev(const smeg_q4 *w, const uint16_t *a, float *partial, size_t m, void *stream);
 int smeg_mlp_finish_dev(float *y, const float *sum, size_t len, void *stream);
 /* The sum over ranks and finish in one kernel over peer memory (no counterpart in the
  * reference, whose Mlp::accumulate, src/mlp.rs:124-146, runs on one device): every rank

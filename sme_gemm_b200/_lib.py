@@ -105,6 +105,7 @@ SIGNATURES = {
     "smeg_mlp_accumulate_dev": (_i, [_vp, _vp, _vp, _sz, _vp]),
     "smeg_mlp_accumulate": (_i, [_vp, _vp, _vp, _sz]),
     "smeg_mlp_partial_dev": (_i, [_vp, _vp, _vp, _sz, _vp]),
+    "smeg_matmul_q4_partial_dev": (_i, [_vp, _vp, _vp, _sz, _vp]),
     "smeg_kv_append_dev": (_i, [_vp, _vp, _vp, _sz, _sz, _sz, _sz, _sz, _sz, _vp]),
     "smeg_attn_kv_causal_dev": (_i, [_vp, _vp, _i, _sz, _vp, _vp, _sz, _sz, _sz, _sz, _sz, C.c_float, _vp]),
     "smeg_mlp_finish_dev": (_i, [_vp, _vp, _sz, _vp]),

@@ -749,6 +749,10 @@ int smeg_matmul_q4_f16_dev(const smeg_q4* w, const uint16_t* a, uint16_t* c, siz
 int smeg_matmul_q4_bf16_dev(const smeg_q4* w, const uint16_t* a, uint16_t* c, size_t m, const ep_desc16* ep, void* stream) {
     return q4_dev(w, a, c, m, ep, 1, (cudaStream_t)stream);
 }
+int smeg_matmul_q4_partial_dev(const smeg_q4* w, const uint16_t* a, float* partial, size_t m, void* stream) {
+    if (!partial) return -4;
+    return q4_dev(w, a, nullptr, m, nullptr, 0, (cudaStream_t)stream, partial);
+}
 
 static int lowbit_dev(const smeg_lowbit* w, const uint16_t* a, uint16_t* c, size_t m, const ep_desc16* ep,
                       int8_t* q_out, float* sa_out, int32_t* sums_out, cudaStream_t stream) {

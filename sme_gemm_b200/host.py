@@ -834,6 +834,14 @@ class Linear:
         self.forward(x, out, m)
         check("smeg_add_f16_to_f32_dev", lib().smeg_add_f16_to_f32_dev(_ptr(y), _ptr(out), m * self.n(), _stream()))
 
+    def partial(self, x, partial, m: int) -> None:
+        """partial (m x n f32) = the un-rounded sums x @ W: one rank's share of a projection whose input width is split
+        over ranks (the rounding and the residual add follow the sum over ranks).  Q4 weights without bias or norm."""
+        assert self.q4 is not None and self.bias is None and self.rms_eps is None, "a partial product takes plain Q4 weights"
+        assert _is_torch(x) and x.dtype == torch.float16 and _numel(x) == m * self.k(), "x is m*k f16 on the device"
+        assert partial.dtype == torch.float32 and _numel(partial) == m * self.n(), "partial is m*n f32"
+        check("smeg_matmul_q4_partial_dev", lib().smeg_matmul_q4_partial_dev(self.q4._h, _ptr(x), _ptr(partial), m, _stream()))
+
 
 class GatedLinear:
     """act(x @ W_gate) * (x @ W_up) from one interleaved 2n-column Q4 matrix
@@ -1104,11 +1112,11 @@ class SelfAttention:
     def cache(self, capacity: int) -> KvCache:
         return KvCache(self._heads, self._kv_heads, self._head_dim, capacity)
 
-    def accumulate(self, x, cache: KvCache, y, m: int) -> None:
-        """y (m x out.n f32) += out(attention(qkv(x))) for m rows of f16 x at the cache's next positions, which this appends."""
+    def attend(self, x, cache: KvCache, m: int):
+        """The block up to the out projection: m rows of f16 x projected, their keys and values appended to the cache,
+        and the attention outputs of the block's heads as m x (heads * head_dim) f16."""
         d = self.width()
         assert _is_torch(x) and x.dtype == torch.float16 and _numel(x) == m * d, "x is m * width"
-        assert _numel(y) == m * self.out.n(), "y is m * out.n()"
         assert cache.heads() == self._heads and cache.kv_heads() == self._kv_heads and cache.head_dim() == self._head_dim, \
             "the cache's heads match the block's"
         assert cache.len() + m <= cache.capacity(), f"{m} rows do not fit in the cache"
@@ -1121,7 +1129,12 @@ class SelfAttention:
         cache._attend(qkv, w, m, att)                       # the queries are the first q_len values of each projected row
         att16 = torch.empty((m, q_len), dtype=torch.float16, device=x.device)
         check("smeg_f32_to_f16_dev", lib().smeg_f32_to_f16_dev(_ptr(att16), _ptr(att), m * q_len, _stream()))
-        self.out.accumulate(att16, y, m)
+        return att16
+
+    def accumulate(self, x, cache: KvCache, y, m: int) -> None:
+        """y (m x out.n f32) += out(attention(qkv(x))) for m rows of f16 x at the cache's next positions, which this appends."""
+        assert _numel(y) == m * self.out.n(), "y is m * out.n()"
+        self.out.accumulate(self.attend(x, cache, m), y, m)
 
 
 class Block:

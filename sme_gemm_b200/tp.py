@@ -1,4 +1,4 @@
-"""Tensor-parallel partition of the Q4 SwiGLU MLP block over the GPUs of one box.
+"""Tensor-parallel partition of the Q4 SwiGLU MLP block, and of the self-attention block, over the GPUs of one box.
 
 The reference is single-process (src/mlp.rs); the partition is new.  Gate/up is
 split by hidden unit in whole 32-unit interleave chunks (src/linear.rs:603-617),
@@ -8,6 +8,10 @@ hidden units = whole 32-deep K-blocks of W_down, so each rank's slice quantises
 to the same codes and scales as the full matrix.  Each rank produces an f32
 partial of the m x d output; one all-reduce sums them; the f16 store rounding
 and the residual add follow on every rank.
+
+Self-attention (src/self_attention.rs; single-process there too) is split by heads: a rank projects, caches and
+attends its own query heads and the key/value heads they use, and multiplies by its rows of the out projection;
+the f32 partial outputs are summed the same way.
 """
 from __future__ import annotations
 
@@ -15,7 +19,7 @@ import os
 
 import numpy as np
 
-from .host import Gate, GatedLinear, Linear, Mlp, Q4Params, WeightLayout
+from .host import Gate, GatedLinear, KvCache, Linear, Mlp, Q4Params, SelfAttention, WeightLayout
 
 FLAG_WORDS = 1288      # SMEG_TP_FLAG_WORDS of include/smeg_api.h
 
@@ -126,6 +130,12 @@ class TpMlp:
         down = Linear.quantize(wd, WeightLayout.OutIn, wd.shape[0], fl, p)
         return TpMlp(Mlp.gated(up, down), world, group)
 
+    def k(self) -> int:
+        return self.mlp.k()
+
+    def n(self) -> int:
+        return self.mlp.n()
+
     def accumulate(self, x, y, m: int, partial=None) -> None:
         """y (m x d f32, replicated) += down(glu(x @ gate_up)) across the ranks."""
         import torch
@@ -150,5 +160,74 @@ class TpMlp:
         if partial is None:
             partial = torch.empty_like(y)
         self.mlp.partial(x, partial, m)
+        dist.all_reduce(partial, group=self.group)
+        Mlp.finish(y, partial)
+
+
+def shard_heads(heads: int, kv_heads: int, rank: int, world: int):
+    """(first query head, query heads, first KV head, KV heads) of `rank`: whole groups of heads / kv_heads query heads
+    with the KV head they share, the same number on every rank."""
+    assert heads % kv_heads == 0 and kv_heads % world == 0, "the KV heads divide evenly over the ranks"
+    kvl = kv_heads // world
+    hl = kvl * (heads // kv_heads)
+    return rank * hl, hl, rank * kvl, kvl
+
+
+def shard_attention_weights(w_qkv, w_out, heads: int, kv_heads: int, head_dim: int, rank: int, world: int):
+    """A rank's rows of the fused projection W_qkv ([(heads + 2 kv_heads) * head_dim][d], rows [q | k | v] in head
+    order) -- again [q | k | v] -- and its input columns of W_out ([d_out][heads * head_dim])."""
+    h0, hl, kv0, kvl = shard_heads(heads, kv_heads, rank, world)
+    q_len, kv_len = heads * head_dim, kv_heads * head_dim
+    assert w_qkv.shape[0] == q_len + 2 * kv_len and w_out.shape[1] == q_len
+    assert (hl * head_dim) % 32 == 0, "a rank's input columns of W_out are whole 32-deep K-blocks"
+    q = w_qkv[h0 * head_dim:(h0 + hl) * head_dim]
+    k = w_qkv[q_len + kv0 * head_dim:q_len + (kv0 + kvl) * head_dim]
+    v = w_qkv[q_len + kv_len + kv0 * head_dim:q_len + kv_len + (kv0 + kvl) * head_dim]
+    return (np.ascontiguousarray(np.concatenate([q, k, v], axis=0)),
+            np.ascontiguousarray(w_out[:, h0 * head_dim:(h0 + hl) * head_dim]))
+
+
+class TpSelfAttention:
+    """One rank's heads of a self-attention block plus the sum over ranks: y (m x d f32, replicated) +=
+    out(attention(qkv(x))).  The rank's KvCache (from `cache`) holds its own KV heads only.  With `peer` (a PeerReduce
+    for the step's m x d) the sum, the f16 rounding and the residual add run as one kernel over peer memory; without it
+    an all-reduce of the library behind torch.distributed and the finishing pass.  Block(norm1, TpSelfAttention, norm2,
+    TpMlp) is a whole tensor-parallel layer over a replicated residual stream."""
+
+    def __init__(self, attn: SelfAttention, world: int, group=None, peer: "PeerReduce | None" = None):
+        self.attn, self.world, self.group, self.peer = attn, world, group, peer
+
+    @staticmethod
+    def quantize(w_qkv, w_out, heads: int, kv_heads: int, head_dim: int, rank: int, world: int,
+                 p: Q4Params | None = None, group=None) -> "TpSelfAttention":
+        wq, wo = shard_attention_weights(np.asarray(w_qkv, np.float32), np.asarray(w_out, np.float32), heads, kv_heads,
+                                         head_dim, rank, world)
+        _, hl, _, kvl = shard_heads(heads, kv_heads, rank, world)
+        qkv = Linear.quantize(wq, WeightLayout.OutIn, wq.shape[0], wq.shape[1], p)
+        out = Linear.quantize(wo, WeightLayout.OutIn, wo.shape[0], wo.shape[1], p)
+        return TpSelfAttention(SelfAttention(qkv, out, hl, kvl, head_dim), world, group)
+
+    def cache(self, capacity: int) -> KvCache:
+        return self.attn.cache(capacity)
+
+    def width(self) -> int:
+        return self.attn.width()
+
+    def out_width(self) -> int:
+        return self.attn.out_width()
+
+    def accumulate(self, x, cache: KvCache, y, m: int) -> None:
+        import torch
+        import torch.distributed as dist
+        if self.world == 1:
+            self.attn.accumulate(x, cache, y, m)
+            return
+        att16 = self.attn.attend(x, cache, m)
+        if self.peer is not None:
+            self.attn.out.partial(att16, self.peer.partial, m)
+            self.peer.finish(y)
+            return
+        partial = torch.empty_like(y)
+        self.attn.out.partial(att16, partial, m)
         dist.all_reduce(partial, group=self.group)
         Mlp.finish(y, partial)

@@ -204,3 +204,37 @@ def test_two_layer_model_from_a_checkpoint_file(tmp_path):
         x = x + orc.f16_bits_to_f32(lin("mlp.c_proj.weight", hid, rows)).reshape(rows, d)
     assert max_rel(got[:rows], x) <= 2e-2
     assert sg.last_status() == 0
+
+
+@pytest.mark.parametrize("m", [1, 3, 5, 70])
+def test_partial_product_is_the_projection_before_its_rounding(m):
+    """Linear.partial (one rank's share of a projection split over its input width): the f32 sums whose f16 rounding is
+    the projection's output; and a one-rank TpSelfAttention is the block itself."""
+    from sme_gemm_b200.tp import TpSelfAttention
+    rng = np.random.default_rng(31)
+    d, heads, kv_heads, hd = 256, 8, 4, 32
+    wo = (rng.standard_normal((d, heads * hd)) * 0.05).astype(np.float32)
+    wq = (rng.standard_normal(((heads + 2 * kv_heads) * hd, d)) * 0.05).astype(np.float32)
+    out = sg.Linear.quantize(wo, sg.WeightLayout.OutIn, d, heads * hd)
+    a = torch.from_numpy(rng.standard_normal((m, heads * hd)).astype(np.float16)).cuda()
+    part = torch.zeros((m, d), dtype=torch.float32, device="cuda")
+    c = torch.zeros((m, d), dtype=torch.float16, device="cuda")
+    out.partial(a, part, m)
+    out.forward(a, c, m)
+    torch.cuda.synchronize()
+    assert max_rel(part.cpu().numpy(), c.float().cpu().numpy()) <= 1e-3
+    deq = orc.f16_bits_to_f32(orc.q4_dequant(*orc.q4_quantize(wo, 0, d, heads * hd)[:2], None, d, heads * hd)).reshape(heads * hd, d)
+    ref = a.cpu().numpy().astype(np.float64) @ deq.astype(np.float64)
+    assert max_rel(part.cpu().numpy(), ref.astype(np.float32)) <= 2e-3
+    with pytest.raises(AssertionError, match="plain Q4 weights"):
+        sg.Linear.quantize(wo, sg.WeightLayout.OutIn, d, heads * hd, bias=np.zeros(d, np.float16)).partial(a, part, m)
+    # world = 1: the tensor-parallel block is the block
+    tp = TpSelfAttention.quantize(wq, wo, heads, kv_heads, hd, 0, 1)
+    one = sg.SelfAttention(sg.Linear.quantize(wq, sg.WeightLayout.OutIn, wq.shape[0], d), out, heads, kv_heads, hd)
+    x = torch.from_numpy(rng.standard_normal((m, d)).astype(np.float16)).cuda()
+    y0 = torch.from_numpy(rng.standard_normal((m, d)).astype(np.float32)).cuda()
+    y1, y2 = y0.clone(), y0.clone()
+    tp.accumulate(x, tp.cache(128), y1, m)
+    one.accumulate(x, one.cache(128), y2, m)
+    torch.cuda.synchronize()
+    assert torch.equal(y1, y2) and sg.last_status() == 0

@@ -182,3 +182,78 @@ def test_a_peer_that_never_arrives_ends_the_wait_with_the_status_raised_and_y_un
     torch.cuda.synchronize()
     assert sg.last_status() == 0
     assert torch.equal(y, torch.full_like(y, 4.0))
+
+
+WORKER_LAYER = r'''
+import os, sys
+import numpy as np
+import torch, torch.distributed as dist
+sys.path.insert(0, os.getcwd())
+import sme_gemm_b200 as sg
+from sme_gemm_b200.tp import PeerReduce, TpMlp, TpSelfAttention
+rank, world = int(os.environ["RANK"]), int(os.environ["WORLD_SIZE"])
+torch.cuda.set_device(rank)
+dist.init_process_group("nccl", device_id=torch.device("cuda", rank))
+d, f, heads, kv_heads, hd = 512, 1024, 16, 8, 32
+rng = np.random.default_rng(21)
+wq = (rng.standard_normal(((heads + 2 * kv_heads) * hd, d)) * 0.05).astype(np.float32)
+wo = (rng.standard_normal((d, heads * hd)) * 0.05).astype(np.float32)
+wg = (rng.standard_normal((f, d)) * 0.05).astype(np.float32)
+wu = (rng.standard_normal((f, d)) * 0.05).astype(np.float32)
+wd = (rng.standard_normal((d, f)) * 0.05).astype(np.float32)
+g1 = (1 + 0.1 * rng.standard_normal(d)).astype(np.float32)
+g2 = (1 + 0.1 * rng.standard_normal(d)).astype(np.float32)
+OutIn = sg.WeightLayout.OutIn
+def norms():
+    return sg.Norm.rms(g1, 1e-5), sg.Norm.rms(g2, 1e-5)
+n1, n2 = norms()
+whole = sg.Block(n1, sg.SelfAttention(sg.Linear.quantize(wq, OutIn, wq.shape[0], d), sg.Linear.quantize(wo, OutIn, d, heads * hd),
+                                      heads, kv_heads, hd),
+                 n2, sg.Mlp.gated(sg.GatedLinear.quantize(wg, wu, OutIn, f, d, sg.Gate.Silu), sg.Linear.quantize(wd, OutIn, d, f)))
+ok = True
+for use_peer in (True, False):
+    n1, n2 = norms()
+    attn = TpSelfAttention.quantize(wq, wo, heads, kv_heads, hd, rank, world)
+    mlp = TpMlp.quantize(wg, wu, wd, rank, world)
+    layer = sg.Block(n1, attn, n2, mlp)
+    cache, cache_w = layer.cache(64), whole.cache(64)
+    assert cache.kv_heads() == kv_heads // world and cache.heads() == heads // world
+    x = torch.from_numpy(rng.standard_normal((9, d)).astype(np.float32)).cuda()
+    xs = [x[:5].contiguous(), x[5:6].contiguous(), x[6:9].contiguous()]         # a prompt, one decode step, three more rows
+    for part in xs:
+        m = part.shape[0]
+        if use_peer:
+            attn.peer = mlp.peer = PeerReduce(m, d)
+        y, want = part.clone(), part.clone()
+        layer.accumulate(y, cache, m)
+        whole.accumulate(want, cache_w, m)
+        torch.cuda.synchronize()
+        rel = float(((y - want).abs() / (1 + want.abs())).max().item())
+        bits = y.view(torch.int32).to(torch.int64).sum().reshape(1)
+        lo, hi = bits.clone(), bits.clone()
+        dist.all_reduce(lo, op=dist.ReduceOp.MIN); dist.all_reduce(hi, op=dist.ReduceOp.MAX)
+        if sg.last_status() != 0 or rel > 1e-2 or int(lo.item()) != int(hi.item()) or cache.len() != cache_w.len():
+            ok = False
+            print(f"rank {rank}: peer={use_peer} m={m}: max_rel {rel}, identical {int(lo.item()) == int(hi.item())}", flush=True)
+    dist.barrier()
+flag = torch.tensor([1 if ok else 0], device="cuda")
+dist.all_reduce(flag, op=dist.ReduceOp.MIN)
+if rank == 0:
+    print("TP_LAYER_OK" if int(flag.item()) == 1 else "TP_LAYER_FAILED", flush=True)
+dist.destroy_process_group()
+'''
+
+
+@pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs two GPUs on one box")
+def test_a_whole_layer_sharded_by_heads_and_hidden_units_matches_the_one_gpu_layer(tmp_path):
+    """Block(norm1, TpSelfAttention, norm2, TpMlp) on two GPUs -- attention split by heads with per-rank KV caches, the MLP by
+    hidden units, both sums over peer memory (then over the collective library) -- against the one-GPU Block through a
+    prompt and decode steps, and bit for bit across ranks."""
+    world = 2
+    script = tmp_path / "worker_layer.py"
+    script.write_text(WORKER_LAYER)
+    env = dict(os.environ, NCCL_NVLS_ENABLE="0")
+    out = subprocess.run([sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={world}",
+                          "--master-addr", "127.0.0.1", "--master-port", "29751", str(script)],
+                         capture_output=True, text=True, timeout=280, env=env, cwd=os.getcwd())
+    assert "TP_LAYER_OK" in out.stdout, out.stdout[-2000:] + out.stderr[-2000:]
