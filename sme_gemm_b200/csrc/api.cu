@@ -816,7 +816,7 @@ static int lowbit_dev(const smeg_lowbit* w, const uint16_t* a, uint16_t* c, size
         aq.m = (int)m; aq.k = (int)k; aq.kq = (int)kq; aq.nbq = (int)nb; aq.log2_block = w->d.log2_block;
         if (tc) {
             aq.sa_t = (float*)(ws + q_bytes + 2 * sa_bytes);
-            aq.qsum_t = (int32_t*)(ws + q_bytes + 2 * sa_bytes + t_bytes);
+            aq.qsum_t = (float*)(ws + q_bytes + 2 * sa_bytes + t_bytes);
             aq.qh = (uint16_t*)(ws + q_bytes + 2 * sa_bytes + 2 * t_bytes);
             aq.mpad = (int)mpad;
         }

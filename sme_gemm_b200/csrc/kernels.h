@@ -76,7 +76,7 @@ struct ActQuantArgs {
     uint16_t* qh;         // optional: the codes as f16 integers, m x kq, for the tensor-core kernels
     int qh_perm;          // qh holds every run of 8 depths in the order 0 2 1 3 4 6 5 7 (B fragments of the 1-bit mma kernel)
     float* sa_t;          // optional: the same scales as nbq x mpad (block-major), for the tensor-core kernel
-    int32_t* qsum_t;      // optional: the same sums as nbq x mpad
+    float* qsum_t;        // optional: the same sums as nbq x mpad floats (exact: |sum| <= 128 * block < 2^24)
     int mpad;
 };
 cudaError_t act_quant_launch(const ActQuantArgs& a, cudaStream_t stream);
@@ -115,13 +115,13 @@ cudaError_t lowbit_direct_launch(LowbitGemvArgs a, int bits, int sm_count, cudaS
 bool lowbit_mma_supported(const LowbitGemvArgs& a, int sm_count);
 cudaError_t lowbit_mma_launch(LowbitGemvArgs a, int bits, int sm_count, cudaStream_t stream);
 
-// ---- 2-bit / 1-bit x int8 activations on tcgen05 kind::i8 (lowbit_tc.cu) ----
+// ---- 2-bit / 1-bit x int8 activations, exact block sums on tcgen05 kind::f16 (lowbit_tc.cu) ----
 struct LowbitTcArgs {
     const unsigned char* codes;   // packed units [n16][ku][512 B]
     const uint16_t* scales;       // f16 bits [n16][nb][16]
     const uint16_t* qh;           // m x kq activation codes as f16 integers (act_quant_kernel)
     const float* sa_t;            // nb x mpad activation scales, block-major
-    const int32_t* qsum_t;        // nb x mpad per-block sums of q (read for 1-bit weights only)
+    const float* qsum_t;          // nb x mpad per-block sums of q, as floats
     int mpad;                     // m rounded up to a multiple of 64
     uint16_t* c;                  // m x n f16 bits
     int32_t* sums_out;            // optional debug: m x n x nb_real exact block sums

@@ -98,7 +98,7 @@ __global__ void __launch_bounds__(128) act_quant_kernel(ActQuantArgs p) {
         p.sa[(size_t)row * p.nbq + b] = sa;
         if (p.qsum) p.qsum[(size_t)row * p.nbq + b] = qsum;
         if (p.sa_t) p.sa_t[(size_t)b * p.mpad + row] = sa;
-        if (p.qsum_t) p.qsum_t[(size_t)b * p.mpad + row] = qsum;
+        if (p.qsum_t) p.qsum_t[(size_t)b * p.mpad + row] = (float)qsum;
     }
 }
 

@@ -69,7 +69,8 @@ __device__ __forceinline__ void tmem_ld8(uint32_t taddr, uint32_t (&r)[8]) {
 
 // TPW = rows one fold warp takes (16 or 32), DW = fold warps per lane quarter (1 or 2): the row
 // tile of a CTA is TPW * DW rows.
-template <int BITS, int TPW, int DW>
+// FAST: K-blocks of one run (256 depths or fewer) and no debug output -- the fold stays in floating point.
+template <int BITS, int TPW, int DW, int FAST>
 __global__ void __launch_bounds__(kLtThreads, 1) lowbit_tc_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant__ LowbitTcArgs p) {
     constexpr int NT = TPW * DW;                               // rows per CTA tile
     constexpr int ACC_STRIDE = NT < 32 ? 32 : NT;              // tensor-memory columns between accumulators
@@ -285,6 +286,47 @@ __global__ void __launch_bounds__(kLtThreads, 1) lowbit_tc_kernel(const __grid_c
             int ri = 0;                                                     // run counter
             for (int blk = 0; blk < p.nb_real && ok; ++blk) {
                 const int fs = blk % kLtNF;
+                if (FAST) {
+                    // One run per block: the accumulator holds S * 2^-24 exactly, so the block's integer sum as a
+                    // float -- what (float)sum is -- comes from one exact fused multiply-add, without the two
+                    // conversions: 2 S - sum(q) = fma(acc, 2^25, -sum(q)); S - 128 sum(q) = fma(acc, 2^24, -128 sum(q)).
+                    const int buf = ri % NACC;
+                    ok = mbar_wait_poll(&acc_full[buf], (ri / NACC) & 1, abort_flag, p.status, STATUS_TMEM_TIMEOUT);
+                    if (!__all_sync(0xffffffffu, ok)) { ok = false; break; }
+                    tc_fence_after();
+                    uint32_t av[TPW];
+#pragma unroll
+                    for (int j0 = 0; j0 < TPW; j0 += 8) {
+                        uint32_t r[8];
+                        tmem_ld8(lane_base + (uint32_t)(buf * ACC_STRIDE + j0), r);
+                        tmem_ld_wait();
+#pragma unroll
+                        for (int j = 0; j < 8; ++j) av[j0 + j] = r[j];
+                    }
+                    tc_fence_before();
+                    __syncwarp();
+                    if (lane == 0) mbar_arrive(&acc_empty[buf]);
+                    ++ri;
+                    ok = mbar_wait_poll(&f_full[fs], (blk / kLtNF) & 1, abort_flag, p.status, STATUS_TMEM_TIMEOUT);
+                    if (!__all_sync(0xffffffffu, ok)) { ok = false; break; }
+                    const unsigned char* fo = ring_f + (size_t)fs * FSLOT;
+                    const float scale = __half2float(__ushort_as_half(*reinterpret_cast<const uint16_t*>(fo + sc_off)));
+                    const float* sa = reinterpret_cast<const float*>(fo) + part * TPW;
+                    const float* qf = reinterpret_cast<const float*>(fo + NT * 4) + part * TPW;
+#pragma unroll
+                    for (int j0 = 0; j0 < TPW; j0 += 4) {
+                        const float4 s0 = *reinterpret_cast<const float4*>(sa + j0);
+                        const float4 q0 = *reinterpret_cast<const float4*>(qf + j0);
+                        const float sv[4] = {s0.x, s0.y, s0.z, s0.w};
+                        const float qv[4] = {q0.x, q0.y, q0.z, q0.w};
+#pragma unroll
+                        for (int j = 0; j < 4; ++j) {
+                            const float a = __uint_as_float(av[j0 + j]);
+                            const float sumf = BITS == 1 ? fmaf(a, 33554432.0f, -qv[j]) : fmaf(a, 16777216.0f, __fmul_rn(qv[j], -128.0f));
+                            tot[j0 + j] = fmaf(sumf, __fmul_rn(scale, sv[j]), tot[j0 + j]);
+                        }
+                    }
+                } else {
                 int sblk[TPW];                                              // the block's integer sums
 #pragma unroll
                 for (int j = 0; j < TPW; ++j) sblk[j] = 0;
@@ -315,13 +357,13 @@ __global__ void __launch_bounds__(kLtThreads, 1) lowbit_tc_kernel(const __grid_c
                 const unsigned char* fo = ring_f + (size_t)fs * FSLOT;
                 const float scale = __half2float(__ushort_as_half(*reinterpret_cast<const uint16_t*>(fo + sc_off)));
                 const float* sa = reinterpret_cast<const float*>(fo) + part * TPW;
-                const int* qs = reinterpret_cast<const int*>(fo + NT * 4) + part * TPW;
+                const float* qs = reinterpret_cast<const float*>(fo + NT * 4) + part * TPW;
 #pragma unroll
                 for (int j0 = 0; j0 < TPW; j0 += 4) {
                     const float4 s0 = *reinterpret_cast<const float4*>(sa + j0);
-                    const int4 q0 = *reinterpret_cast<const int4*>(qs + j0);
+                    const float4 q0 = *reinterpret_cast<const float4*>(qs + j0);
                     const float sv[4] = {s0.x, s0.y, s0.z, s0.w};
-                    const int qv[4] = {q0.x, q0.y, q0.z, q0.w};
+                    const int qv[4] = {__float2int_rn(q0.x), __float2int_rn(q0.y), __float2int_rn(q0.z), __float2int_rn(q0.w)};
 #pragma unroll
                     for (int j = 0; j < 4; ++j) {
                         // 1-bit: u is the sign bit, value = 2 u - 1; 2-bit: u = value + 128
@@ -330,6 +372,7 @@ __global__ void __launch_bounds__(kLtThreads, 1) lowbit_tc_kernel(const __grid_c
                             p.sums_out[((size_t)(row0 + j0 + j) * p.n + col) * p.nb_real + blk] = sum;
                         tot[j0 + j] = fmaf((float)sum, __fmul_rn(scale, sv[j]), tot[j0 + j]);
                     }
+                }
                 }
                 __syncwarp();
                 if (lane == 0) mbar_arrive(&f_empty[fs]);
@@ -351,9 +394,9 @@ __global__ void __launch_bounds__(kLtThreads, 1) lowbit_tc_kernel(const __grid_c
     }
 }
 
-template <int BITS, int TPW, int DW>
+template <int BITS, int TPW, int DW, int FAST>
 cudaError_t launch_lt(const CUtensorMap& tm, const LowbitTcArgs& a, dim3 grid, size_t smem, cudaStream_t stream) {
-    auto kern = lowbit_tc_kernel<BITS, TPW, DW>;
+    auto kern = lowbit_tc_kernel<BITS, TPW, DW, FAST>;
     static int attr_dev = -1;
     int dev = 0;
     cudaGetDevice(&dev);
@@ -371,6 +414,7 @@ cudaError_t launch_lt(const CUtensorMap& tm, const LowbitTcArgs& a, dim3 grid, s
 bool lowbit_tc_supported(int bits, int m, int k, int log2_block) {
     if (bits != 1 && bits != 2) return false;
     if (m < 1 || k < 1 || log2_block < 4) return false;           // an MMA step is 16 deep: K-blocks of 16 and up
+    if (log2_block > 16) return false;                             // a block's sum of activation codes travels as a float
     return tensor_map_encoder() != nullptr;
 }
 
@@ -392,14 +436,16 @@ cudaError_t lowbit_tc_launch(LowbitTcArgs a, cudaStream_t stream) {
     const size_t smem = 1024 + (size_t)kLtNA * kLtATile + (size_t)kLtNB * bslot + (size_t)kLtNK * 8 * ups * kUnitBytes +
                         1024 + (size_t)kLtNF * (nt * 8 + 256) + 64;
     const dim3 grid((a.n + 127) / 128, (a.m + nt - 1) / nt);
-#define SMEG_LT(B)                                                                     \
-    if (a.bits == B) {                                                                 \
-        if (nt == 16) return launch_lt<B, 16, 1>(tm, a, grid, smem, stream);           \
-        if (nt == 32) return launch_lt<B, 16, 2>(tm, a, grid, smem, stream);           \
-        return launch_lt<B, 32, 2>(tm, a, grid, smem, stream);                         \
+    // blocks of one run and no debug output: the floating-point fold
+    const int fast = a.log2_block <= 8 && a.sums_out == nullptr ? 1 : 0;
+#define SMEG_LT(B, F)                                                                  \
+    if (a.bits == B && fast == F) {                                                    \
+        if (nt == 16) return launch_lt<B, 16, 1, F>(tm, a, grid, smem, stream);        \
+        if (nt == 32) return launch_lt<B, 16, 2, F>(tm, a, grid, smem, stream);        \
+        return launch_lt<B, 32, 2, F>(tm, a, grid, smem, stream);                      \
     }
-    SMEG_LT(2)
-    SMEG_LT(1)
+    SMEG_LT(2, 0) SMEG_LT(2, 1)
+    SMEG_LT(1, 0) SMEG_LT(1, 1)
 #undef SMEG_LT
     return cudaErrorInvalidValue;
 }
