@@ -802,7 +802,7 @@ static int lowbit_dev(const smeg_lowbit* w, const uint16_t* a, uint16_t* c, size
             probe.qh = (const uint16_t*)1; probe.sa = (const float*)1; probe.qsum = (const int32_t*)1;   // set below
             mma = lowbit_mma_supported(probe, ds->sm_count);
         }
-        const size_t mpad = (m + 63) / 64 * 64;
+        const size_t mpad = (m + 127) / 128 * 128;                     // whole row tiles of the tensor-core kernel (up to 128 rows)
         const size_t q_bytes = (m * kq + 255) / 256 * 256, sa_bytes = (m * nb * 4 + 255) / 256 * 256;
         const size_t t_bytes = tc ? (mpad * nb * 4 + 255) / 256 * 256 : 0, qh_bytes = (tc || mma) ? ((m + 7) / 8 * 8 * kq * 2 + 255) / 256 * 256 : 0;
         if (cudaMallocAsync(&ws, q_bytes + 2 * sa_bytes + 2 * t_bytes + qh_bytes + 256, stream) != cudaSuccess) {

@@ -122,7 +122,7 @@ struct LowbitTcArgs {
     const uint16_t* qh;           // m x kq activation codes as f16 integers (act_quant_kernel)
     const float* sa_t;            // nb x mpad activation scales, block-major
     const float* qsum_t;          // nb x mpad per-block sums of q, as floats
-    int mpad;                     // m rounded up to a multiple of 64
+    int mpad;                     // m rounded up to a multiple of 128
     uint16_t* c;                  // m x n f16 bits
     int32_t* sums_out;            // optional debug: m x n x nb_real exact block sums
     int m, n, k, kq;

@@ -66,15 +66,26 @@ __device__ __forceinline__ void tmem_ld8(uint32_t taddr, uint32_t (&r)[8]) {
                  : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7])
                  : "r"(taddr));
 }
+__device__ __forceinline__ void tmem_st8(uint32_t taddr, const uint32_t (&r)[8]) {
+    asm volatile("tcgen05.st.sync.aligned.32x32b.x8.b32 [%0], {%1,%2,%3,%4,%5,%6,%7,%8};"
+                 ::"r"(taddr), "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7])
+                 : "memory");
+}
+__device__ __forceinline__ void tmem_st_wait() { asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory"); }
 
 // TPW = rows one fold warp takes (16 or 32), DW = fold warps per lane quarter (1 or 2): the row
 // tile of a CTA is TPW * DW rows.
 // FAST: K-blocks of one run (256 depths or fewer) and no debug output -- the fold stays in floating point.
+// FAST == 2 (TPW 32, DW 2): a tile of 128 rows, so that the weights are expanded half as often; a fold warp then takes
+// 32 rows of either 64-row half, and the running totals live in tensor memory (columns 384..511: lane = weight column,
+// column = row) beside three accumulators instead of in registers.
 template <int BITS, int TPW, int DW, int FAST>
 __global__ void __launch_bounds__(kLtThreads, 1) lowbit_tc_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant__ LowbitTcArgs p) {
-    constexpr int NT = TPW * DW;                               // rows per CTA tile
+    constexpr int NT = FAST == 2 ? 128 : TPW * DW;             // rows per CTA tile
     constexpr int ACC_STRIDE = NT < 32 ? 32 : NT;              // tensor-memory columns between accumulators
-    constexpr int NACC = 512 / ACC_STRIDE;
+    constexpr int NACC = FAST == 2 ? 3 : 512 / ACC_STRIDE;
+    constexpr int TOT_COL = 384;                               // FAST == 2: first column of the running totals
+    constexpr int NA = FAST == 2 ? 5 : kLtNA, NB = NA;         // ring depths: operand, rows (both tiles are 16 KB at 128 rows)
     constexpr int UPS = BITS == 2 ? 4 : 2;                     // packed units per slot and column group (512 depths)
     constexpr int SPU = BITS == 2 ? 2 : 4;                     // stages per unit
     constexpr int KSLOT = 8 * UPS * kUnitBytes;                // bytes of a packed slot
@@ -84,15 +95,15 @@ __global__ void __launch_bounds__(kLtThreads, 1) lowbit_tc_kernel(const __grid_c
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
 
     unsigned char* ring_a = smem_raw;                                          // [NA][16 KB]
-    unsigned char* ring_b = ring_a + (size_t)kLtNA * kLtATile;                 // [NB][BTILE], tiles 1024-byte aligned
+    unsigned char* ring_b = ring_a + (size_t)NA * kLtATile;                 // [NB][BTILE], tiles 1024-byte aligned
     constexpr int BSLOT = (BTILE + 1023) / 1024 * 1024;
-    unsigned char* ring_k = ring_b + (size_t)kLtNB * BSLOT;                    // [NK][KSLOT]
+    unsigned char* ring_k = ring_b + (size_t)NB * BSLOT;                    // [NK][KSLOT]
     uint64_t* bars = reinterpret_cast<uint64_t*>(ring_k + (size_t)kLtNK * KSLOT);
     uint64_t* a_full = bars;                      // [NA] operand written (the stage's two expand warps)
-    uint64_t* a_empty = a_full + kLtNA;           // [NA] the stage's MMAs retired
-    uint64_t* b_full = a_empty + kLtNA;           // [NB] row tile landed
-    uint64_t* b_empty = b_full + kLtNB;           // [NB] the stage's MMAs retired
-    uint64_t* k_full = b_empty + kLtNB;           // [NK] packed units landed
+    uint64_t* a_empty = a_full + NA;           // [NA] the stage's MMAs retired
+    uint64_t* b_full = a_empty + NA;           // [NB] row tile landed
+    uint64_t* b_empty = b_full + NB;           // [NB] the stage's MMAs retired
+    uint64_t* k_full = b_empty + NB;           // [NK] packed units landed
     uint64_t* k_empty = k_full + kLtNK;           // [NK] every stage of the slot has been expanded
     uint64_t* acc_full = k_empty + kLtNK;         // [NACC] a K-block's sums are complete
     uint64_t* acc_empty = acc_full + NACC;        // [NACC] ... and read by every fold warp
@@ -115,8 +126,8 @@ __global__ void __launch_bounds__(kLtThreads, 1) lowbit_tc_kernel(const __grid_c
     const int slots = (stages + kLtSlotStages - 1) / kLtSlotStages;
 
     if (tid == 0) {
-        for (int s = 0; s < kLtNA; ++s) { mbar_init(&a_full[s], 2); mbar_init(&a_empty[s], 1); }
-        for (int s = 0; s < kLtNB; ++s) { mbar_init(&b_full[s], 1); mbar_init(&b_empty[s], 1); }
+        for (int s = 0; s < NA; ++s) { mbar_init(&a_full[s], 2); mbar_init(&a_empty[s], 1); }
+        for (int s = 0; s < NB; ++s) { mbar_init(&b_full[s], 1); mbar_init(&b_empty[s], 1); }
         for (int s = 0; s < kLtNK; ++s) { mbar_init(&k_full[s], 1); mbar_init(&k_empty[s], 2 * kLtSlotStages); }
         for (int s = 0; s < NACC; ++s) { mbar_init(&acc_full[s], 1); mbar_init(&acc_empty[s], 4 * DW); }
         for (int s = 0; s < kLtNF; ++s) { mbar_init(&f_full[s], 1); mbar_init(&f_empty[s], 4 * DW); }
@@ -137,8 +148,8 @@ __global__ void __launch_bounds__(kLtThreads, 1) lowbit_tc_kernel(const __grid_c
         // ===================== row producer =====================
         if (lane == 0) {
             for (int i = 0; i < stages; ++i) {
-                const int slot = i % kLtNB;
-                if (i >= kLtNB && !mbar_wait_poll(&b_empty[slot], ((i / kLtNB) - 1) & 1, abort_flag, p.status, STATUS_TMEM_TIMEOUT)) break;
+                const int slot = i % NB;
+                if (i >= NB && !mbar_wait_poll(&b_empty[slot], ((i / NB) - 1) & 1, abort_flag, p.status, STATUS_TMEM_TIMEOUT)) break;
                 mbar_expect_tx(&b_full[slot], (unsigned)BTILE);
                 tma_load_2d(ring_b + (size_t)slot * BSLOT, &tmap_q, i * kLtStage, tok0, &b_full[slot]);   // x in f16 elements
             }
@@ -179,9 +190,9 @@ __global__ void __launch_bounds__(kLtThreads, 1) lowbit_tc_kernel(const __grid_c
         // ===================== MMA issuer =====================
         const uint32_t idesc = umma_idesc(0, 128, NT);
         for (int i = 0; i < stages; ++i) {
-            const int as = i % kLtNA, bs = i % kLtNB;
-            if (!__all_sync(0xffffffffu, mbar_wait_poll(&b_full[bs], (i / kLtNB) & 1, abort_flag, p.status, STATUS_TMEM_TIMEOUT))) break;
-            if (!__all_sync(0xffffffffu, mbar_wait_poll(&a_full[as], (i / kLtNA) & 1, abort_flag, p.status, STATUS_TMEM_TIMEOUT))) break;
+            const int as = i % NA, bs = i % NB;
+            if (!__all_sync(0xffffffffu, mbar_wait_poll(&b_full[bs], (i / NB) & 1, abort_flag, p.status, STATUS_TMEM_TIMEOUT))) break;
+            if (!__all_sync(0xffffffffu, mbar_wait_poll(&a_full[as], (i / NA) & 1, abort_flag, p.status, STATUS_TMEM_TIMEOUT))) break;
             tc_fence_after();
             const uint64_t a_desc0 = umma_desc_sw128(smem_u32(ring_a + (size_t)as * kLtATile));
             const uint64_t b_desc0 = umma_desc_sw128(smem_u32(ring_b + (size_t)bs * BSLOT));
@@ -222,8 +233,8 @@ __global__ void __launch_bounds__(kLtThreads, 1) lowbit_tc_kernel(const __grid_c
         const int g = lane >> 2, t = lane & 3;
         const int pair = warp >> 1, half = warp & 1;
         for (int i = pair; i < stages; i += 4) {
-            const int gq = i / kLtSlotStages, si = i % kLtSlotStages, ks_slot = gq % kLtNK, as = i % kLtNA;
-            if (i >= kLtNA && !__all_sync(0xffffffffu, mbar_wait_poll(&a_empty[as], ((i / kLtNA) - 1) & 1, abort_flag, p.status, STATUS_TMEM_TIMEOUT))) break;
+            const int gq = i / kLtSlotStages, si = i % kLtSlotStages, ks_slot = gq % kLtNK, as = i % NA;
+            if (i >= NA && !__all_sync(0xffffffffu, mbar_wait_poll(&a_empty[as], ((i / NA) - 1) & 1, abort_flag, p.status, STATUS_TMEM_TIMEOUT))) break;
             if (!__all_sync(0xffffffffu, mbar_wait_poll(&k_full[ks_slot], (gq / kLtNK) & 1, abort_flag, p.status, STATUS_TMEM_TIMEOUT))) break;
             unsigned char* at = ring_a + (size_t)as * kLtATile;
             const int h = si % SPU;                                            // 64-deep part of the unit
@@ -278,6 +289,87 @@ __global__ void __launch_bounds__(kLtThreads, 1) lowbit_tc_kernel(const __grid_c
             const uint32_t lane_base = tmem_base + ((uint32_t)(32 * q) << 16) + (uint32_t)(part * TPW);
             const int row0 = tok0 + part * TPW;                             // first activation row of this warp
             const int sc_off = NT * 8 + (cl >> 4) * 32 + scale_slot(cl & 15) * 2;   // this column's scale inside a fold slot
+            if (FAST == 2) {
+                // ---- 128 rows: rows 32 part .. 32 part + 31 of either 64-row half, totals in tensor memory ----
+                const uint32_t acc_base = tmem_base + ((uint32_t)(32 * q) << 16);
+                const uint32_t tot_base = acc_base + (uint32_t)TOT_COL;
+                {
+                    const uint32_t z[8] = {0u, 0u, 0u, 0u, 0u, 0u, 0u, 0u};
+#pragma unroll
+                    for (int pass = 0; pass < 2; ++pass)
+#pragma unroll
+                        for (int j0 = 0; j0 < 32; j0 += 8) tmem_st8(tot_base + (uint32_t)(64 * pass + 32 * part + j0), z);
+                    tmem_st_wait();
+                }
+                bool ok = true;
+                for (int blk = 0; blk < p.nb_real && ok; ++blk) {              // one run per block: run counter = blk
+                    const int fs = blk % kLtNF, buf = blk % NACC;
+                    ok = mbar_wait_poll(&acc_full[buf], (blk / NACC) & 1, abort_flag, p.status, STATUS_TMEM_TIMEOUT);
+                    if (!__all_sync(0xffffffffu, ok)) { ok = false; break; }
+                    ok = mbar_wait_poll(&f_full[fs], (blk / kLtNF) & 1, abort_flag, p.status, STATUS_TMEM_TIMEOUT);
+                    if (!__all_sync(0xffffffffu, ok)) { ok = false; break; }
+                    tc_fence_after();
+                    const unsigned char* fo = ring_f + (size_t)fs * FSLOT;
+                    const float scale = __half2float(__ushort_as_half(*reinterpret_cast<const uint16_t*>(fo + sc_off)));
+#pragma unroll
+                    for (int pass = 0; pass < 2; ++pass) {
+                        const int ro = 64 * pass + 32 * part;                  // first row of this pass within the tile
+                        uint32_t av[32];
+#pragma unroll
+                        for (int j0 = 0; j0 < 32; j0 += 8) {
+                            uint32_t r[8];
+                            tmem_ld8(acc_base + (uint32_t)(buf * ACC_STRIDE + ro + j0), r);
+                            tmem_ld_wait();
+#pragma unroll
+                            for (int j = 0; j < 8; ++j) av[j0 + j] = r[j];
+                        }
+                        if (pass == 1) {
+                            // the accumulator is in registers: hand it back to the MMA warp
+                            tc_fence_before();
+                            __syncwarp();
+                            if (lane == 0) mbar_arrive(&acc_empty[buf]);
+                        }
+                        const float* sa = reinterpret_cast<const float*>(fo) + ro;
+                        const float* qf = reinterpret_cast<const float*>(fo + NT * 4) + ro;
+#pragma unroll
+                        for (int j0 = 0; j0 < 32; j0 += 8) {
+                            uint32_t tt[8];
+                            tmem_ld8(tot_base + (uint32_t)(ro + j0), tt);
+                            const float4 s0 = *reinterpret_cast<const float4*>(sa + j0), s1 = *reinterpret_cast<const float4*>(sa + j0 + 4);
+                            const float4 q0 = *reinterpret_cast<const float4*>(qf + j0), q1 = *reinterpret_cast<const float4*>(qf + j0 + 4);
+                            const float sv[8] = {s0.x, s0.y, s0.z, s0.w, s1.x, s1.y, s1.z, s1.w};
+                            const float qv[8] = {q0.x, q0.y, q0.z, q0.w, q1.x, q1.y, q1.z, q1.w};
+                            tmem_ld_wait();
+#pragma unroll
+                            for (int j = 0; j < 8; ++j) {
+                                const float a = __uint_as_float(av[j0 + j]);
+                                const float sumf = BITS == 1 ? fmaf(a, 33554432.0f, -qv[j]) : fmaf(a, 16777216.0f, __fmul_rn(qv[j], -128.0f));
+                                tt[j] = __float_as_uint(fmaf(sumf, __fmul_rn(scale, sv[j]), __uint_as_float(tt[j])));
+                            }
+                            tmem_st8(tot_base + (uint32_t)(ro + j0), tt);
+                        }
+                    }
+                    tmem_st_wait();                                            // the totals are read back in the next block
+                    __syncwarp();
+                    if (lane == 0) mbar_arrive(&f_empty[fs]);
+                }
+                if (ok) {                                                      // (warp-uniform: the tensor-memory loads take whole warps)
+#pragma unroll
+                    for (int pass = 0; pass < 2; ++pass)
+#pragma unroll
+                        for (int j0 = 0; j0 < 32; j0 += 8) {
+                            uint32_t tt[8];
+                            tmem_ld8(tot_base + (uint32_t)(64 * pass + 32 * part + j0), tt);
+                            tmem_ld_wait();
+#pragma unroll
+                            for (int j = 0; j < 8; ++j) {
+                                const int row = tok0 + 64 * pass + 32 * part + j0 + j;
+                                if (row < p.m && col < p.n)
+                                    p.c[(size_t)row * p.n + col] = ep_store_value<0>(p.ep, __uint_as_float(tt[j]), (size_t)row, (size_t)col);
+                            }
+                        }
+                }
+            } else {
             float tot[TPW];
 #pragma unroll
             for (int j = 0; j < TPW; ++j) tot[j] = 0.0f;
@@ -384,6 +476,7 @@ __global__ void __launch_bounds__(kLtThreads, 1) lowbit_tc_kernel(const __grid_c
                     if (row < p.m) p.c[(size_t)row * p.n + col] = ep_store_value<0>(p.ep, tot[j], (size_t)row, (size_t)col);
                 }
             }
+            }
         }
     }
     tc_fence_before();
@@ -420,9 +513,16 @@ bool lowbit_tc_supported(int bits, int m, int k, int log2_block) {
 
 // an MMA of 128 weight columns takes 16 rows or more
 int lowbit_tc_row_tile(int m) { return m <= 16 ? 16 : (m <= 32 ? 32 : 64); }
+// ... and 128 rows where the floating-point fold applies, the rows fill more than one 64-row tile and at most one
+// K-block begins per 64-deep stage: the MMA warp takes the accumulators of every run that begins in a stage before it
+// issues the stage, and the 128-row form has a ring of three (smaller blocks would wait for their own stage)
+static int lt_row_tile(int m, int fast, int log2_block) { return fast && m > 64 && log2_block >= 6 ? 128 : lowbit_tc_row_tile(m); }
 
 cudaError_t lowbit_tc_launch(LowbitTcArgs a, cudaStream_t stream) {
-    const int nt = lowbit_tc_row_tile(a.m);
+    // blocks of one run and no debug output: the floating-point fold
+    const int fast = a.log2_block <= 8 && a.sums_out == nullptr ? 1 : 0;
+    const int nt = lt_row_tile(a.m, fast, a.log2_block);
+    const int nab = nt == 128 ? 5 : kLtNA;                         // ring depths of the kernel's NA, NB
     CUtensorMap tm;
     const cuuint64_t gdim[2] = {(cuuint64_t)a.kq, (cuuint64_t)a.m};
     const cuuint64_t gstride[1] = {(cuuint64_t)a.kq * 2};
@@ -433,15 +533,14 @@ cudaError_t lowbit_tc_launch(LowbitTcArgs a, cudaStream_t stream) {
     if (r != CUDA_SUCCESS) return cudaErrorInvalidValue;
     const int ups = a.bits == 2 ? 4 : 2;
     const int bslot = (nt * 128 + 1023) / 1024 * 1024;
-    const size_t smem = 1024 + (size_t)kLtNA * kLtATile + (size_t)kLtNB * bslot + (size_t)kLtNK * 8 * ups * kUnitBytes +
+    const size_t smem = 1024 + (size_t)nab * kLtATile + (size_t)nab * bslot + (size_t)kLtNK * 8 * ups * kUnitBytes +
                         1024 + (size_t)kLtNF * (nt * 8 + 256) + 64;
     const dim3 grid((a.n + 127) / 128, (a.m + nt - 1) / nt);
-    // blocks of one run and no debug output: the floating-point fold
-    const int fast = a.log2_block <= 8 && a.sums_out == nullptr ? 1 : 0;
 #define SMEG_LT(B, F)                                                                  \
     if (a.bits == B && fast == F) {                                                    \
         if (nt == 16) return launch_lt<B, 16, 1, F>(tm, a, grid, smem, stream);        \
         if (nt == 32) return launch_lt<B, 16, 2, F>(tm, a, grid, smem, stream);        \
+        if (nt == 128) return launch_lt<B, 32, 2, 2 * F>(tm, a, grid, smem, stream);   \
         return launch_lt<B, 32, 2, F>(tm, a, grid, smem, stream);                      \
     }
     SMEG_LT(2, 0) SMEG_LT(2, 1)

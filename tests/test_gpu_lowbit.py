@@ -201,3 +201,27 @@ def test_q1_interleave_keeps_every_column():
         w = min(32, n - c0)
         assert torch.equal(cb[:, col:col + w], cg[:, c0:c0 + w]); col += w
         assert torch.equal(cb[:, col:col + w], cu[:, c0:c0 + w]); col += w
+
+
+@pytest.mark.parametrize("m,n,k", [(65, 70, 512), (200, 300, 1024), (130, 1000, 320)])
+def test_many_rows_on_the_tensor_cores_are_the_reference_bits(m, n, k):
+    """Seventeen rows and up run on tcgen05 (64-row tiles, or 128-row tiles with the totals in tensor memory where a
+    K-block is 64 to 256 deep): the plain entry points against the scalar statement, ragged column tiles included."""
+    rng = np.random.default_rng(m + n)
+    a_bits = orc.f32_to_f16_bits(rng.standard_normal((m, k)).astype(np.float32))
+    for block in (16, 64, 128, 256, 1024):
+        nbk = -(-k // block)
+        scales = orc.f32_to_f16_bits(rng.uniform(0.01, 0.05, n * nbk).astype(np.float32))
+        codes = rng.integers(0, 256, (k * n + 3) // 4).astype(np.uint8)
+        book = BOOKS[(block // 16) % 3]
+        w2 = sg.Q2Weights.new(codes, scales, n, k, sg.Q2Params(block).with_codebook(book))
+        c = torch.full((m, n), 9.0, dtype=torch.float16, device="cuda")
+        sg.matmul_q2(f16_bits_dev(a_bits), w2, c, m)
+        want = orc.lowbit_matmul(a_bits, 2, codes, 1, scales, book, n, k, block, m)
+        assert np.array_equal(_canon16(bits_of(c)), _canon16(want)), f"q2 {m}x{n}x{k} block {block}"
+        signs = rng.integers(0, 256, (k * n + 7) // 8).astype(np.uint8)
+        w1 = sg.Q1Weights.new(signs, scales, sg.WeightLayout.OutIn, n, k, block)
+        sg.matmul_q1(f16_bits_dev(a_bits), w1, c, m)
+        want = orc.lowbit_matmul(a_bits, 1, signs, 0, scales, None, n, k, block, m)
+        assert np.array_equal(_canon16(bits_of(c)), _canon16(want)), f"q1 {m}x{n}x{k} block {block}"
+    assert sg.last_status() == 0
