@@ -822,7 +822,7 @@ static int lowbit_dev(const smeg_lowbit* w, const uint16_t* a, uint16_t* c, size
         }
         if (mma) {
             aq.qh = (uint16_t*)(ws + q_bytes + 2 * sa_bytes + 2 * t_bytes);
-            aq.qh_perm = w->bits == 1 ? 1 : 0;
+            aq.qh_perm = w->bits == 1 ? 2 : 0;                         // 1-bit: fragment order, codes scaled by position
             // the rows up to the next multiple of eight are zero rows (the kernel's B fragments read whole tiles of eight)
             if (m % 8 != 0) cudaMemsetAsync(aq.qh + m * kq, 0, (8 - m % 8) * kq * 2, stream);
         }

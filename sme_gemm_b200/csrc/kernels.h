@@ -74,7 +74,7 @@ struct ActQuantArgs {
     int32_t* qsum;        // m x nbq per-block sums of q (1-bit path only; may be null)
     int m, k, kq, nbq, log2_block;
     uint16_t* qh;         // optional: the codes as f16 integers, m x kq, for the tensor-core kernels
-    int qh_perm;          // qh holds every run of 8 depths in the order 0 2 1 3 4 6 5 7 (B fragments of the 1-bit mma kernel)
+    int qh_perm;          // qh holds every run of 8 depths in the order 0 2 1 3 4 6 5 7 (B fragments of the mma kernel); 2: and scaled by 2^8 2^8 1 1 2^6 2^6 2^-2 2^-2 (its 1-bit form)
     float* sa_t;          // optional: the same scales as nbq x mpad (block-major), for the tensor-core kernel
     float* qsum_t;        // optional: the same sums as nbq x mpad floats (exact: |sum| <= 128 * block < 2^24)
     int mpad;

@@ -84,7 +84,17 @@ __global__ void __launch_bounds__(128) act_quant_kernel(ActQuantArgs p) {
             else v = (int)fminf(fmaxf(r, -128.0f), 127.0f);
         }
         qr[d] = (int8_t)v;
-        if (p.qh) p.qh[(size_t)row * p.kq + (p.qh_perm ? ((d & ~(size_t)3) | ((d & 1) << 1) | ((d >> 1) & 1)) : d)] = __half_as_ushort(__int2half_rn(v));
+        if (p.qh) {
+            // qh_perm: depths of a group of four in the order 0 2 1 3 (the fragment order of lowbit_mma_kernel);
+            // 2: also scaled by position in a group of eight -- 2^8 2^8 2^0 2^0 2^6 2^6 2^-2 2^-2, all exact in f16
+            const size_t pos = p.qh_perm ? ((d & ~(size_t)3) | ((d & 1) << 1) | ((d >> 1) & 1)) : d;
+            float fv = (float)v;
+            if (p.qh_perm == 2) {
+                const int e = (int)(pos & 7) >> 1;
+                fv *= e == 0 ? 256.0f : (e == 1 ? 1.0f : (e == 2 ? 64.0f : 0.25f));
+            }
+            p.qh[(size_t)row * p.kq + pos] = __half_as_ushort(__float2half_rn(fv));
+        }
         local += v;
     }
 #pragma unroll

@@ -13,7 +13,11 @@
 // bit pattern is u (1-bit: the sign bit itself, u in {0,1}; 2-bit: codebook value + 128, u in 0..255), i.e. u * 2^-24.
 // Every product u q 2^-24 and every partial sum of up to 512 depths (|sum| < 2^24 units) is exact in f32, so
 // S = (int)(acc * 2^24) = sum u q, and the block sum is 2 S - sum q (1-bit) or S - 128 sum q (2-bit).  Accumulators are
-// drained into integers after every packed unit (128 or 256 depths).
+// drained into integers after every packed unit (128 or 256 depths).  The 1-bit form does not even move its sign bits:
+// bit b of a half word is the f16 number 2^(b-24) for b < 12, so a register of the A fragment is the packed word under
+// one mask, and act_quant_kernel leaves the codes of the matching depths scaled by the inverse power of two (2^8, 2^0,
+// 2^6, 2^-2: still exact f16 numbers), which makes every product u q 2^-16 for one column of a lane and u q 2^-15 for
+// the other.
 //
 // Structure: one CTA of four warps per column group (16 columns) at a time, the warps splitting the depth; small CTAs,
 // so that an SM holds a dozen of them and their latencies overlap (a call of this size is latency, not bandwidth).
@@ -118,7 +122,8 @@ __global__ void __launch_bounds__(kMThreads) lowbit_mma_kernel(const __grid_cons
             for (int n = 0; n < NT; ++n)
 #pragma unroll
                 for (int j = 0; j < 4; ++j) {
-                    iacc[n][j] += __float2int_rn(acc[n][j] * 16777216.0f);
+                    // 2-bit: sums scaled by 2^-24; 1-bit: by 2^-16 (columns g: j = 0, 1) and 2^-15 (columns g + 8)
+                    iacc[n][j] += __float2int_rn(acc[n][j] * (BITS == 2 ? 16777216.0f : (j < 2 ? 65536.0f : 32768.0f)));
                     acc[n][j] = 0.0f;
                 }
         };
@@ -161,11 +166,15 @@ __global__ void __launch_bounds__(kMThreads) lowbit_mma_kernel(const __grid_cons
                     a[1][0] = prmt(ghi, 0u, 0x4140u); a[1][1] = prmt(hhi, 0u, 0x4140u);
                     a[1][2] = prmt(ghi, 0u, 0x4342u); a[1][3] = prmt(hhi, 0u, 0x4342u);
                 } else {
+                    // A sign bit stays where it lies in its half word: bit b of an f16 is the number 2^(b-24) for
+                    // b < 12 (subnormals, then the two smallest exponents), and act_quant_kernel has scaled the codes of
+                    // the matching depths by 2^8, 2^0, 2^6, 2^-2, so every product of weight column g is u q 2^-16 and
+                    // of column g + 8 (one bit higher) u q 2^-15: one AND per register instead of a shift and an AND.
                     const uint32_t v = w >> (4 * (s & 1));
-                    a[0][0] = v & 0x00010001u;         a[0][1] = (v >> 1) & 0x00010001u;          // depths (0, 2)
-                    a[0][2] = (v >> 8) & 0x00010001u;  a[0][3] = (v >> 9) & 0x00010001u;          // depths (1, 3)
-                    a[1][0] = (v >> 2) & 0x00010001u;  a[1][1] = (v >> 3) & 0x00010001u;          // depths (4, 6)
-                    a[1][2] = (v >> 10) & 0x00010001u; a[1][3] = (v >> 11) & 0x00010001u;         // depths (5, 7)
+                    a[0][0] = v & 0x00010001u; a[0][1] = v & 0x00020002u;          // depths (0, 2), codes x 2^8
+                    a[0][2] = v & 0x01000100u; a[0][3] = v & 0x02000200u;          // depths (1, 3), codes x 2^0
+                    a[1][0] = v & 0x00040004u; a[1][1] = v & 0x00080008u;          // depths (4, 6), codes x 2^6
+                    a[1][2] = v & 0x04000400u; a[1][3] = v & 0x08000800u;          // depths (5, 7), codes x 2^-2
                 }
 #pragma unroll
                 for (int n = 0; n < NT; ++n) {
