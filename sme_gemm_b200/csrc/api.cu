@@ -819,6 +819,7 @@ static int lowbit_dev(const smeg_lowbit* w, const uint16_t* a, uint16_t* c, size
             aq.qsum_t = (float*)(ws + q_bytes + 2 * sa_bytes + t_bytes);
             aq.qh = (uint16_t*)(ws + q_bytes + 2 * sa_bytes + 2 * t_bytes);
             aq.mpad = (int)mpad;
+            aq.qh_perm = w->bits == 1 ? 2 : 0;                         // 1-bit: the order and scaling the kernel's operand tiles take
         }
         if (mma) {
             aq.qh = (uint16_t*)(ws + q_bytes + 2 * sa_bytes + 2 * t_bytes);

@@ -16,9 +16,13 @@
 // most 256 depths guarantees (255 * 128 * 256 < 2^24).  A K-block longer than that is accumulated
 // in runs of 256 depths whose integer sums are added in the fold.  (tcgen05.mma.kind::i8 gives the
 // same integers, and an earlier form of this kernel used it, but the int8 tensor path of this
-// part sustains only ~135 TOP/s against ~1500 TFLOP/s for f16.)
+// part sustains only ~135 TOP/s against ~1500 TFLOP/s for f16.)  The 1-bit form does not even move
+// its sign bits: bit b of a half word is the f16 number 2^(b-24) for b < 12, so an operand register
+// is the packed word under one mask, and act_quant_kernel leaves the codes of the matching depths
+// in the matching order, scaled by the inverse power of two (2^8, 1, 2^6, 2^-2: still exact f16
+// numbers); the sums of a lane's two columns then carry 2^-16 and 2^-15, which the fold undoes.
 //
-// One CTA owns 128 weight columns (the MMA's M dimension) x a tile of up to 64 activation rows (the
+// One CTA owns 128 weight columns (the MMA's M dimension) x a tile of up to 128 activation rows (the
 // MMA's N dimension) over the whole depth, walked in 64-deep stages.  Roles (640 threads):
 //   warp 16 (rows)      one TMA tile load per stage of the activation codes (tensor map, 128-byte
 //                       swizzle, rows past m read as zero).
@@ -35,8 +39,10 @@
 //                       warp ever waits for a global load.
 //   warps 8-15 (fold)   thread = weight column: read a finished run per row (tcgen05.ld), release
 //                       the accumulator, and at the end of a K-block fold the block's integer into
-//                       the running f32 total with the block's scale; after the last block the
-//                       epilogue graph runs on the f16-rounded product and C is stored.
+//                       the running f32 total with the block's scale (K-blocks of one run: without
+//                       leaving floating point, the integer being exact there; 128-row tiles: totals
+//                       in tensor memory); after the last block the epilogue graph runs on the
+//                       f16-rounded product and C is stored.
 // Every wait is bounded; a timed-out wait raises the status word and the kernel drains and exits.
 #include "epilogue.cuh"
 #include "kernels.h"
@@ -69,6 +75,22 @@ __device__ __forceinline__ void tmem_ld8(uint32_t taddr, uint32_t (&r)[8]) {
 __device__ __forceinline__ void tmem_st8(uint32_t taddr, const uint32_t (&r)[8]) {
     asm volatile("tcgen05.st.sync.aligned.32x32b.x8.b32 [%0], {%1,%2,%3,%4,%5,%6,%7,%8};"
                  ::"r"(taddr), "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7])
+                 : "memory");
+}
+// 32 consecutive columns of the warp's lanes in one instruction
+__device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t (&r)[32]) {
+    asm volatile("tcgen05.ld.sync.aligned.32x32b.x32.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16,%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31}, [%32];"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]), "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+                 : "r"(taddr));
+}
+__device__ __forceinline__ void tmem_ld16(uint32_t taddr, uint32_t (&r)[16]) {
+    asm volatile("tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15}, [%16];"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
+                 : "r"(taddr));
+}
+__device__ __forceinline__ void tmem_st16(uint32_t taddr, const uint32_t (&r)[16]) {
+    asm volatile("tcgen05.st.sync.aligned.32x32b.x16.b32 [%0], {%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16};"
+                 ::"r"(taddr), "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]), "r"(r[8]), "r"(r[9]), "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15])
                  : "memory");
 }
 __device__ __forceinline__ void tmem_st_wait() { asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory"); }
@@ -255,20 +277,27 @@ __global__ void __launch_bounds__(kLtThreads, 1) lowbit_tc_kernel(const __grid_c
 #pragma unroll
                 for (int s = 0; s < 2; ++s) {
                     // 32-deep step s of the stage: depths 8 t .. 8 t + 7 of columns g (lo) and g + 8 (hi)
-                    uint32_t lo03, lo47, hi03, hi47;                           // four bytes each: u of depths +0..3 / +4..7
+                    uint32_t lo03 = 0, lo47 = 0, hi03 = 0, hi47 = 0;           // 2-bit: four bytes each: u of depths +0..3 / +4..7
                     if (BITS == 2) {
                         const uint32_t w = s ? w1 : w0;
                         const uint32_t e = w & 0x33333333u, o = (w >> 2) & 0x33333333u;
                         lo03 = prmt2(p.lut, 0u, e); lo47 = prmt2(p.lut, 0u, e >> 16);
                         hi03 = prmt2(p.lut, 0u, o); hi47 = prmt2(p.lut, 0u, o >> 16);
-                    } else {
-                        const uint32_t w = w0;
-                        const int sh = 4 * s;
-                        lo03 = (w >> (sh + 0)) & 0x01010101u; lo47 = (w >> (sh + 2)) & 0x01010101u;
-                        hi03 = (w >> (sh + 1)) & 0x01010101u; hi47 = (w >> (sh + 3)) & 0x01010101u;
+                    }
+                    const uint32_t chunk = (uint32_t)(4 * s + t);
+                    if (BITS == 1) {
+                        // A sign bit stays where it lies in its half word: bit b of an f16 is the number 2^(b-24) for
+                        // b < 12, and act_quant_kernel has left the codes of a run of eight depths in the order
+                        // 0 2 1 3 4 6 5 7, scaled by 2^8 2^8 1 1 2^6 2^6 2^-2 2^-2: every product of column g is
+                        // u q 2^-16 and of column g + 8 (one bit higher) u q 2^-15.  One AND per register.
+                        const uint32_t v = w0 >> (4 * s);
+                        *reinterpret_cast<uint4*>(at + off_lo + ((chunk ^ sw_lo) << 4)) =
+                            make_uint4(v & 0x00010001u, v & 0x01000100u, v & 0x00040004u, v & 0x04000400u);
+                        *reinterpret_cast<uint4*>(at + off_hi + ((chunk ^ sw_hi) << 4)) =
+                            make_uint4(v & 0x00020002u, v & 0x02000200u, v & 0x00080008u, v & 0x08000800u);
+                        continue;
                     }
                     const uint2 l0 = widen4(lo03), l1 = widen4(lo47), h0 = widen4(hi03), h1 = widen4(hi47);
-                    const uint32_t chunk = (uint32_t)(4 * s + t);
                     *reinterpret_cast<uint4*>(at + off_lo + ((chunk ^ sw_lo) << 4)) = make_uint4(l0.x, l0.y, l1.x, l1.y);
                     *reinterpret_cast<uint4*>(at + off_hi + ((chunk ^ sw_hi) << 4)) = make_uint4(h0.x, h0.y, h1.x, h1.y);
                 }
@@ -289,6 +318,9 @@ __global__ void __launch_bounds__(kLtThreads, 1) lowbit_tc_kernel(const __grid_c
             const uint32_t lane_base = tmem_base + ((uint32_t)(32 * q) << 16) + (uint32_t)(part * TPW);
             const int row0 = tok0 + part * TPW;                             // first activation row of this warp
             const int sc_off = NT * 8 + (cl >> 4) * 32 + scale_slot(cl & 15) * 2;   // this column's scale inside a fold slot
+            // what turns an accumulator into S = sum u q: 2-bit sums are scaled by 2^-24, 1-bit by 2^-16 (columns g of a
+            // column group) or 2^-15 (columns g + 8)
+            const float unscale = BITS == 2 ? 16777216.0f : ((cl & 8) ? 32768.0f : 65536.0f);
             if (FAST == 2) {
                 // ---- 128 rows: rows 32 part .. 32 part + 31 of either 64-row half, totals in tensor memory ----
                 const uint32_t acc_base = tmem_base + ((uint32_t)(32 * q) << 16);
@@ -314,45 +346,42 @@ __global__ void __launch_bounds__(kLtThreads, 1) lowbit_tc_kernel(const __grid_c
 #pragma unroll
                     for (int pass = 0; pass < 2; ++pass) {
                         const int ro = 64 * pass + 32 * part;                  // first row of this pass within the tile
-                        uint32_t av[32];
-#pragma unroll
-                        for (int j0 = 0; j0 < 32; j0 += 8) {
-                            uint32_t r[8];
-                            tmem_ld8(acc_base + (uint32_t)(buf * ACC_STRIDE + ro + j0), r);
-                            tmem_ld_wait();
-#pragma unroll
-                            for (int j = 0; j < 8; ++j) av[j0 + j] = r[j];
-                        }
-                        if (pass == 1) {
-                            // the accumulator is in registers: hand it back to the MMA warp
-                            tc_fence_before();
-                            __syncwarp();
-                            if (lane == 0) mbar_arrive(&acc_empty[buf]);
-                        }
                         const float* sa = reinterpret_cast<const float*>(fo) + ro;
                         const float* qf = reinterpret_cast<const float*>(fo + NT * 4) + ro;
 #pragma unroll
-                        for (int j0 = 0; j0 < 32; j0 += 8) {
-                            uint32_t tt[8];
-                            tmem_ld8(tot_base + (uint32_t)(ro + j0), tt);
-                            const float4 s0 = *reinterpret_cast<const float4*>(sa + j0), s1 = *reinterpret_cast<const float4*>(sa + j0 + 4);
-                            const float4 q0 = *reinterpret_cast<const float4*>(qf + j0), q1 = *reinterpret_cast<const float4*>(qf + j0 + 4);
-                            const float sv[8] = {s0.x, s0.y, s0.z, s0.w, s1.x, s1.y, s1.z, s1.w};
-                            const float qv[8] = {q0.x, q0.y, q0.z, q0.w, q1.x, q1.y, q1.z, q1.w};
+                        for (int hf = 0; hf < 2; ++hf) {
+                            // sixteen accumulator values and their totals: two loads in flight, one wait
+                            uint32_t av[16], tt[16];
+                            if (pass == 0 && hf == 0) tmem_st_wait();              // the totals stored in the block before
+                            tmem_ld16(acc_base + (uint32_t)(buf * ACC_STRIDE + ro + 16 * hf), av);
+                            tmem_ld16(tot_base + (uint32_t)(ro + 16 * hf), tt);
                             tmem_ld_wait();
-#pragma unroll
-                            for (int j = 0; j < 8; ++j) {
-                                const float a = __uint_as_float(av[j0 + j]);
-                                const float sumf = BITS == 1 ? fmaf(a, 33554432.0f, -qv[j]) : fmaf(a, 16777216.0f, __fmul_rn(qv[j], -128.0f));
-                                tt[j] = __float_as_uint(fmaf(sumf, __fmul_rn(scale, sv[j]), __uint_as_float(tt[j])));
+                            if (pass == 1 && hf == 1) {
+                                // the accumulator has been read: hand it back to the MMA warp
+                                tc_fence_before();
+                                __syncwarp();
+                                if (lane == 0) mbar_arrive(&acc_empty[buf]);
                             }
-                            tmem_st8(tot_base + (uint32_t)(ro + j0), tt);
+#pragma unroll
+                            for (int j0 = 0; j0 < 16; j0 += 4) {
+                                const float4 s0 = *reinterpret_cast<const float4*>(sa + 16 * hf + j0);
+                                const float4 q0 = *reinterpret_cast<const float4*>(qf + 16 * hf + j0);
+                                const float sv[4] = {s0.x, s0.y, s0.z, s0.w};
+                                const float qv[4] = {q0.x, q0.y, q0.z, q0.w};
+#pragma unroll
+                                for (int j = 0; j < 4; ++j) {
+                                    const float a = __uint_as_float(av[j0 + j]);
+                                    const float sumf = BITS == 1 ? fmaf(a, 2.0f * unscale, -qv[j]) : fmaf(a, unscale, __fmul_rn(qv[j], -128.0f));
+                                    tt[j0 + j] = __float_as_uint(fmaf(sumf, __fmul_rn(scale, sv[j]), __uint_as_float(tt[j0 + j])));
+                                }
+                            }
+                            tmem_st16(tot_base + (uint32_t)(ro + 16 * hf), tt);
                         }
                     }
-                    tmem_st_wait();                                            // the totals are read back in the next block
                     __syncwarp();
                     if (lane == 0) mbar_arrive(&f_empty[fs]);
                 }
+                tmem_st_wait();
                 if (ok) {                                                      // (warp-uniform: the tensor-memory loads take whole warps)
 #pragma unroll
                     for (int pass = 0; pass < 2; ++pass)
@@ -379,22 +408,26 @@ __global__ void __launch_bounds__(kLtThreads, 1) lowbit_tc_kernel(const __grid_c
             for (int blk = 0; blk < p.nb_real && ok; ++blk) {
                 const int fs = blk % kLtNF;
                 if (FAST) {
-                    // One run per block: the accumulator holds S * 2^-24 exactly, so the block's integer sum as a
+                    // One run per block: the accumulator holds S / unscale exactly, so the block's integer sum as a
                     // float -- what (float)sum is -- comes from one exact fused multiply-add, without the two
-                    // conversions: 2 S - sum(q) = fma(acc, 2^25, -sum(q)); S - 128 sum(q) = fma(acc, 2^24, -128 sum(q)).
+                    // conversions: 2 S - sum(q) = fma(acc, 2 unscale, -sum(q)); S - 128 sum(q) = fma(acc, unscale, -128 sum(q)).
                     const int buf = ri % NACC;
                     ok = mbar_wait_poll(&acc_full[buf], (ri / NACC) & 1, abort_flag, p.status, STATUS_TMEM_TIMEOUT);
                     if (!__all_sync(0xffffffffu, ok)) { ok = false; break; }
                     tc_fence_after();
-                    uint32_t av[TPW];
+                    uint32_t av[TPW];                                          // every load in flight before the one wait
+                    if constexpr (TPW == 32) {
+                        tmem_ld32(lane_base + (uint32_t)(buf * ACC_STRIDE), av);
+                    } else {
 #pragma unroll
-                    for (int j0 = 0; j0 < TPW; j0 += 8) {
-                        uint32_t r[8];
-                        tmem_ld8(lane_base + (uint32_t)(buf * ACC_STRIDE + j0), r);
-                        tmem_ld_wait();
+                        for (int j0 = 0; j0 < TPW; j0 += 8) {
+                            uint32_t r[8];
+                            tmem_ld8(lane_base + (uint32_t)(buf * ACC_STRIDE + j0), r);
 #pragma unroll
-                        for (int j = 0; j < 8; ++j) av[j0 + j] = r[j];
+                            for (int j = 0; j < 8; ++j) av[j0 + j] = r[j];
+                        }
                     }
+                    tmem_ld_wait();
                     tc_fence_before();
                     __syncwarp();
                     if (lane == 0) mbar_arrive(&acc_empty[buf]);
@@ -414,7 +447,7 @@ __global__ void __launch_bounds__(kLtThreads, 1) lowbit_tc_kernel(const __grid_c
 #pragma unroll
                         for (int j = 0; j < 4; ++j) {
                             const float a = __uint_as_float(av[j0 + j]);
-                            const float sumf = BITS == 1 ? fmaf(a, 33554432.0f, -qv[j]) : fmaf(a, 16777216.0f, __fmul_rn(qv[j], -128.0f));
+                            const float sumf = BITS == 1 ? fmaf(a, 2.0f * unscale, -qv[j]) : fmaf(a, unscale, __fmul_rn(qv[j], -128.0f));
                             tot[j0 + j] = fmaf(sumf, __fmul_rn(scale, sv[j]), tot[j0 + j]);
                         }
                     }
@@ -434,9 +467,9 @@ __global__ void __launch_bounds__(kLtThreads, 1) lowbit_tc_kernel(const __grid_c
                         uint32_t r[8];
                         tmem_ld8(lane_base + (uint32_t)(buf * ACC_STRIDE + j0), r);
                         tmem_ld_wait();
-                        // the accumulator holds (sum of u * q) * 2^-24 exactly
+                        // the accumulator holds (sum of u * q) / unscale exactly
 #pragma unroll
-                        for (int j = 0; j < 8; ++j) sblk[j0 + j] += __float2int_rn(__uint_as_float(r[j]) * 16777216.0f);
+                        for (int j = 0; j < 8; ++j) sblk[j0 + j] += __float2int_rn(__uint_as_float(r[j]) * unscale);
                     }
                     // the accumulator is in registers: hand it back to the MMA warp
                     tc_fence_before();
