@@ -425,3 +425,37 @@ def test_attention_oracle_against_an_f64_statement(heads, kv_heads, hd, start, r
     # one row with start = len - 1 is attention_kv_f16; a row of a block equals the one-row call over its prefix exactly
     one = orc.attention_kv_causal(q[rows - 1:], k, v, n - 1, 1, heads, kv_heads, hd, scale)
     assert np.array_equal(one.reshape(-1), got[rows - 1].reshape(-1))
+
+
+def test_closed_form_products_with_exactly_representable_inputs():
+    """Known answers that need no second implementation (in the spirit of the reference's closed form C = k * a(i) * b(j),
+    tests/concurrency.rs:31-39): constant rows against constant weights whose every partial sum is an exact binary
+    fraction, so the result is known without any rounding."""
+    m, n, k, block = 3, 5, 64, 32
+    # Q4: every code 3, every scale 0.25 -> every weight 0.75; row i of A is the constant 2^(i-1)
+    quants = np.full((k * n + 1) // 2, 0x33, np.uint8)
+    scales = orc.f32_to_f16_bits(np.full(n * (k // block), 0.25, np.float32))
+    a = np.repeat(np.array([0.5, 1.0, 2.0], np.float32), k).reshape(m, k)
+    c = orc.f16_bits_to_f32(orc.matmul_q4(orc.f32_to_f16_bits(a), quants, scales, None, n, k, block, m)).reshape(m, n)
+    assert np.array_equal(c, np.repeat(np.array([24.0, 48.0, 96.0], np.float32), n).reshape(m, n))
+    # the affine form adds the block's minimum to every weight: + 0.25 -> weights of 1.0
+    mins = orc.f32_to_f16_bits(np.full(n * (k // block), 0.25, np.float32))
+    c = orc.f16_bits_to_f32(orc.matmul_q4(orc.f32_to_f16_bits(a), quants, scales, mins, n, k, block, m)).reshape(m, n)
+    assert np.array_equal(c, np.repeat(np.array([32.0, 64.0, 128.0], np.float32), n).reshape(m, n))
+    # 2-bit, codebook [-2, -1, 1, 2], every code 3 (value 2), scale 0.5; a row of constant x quantises to q = 127 with
+    # sa = x / 127, so a block's sum is 2 * 127 * 32 = 8128 and the cell is 2 blocks * 8128 * (0.5 * sa)
+    codes = np.full((k * n + 3) // 4, 0xFF, np.uint8)
+    sc2 = orc.f32_to_f16_bits(np.full(n * (k // block), 0.5, np.float32))
+    c, q, sa, sums = orc.lowbit_matmul(orc.f32_to_f16_bits(a), 2, codes, 1, sc2, [-2, -1, 1, 2], n, k, block, m, debug=True)
+    assert (q == 127).all() and (sums == 8128).all()
+    for i, x in enumerate((0.5, 1.0, 2.0)):
+        s = np.float32(x) / np.float32(127.0)
+        assert (sa[i] == s).all()
+        w = np.float32(0.5) * s
+        tot = np.float32(np.float64(8128.0) * np.float64(w))                               # fmaf(8128, w, 0): one rounding
+        tot = np.float32(np.float64(8128.0) * np.float64(w) + np.float64(tot))             # fmaf(8128, w, tot)
+        assert (orc.f16_bits_to_f32(c[i]) == orc.f16_bits_to_f32(orc.f32_to_f16_bits(np.array([tot], np.float32)))[0]).all()
+    # 1-bit, every sign +: the block's sum is 127 * 32
+    signs = np.full((k * n + 7) // 8, 0xFF, np.uint8)
+    c, q, sa, sums = orc.lowbit_matmul(orc.f32_to_f16_bits(a), 1, signs, 0, sc2, None, n, k, block, m, debug=True)
+    assert (sums == 127 * 32).all()
