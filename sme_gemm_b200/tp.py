@@ -47,7 +47,9 @@ class PeerReduce:
     """The ranks' partial buffers and flag arrays in memory every rank can address (torch symmetric
     memory: CUDA peer mappings over NVLink), and the one-kernel sum + f16 rounding + residual add over
     them (smeg_mlp_reduce_finish_dev).  Collective to construct; every rank then calls `finish` once
-    per step, in the same order."""
+    per step, in the same order.  One object serves the exchanges of one shape and one form: above 64 rows the
+    MLP block pushes its partial rows (other offsets inside the buffers, results as marked words), so an
+    exchange that pulls -- the attention block's -- takes a PeerReduce of its own there."""
 
     def __init__(self, m: int, d: int, group=None):
         import torch
