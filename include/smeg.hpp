@@ -11,6 +11,7 @@
 //   matmul_q2 / q1 {,_ep}{,_mopa}  src/kernels/lowbit/matmul.rs:38-139
 //   Packed<T>, Gemm<T>             src/exec/builder.rs:220-227, 428-813
 //   Linear, GatedLinear, Mlp       src/linear.rs:133-835, src/mlp.rs:56-146
+//   Norm, KvCache                  src/nn.rs:163-230, src/kernels/kv_attention.rs:354-581 (device memory only)
 //
 // Every compute call exists twice: on host slices (the library copies in and out, as the drop-in symbols do) and, with
 // the suffix _dev, on device pointers plus a CUDA stream (what a GPU-resident caller and every timed path use; epilogue
@@ -18,6 +19,7 @@
 #ifndef SMEG_HPP
 #define SMEG_HPP
 
+#include <cmath>
 #include <cstdint>
 #include <cstring>
 #include <stdexcept>
@@ -681,6 +683,71 @@ public:
         require(x.len == m * k(), "x is m*k");
         require(y.len == m * n(), "y is m*n");
         check("smeg_mlp_accumulate_dev", smeg_mlp_accumulate_dev(h_, x.ptr, y.ptr, m, stream));
+    }
+};
+
+// ---- the steps either side of the MLP in a layer, on device memory --------------------------------------------------
+
+// Norm::layer / Norm::rms (src/nn.rs:163-230): f32 rows in, f16 (or f32) rows out.  weight and bias (dim f32 each, bias
+// may be null) are DEVICE pointers, borrowed.
+class Norm {
+    const float* weight_;
+    const float* bias_;
+    size_t dim_;
+    float eps_;
+    bool rms_;
+    Norm(const float* w, const float* b, size_t dim, float eps, bool rms) : weight_(w), bias_(b), dim_(dim), eps_(eps), rms_(rms) {
+        require(dim > 0, "a norm needs at least one feature");
+    }
+
+public:
+    static Norm layer(const float* weight_dev, const float* bias_dev, size_t dim, float eps) { return Norm(weight_dev, bias_dev, dim, eps, false); }
+    static Norm rms(const float* weight_dev, size_t dim, float eps) { return Norm(weight_dev, nullptr, dim, eps, true); }
+    size_t width() const { return dim_; }
+    // x: rows * dim f32 on the device; y16 / y32: either may be null
+    void forward_dev(Slice<const float> x, uint16_t* y16, float* y32, void* stream) const {
+        require(x.len % dim_ == 0, "x holds whole rows of weight.len()");
+        check("smeg_norm_rows_dev", smeg_norm_rows_dev(y16, y32, x.ptr, weight_, bias_, x.len / dim_, dim_, eps_, rms_ ? 1 : 0, stream));
+    }
+};
+
+// KvCache (src/kernels/kv_attention.rs:354-581) over caller-provided DEVICE buffers of capacity * kv_heads * head_dim f16
+// values each: rows appended in order, queries of `heads` heads (a multiple of kv_heads) attending causally.
+class KvCache {
+    uint16_t* k_;
+    uint16_t* v_;
+    size_t heads_, kv_heads_, head_dim_, capacity_, len_ = 0;
+    float scale_;
+
+public:
+    KvCache(uint16_t* k_dev, uint16_t* v_dev, size_t heads, size_t kv_heads, size_t head_dim, size_t capacity)
+        : k_(k_dev), v_(v_dev), heads_(heads), kv_heads_(kv_heads), head_dim_(head_dim), capacity_(capacity) {
+        require(head_dim % 8 == 0 && head_dim >= 8 && head_dim <= 256, "head_dim must be a multiple of 8 in 8..=256");
+        require(kv_heads > 0 && heads > 0 && heads % kv_heads == 0, "heads must be a positive multiple of kv_heads");
+        scale_ = 1.0f / std::sqrt((float)head_dim);             // in f32, as the reference computes it
+    }
+    KvCache& with_scale(float scale) {
+        scale_ = scale;
+        return *this;
+    }
+    size_t len() const { return len_; }
+    bool is_empty() const { return len_ == 0; }
+    size_t capacity() const { return capacity_; }
+    size_t row_len() const { return kv_heads_ * head_dim_; }
+    size_t query_len() const { return heads_ * head_dim_; }
+    float scale() const { return scale_; }
+    void clear() { len_ = 0; }
+    void truncate(size_t n) { len_ = len_ < n ? len_ : n; }
+    // `rows` key and value rows out of rows of src (stride elements apart; keys at k_off, values at v_off of a row)
+    void extend_from_dev(const uint16_t* src, size_t stride, size_t k_off, size_t v_off, size_t rows, void* stream) {
+        require(len_ + rows <= capacity_, "KvCache full: " + std::to_string(len_) + " + " + std::to_string(rows) + " rows over capacity " + std::to_string(capacity_));
+        check("smeg_kv_append_dev", smeg_kv_append_dev(k_, v_, src, stride, k_off, v_off, row_len(), len_, rows, stream));
+        len_ += rows;
+    }
+    // `rows` f16 query rows (q_stride elements apart), row i attending to positions 0..=len - rows + i; out: rows * query_len f32
+    void attend_causal_dev(const uint16_t* q, size_t q_stride, size_t rows, float* out, void* stream) const {
+        require(rows <= len_, "attend_causal: " + std::to_string(rows) + " rows but " + std::to_string(len_) + " cached");
+        check("smeg_attn_kv_causal_dev", smeg_attn_kv_causal_dev(out, q, 0, q_stride, k_, v_, len_ - rows, rows, heads_, kv_heads_, head_dim_, scale_, stream));
     }
 };
 

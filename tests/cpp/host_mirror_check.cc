@@ -125,6 +125,16 @@ static int run_cpu(const char* in_f32, const std::string& out) {
     EXPECT(thrown([&] { Q4Weights::with_params(quants, scales, scales, 4, 4, Q4Params()); }) == "Q4Form::Scale takes no mins array");
     std::vector<float> w(16, 0.5f);
     EXPECT(thrown([&] { Q4Weights::quantize(w, WeightLayout::OutIn, 4, 5); }) == "w is n*k");
+
+    // ---- the cache's bookkeeping and refusals (no device memory is touched before a launch) ----
+    KvCache cache(nullptr, nullptr, 8, 2, 80, 16);
+    EXPECT(cache.scale() == 0.11180339753627777f && cache.row_len() == 160 && cache.query_len() == 640 && cache.is_empty());
+    EXPECT(thrown([] { KvCache(nullptr, nullptr, 8, 2, 20, 4); }) == "head_dim must be a multiple of 8 in 8..=256");
+    EXPECT(thrown([] { KvCache(nullptr, nullptr, 6, 4, 64, 4); }) == "heads must be a positive multiple of kv_heads");
+    EXPECT(thrown([&] { cache.extend_from_dev(nullptr, 960, 640, 800, 17, nullptr); }) == "KvCache full: 0 + 17 rows over capacity 16");
+    EXPECT(thrown([&] { cache.attend_causal_dev(nullptr, 960, 1, nullptr, nullptr); }) == "attend_causal: 1 rows but 0 cached");
+    EXPECT(thrown([] { Norm::rms(nullptr, 0, 1e-5f); }) == "a norm needs at least one feature");
+    EXPECT(Norm::layer(nullptr, nullptr, 96, 1e-5f).width() == 96);
     std::printf(g_failed ? "CPU CHECKS FAILED\n" : "CPU CHECKS OK\n");
     return g_failed;
 }
