@@ -22,6 +22,7 @@
 #include <cmath>
 #include <cstdint>
 #include <cstring>
+#include <memory>
 #include <stdexcept>
 #include <string>
 #include <utility>
@@ -601,36 +602,72 @@ inline std::vector<float> interleave_gate_up(Slice<const float> g, Slice<const f
     return out;
 }
 
-// Linear on Q4 weights with an optional bias, which rides as a leading AddCol (Linear, src/linear.rs:133-155, 440-463).
-// The bias (n f16 bits) is borrowed; for the _dev calls it is a device pointer.
+// Linear (src/linear.rs:133-155): Q4, 2-bit or 1-bit weights with an optional bias, which rides as a leading AddCol
+// (with_lead, :440-463).  2-bit / 1-bit layers run on the int8-activation kernels, or -- opted in with lowbit_mopa() --
+// on the f16 tensor-core path from LOWBIT_MOPA_ROWS rows (:168, 535-552).  The bias (n f16 bits) is borrowed; for the _dev
+// calls it is a device pointer.
 class Linear {
-    Q4Weights w_;
+    std::unique_ptr<Q4Weights> q4_;
+    std::unique_ptr<Q2Weights> q2_;
+    std::unique_ptr<Q1Weights> q1_;
     Bits bias_;
+    bool mopa_ = false;
+
+    void check_bias() const { require(bias_.ptr == nullptr || bias_.len == n(), "bias holds n values"); }
 
 public:
-    explicit Linear(Q4Weights w, Bits bias = Bits()) : w_(std::move(w)), bias_(bias) {
-        require(bias_.ptr == nullptr || bias_.len == w_.n(), "bias holds n values");
-    }
+    static constexpr size_t LOWBIT_MOPA_ROWS = 64;
+
+    explicit Linear(Q4Weights w, Bits bias = Bits()) : q4_(new Q4Weights(std::move(w))), bias_(bias) { check_bias(); }
     static Linear quantize(Slice<const float> w, WeightLayout layout, size_t n, size_t k, Q4Params p = Q4Params(), Bits bias = Bits()) {
         return Linear(Q4Weights::quantize(w, layout, n, k, p), bias);
     }
     static Linear from_q4(Q4Weights w, Bits bias = Bits()) { return Linear(std::move(w), bias); }
-    size_t n() const { return w_.n(); }
-    size_t k() const { return w_.k(); }
-    const Q4Weights& weights() const { return w_; }
+    // Linear::from_q2, src/linear.rs:214
+    static Linear from_q2(Q2Weights w, Bits bias = Bits()) {
+        Linear l;
+        l.q2_.reset(new Q2Weights(std::move(w)));
+        l.bias_ = bias;
+        l.check_bias();
+        return l;
+    }
+    // Linear::from_q1, src/linear.rs:234
+    static Linear from_q1(Q1Weights w, Bits bias = Bits()) {
+        Linear l;
+        l.q1_.reset(new Q1Weights(std::move(w)));
+        l.bias_ = bias;
+        l.check_bias();
+        return l;
+    }
+    // Linear::lowbit_mopa: 2-bit / 1-bit weights on the f16 tensor-core path from LOWBIT_MOPA_ROWS rows
+    Linear& lowbit_mopa(bool on = true) {
+        mopa_ = on;
+        return *this;
+    }
+    size_t n() const { return q4_ ? q4_->n() : (q2_ ? q2_->n() : q1_->n()); }
+    size_t k() const { return q4_ ? q4_->k() : (q2_ ? q2_->k() : q1_->k()); }
+    bool is_q4() const { return (bool)q4_; }
+    const Q4Weights& weights() const {
+        require(is_q4(), "this layer holds no Q4 weights");
+        return *q4_;
+    }
     bool has_bias() const { return bias_.ptr != nullptr; }
-    // y = ep(x @ W + bias): the bias ahead of the caller's graph (with_lead, src/linear.rs:440-463)
+    // y = ep(x @ W + bias): the bias ahead of the caller's graph
     void forward_ep(Bits x, BitsMut y, size_t m, const Epilogue<f16>& ep, void* stream = nullptr, bool dev = false) const {
+        Epilogue<f16> full = ep;
         if (has_bias()) {
             Epilogue<f16> lead;
             lead.add_col(bias_);
-            const Epilogue<f16> full = ep.with_leading(lead);
-            detail::run_q4<f16>(x, w_, y, m, &full, stream, dev);
-        } else {
-            detail::run_q4<f16>(x, w_, y, m, &ep, stream, dev);
+            full = ep.with_leading(lead);
         }
+        if (q4_) detail::run_q4<f16>(x, *q4_, y, m, &full, stream, dev);
+        else detail::run_lowbit(x, q2_ ? static_cast<const LowbitWeights&>(*q2_) : static_cast<const LowbitWeights&>(*q1_), y, m, &full,
+                                mopa_ && m >= LOWBIT_MOPA_ROWS, stream, dev);
     }
     void forward(Bits x, BitsMut y, size_t m, void* stream = nullptr, bool dev = false) const { forward_ep(x, y, m, Epilogue<f16>(), stream, dev); }
+
+private:
+    Linear() = default;
 };
 
 // act(x @ W_gate) * (x @ W_up) from one interleaved 2n-column Q4 matrix (GatedLinear, src/linear.rs:603-656, 779-835).

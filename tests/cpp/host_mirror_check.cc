@@ -187,6 +187,20 @@ static int run_gpu() {
     for (size_t i = 0; i < y.size(); ++i) ok = ok && y1[i] > 0.0f && y[i] == 2.0f * y1[i];
     EXPECT(ok);
     EXPECT(smeg_last_status() == 0);
+    // a 1-bit layer (every sign +, scale 0.5) with a bias, through Linear's routing: rows of constant x quantise to q = 127,
+    // sa = x / 127; the cell is the fold of k / 32 blocks of sum 127 * 32, then + 1
+    std::vector<uint8_t> signs(n * k / 8, 0xFF);
+    std::vector<uint16_t> sc1(n * (k / 32), f32_to_f16_bits(0.5f));
+    Linear l1 = Linear::from_q1(Q1Weights::new_(signs, sc1, WeightLayout::OutIn, n, k, 32), bias);
+    l1.forward(a, c, m);
+    float want3[3];
+    for (size_t i = 0; i < m; ++i) {
+        const float wgt = 0.5f * (rows[i] / 127.0f);
+        float tot = 0.0f;
+        for (size_t blk = 0; blk < k / 32; ++blk) tot = std::fma(4064.0f, wgt, tot);
+        want3[i] = f16_bits_to_f32(f32_to_f16_bits(f16_bits_to_f32(f32_to_f16_bits(tot)) + 1.0f));
+    }
+    EXPECT(all_equal(c, m, n, want3));
     std::printf(g_failed ? "GPU CHECKS FAILED\n" : "GPU CHECKS OK\n");
     return g_failed;
 }
